@@ -1,0 +1,175 @@
+/*
+ * lv_b200 -- C ABI of the B200 (sm_100a) decode kernels that replace the
+ * Vulkan compute path of aodenis/llama-vulkan.
+ *
+ * The reference has no FFI: its host code (llava_session / llava_layer /
+ * llava_command_buffer / llava_buffer / llava_device_memory) calls Vulkan-Hpp
+ * directly.  Each entry point below names the reference interface it stands
+ * in for (file:line relative to the reference project root).
+ *
+ * Conventions: every function returns LV_OK (0) or an LV_ERR_* code and never
+ * throws or aborts; lv_last_error_string() describes the last failure on the
+ * calling thread.  All `void*`/`float*` arguments named as device memory are
+ * device pointers obtained from lv_arena_create.  Kernels are enqueued on the
+ * context's stream and run asynchronously; lv_stream_sync waits for them.
+ * Quantised matrices keep the GGML ggjt-v3 block layout of the model file:
+ * rows of K/32 blocks, a block being an f16 scale followed by 16 nibble bytes
+ * (q4_0, 18 B) or 32 int8 (q8_0, 34 B).  `wtype` is the GGML type code
+ * (2 = q4_0, 8 = q8_0).  K must be a multiple of 256 and matrix base
+ * addresses 16-byte aligned (both hold for every tensor of a 7B/13B file
+ * placed by lv_arena_create).
+ */
+#ifndef LV_B200_H
+#define LV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  1..8 mirror ReturnCode (types.h:45-55) where they overlap. */
+enum {
+    LV_OK = 0,
+    LV_ERR_NOK = 1,            /* generic failure (ReturnCode::nok) */
+    LV_ERR_BAD_ARGUMENTS = 7,  /* ReturnCode::bad_arguments */
+    LV_ERR_CUDA = 100,         /* a CUDA runtime call failed */
+    LV_ERR_DEVICE_WAIT = 101,  /* a bounded device-side wait gave up (error word non-zero) */
+    LV_ERR_TIMEOUT = 102,      /* lv_stream_sync timed out on the host */
+    LV_ERR_COMM = 103          /* NCCL failure */
+};
+
+enum { LV_TYPE_F32 = 0, LV_TYPE_F16 = 1, LV_TYPE_Q4_0 = 2, LV_TYPE_Q8_0 = 8 };
+
+typedef struct lv_ctx lv_ctx;
+typedef struct lv_graph lv_graph;
+
+/* ---- lifecycle: replaces the Vulkan instance/device/queue/pool bring-up of
+ *      llava_context::run (llava_context.cpp:230-282) ---------------------- */
+int lv_device_count(int* count);
+int lv_ctx_create(int device, lv_ctx** out);
+int lv_ctx_destroy(lv_ctx* ctx);
+const char* lv_last_error_string(void);
+/* cudaStream_t of the context, for callers that enqueue their own work */
+void* lv_ctx_stream(lv_ctx* ctx);
+int lv_ctx_sm_count(lv_ctx* ctx);
+
+/* ---- memory: replaces llava_device_memory::freeze / map / unmap
+ *      (llava_device_memory.cpp:23-73) and llava_buffer::load_to_gpu
+ *      (llava_buffer.cpp:464-478).  One arena = one cudaMalloc. ------------ */
+int lv_arena_create(lv_ctx* ctx, size_t bytes, void** dptr);
+int lv_arena_free(lv_ctx* ctx, void* dptr);
+int lv_host_alloc(lv_ctx* ctx, size_t bytes, void** hptr);        /* pinned */
+int lv_host_free(lv_ctx* ctx, void* hptr);
+int lv_upload(lv_ctx* ctx, void* dst, const void* host_src, size_t bytes);          /* blocking */
+int lv_download(lv_ctx* ctx, void* host_dst, const void* src, size_t bytes);        /* blocking, after the stream drains */
+int lv_upload_async(lv_ctx* ctx, void* dst, const void* pinned_src, size_t bytes);  /* on the stream */
+int lv_download_async(lv_ctx* ctx, void* pinned_dst, const void* src, size_t bytes);
+int lv_memset(lv_ctx* ctx, void* dst, int value, size_t bytes);                     /* on the stream */
+int lv_copy_d2d(lv_ctx* ctx, void* dst, const void* src, size_t bytes);             /* on the stream */
+
+/* ---- execution: replaces llava_command_buffer::record_execution / run /
+ *      wait_idle (llava_command_buffer.cpp:25-55): the recorded command list
+ *      becomes a CUDA graph captured from the context's stream. ------------ */
+int lv_graph_begin_capture(lv_ctx* ctx);
+int lv_graph_end_capture(lv_ctx* ctx, lv_graph** out);
+int lv_graph_launch(lv_ctx* ctx, lv_graph* g);
+int lv_graph_destroy(lv_graph* g);
+/* Waits until the stream is idle (timeout_ms <= 0: no limit), then reads the
+ * device error word; LV_ERR_DEVICE_WAIT if a kernel recorded a lost wait. */
+int lv_stream_sync(lv_ctx* ctx, int timeout_ms);
+
+/* ---- decode kernels, one per reference shader ---------------------------- */
+
+/* shaders/normalize.comp via llava_command_buffer::normalize_logit
+ * (llava_command_buffer.cpp:57-59): out = x * w * rsqrt(mean((x-mean x)^2)),
+ * no epsilon.  x, out: f32 [batch][dim]; w: f32 [dim]. */
+int lv_norm_f32(lv_ctx* ctx, float* out, const float* x, const float* w, uint32_t dim, uint32_t batch);
+
+/* shaders/matmul_{dim,ff}{,_q8}_fp16.comp via llava_command_buffer::matmul
+ * (llava_command_buffer.cpp:61-85); add != 0 selects matmul_add_* /
+ * matmul_add_inplace (:87-111): out += W x.  W: [rows][cols] blocks;
+ * x: f32 [batch][cols]; out: f32 [batch][rows].  rows % 4 == 0. */
+int lv_gemv(lv_ctx* ctx, float* out, const void* W, int wtype, const float* x, uint32_t rows, uint32_t cols,
+            uint32_t batch, int add);
+
+/* shaders/matmul_silu_ff*.comp via llava_command_buffer::matmul_silu_ff
+ * (llava_command_buffer.cpp:113-132): out = (w3 x) * (w1 x) / (1 + exp(-(w1 x))). */
+int lv_gemv_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const float* x, uint32_t rows,
+                 uint32_t cols, uint32_t batch);
+
+/* shaders/copy_to_cache.comp via llava_command_buffer::kv_copy (:134-142):
+ * cache[*pos + z][i] = f16(x[z][i]); no rotation.  cache: f16 [ctx_rows][dim];
+ * pos: device u32 (the reference's config_buffer.token_count). */
+int lv_kv_append_f16(lv_ctx* ctx, void* cache, const float* x, const uint32_t* pos, uint32_t dim, uint32_t batch,
+                     uint32_t ctx_rows);
+
+/* Builds the [max_ctx][rot/2] table of (cos, sin) of distance * 10000^(-i/(rot/2))
+ * used by the two attention entry points below (angles in double on the host,
+ * shaders/mhsa.comp:47-49). table: device f32 [max_ctx][rot/2][2]. */
+int lv_rope_table_build(lv_ctx* ctx, float* table, uint32_t max_ctx, uint32_t rot);
+
+/* shaders/mhsa.comp via llava_command_buffer::multi_head_attention (:154-168):
+ * scores[z][p][h] = sum_i <q[z][h][i], R(-(P - p) theta_i) K[p][h][i]>, P = *pos + z,
+ * for p <= P; slots above P (which the reference fills with values that its
+ * softmax then zeroes) are written as 0.  scores: f32 [batch][backlog][heads]. */
+int lv_attn_scores_rope(lv_ctx* ctx, float* scores, const void* k_cache, const float* q, const uint32_t* pos,
+                        const float* rope_table, uint32_t backlog, uint32_t heads, uint32_t rot, uint32_t batch);
+
+/* shaders/softmax.comp via llava_command_buffer::inplace_softmax (:170-177):
+ * a = exp(s / sqrt(rot)), a = 0 for p > P, a /= sum_p a. */
+int lv_softmax_masked(lv_ctx* ctx, float* scores, const uint32_t* pos, uint32_t backlog, uint32_t heads,
+                      uint32_t rot, uint32_t batch);
+
+/* shaders/kqv_matching.comp via llava_command_buffer::perform_kqv_matching
+ * (:179-194): v_out[z][d] = sum_p f32(V[p][d]) * probs[z][p][d / rot]. */
+int lv_attn_values(lv_ctx* ctx, float* v_out, const void* v_cache, const float* probs, uint32_t backlog,
+                   uint32_t heads, uint32_t rot, uint32_t batch);
+
+/* shaders/copy.comp via llava_command_buffer::copy_logit (:144-152). */
+int lv_copy_f32(lv_ctx* ctx, float* dst, const float* src, size_t count);
+/* shaders/add_logits.comp (no caller in the reference): a[i] += b[i]. */
+int lv_add_f32(lv_ctx* ctx, float* a, const float* b, size_t count);
+
+/* llava_buffer::write_f32 (llava_buffer.cpp:339-401) as used for the embedding
+ * rows (llava_session.cpp:219-223): out[z][:] = dequant(table row token_ids[z]).
+ * table: [vocab][cols] blocks (or f32); token_ids: device u32 [n]. */
+int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int wtype, const uint32_t* token_ids,
+                    uint32_t cols, uint32_t n);
+
+/* The deterministic branch of llava_session::get_last_predicted_token
+ * (llava_session.cpp:144-152): first index of the maximum. out: device u32. */
+int lv_argmax_f32(lv_ctx* ctx, uint32_t* out_index, const float* v, uint32_t n);
+
+/* ---- fused forms used by the decode graph -------------------------------- */
+
+/* normalize + matmul wk, wq, wv + two kv_copy (llava_layer.cpp:53-58) in one
+ * launch: K and V rows go straight into the f16 caches at row *pos + z. */
+int lv_norm_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq, const void* wk,
+                         const void* wv, int wtype, const float* x, const float* norm_w, const uint32_t* pos,
+                         uint32_t dim, uint32_t batch, uint32_t ctx_rows);
+
+/* Bytes of scratch lv_attention_fused needs for the given shape. */
+size_t lv_attention_scratch_bytes(uint32_t heads, uint32_t rot, uint32_t max_ctx, uint32_t batch);
+
+/* mhsa + softmax + kqv_matching (llava_layer.cpp:59-62) in one launch, reading
+ * only the P + 1 filled cache rows (the reference's masked slots contribute
+ * exactly 0).  out: f32 [batch][heads*rot].  scratch: device memory of
+ * lv_attention_scratch_bytes, zero-filled once before first use. */
+int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const void* k_cache, const void* v_cache,
+                       const uint32_t* pos, const float* rope_table, void* scratch, uint32_t heads, uint32_t rot,
+                       uint32_t max_ctx, uint32_t batch);
+
+/* normalize + matmul_silu_ff (llava_layer.cpp:68-69) in one launch. */
+int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const float* x,
+                         const float* norm_w, uint32_t ff, uint32_t dim, uint32_t batch);
+
+/* normalize + output matmul (llava_command_buffer.cpp:38-39) in one launch. */
+int lv_norm_gemv(lv_ctx* ctx, float* out, const void* W, int wtype, const float* x, const float* norm_w,
+                 uint32_t rows, uint32_t cols, uint32_t batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LV_B200_H */

@@ -1,0 +1,88 @@
+"""Builds the native libraries of this package in-tree with nvcc / g++.
+
+    python llama-vulkan_b200/build.py [--force]
+
+Outputs (next to this file): liblv_b200.so (sm_100a kernels + C ABI),
+libllava_host.so (C++ host surface) and the vulkan_llama command-line tool.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+HOST = os.path.join(HERE, "host")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
+]
+
+
+def _nvcc():
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found")
+    return nvcc
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def _run(cmd):
+    print("+", " ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+
+
+def _glob(d, exts):
+    return sorted(os.path.join(d, f) for f in os.listdir(d) if f.endswith(exts))
+
+
+def build_kernels(force=False, verbose_ptxas=False):
+    cu = _glob(CSRC, (".cu",))
+    deps = cu + _glob(CSRC, (".cuh", ".h")) + [os.path.join(ROOT, "include", "lv_b200.h")]
+    out = os.path.join(HERE, "liblv_b200.so")
+    if not force and not _newer(out, deps):
+        return out
+    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    if verbose_ptxas:
+        flags += ["-Xptxas", "-v"]
+    _run([_nvcc(), "-shared", "-o", out] + flags + cu + ["-lcudart"])
+    return out
+
+
+def build_host(force=False):
+    if not os.path.isdir(HOST):
+        return None
+    cpp = [f for f in _glob(HOST, (".cpp",)) if not f.endswith("main.cpp")]
+    if not cpp:
+        return None
+    deps = cpp + _glob(HOST, (".h",)) + [os.path.join(ROOT, "include", "lv_b200.h"), os.path.join(ROOT, "include", "llava_host.h")]
+    deps = [d for d in deps if os.path.exists(d)]
+    out = os.path.join(HERE, "libllava_host.so")
+    cxx = shutil.which("g++") or "g++"
+    if force or _newer(out, deps):
+        _run([cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-pthread", "-Wall", "-o", out] + cpp +
+             ["-L" + HERE, "-llv_b200", "-Wl,-rpath,$ORIGIN"])
+    main = os.path.join(HOST, "main.cpp")
+    exe = os.path.join(HERE, "vulkan_llama")
+    if os.path.exists(main) and (force or _newer(exe, [main, out])):
+        _run([cxx, "-std=c++20", "-O2", "-pthread", "-o", exe, main, "-L" + HERE, "-lllava_host", "-llv_b200",
+              "-Wl,-rpath,$ORIGIN"])
+    return out
+
+
+def build_all(force=False):
+    k = build_kernels(force)
+    h = build_host(force)
+    return k, h
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)

@@ -1,0 +1,49 @@
+// Context object behind the C ABI: one device, one stream, one error word.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/lv_b200.h"
+
+struct lv_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    uint32_t* d_err = nullptr;        // device error word, see lv::ERR_* in common.cuh
+    uint32_t* h_err = nullptr;        // pinned mirror used by lv_ctx_check
+    cudaGraph_t capture_graph = nullptr;
+    bool capturing = false;
+    void* comm = nullptr;             // ncclComm_t when a communicator is attached
+    int comm_rank = 0, comm_size = 1;
+};
+
+namespace lv {
+
+// Records a message retrievable through lv_last_error_string (thread local).
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+int gemv_configure(lv_ctx* ctx);
+int attention_configure(lv_ctx* ctx);
+
+#define LV_CUDA(call)                                          \
+    do {                                                       \
+        cudaError_t e__ = (call);                              \
+        if (e__ != cudaSuccess) return lv::cuda_fail(e__, #call); \
+    } while (0)
+
+// First statement of every entry point that takes a context.
+#define LV_ENTER(ctx)                                                        \
+    do {                                                                     \
+        if ((ctx) == nullptr) return lv::fail(LV_ERR_BAD_ARGUMENTS, "null context"); \
+        LV_CUDA(cudaSetDevice((ctx)->device));                               \
+    } while (0)
+
+#define LV_REQUIRE(cond, msg)                                              \
+    do {                                                                   \
+        if (!(cond)) return lv::fail(LV_ERR_BAD_ARGUMENTS, std::string(msg)); \
+    } while (0)
+
+}  // namespace lv

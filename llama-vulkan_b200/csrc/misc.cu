@@ -1,0 +1,182 @@
+// Small element-wise and reduction kernels: normalisation, cache append, copy,
+// add, embedding-row dequantisation, argmax.
+#include <algorithm>
+
+#include "common.cuh"
+#include "ctx.h"
+
+namespace lv {
+
+// shaders/normalize.comp:34-63: one CTA per batch row.
+__global__ void __launch_bounds__(1024) norm_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                                    const float* __restrict__ w, uint32_t dim) {
+    __shared__ float scratch[33];
+    const float* xr = x + size_t(blockIdx.x) * dim;
+    float* orow = out + size_t(blockIdx.x) * dim;
+    float part = 0.f;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) part += xr[i];
+    const float mean = block_sum(part, scratch) / static_cast<float>(dim);
+    part = 0.f;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float c = xr[i] - mean;
+        part = fmaf(c, c, part);
+    }
+    const float factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(dim));   // no epsilon
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = (xr[i] * w[i]) * factor;
+}
+
+// shaders/copy_to_cache.comp:29-37
+__global__ void kv_append_kernel(__half* __restrict__ cache, const float* __restrict__ x, const uint32_t* __restrict__ pos,
+                                 uint32_t dim, uint32_t ctx_rows, uint32_t* err) {
+    const uint32_t z = blockIdx.y;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t row = *pos + z;
+    if (row >= ctx_rows) {               // never write outside the cache
+        if (i == 0) atomicOr(err, ERR_BAD_INDEX);
+        return;
+    }
+    if (i < dim) cache[size_t(row) * dim + i] = __float2half_rn(x[size_t(z) * dim + i]);
+}
+
+__global__ void copy_kernel(float* __restrict__ dst, const float* __restrict__ src, size_t n) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) dst[i] = src[i];
+}
+
+__global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) a[i] += b[i];
+}
+
+// llava_buffer.cpp:360-370 (q4_0 v3), :387-394 (q8_0 v3), :377-381 (f32).
+// One CTA per row; one thread per block of 32 weights.
+__global__ void dequant_rows_kernel(float* __restrict__ out, const uint8_t* __restrict__ table, int wtype,
+                                    const uint32_t* __restrict__ ids, uint32_t cols) {
+    const uint32_t z = blockIdx.x;
+    const uint32_t id = ids[z];
+    float* o = out + size_t(z) * cols;
+    if (wtype == T_F32) {
+        const float* src = reinterpret_cast<const float*>(table) + size_t(id) * cols;
+        for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) o[i] = src[i];
+        return;
+    }
+    const uint32_t nb = cols / 32;
+    const uint32_t bb = wtype == T_Q4_0 ? kQ4BlockBytes : kQ8BlockBytes;
+    const uint8_t* row = table + size_t(id) * nb * bb;
+    for (uint32_t b = threadIdx.x; b < nb; b += blockDim.x) {
+        const uint8_t* blk = row + size_t(b) * bb;
+        const float d = half_bits_to_float(uint32_t(blk[0]) | (uint32_t(blk[1]) << 8));
+        if (wtype == T_Q4_0) {
+            for (int j = 0; j < 16; ++j) {
+                const int qv = blk[2 + j];
+                o[b * 32 + j] = static_cast<float>((qv & 0xf) - 8) * d;
+                o[b * 32 + j + 16] = static_cast<float>((qv >> 4) - 8) * d;
+            }
+        } else {
+            for (int j = 0; j < 32; ++j) o[b * 32 + j] = static_cast<float>(static_cast<int8_t>(blk[2 + j])) * d;
+        }
+    }
+}
+
+// llava_session.cpp:144-152: m = 0; for every i: if (v[i] > v[m]) m = i.
+// Equivalent parallel form: the lowest index holding the maximum of the
+// non-NaN entries; 0 if v[0] is NaN (nothing compares greater than it) or if
+// there is no such entry.
+constexpr uint32_t kNoIndex = 0xffffffffu;
+
+__device__ __forceinline__ void argmax_merge(float& best, uint32_t& bi, float ov, uint32_t oi) {
+    if (oi == kNoIndex) return;
+    if (bi == kNoIndex || ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out, const float* __restrict__ v, uint32_t n) {
+    __shared__ float s_val[32];
+    __shared__ uint32_t s_idx[32];
+    float best = 0.f;
+    uint32_t bi = kNoIndex;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float x = v[i];
+        if (x == x && (bi == kNoIndex || x > best)) { best = x; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_merge(best, bi, ov, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = lane < nw ? s_val[lane] : 0.f;
+        bi = lane < nw ? s_idx[lane] : kNoIndex;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_merge(best, bi, ov, oi);
+        }
+        if (lane == 0) {
+            const float first = v[0];
+            *out = (bi == kNoIndex || first != first) ? 0u : bi;
+        }
+    }
+}
+
+}  // namespace lv
+
+using namespace lv;
+
+extern "C" int lv_norm_f32(lv_ctx* ctx, float* out, const float* x, const float* w, uint32_t dim, uint32_t batch) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && x && w && dim && batch, "bad norm arguments");
+    norm_kernel<<<batch, 1024, 0, ctx->stream>>>(out, x, w, dim);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
+
+extern "C" int lv_kv_append_f16(lv_ctx* ctx, void* cache, const float* x, const uint32_t* pos, uint32_t dim,
+                                uint32_t batch, uint32_t ctx_rows) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(cache && x && pos && dim && batch && batch <= 65535, "bad kv_append arguments");
+    dim3 grid((dim + 255) / 256, batch);
+    kv_append_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<__half*>(cache), x, pos, dim, ctx_rows, ctx->d_err);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
+
+extern "C" int lv_copy_f32(lv_ctx* ctx, float* dst, const float* src, size_t count) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(dst && src, "null argument");
+    if (count == 0) return LV_OK;
+    const unsigned blocks = static_cast<unsigned>(std::min<size_t>((count + 255) / 256, 4096));
+    copy_kernel<<<blocks, 256, 0, ctx->stream>>>(dst, src, count);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
+
+extern "C" int lv_add_f32(lv_ctx* ctx, float* a, const float* b, size_t count) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(a && b, "null argument");
+    if (count == 0) return LV_OK;
+    const unsigned blocks = static_cast<unsigned>(std::min<size_t>((count + 255) / 256, 4096));
+    add_kernel<<<blocks, 256, 0, ctx->stream>>>(a, b, count);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
+
+extern "C" int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int wtype, const uint32_t* token_ids,
+                               uint32_t cols, uint32_t n) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && table && token_ids && n, "bad dequant arguments");
+    LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0, "unsupported table type");
+    LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
+    dequant_rows_kernel<<<n, 256, 0, ctx->stream>>>(out, static_cast<const uint8_t*>(table), wtype, token_ids, cols);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
+
+extern "C" int lv_argmax_f32(lv_ctx* ctx, uint32_t* out_index, const float* v, uint32_t n) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out_index && v && n, "bad argmax arguments");
+    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(out_index, v, n);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}

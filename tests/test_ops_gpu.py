@@ -1,0 +1,320 @@
+"""Parity of every kernel entry point with the CPU oracle, through the C ABI.
+
+Bit-exact for integer/byte work (dequantisation, f16 cache rows, argmax);
+fp32 results differ from the oracle only by summation order, so they are held
+to a relative-L2 of 1e-5 and a max-abs of 1e-4 of the largest output -- two
+orders tighter than the end-to-end logits tolerance (max-abs 1e-2, rel-L2 1e-3).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle_bind as ob
+import quant_np as qn
+
+pytestmark = pytest.mark.gpu
+
+HEADS, ROT = 32, 128
+DIM = HEADS * ROT
+
+
+def close(got, want, rel_l2=1e-5, max_abs_frac=1e-4):
+    got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64).ravel()
+    assert got.shape == want.shape
+    assert np.all(np.isfinite(got))
+    denom = np.linalg.norm(want) or 1.0
+    l2 = np.linalg.norm(got - want) / denom
+    mx = np.abs(got - want).max()
+    assert l2 <= rel_l2, f"rel-L2 {l2:.3e}"
+    assert mx <= max_abs_frac * (np.abs(want).max() or 1.0), f"max-abs {mx:.3e}"
+
+
+def workers_for(cols):
+    return 32 if cols == 5120 else 128      # llava_session.cpp:357-371
+
+
+def u32_dev(gpu, value):
+    return gpu.upload(np.array([value, value, value, value], np.uint32))   # config_buffer: token_count x4
+
+
+@pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0])
+def test_dequant_rows_bit_exact(gpu, pkg, wtype):
+    rng = np.random.default_rng(20)
+    vocab, cols = 64, 4096
+    table = qn.quantize((rng.standard_normal((vocab, cols)) * 0.02).astype(np.float32), wtype)
+    ids = np.array([0, 63, 17, 17, 5], np.uint32)
+    d_out = gpu.alloc(ids.size * cols * 4)
+    pkg.check(gpu.lib.lv_dequant_rows(gpu.handle, d_out, gpu.upload(table), wtype, gpu.upload(ids), cols, ids.size))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, ids.size * cols).reshape(ids.size, cols)
+    rb = qn.row_bytes(wtype, cols)
+    for z, t in enumerate(ids):
+        want = ob.dequant(table[t * rb:(t + 1) * rb], wtype, cols)
+        assert np.array_equal(got[z].view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("dim,batch", [(4096, 1), (5120, 3)])
+def test_norm(gpu, pkg, dim, batch):
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal((batch, dim)) * 3 + 0.2).astype(np.float32)
+    w = (1 + 0.01 * rng.standard_normal(dim)).astype(np.float32)
+    d_out = gpu.alloc(x.nbytes)
+    pkg.check(gpu.lib.lv_norm_f32(gpu.handle, d_out, gpu.upload(x), gpu.upload(w), dim, batch))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, x.size).reshape(batch, dim)
+    for z in range(batch):
+        close(got[z], ob.norm(x[z], w), rel_l2=2e-6, max_abs_frac=2e-6)
+
+
+GEMV_SHAPES = [
+    (qn.Q4_0, 4096, 4096), (qn.Q4_0, 4096, 11008), (qn.Q4_0, 5120, 13824), (qn.Q4_0, 5120, 5120),
+    (qn.Q4_0, 32000, 4096), (qn.Q8_0, 4096, 4096), (qn.Q8_0, 4096, 11008), (qn.Q8_0, 1024, 5120),
+    (qn.Q4_0, 4, 256), (qn.Q8_0, 8, 512),
+]
+
+
+@pytest.mark.parametrize("wtype,rows,cols", GEMV_SHAPES)
+def test_gemv_and_residual_add(gpu, pkg, wtype, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    W = qn.quantize((rng.standard_normal((rows, cols)) * 0.02).astype(np.float32), wtype)
+    x = rng.standard_normal(cols).astype(np.float32)
+    base = rng.standard_normal(rows).astype(np.float32)
+    dW, dx = gpu.upload(W), gpu.upload(x)
+    d_out = gpu.upload(base)
+    pkg.check(gpu.lib.lv_gemv(gpu.handle, d_out, dW, wtype, dx, rows, cols, 1, 0))
+    gpu.sync()
+    want = ob.gemv(W, wtype, x, rows, cols, workers_for(cols))
+    close(gpu.download(d_out, np.float32, rows), want)
+    pkg.check(gpu.lib.lv_upload(gpu.handle, d_out, base.ctypes.data_as(C.c_void_p), base.nbytes))
+    pkg.check(gpu.lib.lv_gemv(gpu.handle, d_out, dW, wtype, dx, rows, cols, 1, 1))      # matmul_add_*
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, rows), base + want)
+    for d in (dW, dx, d_out):
+        gpu.free(d)
+
+
+@pytest.mark.parametrize("wtype,ff,dim", [(qn.Q4_0, 11008, 4096), (qn.Q8_0, 11008, 4096), (qn.Q4_0, 13824, 5120)])
+def test_gemv_silu(gpu, pkg, wtype, ff, dim):
+    rng = np.random.default_rng(ff)
+    w3 = qn.quantize((rng.standard_normal((ff, dim)) * 0.02).astype(np.float32), wtype)
+    w1 = qn.quantize((rng.standard_normal((ff, dim)) * 0.02).astype(np.float32), wtype)
+    x = rng.standard_normal(dim).astype(np.float32)
+    d3, d1, dx = gpu.upload(w3), gpu.upload(w1), gpu.upload(x)
+    d_out = gpu.alloc(ff * 4)
+    pkg.check(gpu.lib.lv_gemv_silu(gpu.handle, d_out, d3, d1, wtype, dx, ff, dim, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, ff), ob.gemv_silu(w3, w1, wtype, x, ff, dim, workers_for(dim)))
+    for d in (d3, d1, dx, d_out):
+        gpu.free(d)
+
+
+def test_gemv_batch_rows_are_independent(gpu, pkg):
+    rng = np.random.default_rng(22)
+    rows, cols, batch = 512, 4096, 3
+    W = qn.quantize_q4_0((rng.standard_normal((rows, cols)) * 0.02).astype(np.float32))
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    d_out = gpu.alloc(batch * rows * 4)
+    pkg.check(gpu.lib.lv_gemv(gpu.handle, d_out, gpu.upload(W), qn.Q4_0, gpu.upload(x), rows, cols, batch, 0))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, batch * rows).reshape(batch, rows)
+    for z in range(batch):
+        close(got[z], ob.gemv(W, qn.Q4_0, x[z], rows, cols, 128))
+
+
+def test_norm_fused_gemv_matches_norm_then_gemv(gpu, pkg):
+    rng = np.random.default_rng(23)
+    rows, cols = 1024, 4096
+    W = qn.quantize_q4_0((rng.standard_normal((rows, cols)) * 0.02).astype(np.float32))
+    x = (rng.standard_normal(cols) * 2).astype(np.float32)
+    nw = (1 + 0.01 * rng.standard_normal(cols)).astype(np.float32)
+    d_out = gpu.alloc(rows * 4)
+    pkg.check(gpu.lib.lv_norm_gemv(gpu.handle, d_out, gpu.upload(W), qn.Q4_0, gpu.upload(x), gpu.upload(nw), rows, cols, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, rows), ob.gemv(W, qn.Q4_0, ob.norm(x, nw), rows, cols, 128))
+
+
+def test_gemv_rejects_bad_arguments(gpu, pkg):
+    lib = gpu.lib
+    d = gpu.alloc(4096)
+    assert lib.lv_gemv(gpu.handle, d, d, 3, d, 4, 256, 1, 0) == pkg.LV_ERR_BAD_ARGUMENTS        # q4_1 unsupported
+    assert lib.lv_gemv(gpu.handle, d, d, qn.Q4_0, d, 4, 96, 1, 0) == pkg.LV_ERR_BAD_ARGUMENTS   # cols % 256
+    assert lib.lv_gemv(gpu.handle, d, d, qn.Q4_0, d, 6, 256, 1, 0) == pkg.LV_ERR_BAD_ARGUMENTS  # rows % 4
+    assert lib.lv_gemv(gpu.handle, d, pkg.offset(d, 2), qn.Q4_0, d, 4, 256, 1, 0) == pkg.LV_ERR_BAD_ARGUMENTS
+    assert lib.lv_gemv(None, d, d, qn.Q4_0, d, 4, 256, 1, 0) == pkg.LV_ERR_BAD_ARGUMENTS
+    assert b"" != lib.lv_last_error_string()
+
+
+def test_kv_append_bit_exact(gpu, pkg):
+    rng = np.random.default_rng(24)
+    batch, ctx_rows, pos = 3, 16, 5
+    x = np.concatenate([rng.standard_normal((batch, DIM - 6)) * 2, np.tile([1e-7, 65519.0, 7e4, -0.0, 6.1e-5, 1.0009766], (batch, 1))], 1).astype(np.float32)
+    cache = gpu.zeros(ctx_rows * DIM * 2)
+    pkg.check(gpu.lib.lv_kv_append_f16(gpu.handle, cache, gpu.upload(x), u32_dev(gpu, pos), DIM, batch, ctx_rows))
+    gpu.sync()
+    got = gpu.download(cache, np.uint16, ctx_rows * DIM).reshape(ctx_rows, DIM)
+    want = np.zeros((ctx_rows, DIM), np.uint16)
+    with np.errstate(over="ignore"):
+        want[pos:pos + batch] = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want)
+    assert np.array_equal(want[pos], ob.f32_to_f16_bits(x[0]))
+    # a row outside the cache is refused and reported, never written
+    pkg.check(gpu.lib.lv_kv_append_f16(gpu.handle, cache, gpu.upload(x), u32_dev(gpu, ctx_rows - 1), DIM, batch, ctx_rows))
+    with pytest.raises(pkg.LvError) as e:
+        gpu.sync()
+    assert e.value.code == pkg.LV_ERR_DEVICE_WAIT
+    gpu.sync()      # the error word was cleared
+
+
+def _caches(rng, n, rows):
+    k = np.zeros((rows, DIM), np.float16)
+    v = np.zeros((rows, DIM), np.float16)
+    k[:n] = (rng.standard_normal((n, DIM)) * 0.7).astype(np.float16)
+    v[:n] = (rng.standard_normal((n, DIM)) * 0.7).astype(np.float16)
+    return k.view(np.uint16), v.view(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def rope_table(gpu, pkg):
+    t = gpu.alloc(2048 * ROT * 4)
+    pkg.check(gpu.lib.lv_rope_table_build(gpu.handle, t, 2048, ROT))
+    return t
+
+
+@pytest.mark.parametrize("pos,backlog", [(0, 128), (1, 128), (63, 128), (64, 128), (127, 128), (300, 512)])
+def test_three_attention_ops_match_reference_shaders(gpu, pkg, rope_table, pos, backlog):
+    rng = np.random.default_rng(100 + pos)
+    k, v = _caches(rng, pos + 1, backlog)
+    q = rng.standard_normal(DIM).astype(np.float32)
+    lib, h = gpu.lib, gpu.handle
+    dk, dv, dq, dpos = gpu.upload(k), gpu.upload(v), gpu.upload(q), u32_dev(gpu, pos)
+    d_scores = gpu.alloc(backlog * HEADS * 4)
+    d_out = gpu.alloc(DIM * 4)
+    pkg.check(lib.lv_attn_scores_rope(h, d_scores, dk, dq, dpos, rope_table, backlog, HEADS, ROT, 1))
+    gpu.sync()
+    scores = gpu.download(d_scores, np.float32, backlog * HEADS).reshape(backlog, HEADS)
+    want_scores = ob.mhsa(k, q, pos, HEADS, ROT)
+    close(scores[: pos + 1], want_scores, rel_l2=2e-6, max_abs_frac=1e-5)
+    assert np.all(scores[pos + 1:] == 0)
+    pkg.check(lib.lv_softmax_masked(h, d_scores, dpos, backlog, HEADS, ROT, 1))
+    gpu.sync()
+    probs = gpu.download(d_scores, np.float32, backlog * HEADS).reshape(backlog, HEADS)
+    want_probs = ob.softmax(want_scores, pos, backlog, HEADS, ROT)
+    close(probs, want_probs, rel_l2=5e-6, max_abs_frac=1e-5)
+    assert np.all(probs[pos + 1:] == 0)
+    pkg.check(lib.lv_attn_values(h, d_out, dv, d_scores, backlog, HEADS, ROT, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, DIM), ob.kqv(v, want_probs, backlog, HEADS, ROT), rel_l2=5e-6, max_abs_frac=2e-5)
+    for d in (dk, dv, dq, d_scores, d_out):
+        gpu.free(d)
+
+
+@pytest.mark.parametrize("pos", [0, 1, 63, 64, 65, 127, 128, 300, 511, 1023, 2047])
+def test_fused_attention(gpu, pkg, rope_table, pos):
+    rng = np.random.default_rng(200 + pos)
+    max_ctx = 2048
+    backlog = 128
+    while backlog <= pos:
+        backlog *= 2
+    k, v = _caches(rng, pos + 1, max_ctx)
+    q = rng.standard_normal(DIM).astype(np.float32)
+    nbytes = gpu.lib.lv_attention_scratch_bytes(HEADS, ROT, max_ctx, 1)
+    assert nbytes > 0
+    scratch = gpu.zeros(nbytes)
+    dk, dv, dq = gpu.upload(k), gpu.upload(v), gpu.upload(q)
+    d_out = gpu.alloc(DIM * 4)
+    want = ob.attention(k, v, q, pos, backlog, HEADS, ROT)
+    for _ in range(2):       # the second launch proves the arrival counters were reset
+        pkg.check(gpu.lib.lv_memset(gpu.handle, d_out, 0xFF, DIM * 4))
+        pkg.check(gpu.lib.lv_attention_fused(gpu.handle, d_out, dq, dk, dv, u32_dev(gpu, pos), rope_table, scratch,
+                                             HEADS, ROT, max_ctx, 1))
+        gpu.sync()
+        close(gpu.download(d_out, np.float32, DIM), want, rel_l2=5e-6, max_abs_frac=2e-5)
+    for d in (dk, dv, dq, d_out, scratch):
+        gpu.free(d)
+
+
+def test_fused_attention_batch_is_causal(gpu, pkg, rope_table):
+    rng = np.random.default_rng(31)
+    batch, pos, max_ctx = 4, 70, 256
+    k, v = _caches(rng, pos + batch, max_ctx)
+    q = rng.standard_normal((batch, DIM)).astype(np.float32)
+    scratch = gpu.zeros(gpu.lib.lv_attention_scratch_bytes(HEADS, ROT, max_ctx, batch))
+    d_out = gpu.alloc(batch * DIM * 4)
+    pkg.check(gpu.lib.lv_attention_fused(gpu.handle, d_out, gpu.upload(q), gpu.upload(k), gpu.upload(v), u32_dev(gpu, pos),
+                                         rope_table, scratch, HEADS, ROT, max_ctx, batch))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, batch * DIM).reshape(batch, DIM)
+    for z in range(batch):       # row z sees cache rows 0 .. pos + z (softmax.comp:35)
+        close(got[z], ob.attention(k, v, q[z], pos + z, 128, HEADS, ROT), rel_l2=5e-6, max_abs_frac=2e-5)
+
+
+def test_qkv_fused_writes_cache_rows_and_query(gpu, pkg):
+    rng = np.random.default_rng(32)
+    ctx_rows, pos, batch = 8, 3, 2
+    ws = [qn.quantize_q4_0((rng.standard_normal((DIM, DIM)) * 0.02).astype(np.float32)) for _ in range(3)]
+    wq, wk, wv = ws
+    x = (rng.standard_normal((batch, DIM)) * 2).astype(np.float32)
+    nw = (1 + 0.01 * rng.standard_normal(DIM)).astype(np.float32)
+    dkc, dvc = gpu.zeros(ctx_rows * DIM * 2), gpu.zeros(ctx_rows * DIM * 2)
+    dq = gpu.alloc(batch * DIM * 4)
+    pkg.check(gpu.lib.lv_norm_qkv_kvappend(gpu.handle, dq, dkc, dvc, gpu.upload(wq), gpu.upload(wk), gpu.upload(wv), qn.Q4_0,
+                                           gpu.upload(x), gpu.upload(nw), u32_dev(gpu, pos), DIM, batch, ctx_rows))
+    gpu.sync()
+    gq = gpu.download(dq, np.float32, batch * DIM).reshape(batch, DIM)
+    gk = gpu.download(dkc, np.uint16, ctx_rows * DIM).reshape(ctx_rows, DIM).view(np.float16).astype(np.float32)
+    gv = gpu.download(dvc, np.uint16, ctx_rows * DIM).reshape(ctx_rows, DIM).view(np.float16).astype(np.float32)
+    for z in range(batch):
+        h = ob.norm(x[z], nw)
+        close(gq[z], ob.gemv(wq, qn.Q4_0, h, DIM, DIM, 128))
+        # f16 rounding of a value that differs in the last fp32 bits may land on the neighbouring half
+        close(gk[pos + z], ob.gemv(wk, qn.Q4_0, h, DIM, DIM, 128), rel_l2=6e-4, max_abs_frac=1e-3)
+        close(gv[pos + z], ob.gemv(wv, qn.Q4_0, h, DIM, DIM, 128), rel_l2=6e-4, max_abs_frac=1e-3)
+    assert not gk[:pos].any() and not gk[pos + batch:].any()
+
+
+def test_argmax_copy_add(gpu, pkg):
+    rng = np.random.default_rng(33)
+    lib, h = gpu.lib, gpu.handle
+    d_idx = gpu.alloc(16)
+    for case in range(4):
+        v = rng.standard_normal(32000).astype(np.float32)
+        if case == 1:
+            v[[31999, 777, 12345]] = v.max() + 1        # ties: lowest index wins
+        if case == 2:
+            v[5] = np.nan
+        if case == 3:
+            v[0] = np.nan
+        pkg.check(lib.lv_argmax_f32(h, d_idx, gpu.upload(v), v.size))
+        gpu.sync()
+        assert gpu.download(d_idx, np.uint32, 1)[0] == ob.load().orc_argmax(ob.ptr(v), v.size)
+    a, b = rng.standard_normal(5000).astype(np.float32), rng.standard_normal(5000).astype(np.float32)
+    da, db, dc = gpu.upload(a), gpu.upload(b), gpu.alloc(a.nbytes)
+    pkg.check(lib.lv_copy_f32(h, dc, da, a.size))
+    pkg.check(lib.lv_add_f32(h, da, db, a.size))
+    gpu.sync()
+    assert np.array_equal(gpu.download(dc, np.float32, a.size), a)
+    assert np.array_equal(gpu.download(da, np.float32, a.size), a + b)
+
+
+def test_graph_capture_replays_with_a_new_position(gpu, pkg, rope_table):
+    """The recorded step reads the position from device memory, so one graph serves every token."""
+    rng = np.random.default_rng(34)
+    ctx_rows = 16
+    x = rng.standard_normal((1, DIM)).astype(np.float32)
+    cache = gpu.zeros(ctx_rows * DIM * 2)
+    dpos, dx = u32_dev(gpu, 2), gpu.upload(x)
+    g = C.c_void_p()
+    pkg.check(gpu.lib.lv_graph_begin_capture(gpu.handle))
+    pkg.check(gpu.lib.lv_kv_append_f16(gpu.handle, cache, dx, dpos, DIM, 1, ctx_rows))
+    pkg.check(gpu.lib.lv_graph_end_capture(gpu.handle, C.byref(g)))
+    for pos in (2, 9):
+        p = np.array([pos] * 4, np.uint32)
+        pkg.check(gpu.lib.lv_upload(gpu.handle, dpos, p.ctypes.data_as(C.c_void_p), 16))
+        pkg.check(gpu.lib.lv_graph_launch(gpu.handle, g))
+        gpu.sync()
+    got = gpu.download(cache, np.uint16, ctx_rows * DIM).reshape(ctx_rows, DIM)
+    want = x.astype(np.float16).view(np.uint16)[0]
+    assert np.array_equal(got[2], want) and np.array_equal(got[9], want)
+    assert not got[[0, 1, 3, 8, 10]].any()
+    pkg.check(gpu.lib.lv_graph_destroy(g))
