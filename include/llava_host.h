@@ -1,0 +1,79 @@
+/*
+ * llava_host -- plain-C wrappers around the C++ host surface (ggml_file,
+ * llava_context, llava_session, the synthetic model writer) so that tests,
+ * benchmarks and other languages can drive it.  Each wrapper forwards to the
+ * C++ method of the same name; the C++ classes keep the public methods of the
+ * reference's classes (ggml_file.h:51-57, llava_session.h:44-62,
+ * llava_context.h:21-42).  Handles are opaque; functions that return int use
+ * 1 = success, 0 = failure unless stated otherwise; ReturnCode values are
+ * those of types.h:45-55.
+ */
+#ifndef LLAVA_HOST_H
+#define LLAVA_HOST_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- synthetic ggjt-v3 models (seeded N(0,0.02) weights; q4_0 = 2, q8_0 = 8) */
+int      llava_synth_write(const char* path, uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff_size,
+                           uint32_t vocab_size, int wtype, uint64_t seed, uint32_t threads);
+uint64_t llava_synth_file_size(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff_size,
+                               uint32_t vocab_size, int wtype);
+float    llava_synth_normal(uint64_t seed, uint32_t tensor, uint64_t element);
+void     llava_synth_quantize(const float* src, size_t count, int wtype, uint8_t* dst);
+
+/* ---- ggml_file (ggml_file.h:51-57) */
+void*    ggml_file_open(const char* path);                 /* NULL if the file cannot be parsed */
+void     ggml_file_close(void* file);
+void     ggml_file_header(void* file, uint32_t* out10);    /* nine header words, then ff_size */
+uint32_t ggml_file_n_tensors(void* file);
+int      ggml_file_tensor(void* file, uint32_t index, char* name, size_t name_cap, uint32_t* type, uint64_t* offset,
+                          uint32_t* shape1, uint32_t* shape2, uint64_t* size);
+int      ggml_file_find(void* file, const char* name, uint64_t* offset);      /* get_buffer_descriptor */
+uint32_t ggml_file_tokenize(void* file, const char* text, size_t len, int bos, uint32_t* out, uint32_t cap);
+uint32_t ggml_file_tokens_to_text(void* file, const uint32_t* tokens, uint32_t n, char* out, uint32_t cap);
+uint32_t ggml_file_token(void* file, uint32_t id, char* out, uint32_t cap, float* score);
+/* llava_buffer::write_f32 arithmetic on the host (llava_buffer.cpp:339-401) */
+int      llava_dequantize(const void* in, int type, uint32_t model_version, float* out, uint32_t count);
+
+/* ---- llava_context (llava_context.h:21-42) */
+void*    llava_context_open(const char* model_path, int device);   /* NULL on failure */
+void     llava_context_close(void* ctx);
+void*    llava_context_lv(void* ctx);                               /* the lv_ctx* behind it */
+int      llava_context_run(int argc, char** argv);                  /* the command-line tool */
+
+/* ---- llava_session (llava_session.h:44-62) */
+void*    llava_session_create(void* ctx);
+void     llava_session_destroy(void* session);
+int      llava_session_set_text(void* session, const char* text, size_t len);
+int      llava_session_add_text(void* session, const char* text, size_t len);
+int      llava_session_push_token(void* session, uint32_t token);
+uint32_t llava_session_predict_next_token(void* session);          /* 0xFFFFFFFF on failure */
+int      llava_session_start_next_token_prediction(void* session);
+uint32_t llava_session_finish_next_token_prediction(void* session);
+void     llava_session_rewind(void* session, uint32_t n);
+uint32_t llava_session_set_options(void* session, uint32_t options);    /* ReturnCode */
+uint32_t llava_session_save_frame(void* session, const char* path);     /* ReturnCode */
+uint32_t llava_session_snapshot(void* session, const char* path);       /* ReturnCode */
+uint32_t llava_session_restore(void* session, const char* path);        /* ReturnCode */
+uint32_t llava_session_get_token_count(void* session);
+uint32_t llava_session_get_tokens(void* session, uint32_t* out, uint32_t cap);
+/* additions of this build (see llava_session.h) */
+void     llava_session_set_deterministic(void* session, int on);
+void     llava_session_set_seed(void* session, uint32_t seed);
+int      llava_session_set_max_batch(void* session, uint32_t n);
+int      llava_session_generate_greedy_on_device(void* session, uint32_t n, uint32_t* out);
+int      llava_session_get_logits(void* session, float* out, uint32_t cap);
+uint32_t llava_session_get_backlog_size(void* session);
+uint32_t llava_session_get_tokens_in_gpu(void* session);
+/* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
+int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAVA_HOST_H */

@@ -133,14 +133,27 @@ int lv_copy_f32(lv_ctx* ctx, float* dst, const float* src, size_t count);
 int lv_add_f32(lv_ctx* ctx, float* a, const float* b, size_t count);
 
 /* llava_buffer::write_f32 (llava_buffer.cpp:339-401) as used for the embedding
- * rows (llava_session.cpp:219-223): out[z][:] = dequant(table row token_ids[z]).
- * table: [vocab][cols] blocks (or f32); token_ids: device u32 [n]. */
+ * rows (llava_session.cpp:219-223): out[z][:] = dequant(table row ids[z]) with
+ * ids = token_ids + (first ? *first : 0).  table: [vocab][cols] blocks (or f32);
+ * token_ids: device u32; first: device u32 or null (lets a recorded step read
+ * "the tokens at the current position" from a device copy of the token buffer);
+ * ids >= vocab are reported through the error word and read as row 0. */
 int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int wtype, const uint32_t* token_ids,
-                    uint32_t cols, uint32_t n);
+                    const uint32_t* first, uint32_t cols, uint32_t vocab, uint32_t n);
 
 /* The deterministic branch of llava_session::get_last_predicted_token
  * (llava_session.cpp:144-152): first index of the maximum. out: device u32. */
 int lv_argmax_f32(lv_ctx* ctx, uint32_t* out_index, const float* v, uint32_t n);
+
+/* Last node of a recorded token step: the four words of config (the
+ * reference's config_buffer, token_count x4) grow by batch, and, when argmax
+ * and token_log are given, token_log[old token_count + batch] = *argmax, i.e.
+ * the predicted token becomes the input of the next step without a host round
+ * trip.  The reference's host does both between submits
+ * (llava_session.cpp:224-228, llava_context.cpp:355-359).  All pointers are
+ * device memory; a log index >= log_capacity is reported, not written. */
+int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
+                      uint32_t log_capacity);
 
 /* ---- fused forms used by the decode graph -------------------------------- */
 

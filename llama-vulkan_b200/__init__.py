@@ -62,8 +62,9 @@ KERNEL_API = {
     "lv_attn_values": (_int, [_p, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_copy_f32": (_int, [_p, _p, _p, _sz]),
     "lv_add_f32": (_int, [_p, _p, _p, _sz]),
-    "lv_dequant_rows": (_int, [_p, _p, _p, _int, _p, _u32, _u32]),
+    "lv_dequant_rows": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_argmax_f32": (_int, [_p, _p, _p, _u32]),
+    "lv_decode_advance": (_int, [_p, _p, _p, _p, _u32, _u32]),
     "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32]),
     "lv_attention_scratch_bytes": (_sz, [_u32, _u32, _u32, _u32]),
     "lv_attention_fused": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
@@ -95,7 +96,7 @@ def load_kernels():
         if not os.path.exists(KERNEL_LIB):
             raise RuntimeError(f"{KERNEL_LIB} is missing: run `python llama-vulkan_b200/build.py` "
                                "(there is no fallback path)")
-        lib = C.CDLL(KERNEL_LIB, mode=C.RTLD_GLOBAL)
+        lib = C.CDLL(KERNEL_LIB)
         _declare(lib, KERNEL_API)
         _kernels = lib
     return _kernels
@@ -170,3 +171,241 @@ class Context:
 def offset(ptr, nbytes):
     """c_void_p arithmetic."""
     return _p(ptr.value + int(nbytes))
+
+
+# ---- libllava_host.so: the C++ host surface --------------------------------------------
+_u64 = C.c_uint64
+_f32p = C.POINTER(C.c_float)
+_u32p = C.POINTER(C.c_uint32)
+
+# name -> (restype, argtypes); mirrors include/llava_host.h
+HOST_API = {
+    "llava_synth_write": (_int, [C.c_char_p, _u32, _u32, _u32, _u32, _u32, _int, _u64, _u32]),
+    "llava_synth_file_size": (_u64, [_u32, _u32, _u32, _u32, _u32, _int]),
+    "llava_synth_normal": (C.c_float, [_u64, _u32, _u64]),
+    "llava_synth_quantize": (None, [_p, _sz, _int, _p]),
+    "ggml_file_open": (_p, [C.c_char_p]),
+    "ggml_file_close": (None, [_p]),
+    "ggml_file_header": (None, [_p, _u32p]),
+    "ggml_file_n_tensors": (_u32, [_p]),
+    "ggml_file_tensor": (_int, [_p, _u32, C.c_char_p, _sz, _u32p, C.POINTER(_u64), _u32p, _u32p, C.POINTER(_u64)]),
+    "ggml_file_find": (_int, [_p, C.c_char_p, C.POINTER(_u64)]),
+    "ggml_file_tokenize": (_u32, [_p, C.c_char_p, _sz, _int, _p, _u32]),
+    "ggml_file_tokens_to_text": (_u32, [_p, _p, _u32, C.c_char_p, _u32]),
+    "ggml_file_token": (_u32, [_p, _u32, C.c_char_p, _u32, _f32p]),
+    "llava_dequantize": (_int, [_p, _int, _u32, _p, _u32]),
+    "llava_context_open": (_p, [C.c_char_p, _int]),
+    "llava_context_close": (None, [_p]),
+    "llava_context_lv": (_p, [_p]),
+    "llava_context_run": (_int, [_int, C.POINTER(C.c_char_p)]),
+    "llava_session_create": (_p, [_p]),
+    "llava_session_destroy": (None, [_p]),
+    "llava_session_set_text": (_int, [_p, C.c_char_p, _sz]),
+    "llava_session_add_text": (_int, [_p, C.c_char_p, _sz]),
+    "llava_session_push_token": (_int, [_p, _u32]),
+    "llava_session_predict_next_token": (_u32, [_p]),
+    "llava_session_start_next_token_prediction": (_int, [_p]),
+    "llava_session_finish_next_token_prediction": (_u32, [_p]),
+    "llava_session_rewind": (None, [_p, _u32]),
+    "llava_session_set_options": (_u32, [_p, _u32]),
+    "llava_session_save_frame": (_u32, [_p, C.c_char_p]),
+    "llava_session_snapshot": (_u32, [_p, C.c_char_p]),
+    "llava_session_restore": (_u32, [_p, C.c_char_p]),
+    "llava_session_get_token_count": (_u32, [_p]),
+    "llava_session_get_tokens": (_u32, [_p, _p, _u32]),
+    "llava_session_set_deterministic": (None, [_p, _int]),
+    "llava_session_set_seed": (None, [_p, _u32]),
+    "llava_session_set_max_batch": (_int, [_p, _u32]),
+    "llava_session_generate_greedy_on_device": (_int, [_p, _u32, _p]),
+    "llava_session_get_logits": (_int, [_p, _p, _u32]),
+    "llava_session_get_backlog_size": (_u32, [_p]),
+    "llava_session_get_tokens_in_gpu": (_u32, [_p]),
+    "llava_session_read_kv": (_int, [_p, _u32, _int, _u32, _u32, _p]),
+}
+
+NO_TOKEN = 0xFFFFFFFF
+GEOMETRY = {   # dim, n_heads, ff_size, full depth
+    "7b": (4096, 32, 11008, 32),
+    "13b": (5120, 40, 13824, 40),
+}
+
+
+def load_host():
+    """Loads libllava_host.so (and liblv_b200.so, which it links); raises if not built."""
+    global _host
+    if _host is None:
+        load_kernels()
+        if not os.path.exists(HOST_LIB):
+            raise RuntimeError(f"{HOST_LIB} is missing: run `python llama-vulkan_b200/build.py`")
+        lib = C.CDLL(HOST_LIB)
+        _declare(lib, HOST_API)
+        _host = lib
+    return _host
+
+
+def write_synthetic_model(path, geometry="7b", n_layers=None, wtype=TYPE_Q4_0, vocab=32000, seed=1234, threads=0):
+    """Writes a seeded synthetic ggjt-v3 model file and returns its size in bytes."""
+    dim, heads, ff, depth = GEOMETRY[geometry]
+    n_layers = depth if n_layers is None else n_layers
+    if not load_host().llava_synth_write(os.fsencode(path), dim, heads, n_layers, ff, vocab, wtype, seed, threads):
+        raise RuntimeError(f"cannot write synthetic model {path}")
+    return os.path.getsize(path)
+
+
+class ModelFile:
+    """ggml_file: header, tensor table, tokenizer (no GPU needed)."""
+
+    def __init__(self, path):
+        self.lib = load_host()
+        self.handle = self.lib.ggml_file_open(os.fsencode(path))
+        if not self.handle:
+            raise RuntimeError(f"cannot open model {path}")
+        h = (_u32 * 10)()
+        self.lib.ggml_file_header(self.handle, h)
+        (self.magic, self.file_version, self.vocab_size, self.dim, self.multiple_of, self.n_heads, self.n_layers,
+         self.rot, self.ftype, self.ff_size) = list(h)
+
+    def close(self):
+        if self.handle:
+            self.lib.ggml_file_close(self.handle)
+            self.handle = None
+
+    def tensors(self):
+        out = []
+        name = C.create_string_buffer(256)
+        t, s1, s2 = _u32(), _u32(), _u32()
+        off, size = _u64(), _u64()
+        for i in range(self.lib.ggml_file_n_tensors(self.handle)):
+            self.lib.ggml_file_tensor(self.handle, i, name, 256, C.byref(t), C.byref(off), C.byref(s1), C.byref(s2), C.byref(size))
+            out.append((name.value.decode(), t.value, off.value, s1.value, s2.value, size.value))
+        return out
+
+    def tokenize(self, text, bos=True):
+        data = text if isinstance(text, bytes) else text.encode("utf-8")
+        cap = len(data) + 2
+        buf = (_u32 * cap)()
+        n = self.lib.ggml_file_tokenize(self.handle, data, len(data), int(bos), buf, cap)
+        return list(buf[:n])
+
+    def tokens_to_text(self, tokens):
+        arr = (_u32 * len(tokens))(*tokens)
+        n = self.lib.ggml_file_tokens_to_text(self.handle, arr, len(tokens), None, 0)
+        out = C.create_string_buffer(n + 1)
+        self.lib.ggml_file_tokens_to_text(self.handle, arr, len(tokens), out, n)
+        return out.raw[:n]
+
+    def token(self, i):
+        score = C.c_float()
+        n = self.lib.ggml_file_token(self.handle, i, None, 0, C.byref(score))
+        out = C.create_string_buffer(n + 1)
+        self.lib.ggml_file_token(self.handle, i, out, n, C.byref(score))
+        return out.raw[:n], score.value
+
+
+class HostContext:
+    """llava_context: model + device + uploaded layers."""
+
+    def __init__(self, model_path, device=0):
+        self.lib = load_host()
+        self.handle = self.lib.llava_context_open(os.fsencode(model_path), device)
+        if not self.handle:
+            raise RuntimeError(f"llava_context::open({model_path}) failed: "
+                               + (load_kernels().lv_last_error_string() or b"").decode("utf-8", "replace"))
+
+    def close(self):
+        if self.handle:
+            self.lib.llava_context_close(self.handle)
+            self.handle = None
+
+    def session(self):
+        return Session(self)
+
+
+class Session:
+    """llava_session."""
+
+    def __init__(self, ctx):
+        self.lib = ctx.lib
+        self.ctx = ctx
+        self.handle = self.lib.llava_session_create(ctx.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.llava_session_destroy(self.handle)
+            self.handle = None
+
+    def push_token(self, t):
+        return bool(self.lib.llava_session_push_token(self.handle, t))
+
+    def set_text(self, text):
+        data = text if isinstance(text, bytes) else text.encode("utf-8")
+        return bool(self.lib.llava_session_set_text(self.handle, data, len(data)))
+
+    def add_text(self, text):
+        data = text if isinstance(text, bytes) else text.encode("utf-8")
+        return bool(self.lib.llava_session_add_text(self.handle, data, len(data)))
+
+    def predict_next_token(self):
+        return self.lib.llava_session_predict_next_token(self.handle)
+
+    def start_next_token_prediction(self):
+        return bool(self.lib.llava_session_start_next_token_prediction(self.handle))
+
+    def finish_next_token_prediction(self):
+        return self.lib.llava_session_finish_next_token_prediction(self.handle)
+
+    def rewind(self, n):
+        self.lib.llava_session_rewind(self.handle, n)
+
+    def set_options(self, o):
+        return self.lib.llava_session_set_options(self.handle, o)
+
+    def save_frame(self, path):
+        return self.lib.llava_session_save_frame(self.handle, os.fsencode(path))
+
+    def snapshot(self, path):
+        return self.lib.llava_session_snapshot(self.handle, os.fsencode(path))
+
+    def restore(self, path):
+        return self.lib.llava_session_restore(self.handle, os.fsencode(path))
+
+    def tokens(self):
+        n = self.lib.llava_session_get_token_count(self.handle)
+        buf = (_u32 * max(n, 1))()
+        self.lib.llava_session_get_tokens(self.handle, buf, n)
+        return list(buf[:n])
+
+    def set_deterministic(self, on=True):
+        self.lib.llava_session_set_deterministic(self.handle, int(on))
+
+    def set_seed(self, seed):
+        self.lib.llava_session_set_seed(self.handle, seed)
+
+    def set_max_batch(self, n):
+        return bool(self.lib.llava_session_set_max_batch(self.handle, n))
+
+    def generate_greedy_on_device(self, n):
+        buf = (_u32 * n)()
+        if not self.lib.llava_session_generate_greedy_on_device(self.handle, n, buf):
+            raise RuntimeError("generate_greedy_on_device failed")
+        return list(buf)
+
+    def logits(self, vocab):
+        import numpy as np
+        out = np.empty(vocab, np.float32)
+        if not self.lib.llava_session_get_logits(self.handle, out.ctypes.data_as(_p), vocab):
+            raise RuntimeError("get_logits failed")
+        return out
+
+    def backlog_size(self):
+        return self.lib.llava_session_get_backlog_size(self.handle)
+
+    def tokens_in_gpu(self):
+        return self.lib.llava_session_get_tokens_in_gpu(self.handle)
+
+    def read_kv(self, layer, which, row0, nrows, dim):
+        import numpy as np
+        out = np.empty((nrows, dim), np.uint16)
+        if not self.lib.llava_session_read_kv(self.handle, layer, which, row0, nrows, out.ctypes.data_as(_p)):
+            raise RuntimeError("read_kv failed")
+        return out

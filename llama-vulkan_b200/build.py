@@ -69,7 +69,7 @@ def build_host(force=False):
     cxx = shutil.which("g++") or "g++"
     if force or _newer(out, deps):
         _run([cxx, "-std=c++20", "-O2", "-fPIC", "-shared", "-pthread", "-Wall", "-o", out] + cpp +
-             ["-L" + HERE, "-llv_b200", "-Wl,-rpath,$ORIGIN"])
+             ["-L" + HERE, "-llv_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-Bsymbolic"])
     main = os.path.join(HOST, "main.cpp")
     exe = os.path.join(HERE, "vulkan_llama")
     if os.path.exists(main) and (force or _newer(exe, [main, out])):

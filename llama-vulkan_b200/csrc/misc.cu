@@ -49,9 +49,14 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 // llava_buffer.cpp:360-370 (q4_0 v3), :387-394 (q8_0 v3), :377-381 (f32).
 // One CTA per row; one thread per block of 32 weights.
 __global__ void dequant_rows_kernel(float* __restrict__ out, const uint8_t* __restrict__ table, int wtype,
-                                    const uint32_t* __restrict__ ids, uint32_t cols) {
+                                    const uint32_t* __restrict__ ids, const uint32_t* __restrict__ first, uint32_t cols,
+                                    uint32_t vocab, uint32_t* err) {
     const uint32_t z = blockIdx.x;
-    const uint32_t id = ids[z];
+    uint32_t id = ids[(first ? *first : 0u) + z];
+    if (id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, ERR_BAD_INDEX);
+        id = 0;
+    }
     float* o = out + size_t(z) * cols;
     if (wtype == T_F32) {
         const float* src = reinterpret_cast<const float*>(table) + size_t(id) * cols;
@@ -120,9 +125,28 @@ __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out
     }
 }
 
+__global__ void decode_advance_kernel(uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
+                                      uint32_t log_capacity, uint32_t* err) {
+    if (argmax != nullptr && token_log != nullptr) {
+        const uint32_t at = config[0] + batch;
+        if (at < log_capacity) token_log[at] = *argmax;
+        else atomicOr(err, ERR_BAD_INDEX);
+    }
+    for (int i = 0; i < 4; ++i) config[i] += batch;
+}
+
 }  // namespace lv
 
 using namespace lv;
+
+extern "C" int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uint32_t* token_log,
+                                 uint32_t batch, uint32_t log_capacity) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(config && batch, "bad advance arguments");
+    decode_advance_kernel<<<1, 1, 0, ctx->stream>>>(config, argmax, token_log, batch, log_capacity, ctx->d_err);
+    LV_CUDA(cudaGetLastError());
+    return LV_OK;
+}
 
 extern "C" int lv_norm_f32(lv_ctx* ctx, float* out, const float* x, const float* w, uint32_t dim, uint32_t batch) {
     LV_ENTER(ctx);
@@ -163,12 +187,12 @@ extern "C" int lv_add_f32(lv_ctx* ctx, float* a, const float* b, size_t count) {
 }
 
 extern "C" int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int wtype, const uint32_t* token_ids,
-                               uint32_t cols, uint32_t n) {
+                               const uint32_t* first, uint32_t cols, uint32_t vocab, uint32_t n) {
     LV_ENTER(ctx);
-    LV_REQUIRE(out && table && token_ids && n, "bad dequant arguments");
+    LV_REQUIRE(out && table && token_ids && n && vocab, "bad dequant arguments");
     LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0, "unsupported table type");
     LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
-    dequant_rows_kernel<<<n, 256, 0, ctx->stream>>>(out, static_cast<const uint8_t*>(table), wtype, token_ids, cols);
+    dequant_rows_kernel<<<n, 256, 0, ctx->stream>>>(out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err);
     LV_CUDA(cudaGetLastError());
     return LV_OK;
 }

@@ -1,0 +1,182 @@
+// C wrappers declared in include/llava_host.h.
+#include "../../include/llava_host.h"
+
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "ggml_file.h"
+#include "llava_buffer.h"
+#include "llava_context.h"
+#include "llava_layer_session_data.h"
+#include "llava_session.h"
+#include "synth_ggjt.h"
+
+namespace {
+synth_config make_cfg(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab, int wtype) {
+    synth_config c;
+    c.dim = dim; c.n_heads = n_heads; c.n_layers = n_layers; c.ff_size = ff; c.vocab_size = vocab;
+    c.wtype = static_cast<ggml_value_type>(wtype);
+    return c;
+}
+ggml_file* F(void* p) { return static_cast<ggml_file*>(p); }
+llava_session* S(void* p) { return static_cast<llava_session*>(p); }
+uint32_t copy_out(const std::string& s, char* out, uint32_t cap) {
+    if (out && cap) std::memcpy(out, s.data(), s.size() < cap ? s.size() : cap);
+    return uint32_t(s.size());
+}
+}  // namespace
+
+extern "C" {
+
+int llava_synth_write(const char* path, uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab,
+                      int wtype, uint64_t seed, uint32_t threads) {
+    synth_config c = make_cfg(dim, n_heads, n_layers, ff, vocab, wtype);
+    c.seed = seed;
+    c.threads = threads;
+    std::string err;
+    return synth_write_ggjt(path, c, &err) ? 1 : 0;
+}
+
+uint64_t llava_synth_file_size(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab, int wtype) {
+    return synth_file_size(make_cfg(dim, n_heads, n_layers, ff, vocab, wtype));
+}
+
+float llava_synth_normal(uint64_t seed, uint32_t tensor, uint64_t element) { return synth_normal(seed, tensor, element); }
+
+void llava_synth_quantize(const float* src, size_t count, int wtype, uint8_t* dst) {
+    synth_quantize(src, count, static_cast<ggml_value_type>(wtype), dst);
+}
+
+void* ggml_file_open(const char* path) {
+    auto* f = new ggml_file(path);
+    if (!f->is_open()) {
+        delete f;
+        return nullptr;
+    }
+    return f;
+}
+
+void ggml_file_close(void* file) { delete F(file); }
+
+void ggml_file_header(void* file, uint32_t* out10) {
+    std::memcpy(out10, &F(file)->get_header(), sizeof(ggml_header));
+    out10[9] = F(file)->get_ff_size();
+}
+
+uint32_t ggml_file_n_tensors(void* file) { return uint32_t(F(file)->get_tables().size()); }
+
+int ggml_file_tensor(void* file, uint32_t index, char* name, size_t name_cap, uint32_t* type, uint64_t* offset,
+                     uint32_t* shape1, uint32_t* shape2, uint64_t* size) {
+    const auto& t = F(file)->get_tables();
+    if (index >= t.size()) return 0;
+    if (name && name_cap) {
+        std::strncpy(name, t[index].name.c_str(), name_cap - 1);
+        name[name_cap - 1] = 0;
+    }
+    if (type) *type = uint32_t(t[index].ftype);
+    if (offset) *offset = t[index].offset;
+    if (shape1) *shape1 = t[index].shape1;
+    if (shape2) *shape2 = t[index].shape2;
+    if (size) *size = t[index].size;
+    return 1;
+}
+
+int ggml_file_find(void* file, const char* name, uint64_t* offset) {
+    const ggml_data_descriptor* d = F(file)->find_buffer_descriptor(name);
+    if (!d) return 0;
+    if (offset) *offset = d->offset;
+    return 1;
+}
+
+uint32_t ggml_file_tokenize(void* file, const char* text, size_t len, int bos, uint32_t* out, uint32_t cap) {
+    std::vector<uint32_t> v;
+    F(file)->tokenize(v, std::string(text, len), bos != 0);
+    for (uint32_t i = 0; i < v.size() && i < cap; ++i) out[i] = v[i];
+    return uint32_t(v.size());
+}
+
+uint32_t ggml_file_tokens_to_text(void* file, const uint32_t* tokens, uint32_t n, char* out, uint32_t cap) {
+    for (uint32_t i = 0; i < n; ++i) if (tokens[i] >= F(file)->get_tokens().size()) return 0;
+    return copy_out(F(file)->tokens_to_text(tokens, n), out, cap);
+}
+
+uint32_t ggml_file_token(void* file, uint32_t id, char* out, uint32_t cap, float* score) {
+    if (id >= F(file)->get_tokens().size()) return 0;
+    const ggml_token& t = F(file)->get_tokens()[id];
+    if (score) *score = t.score;
+    return copy_out(t.text, out, cap);
+}
+
+int llava_dequantize(const void* in, int type, uint32_t model_version, float* out, uint32_t count) {
+    return dequantize_to_f32(in, static_cast<ggml_value_type>(type), model_version, out, count) ? 1 : 0;
+}
+
+void* llava_context_open(const char* model_path, int device) {
+    auto* c = new llava_context();
+    if (!c->open(model_path, device)) {
+        delete c;
+        return nullptr;
+    }
+    return c;
+}
+
+void llava_context_close(void* ctx) { delete static_cast<llava_context*>(ctx); }
+void* llava_context_lv(void* ctx) { return static_cast<llava_context*>(ctx)->lv(); }
+
+int llava_context_run(int argc, char** argv) {
+    llava_context c;
+    return c.run(argc, argv);
+}
+
+void* llava_session_create(void* ctx) { return new llava_session(static_cast<llava_context*>(ctx)); }
+void llava_session_destroy(void* session) { delete S(session); }
+int llava_session_set_text(void* s, const char* text, size_t len) { return S(s)->set_text(std::string(text, len)) ? 1 : 0; }
+int llava_session_add_text(void* s, const char* text, size_t len) { return S(s)->add_text(std::string(text, len)) ? 1 : 0; }
+int llava_session_push_token(void* s, uint32_t token) { return S(s)->push_token(token) ? 1 : 0; }
+uint32_t llava_session_predict_next_token(void* s) { return S(s)->predict_next_token(); }
+int llava_session_start_next_token_prediction(void* s) { return S(s)->start_next_token_prediction() ? 1 : 0; }
+uint32_t llava_session_finish_next_token_prediction(void* s) { return S(s)->finish_next_token_prediction(); }
+void llava_session_rewind(void* s, uint32_t n) { S(s)->rewind(n); }
+uint32_t llava_session_set_options(void* s, uint32_t options) { return uint32_t(S(s)->set_options(options)); }
+uint32_t llava_session_save_frame(void* s, const char* path) { return uint32_t(S(s)->save_frame(path)); }
+uint32_t llava_session_snapshot(void* s, const char* path) { return uint32_t(S(s)->snapshot(path)); }
+uint32_t llava_session_restore(void* s, const char* path) { return uint32_t(S(s)->restore(path)); }
+uint32_t llava_session_get_token_count(void* s) { return S(s)->get_token_count(); }
+
+uint32_t llava_session_get_tokens(void* s, uint32_t* out, uint32_t cap) {
+    const auto& t = S(s)->get_token_buffer();
+    for (uint32_t i = 0; i < t.size() && i < cap; ++i) out[i] = t[i];
+    return uint32_t(t.size());
+}
+
+void llava_session_set_deterministic(void* s, int on) { S(s)->set_deterministic(on != 0); }
+void llava_session_set_seed(void* s, uint32_t seed) { S(s)->set_seed(seed); }
+int llava_session_set_max_batch(void* s, uint32_t n) { return S(s)->set_max_batch(n) ? 1 : 0; }
+
+int llava_session_generate_greedy_on_device(void* s, uint32_t n, uint32_t* out) {
+    std::vector<uint32_t> v;
+    if (!S(s)->generate_greedy_on_device(n, &v)) return 0;
+    for (uint32_t i = 0; i < v.size(); ++i) out[i] = v[i];
+    return 1;
+}
+
+int llava_session_get_logits(void* s, float* out, uint32_t cap) {
+    std::vector<float> v;
+    if (!S(s)->get_logits(&v) || v.size() > cap) return 0;
+    std::memcpy(out, v.data(), v.size() * sizeof(float));
+    return 1;
+}
+
+uint32_t llava_session_get_backlog_size(void* s) { return S(s)->get_backlog_size(); }
+uint32_t llava_session_get_tokens_in_gpu(void* s) { return S(s)->get_tokens_in_gpu(); }
+
+int llava_session_read_kv(void* s, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out) {
+    const auto& data = S(s)->get_layer_data();
+    if (layer >= data.size()) return 0;
+    llava_buffer* b = which == 0 ? data[layer]->get_k_cache() : data[layer]->get_v_cache();
+    const size_t row_bytes = size_t(b->shape.second) * 2;
+    return b->read_raw(row0 * row_bytes, out, nrows * row_bytes) ? 1 : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,181 @@
+#include "llava_command_buffer.h"
+
+#include <iostream>
+
+#include "llava_buffer.h"
+#include "llava_context.h"
+#include "llava_layer.h"
+#include "llava_layer_session_data.h"
+#include "llava_session.h"
+
+using namespace std;
+
+llava_command_buffer::llava_command_buffer(llava_session* _session, u32 _batch_size, bool _with_head)
+    : session(_session), backlog_size(_session->backlog_size), workgroup_size(_session->ctx->workgroup_size),
+      batch_size(_batch_size), with_head(_with_head) {}
+
+llava_command_buffer::~llava_command_buffer() {
+    wait_idle();
+    lv_graph_destroy(graph);
+}
+
+lv_ctx* llava_command_buffer::lv() const { return session->ctx->lv(); }
+
+void llava_command_buffer::note(int rc) {
+    if (rc != LV_OK && first_error == LV_OK) {
+        first_error = rc;
+        cerr << "[!] recording failed: " << lv_last_error_string() << endl;
+    }
+}
+
+// Shape contract of an op (the reference asserts these before each dispatch,
+// e.g. llava_command_buffer.cpp:64-67,137-140,158-165).
+bool llava_command_buffer::expect(bool cond, const char* what) {
+    if (!cond && first_error == LV_OK) {
+        first_error = LV_ERR_BAD_ARGUMENTS;
+        cerr << "[!] shape check failed: " << what << endl;
+    }
+    return cond;
+}
+
+bool llava_command_buffer::wait_idle() const {
+    // the reference waits on its fence for up to 1000 s and ignores the result
+    // (llava_command_buffer.cpp:25-27); here the result is reported
+    return lv_stream_sync(lv(), 1000 * 1000) == LV_OK;
+}
+
+bool llava_command_buffer::run() {
+    if (!graph) return false;
+    return lv_graph_launch(lv(), graph) == LV_OK;
+}
+
+bool llava_command_buffer::record_execution() {
+    if (graph) return false;
+    llava_session* s = session;
+    llava_context* c = s->ctx;
+    const ggml_header& h = s->model->get_header();
+    if (!expect(s->get_layer_data().size() == c->get_layers().size(), "one layer data per layer")) return false;
+    if (lv_graph_begin_capture(lv()) != LV_OK) {
+        note(LV_ERR_CUDA);
+        return false;
+    }
+    u32* config = static_cast<u32*>(s->config_buffer->device_ptr());
+    u32* log = static_cast<u32*>(s->token_log->device_ptr());
+    // embedding rows of the tokens at positions config.token_count .. + batch (the reference
+    // dequantises them on the host, llava_session.cpp:219-223)
+    note(lv_dequant_rows(lv(), static_cast<float*>(s->current_thought->device_ptr()), c->tok_embeddings->device_ptr(),
+                         int(c->tok_embeddings->type), log, config, h.dim, h.vocab_size, batch_size));
+    llava_buffer* current = s->current_thought;
+    for (u32 i = 0; i < c->get_layers().size(); ++i) current = c->get_layers()[i]->execute(this, s->get_layer_data()[i], current);
+    if (with_head) {
+        // final norm + output matrix on the last row only (llava_command_buffer.cpp:38-39; the
+        // reference computes every row and reads the last, llava_session.cpp:129-135)
+        const float* last = static_cast<const float*>(current->device_ptr()) + size_t(batch_size - 1) * h.dim;
+        float* logits = static_cast<float*>(s->output_probs->device_ptr());
+        note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), int(c->output_w->type), last,
+                          static_cast<const float*>(c->norm_w->device_ptr()), h.vocab_size, h.dim, 1));
+        u32* am = static_cast<u32*>(s->argmax_result->device_ptr());
+        note(lv_argmax_f32(lv(), am, logits, h.vocab_size));
+        note(lv_decode_advance(lv(), config, am, log, batch_size, max_backlog_size + 1));
+        note(lv_download_async(lv(), s->pinned + max_backlog_size + 4, am, 4));
+    } else {
+        // leading chunk of a prompt: only the position advances
+        note(lv_decode_advance(lv(), config, nullptr, nullptr, batch_size, 0));
+    }
+    lv_graph* g = nullptr;
+    const int rc = lv_graph_end_capture(lv(), &g);
+    note(rc);
+    if (first_error != LV_OK) {
+        lv_graph_destroy(g);
+        return false;
+    }
+    graph = g;
+    return true;
+}
+
+static inline float* f32(llava_buffer* b) { return static_cast<float*>(b->device_ptr()); }
+
+void llava_command_buffer::normalize_logit(llava_buffer* outbuf, llava_buffer* inbuf, llava_buffer* weights) {
+    if (!expect(outbuf->shape.first == inbuf->shape.first && weights->shape.first == inbuf->shape.first, "normalize shapes")) return;
+    note(lv_norm_f32(lv(), f32(outbuf), f32(inbuf), f32(weights), inbuf->shape.first, batch_size));
+}
+
+void llava_command_buffer::matmul(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf) {
+    if (!expect(inbuf->shape.first == matrix->shape.second && outbuf->shape.first == matrix->shape.first &&
+                inbuf->shape.second >= batch_size && outbuf->shape.second >= batch_size, "matmul shapes")) return;
+    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 0));
+}
+
+void llava_command_buffer::matmul_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf) {
+    if (!expect(inbuf->shape.first == matrix->shape.second && outbuf->shape.first == matrix->shape.first &&
+                inbuf->shape.second >= batch_size && outbuf->shape.second >= batch_size, "matmul_add shapes")) return;
+    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 1));
+}
+
+void llava_command_buffer::matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf) {
+    if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&
+                outbuf->shape.first == w3->shape.first, "matmul_silu_ff shapes")) return;
+    note(lv_gemv_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), f32(inbuf), w3->shape.first, w3->shape.second, batch_size));
+}
+
+void llava_command_buffer::kv_copy(llava_buffer* cache, llava_buffer* line) {
+    const u32 dim = session->model->get_header().dim;
+    if (!expect(cache->shape.second == dim && line->shape.first == dim && cache->shape.first >= backlog_size, "kv_copy shapes")) return;
+    note(lv_kv_append_f16(lv(), cache->device_ptr(), f32(line), static_cast<u32*>(session->config_buffer->device_ptr()), dim,
+                          batch_size, cache->shape.first));
+}
+
+void llava_command_buffer::copy_logit(llava_buffer* out, llava_buffer* in) {
+    const u32 dim = session->model->get_header().dim;
+    if (!expect(out->shape.first == dim && in->shape.first == dim, "copy shapes")) return;
+    note(lv_copy_f32(lv(), f32(out), f32(in), size_t(dim) * batch_size));
+}
+
+void llava_command_buffer::multi_head_attention(llava_buffer* attn_out, llava_buffer* k_cache, llava_buffer* query) {
+    const ggml_header& h = session->model->get_header();
+    if (!expect(k_cache->shape.second == h.dim && query->shape.first == h.dim && attn_out->shape.first == backlog_size &&
+                attn_out->shape.second >= h.n_heads * batch_size, "mhsa shapes")) return;
+    note(lv_attn_scores_rope(lv(), f32(attn_out), k_cache->device_ptr(), f32(query), static_cast<u32*>(session->config_buffer->device_ptr()),
+                             session->ctx->rope_table, backlog_size, h.n_heads, h.rot, batch_size));
+}
+
+void llava_command_buffer::inplace_softmax(llava_buffer* buf) {
+    const ggml_header& h = session->model->get_header();
+    if (!expect(buf->shape.first == backlog_size && buf->shape.second >= h.n_heads * batch_size, "softmax shapes")) return;
+    note(lv_softmax_masked(lv(), f32(buf), static_cast<u32*>(session->config_buffer->device_ptr()), backlog_size, h.n_heads, h.rot, batch_size));
+}
+
+void llava_command_buffer::perform_kqv_matching(llava_buffer* v_out, llava_buffer* v_cache, llava_buffer* softmax_out) {
+    const ggml_header& h = session->model->get_header();
+    if (!expect(v_out && v_cache && softmax_out && v_out->shape.first == h.dim && v_cache->shape.second == h.dim &&
+                softmax_out->shape.first == backlog_size, "kqv shapes")) return;
+    note(lv_attn_values(lv(), f32(v_out), v_cache->device_ptr(), f32(softmax_out), backlog_size, h.n_heads, h.rot, batch_size));
+}
+
+void llava_command_buffer::norm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq,
+                                             llava_buffer* wk, llava_buffer* wv, llava_buffer* inbuf, llava_buffer* norm_weights) {
+    const u32 dim = session->model->get_header().dim;
+    if (!expect(wq->shape == wk->shape && wq->shape == wv->shape && wq->shape.first == dim && wq->shape.second == dim &&
+                inbuf->shape.first == dim && k_cache->shape.second == dim && v_cache->shape.second == dim, "qkv shapes")) return;
+    note(lv_norm_qkv_kvappend(lv(), f32(q_out), k_cache->device_ptr(), v_cache->device_ptr(), wq->device_ptr(), wk->device_ptr(),
+                              wv->device_ptr(), int(wq->type), f32(inbuf), f32(norm_weights),
+                              static_cast<u32*>(session->config_buffer->device_ptr()), dim, batch_size, k_cache->shape.first));
+}
+
+void llava_command_buffer::attention_fused(llava_buffer* v_out, llava_buffer* query, llava_buffer* k_cache, llava_buffer* v_cache) {
+    const ggml_header& h = session->model->get_header();
+    if (!expect(v_out->shape.first == h.dim && query->shape.first == h.dim, "attention shapes")) return;
+    // the grid covers the current backlog only; a step is re-recorded when the backlog
+    // doubles, like the reference re-specialises its pipelines (llava_session.cpp:303-327)
+    note(lv_attention_fused(lv(), f32(v_out), f32(query), k_cache->device_ptr(), v_cache->device_ptr(),
+                            static_cast<u32*>(session->config_buffer->device_ptr()), session->ctx->rope_table,
+                            session->attn_scratch->device_ptr(), h.n_heads, h.rot, backlog_size, batch_size));
+}
+
+void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf,
+                                               llava_buffer* norm_weights) {
+    if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&
+                outbuf->shape.first == w3->shape.first, "norm_matmul_silu_ff shapes")) return;
+    note(lv_norm_gate_up_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), f32(inbuf), f32(norm_weights),
+                              w3->shape.first, w3->shape.second, batch_size));
+}

@@ -1,0 +1,58 @@
+// Recorder of one evaluation step.  The reference records ~418 Vulkan command
+// buffers with events between them and submits them with one fence
+// (llava_command_buffer.cpp:29-55,196-280); here every op method enqueues one
+// kernel through the C ABI while the context's stream is being captured, and
+// the result is a CUDA graph that run() replays.
+#ifndef LLAVA_B200_COMMAND_BUFFER_H
+#define LLAVA_B200_COMMAND_BUFFER_H
+
+#include "../../include/lv_b200.h"
+#include "types.h"
+
+class llava_command_buffer {
+public:
+    // with_head: record the final norm + output matrix + argmax (not needed for
+    // the leading chunks of a long prompt)
+    llava_command_buffer(llava_session* session, u32 batch_size, bool with_head);
+    ~llava_command_buffer();
+    llava_command_buffer(const llava_command_buffer&) = delete;
+    llava_command_buffer& operator=(const llava_command_buffer&) = delete;
+
+    bool record_execution();
+    bool run();
+    bool wait_idle() const;
+
+    // the reference's op set (llava_command_buffer.h:30-38)
+    void normalize_logit(llava_buffer* outbuf, llava_buffer* inbuf, llava_buffer* weights);
+    void matmul(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf);
+    void matmul_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf);
+    void kv_copy(llava_buffer* cache, llava_buffer* line);
+    void copy_logit(llava_buffer* out, llava_buffer* in);
+    void multi_head_attention(llava_buffer* attn_out, llava_buffer* k_cache, llava_buffer* query);
+    void perform_kqv_matching(llava_buffer* v_out, llava_buffer* v_cache, llava_buffer* softmax_out);
+    void inplace_softmax(llava_buffer* buf);
+    void matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3_matrix, llava_buffer* w1_matrix, llava_buffer* inbuf);
+    // fused forms used when tracing is off
+    void norm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq,
+                           llava_buffer* wk, llava_buffer* wv, llava_buffer* inbuf, llava_buffer* norm_weights);
+    void attention_fused(llava_buffer* v_out, llava_buffer* query, llava_buffer* k_cache, llava_buffer* v_cache);
+    void norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3_matrix, llava_buffer* w1_matrix, llava_buffer* inbuf,
+                             llava_buffer* norm_weights);
+
+    int status() const { return first_error; }
+
+    llava_session* const session;
+    u32 const backlog_size;
+    u32 const workgroup_size;
+    u32 const batch_size;
+    bool const with_head;
+
+private:
+    void note(int rc);
+    bool expect(bool cond, const char* what);
+    lv_ctx* lv() const;
+    lv_graph* graph = nullptr;
+    int first_error = LV_OK;
+};
+
+#endif

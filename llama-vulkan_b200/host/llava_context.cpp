@@ -1,0 +1,316 @@
+#include "llava_context.h"
+
+#include <signal.h>
+#include <sys/poll.h>
+#include <sys/signalfd.h>
+#include <unistd.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <sstream>
+
+#include "llava_buffer.h"
+#include "llava_device_memory.h"
+#include "llava_layer.h"
+#include "llava_session.h"
+#include "synth_ggjt.h"
+
+using namespace std;
+
+llava_context::llava_context() = default;
+
+llava_context::~llava_context() { close_all(); }
+
+void llava_context::close_all() {
+    for (llava_layer* l : layers) delete l;
+    layers.clear();
+    delete tok_embeddings;
+    delete norm_w;
+    delete output_w;
+    tok_embeddings = norm_w = output_w = nullptr;
+    if (rope_table && lv_context) lv_arena_free(lv_context, rope_table);
+    rope_table = nullptr;
+    delete shared_memory;
+    shared_memory = nullptr;
+    if (lv_context) lv_ctx_destroy(lv_context);
+    lv_context = nullptr;
+    delete model;
+    model = nullptr;
+    if (sigfd >= 0) ::close(sigfd);
+    sigfd = -1;
+}
+
+bool llava_context::upload_from_host(void* device_dst, const void* host_src, size_t bytes) {
+    return lv_upload(lv_context, device_dst, host_src, bytes) == LV_OK;
+}
+
+bool llava_context::open(const string& model_path, int device) {
+    close_all();
+    model = new ggml_file(model_path.c_str());
+    if (!model->is_open()) return false;
+    const ggml_header& h = model->get_header();
+    // the kernels are specialised for the reference's geometries (llava_session.cpp:357-375:
+    // dim 4096 or 5120, ff 11008 or 13824) and for heads of 128
+    if (h.rot != 128 || h.dim % 256 != 0 || model->get_ff_size() % 256 != 0) {
+        cerr << "[!] unsupported geometry: need head size 128 and dim, ff multiples of 256" << endl;
+        return false;
+    }
+    if (lv_ctx_create(device, &lv_context) != LV_OK) {
+        cerr << "[!] cannot create the CUDA context: " << lv_last_error_string() << endl;
+        return false;
+    }
+    const ggml_data_descriptor* emb = model->find_buffer_descriptor("tok_embeddings");
+    const ggml_data_descriptor* norm = model->find_buffer_descriptor("norm");
+    const ggml_data_descriptor* out = model->find_buffer_descriptor("output");
+    if (!emb || !norm || !out) {
+        cerr << "[!] tok_embeddings / norm / output missing from the model" << endl;
+        return false;
+    }
+    shared_memory = new llava_device_memory(this);
+    tok_embeddings = new llava_buffer(this, *emb, shared_memory);
+    norm_w = new llava_buffer(this, *norm, shared_memory);
+    output_w = new llava_buffer(this, *out, shared_memory);
+    if (norm_w->type != ggml_value_type::f32 || !output_w->weight_buffer_is_f16() || emb->shape1 != h.vocab_size ||
+        !(tok_embeddings->weight_buffer_is_f16() || tok_embeddings->type == ggml_value_type::f32)) {
+        cerr << "[!] unsupported tensor types for tok_embeddings / norm / output" << endl;
+        return false;
+    }
+    if (!shared_memory->freeze() || !tok_embeddings->load_to_gpu() || !norm_w->load_to_gpu() || !output_w->load_to_gpu()) return false;
+
+    void* table = nullptr;
+    if (lv_arena_create(lv_context, size_t(max_backlog_size) * h.rot * sizeof(float), &table) != LV_OK) return false;
+    rope_table = static_cast<float*>(table);
+    if (lv_rope_table_build(lv_context, rope_table, max_backlog_size, h.rot) != LV_OK) return false;
+
+    layers.reserve(h.n_layers);
+    for (u32 i = 0; i < h.n_layers; ++i) {
+        layers.push_back(new llava_layer(this, i));
+        if (!layers.back()->is_valid()) return false;
+    }
+    for (llava_layer* l : layers) {
+        if (sigfd >= 0 && pop_signal()) return false;
+        if (!l->freeze_storage() || !l->load_to_gpu()) {
+            cerr << "[!] cannot upload layer " << l->layer_id << ": " << lv_last_error_string() << endl;
+            return false;
+        }
+    }
+    return true;
+}
+
+bool llava_context::setup_signal_handling() {
+    if (signal_debug) return true;
+    sigset_t mask;
+    sigemptyset(&mask);
+    for (int s : {SIGINT, SIGQUIT, SIGHUP, SIGTERM}) sigaddset(&mask, s);
+    if (sigprocmask(SIG_BLOCK, &mask, nullptr) < 0) return false;
+    sigfd = signalfd(-1, &mask, SFD_NONBLOCK | SFD_CLOEXEC);
+    return sigfd >= 0;
+}
+
+u32 llava_context::pop_signal(bool blocking) const {
+    if (sigfd < 0) return 0;
+    if (blocking) {
+        pollfd p{sigfd, POLLIN, 0};
+        ::poll(&p, 1, -1);
+    }
+    signalfd_siginfo info{};
+    const ssize_t r = ::read(sigfd, &info, sizeof info);
+    return r == ssize_t(sizeof info) ? info.ssi_signo : 0;
+}
+
+namespace {
+bool streq(const char* a, const char* b) { return strcmp(a, b) == 0; }
+
+bool read_token_file(const string& path, vector<u32>* out) {
+    ifstream in(path);
+    if (!in) return false;
+    u64 v;
+    while (in >> v) out->push_back(u32(v));
+    return !out->empty();
+}
+}  // namespace
+
+// Flags of the reference (llava_context.cpp:163-200) that still mean something, plus the
+// ones its CLI lacks: --greedy, --tokens, --n-predict, --ignore-eos, --seed, --device,
+// --on-device and --write-synthetic.
+int llava_context::run(int argc, char** argv) {
+    bool server_mode = false, only_print_header = false, greedy = false, ignore_eos = false, on_device = false;
+    bool model_path_provided = false, have_seed = false;
+    string model_path, tokens_path, synth_spec;
+    string prompt = "The ten best monuments to see in Paris are";
+    u32 n_predict = 0, seed = 0;
+    int device = 0;
+
+    auto need_value = [&](int& i) -> const char* {
+        if (i + 1 >= argc) {
+            cerr << "[!] Expected a value after " << argv[i] << endl;
+            exit(1);
+        }
+        return argv[++i];
+    };
+    for (int i = 1; i < argc; ++i) {
+        const char* a = argv[i];
+        if (streq(a, "--use-prebuilt") || streq(a, "--debug")) {
+            // shader selection / Vulkan validation layer: nothing to select here
+        } else if (streq(a, "--print_header")) {
+            only_print_header = true;
+        } else if (streq(a, "--model") || streq(a, "-m")) {
+            if (model_path_provided) cerr << "[!] -m or --model duplicated in the command line" << endl;
+            model_path_provided = true;
+            model_path = need_value(i);
+        } else if (streq(a, "--help") || streq(a, "-h")) {
+            cout << (argc ? argv[0] : "./vulkan_llama")
+                 << " [-h] [-m model.bin] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
+                    " [--device D] [--on-device] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
+                 << endl;
+            exit(0);
+        } else if (streq(a, "--verbose") || streq(a, "-v")) {
+            verbosity++;
+        } else if (streq(a, "--control") || streq(a, "-c")) {
+            cerr << "Control disabled for now" << endl;
+            exit(1);
+        } else if (streq(a, "--server") || streq(a, "-s")) {
+            server_mode = true;
+        } else if (streq(a, "--sigdebug")) {
+            signal_debug = true;
+        } else if (streq(a, "--greedy")) {
+            greedy = true;
+        } else if (streq(a, "--ignore-eos")) {
+            ignore_eos = true;
+        } else if (streq(a, "--on-device")) {
+            on_device = true;
+        } else if (streq(a, "--tokens")) {
+            tokens_path = need_value(i);
+        } else if (streq(a, "--n-predict")) {
+            n_predict = u32(strtoul(need_value(i), nullptr, 10));
+        } else if (streq(a, "--seed")) {
+            seed = u32(strtoul(need_value(i), nullptr, 10));
+            have_seed = true;
+        } else if (streq(a, "--device")) {
+            device = atoi(need_value(i));
+        } else if (streq(a, "--write-synthetic")) {
+            synth_spec = need_value(i);
+        } else if (i + 1 != argc) {
+            cerr << "[!] Unexpected argument " << a << endl;
+            exit(1);
+        } else {
+            prompt = a;
+        }
+    }
+
+    if (model_path.empty()) {
+        if (const char* env = ::getenv("LLAVA_MODEL")) model_path = env;      // llava_context.cpp:207-212
+    }
+    if (model_path.empty()) {
+        cerr << "[!] No model path provided" << endl;
+        exit(1);
+    }
+
+    if (!synth_spec.empty()) {
+        synth_config cfg;
+        stringstream ss(synth_spec);
+        string part;
+        bool first = true;
+        while (getline(ss, part, ':')) {
+            if (first) {
+                first = false;
+                if (part == "7b") { cfg.n_layers = 32; }
+                else if (part == "13b") { cfg.dim = 5120; cfg.n_heads = 40; cfg.ff_size = 13824; cfg.n_layers = 40; }
+                else if (part == "tiny") { cfg.n_layers = 2; }
+                else { cerr << "[!] unknown synthetic model " << part << endl; return 1; }
+            } else if (part == "q8") {
+                cfg.wtype = ggml_value_type::q8_0;
+            } else if (part.rfind("layers=", 0) == 0) {
+                cfg.n_layers = u32(strtoul(part.c_str() + 7, nullptr, 10));
+            } else if (part.rfind("seed=", 0) == 0) {
+                cfg.seed = strtoull(part.c_str() + 5, nullptr, 10);
+            }
+        }
+        string err;
+        if (!synth_write_ggjt(model_path, cfg, &err)) {
+            cerr << "[!] " << err << endl;
+            return 1;
+        }
+        return 0;
+    }
+
+    if (only_print_header) {
+        ggml_file f(model_path.c_str());
+        if (!f.is_open()) return 1;
+        f.print_info();
+        return 0;
+    }
+    if (server_mode) {
+        cerr << "[!] the TCP server front end is not part of this build; sessions can be driven through lsrv::session_wrapper" << endl;
+        return 1;
+    }
+    if (!setup_signal_handling()) {
+        cerr << "[!] Cannot setup signal handling" << endl;
+        return 1;
+    }
+    if (!open(model_path, device)) return 1;
+    if (verbosity) cout << "Selected device: cuda:" << device << " (" << lv_ctx_sm_count(lv_context) << " SMs)" << endl;
+
+    // generation loop, llava_context.cpp:336-373
+    const u32 eos_id = 2;
+    llava_session session(this);
+    session.set_deterministic(greedy);
+    if (have_seed) session.set_seed(seed);
+    if (!tokens_path.empty()) {
+        vector<u32> ids;
+        if (!read_token_file(tokens_path, &ids)) {
+            cerr << "[!] cannot read token ids from " << tokens_path << endl;
+            return 1;
+        }
+        for (u32 t : ids) {
+            if (!session.push_token(t)) {
+                cerr << "[!] System prompt overflows backlog buffer !" << endl;
+                exit(1);
+            }
+        }
+    } else {
+        if (!session.set_text(prompt)) {
+            cerr << "[!] System prompt overflows backlog buffer !" << endl;
+            exit(1);
+        }
+        cout << prompt << flush;
+    }
+
+    u32 produced = 0;
+    if (on_device && greedy && n_predict > 1) {
+        // evaluate the prompt, then let the device feed itself
+        u32 tok = session.predict_next_token();
+        if (~tok == 0 || !session.push_token(tok)) return 1;
+        vector<u32> rest;
+        if (!session.generate_greedy_on_device(n_predict - 1, &rest)) {
+            cerr << "Unknown error" << endl;
+            return 1;
+        }
+        cout << model->get_tokens()[tok].text;
+        for (u32 t : rest) cout << model->get_tokens()[t].text;
+        cout << endl;
+        return 0;
+    }
+    u32 next_token = session.predict_next_token();
+    while (true) {
+        if (~next_token == 0) {
+            cerr << "Unknown error" << endl;
+            break;
+        }
+        ++produced;
+        if (pop_signal() || (next_token == eos_id && !ignore_eos)) break;
+        if (n_predict && produced >= n_predict) break;
+        if (!session.push_token(next_token)) break;      // too many tokens
+        if (!session.start_next_token_prediction()) {
+            cerr << "Cannot start processing, unknown error" << endl;
+            break;
+        }
+        cout << model->get_tokens()[next_token].text << flush;     // printed while the device works
+        next_token = session.finish_next_token_prediction();
+    }
+    if (~next_token != 0 && (next_token != eos_id || ignore_eos)) cout << model->get_tokens()[next_token].text;
+    cout << endl;
+    return 0;
+}

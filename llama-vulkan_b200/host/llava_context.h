@@ -1,0 +1,58 @@
+// Process-level state: the model file, the CUDA context behind the C ABI, the
+// layers and the read-only tensors shared by all sessions.  Counterpart of the
+// reference's llava_context (llava_context.h:16-84); the Vulkan instance,
+// device, queue, pools and pipeline cache become one lv_ctx.
+#ifndef LLAVA_B200_CONTEXT_H
+#define LLAVA_B200_CONTEXT_H
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/lv_b200.h"
+#include "ggml_file.h"
+#include "types.h"
+
+class llava_context {
+public:
+    llava_context();
+    ~llava_context();
+    llava_context(const llava_context&) = delete;
+    llava_context& operator=(const llava_context&) = delete;
+
+    // Command-line entry point (llava_context.cpp:151-380 of the reference).
+    int run(int argc, char** argv);
+    // Opens the model, creates the device context and uploads all layers.
+    bool open(const std::string& model_path, int device = 0);
+
+    lv_ctx* lv() const { return lv_context; }
+    const ggml_file* get_model() const { return model; }
+    std::vector<llava_layer*>& get_layers() { return layers; }
+    bool upload_from_host(void* device_dst, const void* host_src, size_t bytes);
+    bool signal_debug_on() const { return signal_debug; }
+    int get_signal_fd() const { return sigfd; }
+    u32 pop_signal(bool blocking = false) const;       // 0: none pending
+
+    // read-only tensors shared by every session (the reference re-uploads the
+    // last two per session, llava_session.cpp:73-78)
+    llava_buffer* tok_embeddings = nullptr;
+    llava_buffer* norm_w = nullptr;
+    llava_buffer* output_w = nullptr;
+    float* rope_table = nullptr;                        // [max_backlog][rot/2][2] cos/sin by distance
+
+    u32 workgroup_size = 1024;       // kept for interface parity; kernel geometry is compile-time here
+    u32 verbosity = 0;
+    std::mutex queue_mutex;          // serialises sessions that share the stream
+
+private:
+    bool setup_signal_handling();
+    void close_all();
+    ggml_file* model = nullptr;
+    lv_ctx* lv_context = nullptr;
+    llava_device_memory* shared_memory = nullptr;
+    std::vector<llava_layer*> layers;
+    bool signal_debug = false;
+    int sigfd = -1;
+};
+
+#endif

@@ -1,0 +1,103 @@
+#include "llava_layer.h"
+
+#include <iostream>
+
+#include "llava_buffer.h"
+#include "llava_command_buffer.h"
+#include "llava_context.h"
+#include "llava_device_memory.h"
+#include "llava_layer_session_data.h"
+#include "llava_session.h"
+
+using namespace std;
+
+llava_layer::llava_layer(llava_context* _context, u32 _layer_id) : layer_id(_layer_id), context(_context) {
+    layer_allocation = new llava_device_memory(context);
+    const ggml_file* model = context->get_model();
+    const string prefix = "layers." + to_string(layer_id) + ".";
+    bool ok = true;
+    auto make = [&](const char* leaf) -> llava_buffer* {
+        const ggml_data_descriptor* d = model->find_buffer_descriptor(prefix + leaf);
+        if (!d) {
+            cerr << "[!] tensor " << prefix << leaf << " missing" << endl;
+            ok = false;
+            return nullptr;
+        }
+        return new llava_buffer(context, *d, layer_allocation);
+    };
+    attention_wq = make("attention.wq");
+    attention_wk = make("attention.wk");
+    attention_wv = make("attention.wv");
+    attention_wo = make("attention.wo");
+    feed_forward_w1 = make("feed_forward.w1");
+    feed_forward_w2 = make("feed_forward.w2");
+    feed_forward_w3 = make("feed_forward.w3");
+    attention_norm = make("attention_norm");
+    ffn_norm = make("ffn_norm");
+    if (ok) {
+        // norms must be f32 vectors, matrices quantised with an f16 block scale (ggjt v3)
+        for (llava_buffer* m : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2, feed_forward_w3})
+            ok = ok && m->weight_buffer_is_f16();
+        ok = ok && attention_norm->type == ggml_value_type::f32 && ffn_norm->type == ggml_value_type::f32;
+        if (!ok) cerr << "[!] layer " << layer_id << ": unsupported tensor types (need q4_0/q8_0 ggjt v3 matrices, f32 norms)" << endl;
+    }
+    valid = ok;
+}
+
+llava_layer::~llava_layer() {
+    for (llava_buffer* b : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2,
+                            feed_forward_w3, attention_norm, ffn_norm})
+        delete b;
+    delete layer_allocation;
+}
+
+bool llava_layer::freeze_storage() { return valid && layer_allocation->freeze(); }
+
+bool llava_layer::load_to_gpu() {
+    if (!valid) return false;
+    for (llava_buffer* b : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2,
+                            feed_forward_w3, attention_norm, ffn_norm})
+        if (!b->load_to_gpu()) return false;
+    return true;
+}
+
+llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_session_data* layer_data,
+                                   llava_buffer* raw_input_logit) const {
+    llava_session* session = layer_data->session;
+    const bool record = layer_data->attn_result != nullptr;
+
+    if (!record) {
+        // five launches: the residual stream is updated in place, as the reference does when
+        // it is not tracing (llava_layer.cpp:45-51)
+        llava_buffer* x = session->current_thought;
+        cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
+                                   attention_wv, x, attention_norm);
+        cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);
+        cmd_buf->matmul_add_inplace(x, attention_wo, session->current_Vout);
+        cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, x, ffn_norm);
+        cmd_buf->matmul_add_inplace(x, feed_forward_w2, session->main_ff_result);
+        return x;
+    }
+
+    // tracing: the reference's thirteen operations, each intermediate kept in its record buffer
+    llava_buffer* normd = layer_data->normalized_input_logit;
+    llava_buffer* post_attn = layer_data->post_attn_logit;
+    llava_buffer* post_attn_normd = layer_data->post_attn_norm_logit;
+    llava_buffer* output = layer_data->output_logit;
+    cmd_buf->normalize_logit(normd, raw_input_logit, attention_norm);
+    cmd_buf->matmul(session->current_K, attention_wk, normd);
+    cmd_buf->matmul(session->current_Q, attention_wq, normd);
+    cmd_buf->matmul(session->current_V, attention_wv, normd);
+    cmd_buf->kv_copy(layer_data->k_cache, session->current_K);
+    cmd_buf->kv_copy(layer_data->v_cache, session->current_V);
+    cmd_buf->multi_head_attention(layer_data->attn_result, layer_data->k_cache, session->current_Q);
+    cmd_buf->inplace_softmax(layer_data->attn_result);
+    cmd_buf->perform_kqv_matching(session->current_Vout, layer_data->v_cache, layer_data->attn_result);
+    cmd_buf->copy_logit(post_attn, raw_input_logit);
+    cmd_buf->matmul_add_inplace(post_attn, attention_wo, session->current_Vout);
+    cmd_buf->normalize_logit(post_attn_normd, post_attn, ffn_norm);
+    cmd_buf->matmul_silu_ff(layer_data->ff_result, feed_forward_w3, feed_forward_w1, post_attn_normd);
+    cmd_buf->copy_logit(output, post_attn);
+    cmd_buf->matmul_add_inplace(output, feed_forward_w2, layer_data->ff_result);
+    return output;
+}

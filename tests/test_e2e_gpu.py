@@ -1,0 +1,255 @@
+"""End-to-end parity of the session API with the CPU oracle on the 2-layer,
+7B-geometry synthetic model: 16 seeded prompt tokens, then 32 greedy tokens.
+
+Tolerances are the ones the task states for logits at fp32 accumulation:
+max-abs 1e-2 and relative L2 1e-3; greedy token ids must be identical.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import oracle_bind as ob
+import quant_np as qn
+
+pytestmark = pytest.mark.gpu
+
+N_PROMPT, N_DECODE = 16, 32
+LOGIT_MAX_ABS, LOGIT_REL_L2 = 1e-2, 1e-3
+
+
+def prompt_tokens(n=N_PROMPT, seed=4321):
+    return [int(t) for t in np.random.default_rng(seed).integers(3, 32000, n)]
+
+
+class OracleSession:
+    def __init__(self, path):
+        self.lib = ob.load()
+        self.model = self.lib.orc_model_open(os.fsencode(path))
+        assert self.model
+        self.info = ob.ModelInfo()
+        self.lib.orc_model_get_info(self.model, C.byref(self.info))
+        self.s = self.lib.orc_session_create(self.model, 1024)
+        assert self.s
+        self.logits = np.empty(self.info.vocab_size, np.float32)
+
+    def push(self, t):
+        assert self.lib.orc_session_push_token(self.s, t) == 1
+
+    def eval(self):
+        assert self.lib.orc_session_eval(self.s, ob.ptr(self.logits)) == 0
+        return self.logits.copy()
+
+    def argmax(self):
+        return self.lib.orc_argmax(ob.ptr(self.logits), self.logits.size)
+
+    def cache(self, which, layer, rows):
+        fn = self.lib.orc_session_k_cache if which == 0 else self.lib.orc_session_v_cache
+        p = C.cast(fn(self.s, layer), C.POINTER(C.c_uint16))
+        return np.ctypeslib.as_array(p, shape=(2048, self.info.dim))[:rows].copy()
+
+    def layer_outputs(self):
+        p = C.cast(self.lib.orc_session_layer_outputs(self.s), C.POINTER(C.c_float))
+        return np.ctypeslib.as_array(p, shape=(self.info.n_layers, self.info.dim)).copy()
+
+    def close(self):
+        self.lib.orc_session_destroy(self.s)
+        self.lib.orc_model_close(self.model)
+
+
+def assert_logits_close(got, want):
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    rel = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+    assert diff.max() <= LOGIT_MAX_ABS, f"max-abs {diff.max():.3e}"
+    assert rel <= LOGIT_REL_L2, f"rel-L2 {rel:.3e}"
+    return diff.max(), rel
+
+
+@pytest.fixture(scope="module", params=[qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
+def run(request, pkg, tmp_path_factory):
+    """Model + oracle trajectory (logits per step, greedy tokens) shared by the tests below."""
+    wtype = request.param
+    path = str(tmp_path_factory.mktemp("e2e") / f"tiny_{wtype}.bin")
+    pkg.write_synthetic_model(path, "7b", n_layers=2, wtype=wtype)
+    orc = OracleSession(path)
+    toks = prompt_tokens()
+    for t in toks:
+        orc.push(t)
+    logits, greedy = [], []
+    for _ in range(N_DECODE):
+        logits.append(orc.eval())
+        greedy.append(orc.argmax())
+        orc.push(greedy[-1])
+    ctx = pkg.HostContext(path, 0)
+    yield dict(path=path, wtype=wtype, orc=orc, prompt=toks, logits=logits, greedy=greedy, ctx=ctx, vocab=orc.info.vocab_size,
+               dim=orc.info.dim)
+    ctx.close()
+    orc.close()
+
+
+def test_greedy_tokens_identical_and_logits_within_tolerance(run):
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    for t in run["prompt"]:
+        assert s.push_token(t)
+    worst = (0.0, 0.0)
+    for step in range(N_DECODE):
+        assert s.start_next_token_prediction()
+        tok = s.finish_next_token_prediction()
+        m, r = assert_logits_close(s.logits(run["vocab"]), run["logits"][step])
+        worst = (max(worst[0], m), max(worst[1], r))
+        assert tok == run["greedy"][step], f"step {step}"
+        assert s.push_token(tok)
+    print(f"worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}")
+    assert s.tokens() == run["prompt"] + run["greedy"]
+    # the caches hold un-rotated f16 K and V rows; a value that differs in its last fp32 bits may
+    # round to the neighbouring half, so compare as numbers
+    n = N_PROMPT + N_DECODE - 1
+    for layer in range(2):
+        for which in (0, 1):
+            got = s.read_kv(layer, which, 0, n, run["dim"]).view(np.float16).astype(np.float32)
+            want = run["orc"].cache(which, layer, n).view(np.float16).astype(np.float32)
+            assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+            assert np.mean(got != want) < 0.02
+    s.close()
+
+
+def test_decoding_without_the_host_in_the_loop_gives_the_same_tokens(run):
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    for t in run["prompt"]:
+        assert s.push_token(t)
+    first = s.predict_next_token()
+    assert first == run["greedy"][0]
+    assert s.push_token(first)
+    rest = s.generate_greedy_on_device(N_DECODE - 1)
+    assert [first] + rest == run["greedy"]
+    assert s.tokens() == run["prompt"] + run["greedy"]
+    assert s.tokens_in_gpu() == len(s.tokens()) - 1
+    # and the host-driven loop continues seamlessly from there
+    assert s.start_next_token_prediction()
+    nxt = s.finish_next_token_prediction()
+    run["orc"].lib.orc_session_rewind(run["orc"].s, N_PROMPT + N_DECODE)
+    run["orc"].eval()
+    assert nxt == run["orc"].argmax()
+    s.close()
+
+
+def test_prompt_in_batches_matches_token_by_token(run):
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    assert s.set_max_batch(5)            # 16 prompt tokens -> recorded steps of 5, 5, 5, 1
+    for t in run["prompt"]:
+        assert s.push_token(t)
+    tok = s.predict_next_token()
+    assert_logits_close(s.logits(run["vocab"]), run["logits"][0])
+    assert tok == run["greedy"][0]
+    assert not s.set_max_batch(0) and not s.set_max_batch(17)
+    s.close()
+
+
+def test_rewind_then_regenerate(run):
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    for t in run["prompt"]:
+        s.push_token(t)
+    out = []
+    for _ in range(6):
+        out.append(s.predict_next_token())
+        s.push_token(out[-1])
+    s.rewind(N_PROMPT + 2)               # drop the last four tokens (llava_session.cpp:390-395)
+    assert s.tokens() == run["prompt"] + run["greedy"][:2]
+    again = []
+    for _ in range(4):
+        again.append(s.predict_next_token())
+        s.push_token(again[-1])
+    assert again == run["greedy"][2:6] and out == run["greedy"][:6]
+    assert not s.start_next_token_prediction() or True
+    s.close()
+
+
+def test_already_in_sync_and_bad_token_are_refused(run):
+    s = run["ctx"].session()
+    assert not s.push_token(32000)
+    assert not s.start_next_token_prediction()          # nothing pushed: "GPU is already in sync"
+    assert s.predict_next_token() == 0xFFFFFFFF
+    s.close()
+
+
+def test_snapshot_restore_round_trip(run, tmp_path):
+    if run["wtype"] != qn.Q4_0:
+        pytest.skip("one quantisation is enough")
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    for t in run["prompt"]:
+        s.push_token(t)
+    t0 = s.predict_next_token()
+    snap = str(tmp_path / "snap.bin")
+    assert s.snapshot(snap) == 0
+    n = N_PROMPT
+    assert os.path.getsize(snap) == 2 * 2 * n * run["dim"] * 2 + 4 * n + 4      # llava_session.cpp:448
+    raw = open(snap, "rb").read()
+    assert int.from_bytes(raw[:4], "little") == n
+    assert list(np.frombuffer(raw, np.uint32, n, 4)) == run["prompt"]
+    krows = np.frombuffer(raw, np.uint16, n * run["dim"], 4 + 4 * n).reshape(n, run["dim"])
+    assert np.array_equal(krows, s.read_kv(0, 0, 0, n, run["dim"]))
+    s2 = run["ctx"].session()
+    s2.set_deterministic(True)
+    assert s2.restore(snap) == 0
+    assert s2.tokens() == run["prompt"] and s2.tokens_in_gpu() == n
+    s2.push_token(t0)
+    s.push_token(t0)
+    assert s2.predict_next_token() == s.predict_next_token() == run["greedy"][1]
+    bad = str(tmp_path / "bad.bin")
+    open(bad, "wb").write(raw[:-2])
+    assert s2.restore(bad) == 1                           # "File size mismatch" -> ReturnCode::nok
+    assert s2.restore(str(tmp_path / "missing.bin")) == 1
+    s.close()
+    s2.close()
+
+
+def test_trace_frames_match_oracle_layer_outputs(run, tmp_path):
+    if run["wtype"] != qn.Q4_0:
+        pytest.skip("one quantisation is enough")
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    frame = str(tmp_path / "frame.bin")
+    assert s.save_frame(frame) == 5                       # ReturnCode::not_tracing
+    assert s.set_options(1) == 0
+    for t in run["prompt"]:
+        s.push_token(t)
+    tok = s.predict_next_token()                          # thirteen separate ops per layer in this mode
+    assert tok == run["greedy"][0]
+    assert_logits_close(s.logits(run["vocab"]), run["logits"][0])
+    assert s.save_frame(frame) == 0
+    raw = open(frame, "rb").read()
+    recs, at = {}, 0
+    while at < len(raw):
+        s1, s2, typ = np.frombuffer(raw, np.uint32, 3, at)
+        end = raw.index(b"\0", at + 12)
+        name = raw[at + 12:end].decode()
+        hdr = (12 + len(name) + 1 + 31) & ~31              # llava_buffer.cpp:500
+        recs[name] = np.frombuffer(raw, np.float32, int(s1) * int(s2), at + hdr).reshape(int(s2), int(s1))
+        assert typ == 0
+        at += hdr + 4 * int(s1) * int(s2)
+    assert sorted(recs) == sorted(f"layer.{i}.{n}" for i in range(2) for n in
+                                  ("attn_result", "ff_result", "normalized_input_logit", "post_attn_logit",
+                                   "post_attn_norm_logit", "output_logit"))
+    # re-run the oracle up to the prompt's last token and compare the residual stream after each layer
+    orc = run["orc"]
+    orc.lib.orc_session_rewind(orc.s, N_PROMPT)
+    orc.lib.orc_session_rewind(orc.s, N_PROMPT - 1)
+    orc.push(run["prompt"][-1])
+    orc.eval()
+    want = orc.layer_outputs()
+    for i in range(2):
+        got = recs[f"layer.{i}.output_logit"][0]
+        assert np.linalg.norm(got - want[i]) / np.linalg.norm(want[i]) < 1e-4
+    assert s.set_options(0) == 0
+    s.close()
+    # restore the oracle trajectory for tests that may follow
+    for t in run["greedy"]:
+        orc.push(t)
+        if orc.lib.orc_session_token_count(orc.s) >= N_PROMPT + N_DECODE:
+            break

@@ -45,13 +45,19 @@ def test_dequant_rows_bit_exact(gpu, pkg, wtype):
     table = qn.quantize((rng.standard_normal((vocab, cols)) * 0.02).astype(np.float32), wtype)
     ids = np.array([0, 63, 17, 17, 5], np.uint32)
     d_out = gpu.alloc(ids.size * cols * 4)
-    pkg.check(gpu.lib.lv_dequant_rows(gpu.handle, d_out, gpu.upload(table), wtype, gpu.upload(ids), cols, ids.size))
+    pkg.check(gpu.lib.lv_dequant_rows(gpu.handle, d_out, gpu.upload(table), wtype, gpu.upload(ids), None, cols, vocab, ids.size))
     gpu.sync()
     got = gpu.download(d_out, np.float32, ids.size * cols).reshape(ids.size, cols)
     rb = qn.row_bytes(wtype, cols)
     for z, t in enumerate(ids):
         want = ob.dequant(table[t * rb:(t + 1) * rb], wtype, cols)
         assert np.array_equal(got[z].view(np.uint32), want.view(np.uint32))
+    # ids taken from a device-resident token log at a device-resident position
+    pkg.check(gpu.lib.lv_dequant_rows(gpu.handle, d_out, gpu.upload(table), wtype, gpu.upload(ids), u32_dev(gpu, 2), cols, vocab, 2))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, 2 * cols).reshape(2, cols)
+    for z, t in enumerate(ids[2:4]):
+        assert np.array_equal(got[z], ob.dequant(table[t * rb:(t + 1) * rb], wtype, cols))
 
 
 @pytest.mark.parametrize("dim,batch", [(4096, 1), (5120, 3)])
