@@ -67,6 +67,8 @@ void     llava_session_set_deterministic(void* session, int on);
 void     llava_session_set_seed(void* session, uint32_t seed);
 int      llava_session_set_max_batch(void* session, uint32_t n);
 int      llava_session_generate_greedy_on_device(void* session, uint32_t n, uint32_t* out);
+int      llava_session_enqueue_greedy_on_device(void* session, uint32_t n);     /* returns once queued */
+int      llava_session_collect_greedy_on_device(void* session, uint32_t* out, uint32_t cap);
 int      llava_session_get_logits(void* session, float* out, uint32_t cap);
 uint32_t llava_session_get_backlog_size(void* session);
 uint32_t llava_session_get_tokens_in_gpu(void* session);

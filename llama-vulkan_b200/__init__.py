@@ -217,6 +217,8 @@ HOST_API = {
     "llava_session_set_seed": (None, [_p, _u32]),
     "llava_session_set_max_batch": (_int, [_p, _u32]),
     "llava_session_generate_greedy_on_device": (_int, [_p, _u32, _p]),
+    "llava_session_enqueue_greedy_on_device": (_int, [_p, _u32]),
+    "llava_session_collect_greedy_on_device": (_int, [_p, _p, _u32]),
     "llava_session_get_logits": (_int, [_p, _p, _u32]),
     "llava_session_get_backlog_size": (_u32, [_p]),
     "llava_session_get_tokens_in_gpu": (_u32, [_p]),
@@ -388,6 +390,18 @@ class Session:
         buf = (_u32 * n)()
         if not self.lib.llava_session_generate_greedy_on_device(self.handle, n, buf):
             raise RuntimeError("generate_greedy_on_device failed")
+        return list(buf)
+
+    def enqueue_greedy_on_device(self, n):
+        if not self.lib.llava_session_enqueue_greedy_on_device(self.handle, n):
+            raise RuntimeError("enqueue_greedy_on_device failed")
+        self._enqueued = n
+
+    def collect_greedy_on_device(self):
+        n = self._enqueued
+        buf = (_u32 * n)()
+        if not self.lib.llava_session_collect_greedy_on_device(self.handle, buf, n):
+            raise RuntimeError("collect_greedy_on_device failed")
         return list(buf)
 
     def logits(self, vocab):

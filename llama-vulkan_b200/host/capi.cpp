@@ -161,6 +161,15 @@ int llava_session_generate_greedy_on_device(void* s, uint32_t n, uint32_t* out) 
     return 1;
 }
 
+int llava_session_enqueue_greedy_on_device(void* s, uint32_t n) { return S(s)->enqueue_greedy_on_device(n) ? 1 : 0; }
+
+int llava_session_collect_greedy_on_device(void* s, uint32_t* out, uint32_t cap) {
+    std::vector<uint32_t> v;
+    if (!S(s)->collect_greedy_on_device(&v)) return 0;
+    for (uint32_t i = 0; i < v.size() && i < cap; ++i) out[i] = v[i];
+    return 1;
+}
+
 int llava_session_get_logits(void* s, float* out, uint32_t cap) {
     std::vector<float> v;
     if (!S(s)->get_logits(&v) || v.size() > cap) return 0;

@@ -227,24 +227,34 @@ u32 llava_session::sample_from_logits(vector<float>& p) {
 }
 
 bool llava_session::generate_greedy_on_device(u32 n, vector<u32>* out) {
-    if (n == 0) return true;
+    return enqueue_greedy_on_device(n) && collect_greedy_on_device(out);
+}
+
+bool llava_session::enqueue_greedy_on_device(u32 n) {
+    if (n == 0 || enqueued_greedy != 0) return false;
     if (!ensure_buffers_created()) return false;
     if (token_buffer.empty() || token_buffer.size() - current_tokens_in_gpu != 1) return false;
     u32 need = backlog_size;
     while (token_buffer.size() + n > need) need <<= 1;
     if (need > max_backlog_size || !set_backlog_size(need)) return false;
+    lock_guard<mutex> guard(ctx->queue_mutex);
+    if (!sync_device_position(current_tokens_in_gpu)) return false;
+    if (!upload_pending_tokens(current_tokens_in_gpu, 1)) return false;
+    llava_command_buffer* cb = get_command_buffer(1, true);
+    if (cb == nullptr) return false;
+    for (u32 i = 0; i < n; ++i) if (!cb->run()) return false;      // each step consumes the previous step's argmax
+    batch_size = 1;
+    last_command_buffer = cb;
+    enqueued_greedy = n;
+    return true;
+}
+
+bool llava_session::collect_greedy_on_device(vector<u32>* out) {
+    const u32 n = enqueued_greedy;
+    if (n == 0 || last_command_buffer == nullptr) return false;
+    enqueued_greedy = 0;
+    if (!last_command_buffer->wait_idle()) return false;
     const u32 start = u32(token_buffer.size());
-    {
-        lock_guard<mutex> guard(ctx->queue_mutex);
-        if (!sync_device_position(current_tokens_in_gpu)) return false;
-        if (!upload_pending_tokens(current_tokens_in_gpu, 1)) return false;
-        llava_command_buffer* cb = get_command_buffer(1, true);
-        if (cb == nullptr) return false;
-        for (u32 i = 0; i < n; ++i) if (!cb->run()) return false;      // each step consumes the previous step's argmax
-        batch_size = 1;
-        last_command_buffer = cb;
-        if (!cb->wait_idle()) return false;
-    }
     vector<u32> fresh(n);
     if (!token_log->read_raw(size_t(start) * 4, fresh.data(), size_t(n) * 4)) return false;
     token_buffer.insert(token_buffer.end(), fresh.begin(), fresh.end());

@@ -55,6 +55,11 @@ public:
     // recorded step feeds its own argmax back in.  Requires every token pushed
     // so far to be evaluated except the last one.  Appends to the token buffer.
     bool generate_greedy_on_device(u32 n, std::vector<u32>* out);
+    // The two halves of generate_greedy_on_device, for callers that time the
+    // device work themselves: enqueue returns as soon as the n steps are queued,
+    // collect waits for them and appends the n tokens.
+    bool enqueue_greedy_on_device(u32 n);
+    bool collect_greedy_on_device(std::vector<u32>* out);
     // logits of the last evaluated token (vocab floats)
     bool get_logits(std::vector<float>* out);
     u32 get_backlog_size() const { return backlog_size; }
@@ -120,6 +125,7 @@ private:
     bool upload_pending_tokens(u32 first, u32 count);
     bool sync_device_position(u32 pos);
 
+    u32 enqueued_greedy = 0;      // steps queued by enqueue_greedy_on_device and not yet collected
     u32 options = 0;              // non-zero: tracing
     bool flush_layers_data_buffers();
     bool failed = false;
