@@ -1,0 +1,104 @@
+#!/usr/bin/env python
+"""Kernel microbenchmark of the quantised GEMV family (seeded N(0, 0.02)
+weights, N(0, 1) activations), one line of JSON per shape:
+
+    python llama-vulkan_b200/microbench.py [--shape NAME ...] [--wtype q4_0|q8_0] [--batch Z] [--iters N]
+
+Every timed launch reads a different copy of the matrix from a ring of copies
+larger than the 126 MB L2, so the figure is HBM bandwidth, not L2 bandwidth.
+GB/s = quantised matrix bytes / time.
+"""
+import argparse
+import ctypes as C
+import importlib.util
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+SHAPES = {                      # rows, cols, kind
+    "wq": (4096, 4096, "plain"),
+    "gate_up": (11008, 4096, "silu"),
+    "w2": (4096, 11008, "add"),
+    "w2_13b": (5120, 13824, "add"),
+    "head": (32000, 4096, "plain"),
+}
+
+
+def load_pkg():
+    name = "llama_vulkan_b200"
+    if name not in sys.modules:
+        spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "__init__.py"), submodule_search_locations=[HERE])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules[name]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", nargs="*", default=sorted(SHAPES))
+    ap.add_argument("--wtype", default="q4_0", choices=["q4_0", "q8_0"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--ring-mb", type=int, default=400)
+    args = ap.parse_args()
+
+    import numpy as np
+    import torch
+    import quant_np as qn
+    pkg = load_pkg()
+    wtype = qn.Q4_0 if args.wtype == "q4_0" else qn.Q8_0
+    peak = 6520.5
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        peak = float(json.load(open(p))["hbm_gbs"])
+    with pkg.Context(0) as gpu:
+        lib, h = gpu.lib, gpu.handle
+        stream = torch.cuda.ExternalStream(lib.lv_ctx_stream(h), device=0)
+        rng = np.random.default_rng(99)
+        for name in args.shape:
+            rows, cols, kind = SHAPES[name]
+            nmat = 2 if kind == "silu" else 1
+            rb = qn.row_bytes(wtype, cols)
+            slab_rows = 256
+            slab = qn.quantize((rng.standard_normal((slab_rows, cols)) * 0.02).astype(np.float32), wtype)
+            host = np.tile(slab, -(-rows // slab_rows))[: rows * rb]
+            mat_bytes = rows * rb
+            copies = max(3, int(args.ring_mb * 1e6 // (nmat * mat_bytes)) + 1)
+            ring = gpu.alloc(copies * nmat * mat_bytes)
+            for i in range(copies * nmat):
+                pkg.check(lib.lv_upload(h, pkg.offset(ring, i * mat_bytes), host.ctypes.data_as(C.c_void_p), mat_bytes))
+            x = gpu.upload(rng.standard_normal((args.batch, cols)).astype(np.float32))
+            out = gpu.zeros(args.batch * rows * 4)
+
+            def launch(i):
+                w = pkg.offset(ring, (i % copies) * nmat * mat_bytes)
+                if kind == "silu":
+                    pkg.check(lib.lv_gemv_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, x, rows, cols, args.batch))
+                else:
+                    pkg.check(lib.lv_gemv(h, out, w, wtype, x, rows, cols, args.batch, 1 if kind == "add" else 0))
+
+            for i in range(min(copies, 8)):
+                launch(i)
+            gpu.sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(args.iters):
+                launch(i)
+            e1.record(stream)
+            gpu.sync()
+            sec = e0.elapsed_time(e1) * 1e-3 / args.iters
+            gbs = nmat * mat_bytes / sec / 1e9
+            print(json.dumps({"shape": name, "rows": rows, "cols": cols, "kind": kind, "wtype": args.wtype, "batch": args.batch,
+                              "us_per_launch": sec * 1e6, "bytes": nmat * mat_bytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / peak,
+                              "ring_copies": copies}), flush=True)
+            for d in (ring, x, out):
+                gpu.free(d)
+
+
+if __name__ == "__main__":
+    main()
