@@ -7,42 +7,49 @@
 namespace lv {
 
 // Shared memory map of one CTA:
-//   [ring: warps x stages x kStageBytes][mbarriers][reduction scratch][activations, padded]
-constexpr size_t kRingBytes = size_t(kGemvWarps) * kStages * kStageBytes;
-constexpr size_t kBarBytes = 128;
+//   [ring: warps x stages x stage bytes][mbarriers][reduction scratch][activation records]
+constexpr size_t kBarBytes = 256;
 constexpr size_t kScratchBytes = 256;
 
+template <int QT, int NS>
+__host__ __device__ constexpr size_t stage_bytes() { return size_t(NS) * kSegBlocks * QTraits<QT>::kBlockBytes; }
+
+template <int QT, int NS>
 static size_t gemv_smem_bytes(uint32_t K) {
-    return kRingBytes + kBarBytes + kScratchBytes + size_t(K / 32) * kXPad * sizeof(float);
+    return size_t(QTraits<QT>::kWarps) * kStages * stage_bytes<QT, NS>() + kBarBytes + kScratchBytes + size_t(K / 64) * kPairBytes;
 }
 
-template <int QT, bool SILU>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
+// NS row streams per work item: NS consecutive rows, or NS/2 rows of each of the
+// two matrices of the SiLU-gated pair (streams ordered w3 r0, w1 r0, w3 r1, w1 r1).
+template <int QT, int NS, bool SILU>
+__global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const GemvParams p) {
     using Q = QTraits<QT>;
-    constexpr int kRowsPerItem = SILU ? 2 : 4;
-    constexpr int kStreamStride = Q::kSegBlocks * Q::kBlockBytes;   // bytes between streams in a stage
+    constexpr int kWarps = Q::kWarps;
+    constexpr int kRowsPerItem = SILU ? NS / 2 : NS;
+    constexpr int kStreamStride = kSegBlocks * Q::kBlockBytes;   // bytes between streams in a stage
+    constexpr size_t kStage = stage_bytes<QT, NS>();
+    constexpr size_t kRing = size_t(kWarps) * kStages * kStage;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRingBytes);
-    float* scratch = reinterpret_cast<float*>(smem + kRingBytes + kBarBytes);
-    float* xs = reinterpret_cast<float*>(smem + kRingBytes + kBarBytes + kScratchBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRing);
+    float* scratch = reinterpret_cast<float*>(smem + kRing + kBarBytes);
+    uint8_t* xrec = smem + kRing + kBarBytes + kScratchBytes;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t z = blockIdx.y;
     const uint32_t nb = p.K / 32;
-    const uint32_t nseg = (nb + Q::kSegBlocks - 1) / Q::kSegBlocks;
+    const uint32_t nseg = (nb + kSegBlocks - 1) / kSegBlocks;
 
-    // groups of kRowsPerItem rows, numbered across the (up to three) matrices
+    // groups of kRowsPerItem rows, numbered across the (up to three) matrices; every CTA
+    // takes a contiguous share, its warps take the groups of that share round robin
     const uint32_t g0 = p.m[0].rows / kRowsPerItem;
     const uint32_t g1 = g0 + (p.n_mat > 1 ? p.m[1].rows / kRowsPerItem : 0);
     const uint32_t g2 = g1 + (p.n_mat > 2 ? p.m[2].rows / kRowsPerItem : 0);
-    const uint32_t gw = blockIdx.x * kGemvWarps + warp;
-    const uint32_t gstride = gridDim.x * kGemvWarps;
-    const uint32_t my_groups = gw < g2 ? (g2 - gw + gstride - 1) / gstride : 0;
-    const uint32_t total = my_groups * nseg;
+    const uint32_t cta_first = uint32_t(uint64_t(g2) * blockIdx.x / gridDim.x);
+    const uint32_t cta_end = uint32_t(uint64_t(g2) * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t first = cta_first + warp;
 
-    uint8_t* my_ring = ring + size_t(warp) * kStages * kStageBytes;
+    uint8_t* my_ring = smem + size_t(warp) * kStages * kStage;
     uint64_t* my_bars = bars + warp * kStages;
 
     if (lane == 0) {
@@ -53,92 +60,109 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
 
     const uint64_t policy = l2_policy_evict_first();
 
-    // lane 0: start the copies of work item t into ring slot `slot`
-    auto issue = [&](uint32_t t, int slot) {
-        const uint32_t gg = gw + (t / nseg) * gstride;
-        const uint32_t seg = t % nseg;
-        const int mi = gg < g0 ? 0 : (gg < g1 ? 1 : 2);
-        const uint32_t lg = gg - (mi == 0 ? 0 : (mi == 1 ? g0 : g1));
-        const GemvMatrix& M = p.m[mi];
-        const uint32_t segblocks = min(uint32_t(Q::kSegBlocks), nb - seg * Q::kSegBlocks);
+    // which matrix a group belongs to, and its index inside that matrix
+    auto locate = [&](uint32_t gg, uint32_t& lg) -> const GemvMatrix& {
+        if (gg < g0) { lg = gg; return p.m[0]; }
+        if (gg < g1) { lg = gg - g0; return p.m[1]; }
+        lg = gg - g1;
+        return p.m[2];
+    };
+
+    // lanes 0..NS-1: each starts the copy of one stream of (group gg, segment seg) into ring slot `slot`
+    auto issue = [&](uint32_t gg, uint32_t seg, int slot) {
+        uint32_t lg;
+        const GemvMatrix& M = locate(gg, lg);
+        const uint32_t segblocks = min(uint32_t(kSegBlocks), nb - seg * kSegBlocks);
         const uint32_t bytes = segblocks * Q::kBlockBytes;
-        const size_t col_off = size_t(seg) * kStreamStride;
-        uint8_t* dst = my_ring + slot * kStageBytes;
-        mbar_expect_tx(&my_bars[slot], kStreams * bytes);
-        if constexpr (SILU) {
-            const size_t r0 = size_t(lg) * 2 * p.row_bytes + col_off;
-            bulk_g2s_stream(dst + 0 * kStreamStride, M.w + r0, bytes, &my_bars[slot], policy);
-            bulk_g2s_stream(dst + 1 * kStreamStride, M.w_gate + r0, bytes, &my_bars[slot], policy);
-            bulk_g2s_stream(dst + 2 * kStreamStride, M.w + r0 + p.row_bytes, bytes, &my_bars[slot], policy);
-            bulk_g2s_stream(dst + 3 * kStreamStride, M.w_gate + r0 + p.row_bytes, bytes, &my_bars[slot], policy);
-        } else {
-            const size_t r0 = size_t(lg) * 4 * p.row_bytes + col_off;
-            if (nseg == 1 && p.row_bytes == uint32_t(kStreamStride)) {
-                bulk_g2s_stream(dst, M.w + r0, 4 * bytes, &my_bars[slot], policy);   // four whole rows, contiguous
+        if (lane == 0) mbar_expect_tx(&my_bars[slot], NS * bytes);
+        __syncwarp();
+        if (lane < NS) {
+            const uint8_t* base;
+            uint32_t row;
+            if constexpr (SILU) {
+                base = (lane & 1) ? M.w_gate : M.w;
+                row = lg * kRowsPerItem + (lane >> 1);
             } else {
-#pragma unroll
-                for (int i = 0; i < kStreams; ++i)
-                    bulk_g2s_stream(dst + i * kStreamStride, M.w + r0 + size_t(i) * p.row_bytes, bytes, &my_bars[slot], policy);
+                base = M.w;
+                row = lg * kRowsPerItem + lane;
             }
+            bulk_g2s_stream(my_ring + slot * kStage + lane * kStreamStride,
+                            base + size_t(row) * p.row_bytes + size_t(seg) * kStreamStride, bytes, &my_bars[slot], policy);
         }
     };
 
-    if (lane == 0) {
-        for (uint32_t t = 0; t < uint32_t(kStages) && t < total; ++t) issue(t, int(t));
+    // issue cursor (ig, is) runs kStages work items ahead of the consume cursor (cg, cs)
+    uint32_t ig = first, is = 0;
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+        if (ig < cta_end) {
+            issue(ig, is, s);
+            if (++is == nseg) { is = 0; ig += kWarps; }
+        }
     }
 
-    // activations (optionally normalised) while the first weight bytes are in flight
-    stage_activations(xs, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
+    // activation records (optionally normalised) while the first weight bytes are in flight
+    stage_activations<Q::kFracBits>(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
     __syncthreads();
 
-    float acc[kStreams] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t t = 0; t < total; ++t) {
-        const int slot = int(t % kStages);
-        const uint32_t parity = (t / kStages) & 1u;
+    float acc[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) acc[i] = 0.f;
+
+    int slot = 0;
+    uint32_t parity = 0;
+    for (uint32_t cg = first, cs = 0; cg < cta_end;) {
         if (!mbar_wait(&my_bars[slot], parity, p.err)) break;
 
-        const uint32_t seg = t % nseg;
-        const uint32_t segblocks = min(uint32_t(Q::kSegBlocks), nb - seg * Q::kSegBlocks);
-        const uint32_t npairs = segblocks / 2;
-        const uint8_t* stage = my_ring + slot * kStageBytes;
-
-        for (uint32_t pp = lane; pp < npairs; pp += 32) {
-            float x[64];
-            const float4* xb = reinterpret_cast<const float4*>(xs + size_t(seg * Q::kSegBlocks + 2 * pp) * kXPad);
+        const uint32_t segblocks = min(uint32_t(kSegBlocks), nb - cs * kSegBlocks);
+        const uint8_t* stage = my_ring + slot * kStage;
+        if (uint32_t(lane) * 2 < segblocks) {
+            PairX px;
+            load_pair_x(px, xrec + size_t(cs * (kSegBlocks / 2) + lane) * kPairBytes);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 a = xb[i];
-                x[4 * i] = a.x; x[4 * i + 1] = a.y; x[4 * i + 2] = a.z; x[4 * i + 3] = a.w;
-                const float4 b = xb[kXPad / 4 + i];
-                x[32 + 4 * i] = b.x; x[32 + 4 * i + 1] = b.y; x[32 + 4 * i + 2] = b.z; x[32 + 4 * i + 3] = b.w;
-            }
-#pragma unroll
-            for (int i = 0; i < kStreams; ++i) {
-                const uint32_t* sw = reinterpret_cast<const uint32_t*>(stage + i * kStreamStride) + size_t(pp) * Q::kPairWords;
-                acc[i] += dot_pair<QT>(sw, x);
+            for (int i = 0; i < NS; ++i) {
+                const uint32_t* sw = reinterpret_cast<const uint32_t*>(stage + i * kStreamStride) + lane * Q::kPairWords;
+                acc[i] += dot_pair<QT>(sw, px);
             }
         }
         __syncwarp();
-        if (lane == 0 && t + kStages < total) issue(t + kStages, slot);
+        if (ig < cta_end) {
+            issue(ig, is, slot);
+            if (++is == nseg) { is = 0; ig += kWarps; }
+        }
+        slot ^= 1;
+        parity ^= uint32_t(slot == 0);
 
-        if (seg == nseg - 1) {
-            const uint32_t gg = gw + (t / nseg) * gstride;
-            const int mi = gg < g0 ? 0 : (gg < g1 ? 1 : 2);
-            const uint32_t lg = gg - (mi == 0 ? 0 : (mi == 1 ? g0 : g1));
-            const GemvMatrix& M = p.m[mi];
-            const float u = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
-            float v = u;
+        if (cs == nseg - 1) {
+            uint32_t lg;
+            const GemvMatrix& M = locate(cg, lg);
+            float v;
             uint32_t row;
             bool writer;
-            if constexpr (SILU) {
-                // streams: (w3 r0, w1 r0, w3 r1, w1 r1); lanes 0 and 16 finish rows r0 and r1
-                const float gate = __shfl_xor_sync(0xffffffffu, u, 8);
-                v = u * gate / (expf(-gate) + 1.0f);                 // matmul_silu_ff.comp:95
-                row = lg * 2 + (lane >> 4);
-                writer = (lane & 15) == 0;
+            if constexpr (NS == 4) {
+                const float u = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
+                if constexpr (SILU) {
+                    const float gate = __shfl_xor_sync(0xffffffffu, u, 8);
+                    v = u * gate / (expf(-gate) + 1.0f);                 // matmul_silu_ff.comp:95
+                    row = lg * 2 + (lane >> 4);
+                    writer = (lane & 15) == 0;
+                } else {
+                    v = u;
+                    row = lg * 4 + (lane >> 3);
+                    writer = (lane & 7) == 0;
+                }
             } else {
-                row = lg * 4 + (lane >> 3);
-                writer = (lane & 7) == 0;
+                const float u = warp_sum2(acc[0], acc[1], lane);
+                if constexpr (SILU) {
+                    const float gate = __shfl_xor_sync(0xffffffffu, u, 16);
+                    v = u * gate / (expf(-gate) + 1.0f);
+                    row = lg;
+                    writer = lane == 0;
+                } else {
+                    v = u;
+                    row = lg * 2 + (lane >> 4);
+                    writer = (lane & 15) == 0;
+                }
             }
             if (writer) {
                 if (M.epilogue == EPI_STORE_F16_AT_POS) {
@@ -151,31 +175,57 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
                     *o = (M.epilogue == EPI_ADD) ? (*o + v) : v;                       // matmul.glsl:68-72
                 }
             }
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) acc[i] = 0.f;
+            cs = 0;
+            cg += kWarps;
+        } else {
+            ++cs;
         }
     }
 }
 
-template <int QT, bool SILU>
-static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch) {
-    constexpr int rpi = SILU ? 2 : 4;
-    uint32_t groups = 0;
-    for (int i = 0; i < p.n_mat; ++i) groups += p.m[i].rows / rpi;
-    const size_t smem = gemv_smem_bytes(p.K);
+template <int QT, int NS, bool SILU>
+static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_t groups) {
+    const size_t smem = gemv_smem_bytes<QT, NS>(p.K);
     LV_REQUIRE(smem <= size_t(ctx->max_smem_optin), "lv_gemv: K too large for the shared-memory activation buffer");
-    auto kern = gemv_kernel<QT, SILU>;
-    const uint32_t ctas = min(uint32_t(ctx->sm_count), (groups + kGemvWarps - 1) / kGemvWarps);
+    const uint32_t ctas = min(uint32_t(ctx->sm_count), groups);
     dim3 grid(ctas, batch);
-    kern<<<grid, kGemvThreads, smem, ctx->stream>>>(p);
+    gemv_kernel<QT, NS, SILU><<<grid, QTraits<QT>::kWarps * 32, smem, ctx->stream>>>(p);
     LV_CUDA(cudaGetLastError());
     return LV_OK;
 }
 
+template <int QT, bool SILU>
+static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t batch) {
+    uint32_t rows = 0;
+    for (int i = 0; i < p.n_mat; ++i) rows += p.m[i].rows;
+    // four streams per item reuse each activation record twice as often, but only pay off
+    // when there are enough row groups to keep every warp of every SM busy
+    const uint32_t groups4 = SILU ? rows / 2 : rows / 4;
+    const uint32_t warps = uint32_t(ctx->sm_count) * QTraits<QT>::kWarps;
+    if (groups4 >= 2 * warps) return launch_gemv<QT, 4, SILU>(ctx, p, batch, groups4);
+    return launch_gemv<QT, 2, SILU>(ctx, p, batch, groups4 * 2);
+}
+
+// Raises the dynamic shared-memory limit of every instantiation; called once
+// per context with its device current.
+int gemv_configure(lv_ctx* ctx) {
+    const int lim = ctx->max_smem_optin;
+#define LV_CFG(QT, NS, SILU) LV_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, NS, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim))
+    LV_CFG(T_Q4_0, 4, false); LV_CFG(T_Q4_0, 4, true); LV_CFG(T_Q4_0, 2, false); LV_CFG(T_Q4_0, 2, true);
+    LV_CFG(T_Q8_0, 4, false); LV_CFG(T_Q8_0, 4, true); LV_CFG(T_Q8_0, 2, false); LV_CFG(T_Q8_0, 2, true);
+#undef LV_CFG
+    return LV_OK;
+}
+
 static int check_matrix_args(const void* const* ws, int nw, int wtype, uint32_t cols, uint32_t rows_mult,
-                             const uint32_t* rows, uint32_t batch, uint32_t* row_bytes) {
+                             const uint32_t* rows, uint32_t batch, uint32_t* row_bytes, const float* x, const float* norm_w) {
     LV_REQUIRE(wtype == T_Q4_0 || wtype == T_Q8_0, "matrix type must be q4_0 (2) or q8_0 (8)");
     LV_REQUIRE(cols != 0 && cols % 256 == 0, "cols must be a non-zero multiple of 256");
     LV_REQUIRE(batch >= 1 && batch <= 65535, "batch out of range");
+    LV_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(norm_w) & 15u) == 0,
+               "activation and norm vectors must be 16-byte aligned");
     for (int i = 0; i < nw; ++i) {
         LV_REQUIRE(ws[i] != nullptr && (reinterpret_cast<uintptr_t>(ws[i]) & 15u) == 0, "matrix pointer null or not 16-byte aligned");
         LV_REQUIRE(rows[i] != 0 && rows[i] % rows_mult == 0, "rows must be a non-zero multiple of 4");
@@ -184,20 +234,9 @@ static int check_matrix_args(const void* const* ws, int nw, int wtype, uint32_t 
     return LV_OK;
 }
 
-// Raises the dynamic shared-memory limit of every instantiation; called once
-// per context with its device current.
-int gemv_configure(lv_ctx* ctx) {
-    const int lim = ctx->max_smem_optin;
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<T_Q4_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<T_Q4_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<T_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<T_Q8_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    return LV_OK;
-}
-
 static int gemv_dispatch(lv_ctx* ctx, const GemvParams& p, int wtype, bool silu, uint32_t batch) {
-    if (wtype == T_Q4_0) return silu ? launch_gemv<T_Q4_0, true>(ctx, p, batch) : launch_gemv<T_Q4_0, false>(ctx, p, batch);
-    return silu ? launch_gemv<T_Q8_0, true>(ctx, p, batch) : launch_gemv<T_Q8_0, false>(ctx, p, batch);
+    if (wtype == T_Q4_0) return silu ? launch_gemv_pick_streams<T_Q4_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q4_0, false>(ctx, p, batch);
+    return silu ? launch_gemv_pick_streams<T_Q8_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q8_0, false>(ctx, p, batch);
 }
 
 }  // namespace lv
@@ -210,7 +249,7 @@ static int gemv_single(lv_ctx* ctx, float* out, const void* W, int wtype, const 
     LV_REQUIRE(out && x, "null argument");
     GemvParams p{};
     const void* ws[1] = {W};
-    if (int rc = check_matrix_args(ws, 1, wtype, cols, 4, &rows, batch, &p.row_bytes)) return rc;
+    if (int rc = check_matrix_args(ws, 1, wtype, cols, 4, &rows, batch, &p.row_bytes, x, norm_w)) return rc;
     p.m[0] = {static_cast<const uint8_t*>(W), nullptr, out, rows, add ? EPI_ADD : EPI_STORE};
     p.n_mat = 1;
     p.x = x;
@@ -242,7 +281,7 @@ extern "C" int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, con
     GemvParams p{};
     const void* ws[2] = {w3, w1};
     const uint32_t rows[2] = {ff, ff};
-    if (int rc = check_matrix_args(ws, 2, wtype, dim, 2, rows, batch, &p.row_bytes)) return rc;
+    if (int rc = check_matrix_args(ws, 2, wtype, dim, 2, rows, batch, &p.row_bytes, x, norm_w)) return rc;
     p.m[0] = {static_cast<const uint8_t*>(w3), static_cast<const uint8_t*>(w1), out, ff, EPI_STORE};
     p.n_mat = 1;
     p.x = x;
@@ -261,7 +300,7 @@ extern "C" int lv_norm_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, vo
     GemvParams p{};
     const void* ws[3] = {wk, wq, wv};
     const uint32_t rows[3] = {dim, dim, dim};
-    if (int rc = check_matrix_args(ws, 3, wtype, dim, 4, rows, batch, &p.row_bytes)) return rc;
+    if (int rc = check_matrix_args(ws, 3, wtype, dim, 4, rows, batch, &p.row_bytes, x, norm_w)) return rc;
     // same order as the reference records them: K, Q, V (llava_layer.cpp:54-56)
     p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, k_cache, dim, EPI_STORE_F16_AT_POS};
     p.m[1] = {static_cast<const uint8_t*>(wq), nullptr, q_out, dim, EPI_STORE};

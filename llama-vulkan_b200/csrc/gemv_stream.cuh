@@ -3,37 +3,45 @@
 //
 // Replaces the reference's matmul.glsl / matmul_q8.glsl / matmul_silu_ff*.comp
 // family.  Each warp owns a private two-stage ring in shared memory that it
-// fills with bulk (TMA) copies of four "row streams" (four consecutive rows,
-// or two rows of each of two matrices for the SiLU-gated pair) and drains with
-// all 32 lanes: a lane handles a pair of adjacent blocks (36 B / 68 B, an odd
-// number of 32-bit words, hence bank-conflict free), keeps the 64 matching
-// activations in registers and reuses them for all four streams.  Nibbles are
-// widened in registers, accumulation is fp32, the block scale multiplies the
-// 32-term partial sum once (as the reference shaders do), lanes are combined by
-// shuffles in a fixed order.
+// fills with bulk (TMA) copies of its "row streams" (consecutive rows, or rows
+// of the two matrices of the SiLU-gated pair) and drains with all 32 lanes: a
+// lane handles a pair of adjacent blocks (36 B / 68 B, an odd number of 32-bit
+// words, hence bank-conflict free).
+//
+// Arithmetic.  B200 has about three issue slots per weight at the HBM
+// roofline, so widening every nibble to fp32 cannot keep up.  Instead each
+// block of 32 activations is turned, once per CTA, into fixed point
+// X_e = rint(x_e * S / max|x|), S = 126 * 2^14, split into three base-128
+// digits (X = a*2^14 + b*2^7 + c; a in [-126, 126], b and c in [-64, 63]), and the inner sums
+// sum_e q_e * X_e are formed exactly in int32 with dp4a.  The block result is
+// converted to fp32 once and multiplied by d * max|x| / S; rows are
+// accumulated in fp32 and lanes combined by shuffles in a fixed order.  The
+// only rounding beyond fp32 is that of x_e to about 22 bits relative to its block
+// maximum, of the order of the reordering noise of an fp32 accumulation.
 #pragma once
 
 #include "common.cuh"
 
 namespace lv {
 
-constexpr int kGemvWarps = 8;              // consumer warps per CTA
-constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kStreams = 4;                // row streams per work item
 constexpr int kStages = 2;                 // ring depth per warp
-constexpr int kStageBytes = 9216;          // 4 streams x 2304 B
-constexpr int kXPad = 36;                  // floats per activation block in shared memory (32 + 4 pad)
+constexpr int kSegBlocks = 64;             // blocks of one row per stage (32 lane pairs)
+constexpr int kPairBytes = 208;            // activation record of one block pair in shared memory:
+                                           //   a[64] b[64] c[64] int8, T8[2] int32, scale[2] f32
+constexpr int kMaxStreams = 4;
 
 template <int QT> struct QTraits;
 template <> struct QTraits<T_Q4_0> {
     static constexpr int kBlockBytes = kQ4BlockBytes;
-    static constexpr int kSegBlocks = 128;                  // blocks per row segment (2304 B)
     static constexpr int kPairWords = 9;
+    static constexpr int kWarps = 16;                 // consumer warps per CTA
+    static constexpr int kFracBits = 20;              // activations are scaled to +-1.99 * 2^kFracBits
 };
 template <> struct QTraits<T_Q8_0> {
     static constexpr int kBlockBytes = kQ8BlockBytes;
-    static constexpr int kSegBlocks = 64;                   // 2176 B
     static constexpr int kPairWords = 17;
+    static constexpr int kWarps = 8;
+    static constexpr int kFracBits = 20;
 };
 
 // What to do with a finished row.
@@ -59,44 +67,72 @@ struct GemvParams {
     uint32_t* err;
 };
 
-// 32 dequantised-weight x activation products of one q4_0 block.  `q` holds the
-// 16 nibble bytes: byte j carries element j (low nibble) and j+16 (high).
-__device__ __forceinline__ float dot_block_q4(const uint32_t (&q)[4], const float* __restrict__ x) {
-    float s = 0.f;
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a_s8x4, uint32_t b_s8x4, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_s8x4), "r"(b_s8x4), "r"(c));
+    return d;
+}
+
+// Activation record of one block pair as a lane holds it in registers.
+struct PairX {
+    uint32_t a[16], b[16], c[16];   // digit words: [0..7] block 0 (elements 4k..4k+3), [8..15] block 1
+    int t8[2];                      // 8 * sum_e X_e per block (the q4_0 offset of 8, folded in once)
+    float scale[2];                 // max|x| / 2^F per block
+};
+
+__device__ __forceinline__ void load_pair_x(PairX& px, const uint8_t* __restrict__ rec) {
+    const uint4* r = reinterpret_cast<const uint4*>(rec);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 va = r[i], vb = r[4 + i], vc = r[8 + i];
+        px.a[4 * i] = va.x; px.a[4 * i + 1] = va.y; px.a[4 * i + 2] = va.z; px.a[4 * i + 3] = va.w;
+        px.b[4 * i] = vb.x; px.b[4 * i + 1] = vb.y; px.b[4 * i + 2] = vb.z; px.b[4 * i + 3] = vb.w;
+        px.c[4 * i] = vc.x; px.c[4 * i + 1] = vc.y; px.c[4 * i + 2] = vc.z; px.c[4 * i + 3] = vc.w;
+    }
+    const uint4 meta = r[12];
+    px.t8[0] = int(meta.x); px.t8[1] = int(meta.y);
+    px.scale[0] = __uint_as_float(meta.z); px.scale[1] = __uint_as_float(meta.w);
+}
+
+// sum_e (nibble_e - 8) * X_e of one q4_0 block, exactly.  q: the 16 nibble bytes
+// (byte j carries element j in the low and element j + 16 in the high nibble).
+__device__ __forceinline__ int block_sum_q4(const uint32_t (&q)[4], const uint32_t* __restrict__ a,
+                                            const uint32_t* __restrict__ b, const uint32_t* __restrict__ c, int t8) {
+    int al = 0, bl = 0, cl = 0, ah = 0, bh = 0, ch = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const uint32_t lo = q[k] & 0x0f0f0f0fu;
-        const uint32_t hi = (q[k] >> 4) & 0x0f0f0f0fu;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // byte j -> 0x4B0000nn = 2^23 + n; subtracting 2^23 + 8 gives n - 8 exactly
-            const float fl = __uint_as_float(__byte_perm(lo, 0x4b000000u, 0x7540 + j)) - 8388616.0f;
-            const float fh = __uint_as_float(__byte_perm(hi, 0x4b000000u, 0x7540 + j)) - 8388616.0f;
-            s = fmaf(fl, x[4 * k + j], s);
-            s = fmaf(fh, x[16 + 4 * k + j], s);
-        }
+        const uint32_t lo = q[k] & 0x0f0f0f0fu;          // elements 4k..4k+3
+        const uint32_t hi = q[k] & 0xf0f0f0f0u;          // elements 16+4k.., scaled by 16
+        al = dp4a_us(lo, a[k], al); bl = dp4a_us(lo, b[k], bl); cl = dp4a_us(lo, c[k], cl);
+        ah = dp4a_us(hi, a[4 + k], ah); bh = dp4a_us(hi, b[4 + k], bh); ch = dp4a_us(hi, c[4 + k], ch);
     }
-    return s;
+    // the high-nibble sums are exact multiples of 16
+    const int hi_ab = (ah * 128 + bh) >> 4;
+    return ((al * 128 + bl + hi_ab) * 128 + cl + (ch >> 4)) - t8;
 }
 
-// Same for one q8_0 block: 32 signed bytes in element order.
-__device__ __forceinline__ float dot_block_q8(const uint32_t (&q)[8], const float* __restrict__ x) {
-    float s = 0.f;
+// sum_e int8_e * X_e of one q8_0 block.  The exact integer can reach 2^32, so the two upper
+// digits and the lowest one are converted separately (the first conversion rounds to 24 bits,
+// like any fp32 accumulation would).
+__device__ __forceinline__ float block_sum_q8(const uint32_t (&q)[8], const uint32_t* __restrict__ a,
+                                              const uint32_t* __restrict__ b, const uint32_t* __restrict__ c) {
+    int sa = 0, sb = 0, sc = 0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const uint32_t biased = q[k] ^ 0x80808080u;      // byte + 128
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float f = __uint_as_float(__byte_perm(biased, 0x4b000000u, 0x7540 + j)) - 8388736.0f;   // 2^23 + 128
-            s = fmaf(f, x[4 * k + j], s);
-        }
+        sa = dp4a_ss(q[k], a[k], sa); sb = dp4a_ss(q[k], b[k], sb); sc = dp4a_ss(q[k], c[k], sc);
     }
-    return s;
+    return fmaf(static_cast<float>(sa * 128 + sb), 128.0f, static_cast<float>(sc));
 }
 
-// Partial dot product of one lane's block pair for one row stream.
+// Contribution of one lane's block pair to one row stream.
 template <int QT>
-__device__ __forceinline__ float dot_pair(const uint32_t* __restrict__ sw, const float (&x)[64]) {
+__device__ __forceinline__ float dot_pair(const uint32_t* __restrict__ sw, const PairX& px) {
     if constexpr (QT == T_Q4_0) {
         uint32_t w[9];
 #pragma unroll
@@ -108,9 +144,11 @@ __device__ __forceinline__ float dot_pair(const uint32_t* __restrict__ sw, const
             q0[k] = __funnelshift_r(w[k], w[k + 1], 16);
             q1[k] = w[5 + k];
         }
-        const float d0 = half_bits_to_float(w[0] & 0xffffu);
-        const float d1 = half_bits_to_float(w[4] >> 16);
-        return dot_block_q4(q0, &x[0]) * d0 + dot_block_q4(q1, &x[32]) * d1;
+        const float d0 = half_bits_to_float(w[0] & 0xffffu) * px.scale[0];
+        const float d1 = half_bits_to_float(w[4] >> 16) * px.scale[1];
+        const int i0 = block_sum_q4(q0, &px.a[0], &px.b[0], &px.c[0], px.t8[0]);
+        const int i1 = block_sum_q4(q1, &px.a[8], &px.b[8], &px.c[8], px.t8[1]);
+        return fmaf(static_cast<float>(i0), d0, static_cast<float>(i1) * d1);
     } else {
         uint32_t w[17];
 #pragma unroll
@@ -122,9 +160,11 @@ __device__ __forceinline__ float dot_pair(const uint32_t* __restrict__ sw, const
             q0[k] = __funnelshift_r(w[k], w[k + 1], 16);
             q1[k] = w[9 + k];
         }
-        const float d0 = half_bits_to_float(w[0] & 0xffffu);
-        const float d1 = half_bits_to_float(w[8] >> 16);
-        return dot_block_q8(q0, &x[0]) * d0 + dot_block_q8(q1, &x[32]) * d1;
+        const float d0 = half_bits_to_float(w[0] & 0xffffu) * px.scale[0];
+        const float d1 = half_bits_to_float(w[8] >> 16) * px.scale[1];
+        const float f0 = block_sum_q8(q0, &px.a[0], &px.b[0], &px.c[0]);
+        const float f1 = block_sum_q8(q1, &px.a[8], &px.b[8], &px.c[8]);
+        return fmaf(f0, d0, f1 * d1);
     }
 }
 
@@ -146,28 +186,109 @@ __device__ __forceinline__ float warp_sum4(float a0, float a1, float a2, float a
     return u;
 }
 
-// Copies activations into the padded shared layout (block b at float b*kXPad).
-// With norm_w the reference's normalisation is applied on the way
-// (shaders/normalize.comp:39-63): m = mean(x), v = mean((x-m)^2),
-// out = x * w * rsqrt(v); no epsilon, numerator not centred.
-__device__ __forceinline__ void stage_activations(float* __restrict__ xs, const float* __restrict__ x,
+// Same for two values: lanes 0-15 end up with the total of a0, lanes 16-31 with a1.
+__device__ __forceinline__ float warp_sum2(float a0, float a1, int lane) {
+    const bool up16 = lane & 16;
+    float u = up16 ? a1 : a0;
+    const float v = up16 ? a0 : a1;
+    u += __shfl_xor_sync(0xffffffffu, v, 16);
+    u += __shfl_xor_sync(0xffffffffu, u, 8);
+    u += __shfl_xor_sync(0xffffffffu, u, 4);
+    u += __shfl_xor_sync(0xffffffffu, u, 2);
+    u += __shfl_xor_sync(0xffffffffu, u, 1);
+    return u;
+}
+
+// Builds the activation records of all K/64 block pairs in shared memory.
+// A thread owns four consecutive elements (one 16-byte load), eight adjacent
+// lanes own a block.  Everything a thread needs is fetched before anything
+// depends on it, so the vector costs one trip to L2.  With norm_w the
+// reference's normalisation is applied first (shaders/normalize.comp:39-63):
+// m = mean(x), v = mean((x-m)^2), x * w * rsqrt(v); no epsilon, numerator not
+// centred.  `scratch` holds 33 floats.
+constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
+
+__device__ __forceinline__ void digits_of(int X, int& a, int& b, int& c) {
+    c = ((X + 64) & 127) - 64;
+    const int X1 = (X - c) >> 7;
+    b = ((X1 + 64) & 127) - 64;
+    a = (X1 - b) >> 7;
+}
+
+__device__ __forceinline__ uint32_t pack4(int b0, int b1, int b2, int b3) {
+    return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+
+template <int FRAC_BITS>
+__device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
                                                   const float* __restrict__ norm_w, uint32_t K, float* scratch) {
-    float factor = 1.f;
-    if (norm_w != nullptr) {
-        float part = 0.f;
-        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) part += x[i];
-        const float mean = block_sum(part, scratch) / static_cast<float>(K);
-        part = 0.f;
-        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
-            const float c = x[i] - mean;
-            part = fmaf(c, c, part);
+    const int lane = threadIdx.x & 31;
+    // largest fixed-point magnitude: 126 * 2^14, which keeps the top digit within int8 after the
+    // two lower digits have been balanced around zero
+    constexpr float kTwoF = static_cast<float>((126u << FRAC_BITS) >> 6);
+    const uint32_t stride = blockDim.x * 4;
+
+    for (uint32_t chunk = 0; chunk < K; chunk += stride * kActIters) {
+        float4 v[kActIters], w[kActIters];
+#pragma unroll
+        for (int i = 0; i < kActIters; ++i) {
+            const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
+            v[i] = e < K ? *reinterpret_cast<const float4*>(x + e) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(K));
-    }
-    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
-        float v = x[i];
-        if (norm_w != nullptr) v = (v * norm_w[i]) * factor;
-        xs[(i >> 5) * kXPad + (i & 31)] = v;
+        if (norm_w != nullptr) {
+            // normalised inputs have length dim, which always fits one chunk
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) {
+                const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
+                w[i] = e < K ? *reinterpret_cast<const float4*>(norm_w + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) part += (v[i].x + v[i].y) + (v[i].z + v[i].w);      // absent elements hold 0
+            const float mean = block_sum(part, scratch) / static_cast<float>(K);
+            part = 0.f;
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) {
+                if (chunk + uint32_t(i) * stride + threadIdx.x * 4 < K) {
+                    const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+                    part += (a * a + b * b) + (c * c + d * d);
+                }
+            }
+            const float factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(K));
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) {
+                v[i].x = (v[i].x * w[i].x) * factor; v[i].y = (v[i].y * w[i].y) * factor;
+                v[i].z = (v[i].z * w[i].z) * factor; v[i].w = (v[i].w * w[i].w) * factor;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kActIters; ++i) {
+            const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
+            if (e >= K) break;              // K is a multiple of 32: the eight lanes of a block leave together
+            float m = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+            const float inv = m > 0.f ? kTwoF / m : 0.f;
+            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 126 * 2^14
+            const int X2 = __float2int_rn(v[i].z * inv), X3 = __float2int_rn(v[i].w * inv);
+            int a0, b0, c0, a1, b1, c1, a2, b2, c2, a3, b3, c3;
+            digits_of(X0, a0, b0, c0); digits_of(X1, a1, b1, c1); digits_of(X2, a2, b2, c2); digits_of(X3, a3, b3, c3);
+            int T = (X0 + X1) + (X2 + X3);
+            T += __shfl_xor_sync(0xffffffffu, T, 1);
+            T += __shfl_xor_sync(0xffffffffu, T, 2);
+            T += __shfl_xor_sync(0xffffffffu, T, 4);
+            const uint32_t blk = e >> 5;
+            uint8_t* rec = xrec + size_t(blk >> 1) * kPairBytes;
+            const uint32_t at = (blk & 1) * 32 + (lane & 7) * 4;
+            *reinterpret_cast<uint32_t*>(rec + at) = pack4(a0, a1, a2, a3);
+            *reinterpret_cast<uint32_t*>(rec + 64 + at) = pack4(b0, b1, b2, b3);
+            *reinterpret_cast<uint32_t*>(rec + 128 + at) = pack4(c0, c1, c2, c3);
+            if ((lane & 7) == 0) {
+                reinterpret_cast<int*>(rec + 192)[blk & 1] = 8 * T;
+                reinterpret_cast<float*>(rec + 200)[blk & 1] = m / kTwoF;
+            }
+        }
     }
 }
 

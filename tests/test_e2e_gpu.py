@@ -102,6 +102,10 @@ def test_greedy_tokens_identical_and_logits_within_tolerance(run):
         assert tok == run["greedy"][step], f"step {step}"
         assert s.push_token(tok)
     print(f"worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}")
+    report = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(report):
+        with open(os.path.join(report, "parity_report.txt"), "a") as f:
+            f.write(f"config0 wtype={run['wtype']} 32 greedy tokens identical; worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}\n")
     assert s.tokens() == run["prompt"] + run["greedy"]
     # the caches hold un-rotated f16 K and V rows; a value that differs in its last fp32 bits may
     # round to the neighbouring half, so compare as numbers
