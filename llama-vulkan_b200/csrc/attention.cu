@@ -41,6 +41,8 @@ __device__ __forceinline__ float rope_score(const float4 q4, const __half* __res
 __global__ void __launch_bounds__(kAttnThreads) attn_scores_kernel(float* __restrict__ scores, const __half* __restrict__ kc,
                                                                   const float* __restrict__ q, const uint32_t* __restrict__ pos,
                                                                   const float* __restrict__ table, uint32_t backlog, uint32_t heads) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint32_t z = blockIdx.y;
     const uint32_t P = *pos + z;
@@ -59,6 +61,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_scores_kernel(float* __rest
 // In-place masked softmax over p for each (z, h).  One warp per (z, h).
 __global__ void __launch_bounds__(kAttnThreads) softmax_kernel(float* __restrict__ scores, const uint32_t* __restrict__ pos,
                                                               uint32_t backlog, uint32_t heads, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint32_t z = blockIdx.y;
     const uint32_t P = *pos + z;
@@ -82,6 +86,8 @@ __global__ void __launch_bounds__(kAttnThreads) softmax_kernel(float* __restrict
 // v_out[z][d] = sum_p V[p][d] * probs[z][p][d / rot].  One thread per d, two halves of p per CTA.
 __global__ void __launch_bounds__(kAttnThreads) attn_values_kernel(float* __restrict__ vout, const __half* __restrict__ vc,
                                                                   const float* __restrict__ probs, uint32_t backlog, uint32_t heads) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float part[kRot];
     const uint32_t z = blockIdx.y, h = blockIdx.x;
     const uint32_t dim = heads * kRot;
@@ -118,6 +124,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_fused_kernel(float* __
                                                                       const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                       float* __restrict__ partial, uint32_t* __restrict__ counters,
                                                                       uint32_t heads, uint32_t nchunks, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float s_e[kAttnChunk];
     __shared__ float s_part[kRot];
     __shared__ float s_red[2];
@@ -237,8 +245,7 @@ extern "C" int lv_attn_scores_rope(lv_ctx* ctx, float* scores, const void* k_cac
     if (int rc = check_attn_shape(backlog, heads, rot, batch)) return rc;
     const uint32_t warps = backlog * heads;
     dim3 grid((warps + kAttnThreads / 32 - 1) / (kAttnThreads / 32), batch);
-    attn_scores_kernel<<<grid, kAttnThreads, 0, ctx->stream>>>(scores, static_cast<const __half*>(k_cache), q, pos, rope_table, backlog, heads);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, attn_scores_kernel, grid, dim3(kAttnThreads), 0, scores, static_cast<const __half*>(k_cache), q, pos, rope_table, backlog, heads));
     return LV_OK;
 }
 
@@ -248,8 +255,7 @@ extern "C" int lv_softmax_masked(lv_ctx* ctx, float* scores, const uint32_t* pos
     LV_REQUIRE(scores && pos, "null argument");
     if (int rc = check_attn_shape(backlog, heads, rot, batch)) return rc;
     dim3 grid((heads + kAttnThreads / 32 - 1) / (kAttnThreads / 32), batch);
-    softmax_kernel<<<grid, kAttnThreads, 0, ctx->stream>>>(scores, pos, backlog, heads, 1.0f / sqrtf(static_cast<float>(rot)));
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, softmax_kernel, grid, dim3(kAttnThreads), 0, scores, pos, backlog, heads, 1.0f / sqrtf(static_cast<float>(rot))));
     return LV_OK;
 }
 
@@ -259,8 +265,7 @@ extern "C" int lv_attn_values(lv_ctx* ctx, float* v_out, const void* v_cache, co
     LV_REQUIRE(v_out && v_cache && probs, "null argument");
     if (int rc = check_attn_shape(backlog, heads, rot, batch)) return rc;
     dim3 grid(heads, batch);
-    attn_values_kernel<<<grid, kAttnThreads, 0, ctx->stream>>>(v_out, static_cast<const __half*>(v_cache), probs, backlog, heads);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, attn_values_kernel, grid, dim3(kAttnThreads), 0, v_out, static_cast<const __half*>(v_cache), probs, backlog, heads));
     return LV_OK;
 }
 
@@ -280,9 +285,8 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
     dim3 grid(heads, nchunks, batch);
-    attention_fused_kernel<<<grid, kAttnThreads, 0, ctx->stream>>>(out, q, static_cast<const __half*>(k_cache),
-                                                                  static_cast<const __half*>(v_cache), pos, rope_table, partial,
-                                                                  counters, heads, nchunks, 1.0f / sqrtf(static_cast<float>(rot)));
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kAttnThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                       static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                       1.0f / sqrtf(static_cast<float>(rot))));
     return LV_OK;
 }

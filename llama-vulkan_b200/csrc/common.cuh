@@ -100,6 +100,13 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     return p;
 }
 
+// Programmatic dependent launch.  Every kernel of this library lets its successor start
+// launching at once (the successor's prologue -- barrier set-up, the first weight copies --
+// then overlaps this kernel's tail) and waits for its predecessor to finish before it reads
+// activations or writes anything.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

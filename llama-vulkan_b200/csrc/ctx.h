@@ -46,4 +46,21 @@ int attention_configure(lv_ctx* ctx);
         if (!(cond)) return lv::fail(LV_ERR_BAD_ARGUMENTS, std::string(msg)); \
     } while (0)
 
+// Launches `kernel` on the context's stream with programmatic stream serialisation, so
+// that it may begin while its predecessor drains (see pdl_wait in common.cuh).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(lv_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace lv

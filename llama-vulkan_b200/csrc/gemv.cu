@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
     constexpr size_t kStage = stage_bytes<QT, NS>();
     constexpr size_t kRing = size_t(kWarps) * kStages * kStage;
 
+    pdl_launch_dependents();
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRing);
     float* scratch = reinterpret_cast<float*>(smem + kRing + kBarBytes);
@@ -101,6 +102,8 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
         }
     }
 
+    // weights never depend on the previous kernel; everything below does
+    pdl_wait();
     // activation records (optionally normalised) while the first weight bytes are in flight
     stage_activations<Q::kFracBits>(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
     __syncthreads();
@@ -191,8 +194,7 @@ static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_
     LV_REQUIRE(smem <= size_t(ctx->max_smem_optin), "lv_gemv: K too large for the shared-memory activation buffer");
     const uint32_t ctas = min(uint32_t(ctx->sm_count), groups);
     dim3 grid(ctas, batch);
-    gemv_kernel<QT, NS, SILU><<<grid, QTraits<QT>::kWarps * 32, smem, ctx->stream>>>(p);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, gemv_kernel<QT, NS, SILU>, grid, dim3(QTraits<QT>::kWarps * 32), smem, p));
     return LV_OK;
 }
 

@@ -10,6 +10,8 @@ namespace lv {
 // shaders/normalize.comp:34-63: one CTA per batch row.
 __global__ void __launch_bounds__(1024) norm_kernel(float* __restrict__ out, const float* __restrict__ x,
                                                     const float* __restrict__ w, uint32_t dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const float* xr = x + size_t(blockIdx.x) * dim;
     float* orow = out + size_t(blockIdx.x) * dim;
@@ -28,6 +30,8 @@ __global__ void __launch_bounds__(1024) norm_kernel(float* __restrict__ out, con
 // shaders/copy_to_cache.comp:29-37
 __global__ void kv_append_kernel(__half* __restrict__ cache, const float* __restrict__ x, const uint32_t* __restrict__ pos,
                                  uint32_t dim, uint32_t ctx_rows, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t z = blockIdx.y;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t row = *pos + z;
@@ -39,10 +43,14 @@ __global__ void kv_append_kernel(__half* __restrict__ cache, const float* __rest
 }
 
 __global__ void copy_kernel(float* __restrict__ dst, const float* __restrict__ src, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) dst[i] = src[i];
 }
 
 __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) a[i] += b[i];
 }
 
@@ -51,6 +59,8 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 __global__ void dequant_rows_kernel(float* __restrict__ out, const uint8_t* __restrict__ table, int wtype,
                                     const uint32_t* __restrict__ ids, const uint32_t* __restrict__ first, uint32_t cols,
                                     uint32_t vocab, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t z = blockIdx.x;
     uint32_t id = ids[(first ? *first : 0u) + z];
     if (id >= vocab) {
@@ -93,6 +103,8 @@ __device__ __forceinline__ void argmax_merge(float& best, uint32_t& bi, float ov
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out, const float* __restrict__ v, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float s_val[32];
     __shared__ uint32_t s_idx[32];
     float best = 0.f;
@@ -127,6 +139,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out
 
 __global__ void decode_advance_kernel(uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
                                       uint32_t log_capacity, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (argmax != nullptr && token_log != nullptr) {
         const uint32_t at = config[0] + batch;
         if (at < log_capacity) token_log[at] = *argmax;
@@ -143,16 +157,14 @@ extern "C" int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* 
                                  uint32_t batch, uint32_t log_capacity) {
     LV_ENTER(ctx);
     LV_REQUIRE(config && batch, "bad advance arguments");
-    decode_advance_kernel<<<1, 1, 0, ctx->stream>>>(config, argmax, token_log, batch, log_capacity, ctx->d_err);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, decode_advance_kernel, dim3(1), dim3(1), 0, config, argmax, token_log, batch, log_capacity, ctx->d_err));
     return LV_OK;
 }
 
 extern "C" int lv_norm_f32(lv_ctx* ctx, float* out, const float* x, const float* w, uint32_t dim, uint32_t batch) {
     LV_ENTER(ctx);
     LV_REQUIRE(out && x && w && dim && batch, "bad norm arguments");
-    norm_kernel<<<batch, 1024, 0, ctx->stream>>>(out, x, w, dim);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, norm_kernel, dim3(batch), dim3(1024), 0, out, x, w, dim));
     return LV_OK;
 }
 
@@ -161,8 +173,7 @@ extern "C" int lv_kv_append_f16(lv_ctx* ctx, void* cache, const float* x, const 
     LV_ENTER(ctx);
     LV_REQUIRE(cache && x && pos && dim && batch && batch <= 65535, "bad kv_append arguments");
     dim3 grid((dim + 255) / 256, batch);
-    kv_append_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<__half*>(cache), x, pos, dim, ctx_rows, ctx->d_err);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, kv_append_kernel, grid, dim3(256), 0, static_cast<__half*>(cache), x, pos, dim, ctx_rows, ctx->d_err));
     return LV_OK;
 }
 
@@ -171,8 +182,7 @@ extern "C" int lv_copy_f32(lv_ctx* ctx, float* dst, const float* src, size_t cou
     LV_REQUIRE(dst && src, "null argument");
     if (count == 0) return LV_OK;
     const unsigned blocks = static_cast<unsigned>(std::min<size_t>((count + 255) / 256, 4096));
-    copy_kernel<<<blocks, 256, 0, ctx->stream>>>(dst, src, count);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, copy_kernel, dim3(blocks), dim3(256), 0, dst, src, count));
     return LV_OK;
 }
 
@@ -181,8 +191,7 @@ extern "C" int lv_add_f32(lv_ctx* ctx, float* a, const float* b, size_t count) {
     LV_REQUIRE(a && b, "null argument");
     if (count == 0) return LV_OK;
     const unsigned blocks = static_cast<unsigned>(std::min<size_t>((count + 255) / 256, 4096));
-    add_kernel<<<blocks, 256, 0, ctx->stream>>>(a, b, count);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, add_kernel, dim3(blocks), dim3(256), 0, a, b, count));
     return LV_OK;
 }
 
@@ -192,15 +201,13 @@ extern "C" int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int w
     LV_REQUIRE(out && table && token_ids && n && vocab, "bad dequant arguments");
     LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0, "unsupported table type");
     LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
-    dequant_rows_kernel<<<n, 256, 0, ctx->stream>>>(out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, dequant_rows_kernel, dim3(n), dim3(256), 0, out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err));
     return LV_OK;
 }
 
 extern "C" int lv_argmax_f32(lv_ctx* ctx, uint32_t* out_index, const float* v, uint32_t n) {
     LV_ENTER(ctx);
     LV_REQUIRE(out_index && v && n, "bad argmax arguments");
-    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(out_index, v, n);
-    LV_CUDA(cudaGetLastError());
+    LV_CUDA(launch_pdl(ctx, argmax_kernel, dim3(1), dim3(1024), 0, out_index, v, n));
     return LV_OK;
 }
