@@ -45,6 +45,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--ring-mb", type=int, default=400)
+    ap.add_argument("--copies", type=int, default=0,
+                    help="override the ring length; 1 keeps the matrix resident in L2 and shows the kernel's compute ceiling")
     args = ap.parse_args()
 
     import numpy as np
@@ -68,7 +70,7 @@ def main():
             slab = qn.quantize((rng.standard_normal((slab_rows, cols)) * 0.02).astype(np.float32), wtype)
             host = np.tile(slab, -(-rows // slab_rows))[: rows * rb]
             mat_bytes = rows * rb
-            copies = max(3, int(args.ring_mb * 1e6 // (nmat * mat_bytes)) + 1)
+            copies = args.copies if args.copies > 0 else max(3, int(args.ring_mb * 1e6 // (nmat * mat_bytes)) + 1)
             ring = gpu.alloc(copies * nmat * mat_bytes)
             for i in range(copies * nmat):
                 pkg.check(lib.lv_upload(h, pkg.offset(ring, i * mat_bytes), host.ctypes.data_as(C.c_void_p), mat_bytes))
