@@ -174,6 +174,27 @@ int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const void* k_ca
                        const uint32_t* pos, const float* rope_table, void* scratch, uint32_t heads, uint32_t rot,
                        uint32_t max_ctx, uint32_t batch);
 
+/* Same computation as lv_attention_fused for callers that cannot allocate
+ * device memory at the point where they need attention -- code that runs
+ * inside a stream capture or behind a host that hands out no allocator, an
+ * embedder whose memory budget was fixed at start-up, a plug-in that is only
+ * given input and output buffers.  The chunk partials live in a buffer built
+ * into the library image (lv_attention_static_scratch_limit() bytes, 1 MiB,
+ * present on every GPU that loads the library until the process exits), so
+ * the call performs no cudaMalloc/cudaFree and calls nothing that allocates.
+ * Shapes whose scratch (lv_attention_scratch_bytes) exceeds that limit are
+ * rejected with LV_ERR_BAD_ARGUMENTS: 7B and 13B geometry at 2048 rows fit
+ * with batch 1.  The first call on a device looks up the buffer's device
+ * address; make that call before any stream capture.  All calls on a device
+ * share the one buffer: calls that overlap on the GPU (different streams or
+ * contexts) race; calls on one stream are safe.  Stale contents of earlier
+ * calls are harmless (the arrival counters are cleared by each call).
+ * No counterpart in the reference. */
+size_t lv_attention_static_scratch_limit(void);
+int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q, const void* k_cache, const void* v_cache,
+                              const uint32_t* pos, const float* rope_table, uint32_t heads, uint32_t rot,
+                              uint32_t max_ctx, uint32_t batch);
+
 /* normalize + matmul_silu_ff (llava_layer.cpp:68-69) in one launch. */
 int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const float* x,
                          const float* norm_w, uint32_t ff, uint32_t dim, uint32_t batch);

@@ -68,6 +68,8 @@ KERNEL_API = {
     "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32]),
     "lv_attention_scratch_bytes": (_sz, [_u32, _u32, _u32, _u32]),
     "lv_attention_fused": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
+    "lv_attention_static_scratch_limit": (_sz, []),
+    "lv_attention_fused_static": (_int, [_p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_norm_gate_up_silu": (_int, [_p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_norm_gemv": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
 }

@@ -8,6 +8,8 @@
 // host builds once in double precision.
 #include <math.h>
 
+#include <mutex>
+#include <string>
 #include <vector>
 
 #include "common.cuh"
@@ -209,6 +211,29 @@ __global__ void __launch_bounds__(kAttnThreads) attention_fused_kernel(float* __
 
 int attention_configure(lv_ctx*) { return LV_OK; }
 
+// Scratch of lv_attention_fused_static.  It lives in the library image: every GPU that loads
+// the library holds these bytes until the process exits, whether or not the entry point is used.
+constexpr size_t kStaticScratchBytes = size_t(1) << 20;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+// In host code the name above is only a handle for the symbol, not an address a kernel can
+// use; the device address is looked up once per device, with that device current.
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for(lv_ctx* ctx, void** out) {
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(LV_ERR_BAD_ARGUMENTS, "device index out of range");
+    std::lock_guard<std::mutex> guard(g_static_scratch_mutex);
+    if (g_static_scratch_addr[ctx->device] == nullptr) {
+        void* p = nullptr;
+        LV_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));      // cudaSetDevice(ctx->device) was done by LV_ENTER
+        g_static_scratch_addr[ctx->device] = p;
+    }
+    *out = g_static_scratch_addr[ctx->device];
+    return LV_OK;
+}
+
 }  // namespace lv
 
 using namespace lv;
@@ -284,6 +309,33 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     const uint32_t nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
+    dim3 grid(heads, nchunks, batch);
+    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kAttnThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                       static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                       1.0f / sqrtf(static_cast<float>(rot))));
+    return LV_OK;
+}
+
+extern "C" size_t lv_attention_static_scratch_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q, const void* k_cache, const void* v_cache,
+                                         const uint32_t* pos, const float* rope_table, uint32_t heads, uint32_t rot,
+                                         uint32_t max_ctx, uint32_t batch) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && q && k_cache && v_cache && pos && rope_table, "null argument");
+    if (int rc = check_attn_shape(max_ctx, heads, rot, batch)) return rc;
+    const size_t need = lv_attention_scratch_bytes(heads, rot, max_ctx, batch);
+    if (need == 0 || need > kStaticScratchBytes)
+        return fail(LV_ERR_BAD_ARGUMENTS, "lv_attention_fused_static: heads x context x batch needs " + std::to_string(need) +
+                                              " bytes of scratch, the built-in buffer holds " + std::to_string(kStaticScratchBytes) +
+                                              "; use lv_attention_fused with caller-provided scratch");
+    void* scratch = nullptr;
+    if (int rc = static_scratch_for(ctx, &scratch)) return rc;
+    const uint32_t nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+    float* partial = static_cast<float*>(scratch);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
+    // the buffer keeps whatever the last call left; only the arrival counters must start at zero
+    LV_CUDA(cudaMemsetAsync(counters, 0, size_t(batch) * heads * sizeof(uint32_t), ctx->stream));
     dim3 grid(heads, nchunks, batch);
     LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kAttnThreads), 0, out, q, static_cast<const __half*>(k_cache),
                        static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
