@@ -278,18 +278,39 @@ def main():
         raise SystemExit("prompt + warm-up + steps exceeds the 2048-token context of the reference")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); got WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    nccl_id = None
+    klib = pkg.load_kernels()
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        raise SystemExit("tensor-parallel decode is not wired into bench.py yet")
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            pkg.check(klib.lv_comm_unique_id(buf))
+            ident = torch.tensor(list(buf), dtype=torch.uint8, device="cuda")
+        dist.broadcast(ident, 0)
+        nccl_id = bytes(ident.cpu().tolist())
 
-    torch.cuda.set_device(local_rank)
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(seconds):
+        if dist is None:
+            return seconds
+        t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     path = ensure_model(pkg, args.workload, w, rank, world)
+    barrier()
     t0 = time.time()
-    ctx = pkg.HostContext(path, local_rank)
-    print(f"[bench] model on device in {time.time() - t0:.1f} s", file=sys.stderr)
+    ctx = pkg.HostContext(path, local_rank, rank, world, nccl_id)
+    print(f"[bench] rank {rank}: model on device in {time.time() - t0:.1f} s", file=sys.stderr)
     lv = C.c_void_p(ctx.lib.llava_context_lv(ctx.handle))
-    klib = pkg.load_kernels()
     stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=local_rank)
 
     def fresh_session():
@@ -308,13 +329,15 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     pkg.check(klib.lv_stream_sync(lv, 0))
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     s.enqueue_greedy_on_device(args.steps)
     e1.record(stream)
     toks_dev = s.collect_greedy_on_device()
     pkg.check(klib.lv_stream_sync(lv, 0))
-    sec_dev = e0.elapsed_time(e1) * 1e-3
+    barrier()
+    sec_dev = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
     s.close()
 
     # ---- end to end through the session API: token id in, argmax out, host in the loop -------
@@ -322,6 +345,7 @@ def main():
     for _ in range(args.warmup):
         s.push_token(s.predict_next_token())
     pkg.check(klib.lv_stream_sync(lv, 0))
+    barrier()
     toks_e2e = []
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -329,7 +353,8 @@ def main():
         tok = s.finish_next_token_prediction()          # D2H: the argmax (pinned, 4 B)
         toks_e2e.append(tok)
         s.push_token(tok)
-    sec_e2e = time.perf_counter() - t0
+    sec_e2e = max_over_ranks(time.perf_counter() - t0)
+    barrier()
     clocks = sampler.stop()
     s.close()
     if toks_e2e != toks_dev:
@@ -337,20 +362,29 @@ def main():
 
     # ---- roofline of the dominant kernel ---------------------------------------------------
     peak, peak_kind = measured_peaks()
-    k_sec, k_bytes = time_dominant_kernel(pkg, lv, dim, ff, w["wtype"], stream, torch)
+    k_sec, k_bytes = time_dominant_kernel(pkg, lv, dim, ff // world, w["wtype"], stream, torch)
     first_pos = n_prompt + 1 + args.warmup               # cache rows already filled when the timed steps start
     mean_pos = first_pos + (args.steps - 1) / 2
     bytes_per_token = weight_bytes_per_token(dim, ff, n_layers, 32000, w["wtype"]) + kv_bytes_per_token(dim, n_layers, mean_pos)
     tps = args.steps / sec_dev
     achieved = k_bytes / k_sec / 1e9
+    peak_all = peak * world                               # aggregate bandwidth of the N GPUs for the whole step
     roofline = {"bound": "hbm", "kernel": "gemv_kernel<q4_0, SILU> (norm + gate/up + SiLU, 11008x4096 pair)" if w["wtype"] == 2
                 else "gemv_kernel<q8_0, SILU>", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": f"of {peak_kind}", "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
+                "peak_source": f"of {peak_kind}",
+                # dram__bytes_read + dram__bytes_write of one launch of this kernel at this shape (ncu capture summarised
+                # in profiles/gemv_silu_q4_0_11008x4096.md); no capture exists for the other shapes
+                "traffic": 50793728 if (w["wtype"] == 2 and dim == 4096 and world == 1) else None,
+                "algorithmic_bytes_per_launch": k_bytes,
                 "whole_step": {"bytes_per_token": bytes_per_token, "achieved": bytes_per_token * tps / 1e9,
-                               "frac": bytes_per_token * tps / 1e9 / peak}}
+                               "aggregate_peak": peak_all, "frac": bytes_per_token * tps / 1e9 / peak_all}}
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if rank != 0:
+        ctx.close()
+        barrier()
+        return
+    if not args.no_cpu_baseline and world == 1:
         ctx.close()
         ctx = None
         v, timed, threads = cpu_oracle_tokens_per_s(path, 12, 20.0)
@@ -359,7 +393,7 @@ def main():
     if ctx is not None:
         ctx.close()
 
-    launches_per_token = 1 + 5 * n_layers + 3
+    launches_per_token = 1 + (5 if world == 1 else 7) * n_layers + 3    # TP adds two residual adds per layer (NCCL's kernels not counted)
     line = {
         "metric": "decode tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec_dev * 1e3 / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -373,6 +407,7 @@ def main():
         "gpu_launches": launches_per_token * args.steps, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
+    barrier()
 
 
 if __name__ == "__main__":

@@ -42,6 +42,15 @@ int      llava_dequantize(const void* in, int type, uint32_t model_version, floa
 
 /* ---- llava_context (llava_context.h:21-42) */
 void*    llava_context_open(const char* model_path, int device);   /* NULL on failure */
+/* tensor-parallel: this process is rank `rank` of `n_ranks`, one GPU each; nccl_id = the 128 bytes
+ * of lv_comm_unique_id made by rank 0 (ignored when n_ranks == 1) */
+void*    llava_context_open_sharded(const char* model_path, int device, uint32_t rank, uint32_t n_ranks,
+                                    const uint8_t* nccl_id);
+/* shard geometry and packing (host/tp_shard.h): how = 1 rows, 2 columns */
+int      llava_tp_shape(int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank, uint32_t n_ranks,
+                        uint32_t* out_rows, uint32_t* out_cols, uint32_t* out_cols_used, uint64_t* out_bytes);
+int      llava_tp_pack(const uint8_t* src, int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank,
+                       uint32_t n_ranks, uint8_t* dst);
 void     llava_context_close(void* ctx);
 void*    llava_context_lv(void* ctx);                               /* the lv_ctx* behind it */
 int      llava_context_run(int argc, char** argv);                  /* the command-line tool */

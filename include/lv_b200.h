@@ -158,10 +158,12 @@ int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uin
 /* ---- fused forms used by the decode graph -------------------------------- */
 
 /* normalize + matmul wk, wq, wv + two kv_copy (llava_layer.cpp:53-58) in one
- * launch: K and V rows go straight into the f16 caches at row *pos + z. */
+ * launch: K and V rows go straight into the f16 caches at row *pos + z.
+ * rows = output features of each of the three matrices (dim, or dim / n_ranks
+ * for a row shard); q_out is f32 [batch][rows], the caches f16 [ctx_rows][rows]. */
 int lv_norm_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq, const void* wk,
                          const void* wv, int wtype, const float* x, const float* norm_w, const uint32_t* pos,
-                         uint32_t dim, uint32_t batch, uint32_t ctx_rows);
+                         uint32_t rows, uint32_t dim, uint32_t batch, uint32_t ctx_rows);
 
 /* Bytes of scratch lv_attention_fused needs for the given shape. */
 size_t lv_attention_scratch_bytes(uint32_t heads, uint32_t rot, uint32_t max_ctx, uint32_t batch);
@@ -202,6 +204,21 @@ int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1
 /* normalize + output matmul (llava_command_buffer.cpp:38-39) in one launch. */
 int lv_norm_gemv(lv_ctx* ctx, float* out, const void* W, int wtype, const float* x, const float* norm_w,
                  uint32_t rows, uint32_t cols, uint32_t batch);
+
+/* ---- multi-GPU: one process per GPU, one communicator per context.  The
+ *      reference is single-device (llava_context.cpp:264-279 takes one queue of
+ *      one device); these entry points add the exchange step of the
+ *      tensor-parallel decoder: an fp32 sum all-reduce of `dim` floats after the
+ *      wo and after the w2 product (the TP forms of matmul_add_inplace,
+ *      llava_layer.cpp:67,73).  NCCL is loaded at run time. ------------------- */
+/* rank 0 makes the 128-byte id and hands it to the other ranks by any means */
+int lv_comm_unique_id(uint8_t* out128);
+int lv_comm_init_rank(lv_ctx* ctx, const uint8_t* id128, int n_ranks, int rank);
+/* in place, on the context's stream (capturable); a no-op without a communicator */
+int lv_allreduce_f32(lv_ctx* ctx, float* buf, size_t count);
+int lv_comm_status(lv_ctx* ctx);     /* LV_ERR_COMM if NCCL reported an asynchronous error */
+int lv_comm_abort(lv_ctx* ctx);
+int lv_comm_destroy(lv_ctx* ctx);
 
 #ifdef __cplusplus
 }

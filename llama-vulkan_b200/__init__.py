@@ -65,7 +65,13 @@ KERNEL_API = {
     "lv_dequant_rows": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_argmax_f32": (_int, [_p, _p, _p, _u32]),
     "lv_decode_advance": (_int, [_p, _p, _p, _p, _u32, _u32]),
-    "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32]),
+    "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32, _u32]),
+    "lv_comm_unique_id": (_int, [_p]),
+    "lv_comm_init_rank": (_int, [_p, _p, _int, _int]),
+    "lv_allreduce_f32": (_int, [_p, _p, _sz]),
+    "lv_comm_status": (_int, [_p]),
+    "lv_comm_abort": (_int, [_p]),
+    "lv_comm_destroy": (_int, [_p]),
     "lv_attention_scratch_bytes": (_sz, [_u32, _u32, _u32, _u32]),
     "lv_attention_fused": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_attention_static_scratch_limit": (_sz, []),
@@ -197,6 +203,9 @@ HOST_API = {
     "ggml_file_token": (_u32, [_p, _u32, C.c_char_p, _u32, _f32p]),
     "llava_dequantize": (_int, [_p, _int, _u32, _p, _u32]),
     "llava_context_open": (_p, [C.c_char_p, _int]),
+    "llava_context_open_sharded": (_p, [C.c_char_p, _int, _u32, _u32, _p]),
+    "llava_tp_shape": (_int, [_int, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _u32p, C.POINTER(_u64)]),
+    "llava_tp_pack": (_int, [_p, _int, _u32, _u32, _u32, _u32, _u32, _p]),
     "llava_context_close": (None, [_p]),
     "llava_context_lv": (_p, [_p]),
     "llava_context_run": (_int, [_int, C.POINTER(C.c_char_p)]),
@@ -309,9 +318,13 @@ class ModelFile:
 class HostContext:
     """llava_context: model + device + uploaded layers."""
 
-    def __init__(self, model_path, device=0):
+    def __init__(self, model_path, device=0, rank=0, n_ranks=1, nccl_id=None):
         self.lib = load_host()
-        self.handle = self.lib.llava_context_open(os.fsencode(model_path), device)
+        if n_ranks == 1:
+            self.handle = self.lib.llava_context_open(os.fsencode(model_path), device)
+        else:
+            buf = (C.c_uint8 * 128).from_buffer_copy(bytes(nccl_id))
+            self.handle = self.lib.llava_context_open_sharded(os.fsencode(model_path), device, rank, n_ranks, buf)
         if not self.handle:
             raise RuntimeError(f"llava_context::open({model_path}) failed: "
                                + (load_kernels().lv_last_error_string() or b"").decode("utf-8", "replace"))

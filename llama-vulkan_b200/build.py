@@ -53,7 +53,7 @@ def build_kernels(force=False, verbose_ptxas=False):
     flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
     if verbose_ptxas:
         flags += ["-Xptxas", "-v"]
-    _run([_nvcc(), "-shared", "-o", out] + flags + cu + ["-lcudart"])
+    _run([_nvcc(), "-shared", "-o", out] + flags + cu + ["-lcudart", "-ldl"])
     return out
 
 

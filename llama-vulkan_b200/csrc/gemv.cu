@@ -295,18 +295,19 @@ extern "C" int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, con
 
 extern "C" int lv_norm_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq,
                                     const void* wk, const void* wv, int wtype, const float* x, const float* norm_w,
-                                    const uint32_t* pos, uint32_t dim, uint32_t batch, uint32_t ctx_rows) {
+                                    const uint32_t* pos, uint32_t rows_each, uint32_t dim, uint32_t batch,
+                                    uint32_t ctx_rows) {
     LV_ENTER(ctx);
     LV_REQUIRE(q_out && k_cache && v_cache && x && pos, "null argument");
     LV_REQUIRE(ctx_rows >= batch, "cache smaller than the batch");
     GemvParams p{};
     const void* ws[3] = {wk, wq, wv};
-    const uint32_t rows[3] = {dim, dim, dim};
+    const uint32_t rows[3] = {rows_each, rows_each, rows_each};
     if (int rc = check_matrix_args(ws, 3, wtype, dim, 4, rows, batch, &p.row_bytes, x, norm_w)) return rc;
     // same order as the reference records them: K, Q, V (llava_layer.cpp:54-56)
-    p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, k_cache, dim, EPI_STORE_F16_AT_POS};
-    p.m[1] = {static_cast<const uint8_t*>(wq), nullptr, q_out, dim, EPI_STORE};
-    p.m[2] = {static_cast<const uint8_t*>(wv), nullptr, v_cache, dim, EPI_STORE_F16_AT_POS};
+    p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, k_cache, rows_each, EPI_STORE_F16_AT_POS};
+    p.m[1] = {static_cast<const uint8_t*>(wq), nullptr, q_out, rows_each, EPI_STORE};
+    p.m[2] = {static_cast<const uint8_t*>(wv), nullptr, v_cache, rows_each, EPI_STORE_F16_AT_POS};
     p.n_mat = 3;
     p.x = x;
     p.norm_w = norm_w;

@@ -11,6 +11,7 @@
 #include "llava_layer_session_data.h"
 #include "llava_session.h"
 #include "synth_ggjt.h"
+#include "tp_shard.h"
 
 namespace {
 synth_config make_cfg(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab, int wtype) {
@@ -119,6 +120,28 @@ void* llava_context_open(const char* model_path, int device) {
         return nullptr;
     }
     return c;
+}
+
+void* llava_context_open_sharded(const char* model_path, int device, uint32_t rank, uint32_t n_ranks, const uint8_t* nccl_id) {
+    auto* c = new llava_context();
+    if (!c->open_sharded(model_path, device, rank, n_ranks, nccl_id)) {
+        delete c;
+        return nullptr;
+    }
+    return c;
+}
+
+int llava_tp_shape(int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank, uint32_t n_ranks, uint32_t* out_rows,
+                   uint32_t* out_cols, uint32_t* out_cols_used, uint64_t* out_bytes) {
+    const tp_shard_shape s = tp_shape(static_cast<ggml_value_type>(type), rows, cols, static_cast<tp_split>(how), rank, n_ranks);
+    if (!s.valid) return 0;
+    *out_rows = s.rows; *out_cols = s.cols; *out_cols_used = s.cols_used; *out_bytes = s.bytes;
+    return 1;
+}
+
+int llava_tp_pack(const uint8_t* src, int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank, uint32_t n_ranks,
+                  uint8_t* dst) {
+    return tp_pack(src, static_cast<ggml_value_type>(type), rows, cols, static_cast<tp_split>(how), rank, n_ranks, dst) ? 1 : 0;
 }
 
 void llava_context_close(void* ctx) { delete static_cast<llava_context*>(ctx); }

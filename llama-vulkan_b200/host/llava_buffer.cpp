@@ -18,7 +18,8 @@ llava_buffer::llava_buffer(llava_context* _context, ggml_value_type _type, u32 s
                            llava_device_memory* _device_memory, string _name)
     : context(_context), pretty_name(std::move(_name)), type(_type), shape(shape1, shape2),
       device_memory_is_shared(_device_memory != nullptr),
-      device_memory(_device_memory ? _device_memory : new llava_device_memory(_context)), model_version(0) {
+      device_memory(_device_memory ? _device_memory : new llava_device_memory(_context)), model_version(0),
+      file_shape(shape1, shape2), used_cols(shape2) {
     device_memory->register_llava_buffer(this);
     bytes = size_t(shape1) * shape2 * (type == ggml_value_type::f32 ? 4 : 2);
     offset = device_memory->register_buffer(kBufferAlignment, bytes);
@@ -29,10 +30,29 @@ llava_buffer::llava_buffer(llava_context* _context, const ggml_data_descriptor& 
     : context(_context), backing_buffer_name(table.name), type(table.ftype), shape(table.shape1, table.shape2),
       device_memory_is_shared(_device_memory != nullptr),
       device_memory(_device_memory ? _device_memory : new llava_device_memory(_context)),
-      model_version(table.model_version) {
+      model_version(table.model_version), file_shape(table.shape1, table.shape2), used_cols(table.shape2) {
     device_memory->register_llava_buffer(this);
     bytes = table.size;
     offset = device_memory->register_buffer(kBufferAlignment, bytes);
+    if (!device_memory_is_shared) device_memory->freeze();
+}
+
+static std::pair<u32, u32> local_shape(const ggml_data_descriptor& t, tp_split how, u32 rank, u32 n) {
+    const tp_shard_shape s = tp_shape(t.ftype, t.shape1, t.shape2, how, rank, n);
+    return s.valid ? std::make_pair(s.rows, s.cols) : std::make_pair(0u, 0u);
+}
+
+llava_buffer::llava_buffer(llava_context* _context, const ggml_data_descriptor& table, llava_device_memory* _device_memory,
+                           tp_split how, u32 rank, u32 n_ranks)
+    : context(_context), backing_buffer_name(table.name), type(table.ftype), shape(local_shape(table, how, rank, n_ranks)),
+      device_memory_is_shared(_device_memory != nullptr),
+      device_memory(_device_memory ? _device_memory : new llava_device_memory(_context)),
+      model_version(table.model_version), split(how), tp_rank(rank), tp_ranks(n_ranks), file_shape(table.shape1, table.shape2) {
+    device_memory->register_llava_buffer(this);
+    const tp_shard_shape s = tp_shape(table.ftype, table.shape1, table.shape2, how, rank, n_ranks);
+    bytes = s.bytes;
+    used_cols = s.cols_used;
+    offset = device_memory->register_buffer(kBufferAlignment, bytes ? bytes : 16);
     if (!device_memory_is_shared) device_memory->freeze();
 }
 
@@ -119,7 +139,13 @@ bool llava_buffer::load_to_gpu() {
     if (!is_allocated()) return false;
     const ggml_file* model = context->get_model();
     const ggml_data_descriptor& table = model->get_buffer_descriptor(backing_buffer_name);
-    return context->upload_from_host(device_ptr(), model->data() + table.offset, table.size);
+    if (split == tp_split::none) return context->upload_from_host(device_ptr(), model->data() + table.offset, table.size);
+    if (bytes == 0) return false;                      // the tensor cannot be split this way
+    if (split == tp_split::rows)                       // a contiguous range of the file tensor
+        return context->upload_from_host(device_ptr(), model->data() + table.offset + size_t(tp_rank) * bytes, bytes);
+    std::vector<u8> packed(bytes);
+    return tp_pack(model->data() + table.offset, type, file_shape.first, file_shape.second, split, tp_rank, tp_ranks, packed.data()) &&
+           context->upload_from_host(device_ptr(), packed.data(), bytes);
 }
 
 void llava_buffer::dump_raw(int out_fd, const string& name) {

@@ -9,6 +9,7 @@
 #include <utility>
 
 #include "ggml_file.h"
+#include "tp_shard.h"
 #include "types.h"
 
 class llava_buffer {
@@ -18,6 +19,9 @@ public:
                  llava_device_memory* device_memory = nullptr, std::string name = "");
     // tensor of the model file (shape1 rows of shape2 columns)
     llava_buffer(llava_context* context, const ggml_data_descriptor& table, llava_device_memory* device_memory = nullptr);
+    // shard of a file matrix for rank `rank` of `n_ranks` (see tp_shard.h); shape = local shape
+    llava_buffer(llava_context* context, const ggml_data_descriptor& table, llava_device_memory* device_memory,
+                 tp_split how, u32 rank, u32 n_ranks);
     ~llava_buffer();
     llava_buffer(const llava_buffer&) = delete;
     llava_buffer& operator=(const llava_buffer&) = delete;
@@ -47,8 +51,13 @@ public:
     const bool device_memory_is_shared;
     llava_device_memory* const device_memory;
     const u32 model_version;
+    const tp_split split = tp_split::none;
+    const u32 tp_rank = 0, tp_ranks = 1;
+    const std::pair<u32, u32> file_shape;      // shape of the whole tensor in the file
+    u32 cols_used() const { return used_cols; }   // local columns that carry weights (< shape.second when padded)
 
 private:
+    u32 used_cols = 0;
     size_t bytes = 0;
     size_t offset = 0;
 };

@@ -155,27 +155,38 @@ void llava_command_buffer::perform_kqv_matching(llava_buffer* v_out, llava_buffe
 void llava_command_buffer::norm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq,
                                              llava_buffer* wk, llava_buffer* wv, llava_buffer* inbuf, llava_buffer* norm_weights) {
     const u32 dim = session->model->get_header().dim;
-    if (!expect(wq->shape == wk->shape && wq->shape == wv->shape && wq->shape.first == dim && wq->shape.second == dim &&
-                inbuf->shape.first == dim && k_cache->shape.second == dim && v_cache->shape.second == dim, "qkv shapes")) return;
+    if (!expect(wq->shape == wk->shape && wq->shape == wv->shape && wq->shape.second == dim && inbuf->shape.first == dim &&
+                q_out->shape.first == wq->shape.first && k_cache->shape.second == wq->shape.first &&
+                v_cache->shape.second == wq->shape.first, "qkv shapes")) return;
     note(lv_norm_qkv_kvappend(lv(), f32(q_out), k_cache->device_ptr(), v_cache->device_ptr(), wq->device_ptr(), wk->device_ptr(),
                               wv->device_ptr(), int(wq->type), f32(inbuf), f32(norm_weights),
-                              static_cast<u32*>(session->config_buffer->device_ptr()), dim, batch_size, k_cache->shape.first));
+                              static_cast<u32*>(session->config_buffer->device_ptr()), wq->shape.first, dim, batch_size,
+                              k_cache->shape.first));
 }
 
 void llava_command_buffer::attention_fused(llava_buffer* v_out, llava_buffer* query, llava_buffer* k_cache, llava_buffer* v_cache) {
     const ggml_header& h = session->model->get_header();
-    if (!expect(v_out->shape.first == h.dim && query->shape.first == h.dim, "attention shapes")) return;
+    const u32 local_heads = h.n_heads / session->ctx->tp_size();
+    if (!expect(query->shape.first == local_heads * h.rot && v_out->shape.first >= local_heads * h.rot &&
+                k_cache->shape.second == local_heads * h.rot, "attention shapes")) return;
     // the grid covers the current backlog only; a step is re-recorded when the backlog
     // doubles, like the reference re-specialises its pipelines (llava_session.cpp:303-327)
     note(lv_attention_fused(lv(), f32(v_out), f32(query), k_cache->device_ptr(), v_cache->device_ptr(),
                             static_cast<u32*>(session->config_buffer->device_ptr()), session->ctx->rope_table,
-                            session->attn_scratch->device_ptr(), h.n_heads, h.rot, backlog_size, batch_size));
+                            session->attn_scratch->device_ptr(), local_heads, h.rot, backlog_size, batch_size));
+}
+
+void llava_command_buffer::allreduce_add(llava_buffer* residual, llava_buffer* partial) {
+    const u32 dim = session->model->get_header().dim;
+    if (!expect(residual->shape.first == dim && partial->shape.first == dim, "allreduce shapes")) return;
+    note(lv_allreduce_f32(lv(), f32(partial), size_t(dim) * batch_size));
+    note(lv_add_f32(lv(), f32(residual), f32(partial), size_t(dim) * batch_size));
 }
 
 void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf,
                                                llava_buffer* norm_weights) {
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&
-                outbuf->shape.first == w3->shape.first, "norm_matmul_silu_ff shapes")) return;
+                outbuf->shape.first >= w3->shape.first, "norm_matmul_silu_ff shapes")) return;
     note(lv_norm_gate_up_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), f32(inbuf), f32(norm_weights),
                               w3->shape.first, w3->shape.second, batch_size));
 }

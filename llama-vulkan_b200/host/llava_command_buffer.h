@@ -39,6 +39,9 @@ public:
     void norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3_matrix, llava_buffer* w1_matrix, llava_buffer* inbuf,
                              llava_buffer* norm_weights);
 
+    // tensor-parallel: partial <- sum over ranks of partial; residual += partial
+    void allreduce_add(llava_buffer* residual, llava_buffer* partial);
+
     int status() const { return first_error; }
 
     llava_session* const session;

@@ -36,6 +36,8 @@ void llava_context::close_all() {
     shared_memory = nullptr;
     if (lv_context) lv_ctx_destroy(lv_context);
     lv_context = nullptr;
+    rank_ = 0;
+    n_ranks_ = 1;
     delete model;
     model = nullptr;
     if (sigfd >= 0) ::close(sigfd);
@@ -46,11 +48,31 @@ bool llava_context::upload_from_host(void* device_dst, const void* host_src, siz
     return lv_upload(lv_context, device_dst, host_src, bytes) == LV_OK;
 }
 
+bool llava_context::open_sharded(const string& model_path, int device, u32 rank, u32 n_ranks, const u8* nccl_id) {
+    if (n_ranks == 0 || rank >= n_ranks || (n_ranks > 1 && nccl_id == nullptr)) return false;
+    rank_ = rank;
+    n_ranks_ = n_ranks;
+    if (!open(model_path, device)) return false;
+    if (n_ranks > 1 && lv_comm_init_rank(lv_context, nccl_id, int(n_ranks), int(rank)) != LV_OK) {
+        cerr << "[!] cannot create the communicator: " << lv_last_error_string() << endl;
+        return false;
+    }
+    return true;
+}
+
 bool llava_context::open(const string& model_path, int device) {
+    const u32 keep_rank = rank_, keep_ranks = n_ranks_;
     close_all();
+    rank_ = keep_rank;
+    n_ranks_ = keep_ranks;
     model = new ggml_file(model_path.c_str());
     if (!model->is_open()) return false;
     const ggml_header& h = model->get_header();
+    if (h.n_heads % n_ranks_ != 0 || (h.dim / 32) % n_ranks_ != 0 || (model->get_ff_size() / 32) % n_ranks_ != 0 ||
+        model->get_ff_size() % (2 * n_ranks_) != 0) {
+        cerr << "[!] heads, dim and ff must divide evenly over " << n_ranks_ << " ranks" << endl;
+        return false;
+    }
     // the kernels are specialised for the reference's geometries (llava_session.cpp:357-375:
     // dim 4096 or 5120, ff 11008 or 13824) and for heads of 128
     if (h.rot != 128 || h.dim % 256 != 0 || model->get_ff_size() % 256 != 0) {

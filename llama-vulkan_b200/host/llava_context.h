@@ -24,6 +24,11 @@ public:
     int run(int argc, char** argv);
     // Opens the model, creates the device context and uploads all layers.
     bool open(const std::string& model_path, int device = 0);
+    // Tensor-parallel open: this process is rank `rank` of `n_ranks` (one GPU each) and uploads
+    // only its shard of every layer.  nccl_id: the 128 bytes of lv_comm_unique_id made by rank 0.
+    bool open_sharded(const std::string& model_path, int device, u32 rank, u32 n_ranks, const u8* nccl_id);
+    u32 tp_rank() const { return rank_; }
+    u32 tp_size() const { return n_ranks_; }
 
     lv_ctx* lv() const { return lv_context; }
     const ggml_file* get_model() const { return model; }
@@ -53,6 +58,7 @@ private:
     std::vector<llava_layer*> layers;
     bool signal_debug = false;
     int sigfd = -1;
+    u32 rank_ = 0, n_ranks_ = 1;
 };
 
 #endif

@@ -16,24 +16,32 @@ llava_layer::llava_layer(llava_context* _context, u32 _layer_id) : layer_id(_lay
     const ggml_file* model = context->get_model();
     const string prefix = "layers." + to_string(layer_id) + ".";
     bool ok = true;
-    auto make = [&](const char* leaf) -> llava_buffer* {
+    const u32 rank = context->tp_rank(), n_ranks = context->tp_size();
+    auto make = [&](const char* leaf, tp_split how) -> llava_buffer* {
         const ggml_data_descriptor* d = model->find_buffer_descriptor(prefix + leaf);
         if (!d) {
             cerr << "[!] tensor " << prefix << leaf << " missing" << endl;
             ok = false;
             return nullptr;
         }
-        return new llava_buffer(context, *d, layer_allocation);
+        if (n_ranks == 1 || how == tp_split::none) return new llava_buffer(context, *d, layer_allocation);
+        auto* b = new llava_buffer(context, *d, layer_allocation, how, rank, n_ranks);
+        if (b->byte_size() == 0) {
+            cerr << "[!] tensor " << prefix << leaf << " cannot be split over " << n_ranks << " ranks" << endl;
+            ok = false;
+        }
+        return b;
     };
-    attention_wq = make("attention.wq");
-    attention_wk = make("attention.wk");
-    attention_wv = make("attention.wv");
-    attention_wo = make("attention.wo");
-    feed_forward_w1 = make("feed_forward.w1");
-    feed_forward_w2 = make("feed_forward.w2");
-    feed_forward_w3 = make("feed_forward.w3");
-    attention_norm = make("attention_norm");
-    ffn_norm = make("ffn_norm");
+    // Megatron-style split: output features of wq/wk/wv/w1/w3, input features of wo/w2
+    attention_wq = make("attention.wq", tp_split::rows);
+    attention_wk = make("attention.wk", tp_split::rows);
+    attention_wv = make("attention.wv", tp_split::rows);
+    attention_wo = make("attention.wo", tp_split::columns);
+    feed_forward_w1 = make("feed_forward.w1", tp_split::rows);
+    feed_forward_w2 = make("feed_forward.w2", tp_split::columns);
+    feed_forward_w3 = make("feed_forward.w3", tp_split::rows);
+    attention_norm = make("attention_norm", tp_split::none);
+    ffn_norm = make("ffn_norm", tp_split::none);
     if (ok) {
         // norms must be f32 vectors, matrices quantised with an f16 block scale (ggjt v3)
         for (llava_buffer* m : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2, feed_forward_w3})
@@ -73,9 +81,19 @@ llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_se
         cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
                                    attention_wv, x, attention_norm);
         cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);
-        cmd_buf->matmul_add_inplace(x, attention_wo, session->current_Vout);
-        cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, x, ffn_norm);
-        cmd_buf->matmul_add_inplace(x, feed_forward_w2, session->main_ff_result);
+        if (context->tp_size() == 1) {
+            cmd_buf->matmul_add_inplace(x, attention_wo, session->current_Vout);
+            cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, x, ffn_norm);
+            cmd_buf->matmul_add_inplace(x, feed_forward_w2, session->main_ff_result);
+        } else {
+            // every rank holds a column shard of wo and w2: partial products, summed over the
+            // ranks, then added to the (replicated) residual stream
+            cmd_buf->matmul(session->tp_partial, attention_wo, session->current_Vout);
+            cmd_buf->allreduce_add(x, session->tp_partial);
+            cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, x, ffn_norm);
+            cmd_buf->matmul(session->tp_partial, feed_forward_w2, session->main_ff_result);
+            cmd_buf->allreduce_add(x, session->tp_partial);
+        }
         return x;
     }
 

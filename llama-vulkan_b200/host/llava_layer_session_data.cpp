@@ -8,7 +8,7 @@
 using namespace std;
 
 llava_layer_session_data::llava_layer_session_data(llava_session* _session) : session(_session) {
-    const u32 dim = session->model->get_header().dim;
+    const u32 dim = session->model->get_header().dim / session->ctx->tp_size();     // this rank's heads
     // both caches for the maximum context, zero filled (the reference zero-fills and regrows
     // them as the backlog doubles, llava_layer_session_data.cpp:100-127)
     cache_allocation = new llava_device_memory(session->ctx);

@@ -64,23 +64,31 @@ bool llava_session::recreate_buffers() {
     reset_main_buffers();
     const ggml_header& h = model->get_header();
     const u32 dim = h.dim, ff = model->get_ff_size(), B = max_batch;
+    const u32 ranks = ctx->tp_size(), rank = ctx->tp_rank();
+    // per-rank sizes: heads (and with them Q, K, V, the attention output) and the FFN width are
+    // split; the inputs of the column-sharded wo and w2 are padded like their shards
+    const u32 local_dim = dim / ranks;
+    const auto Wt = ctx->output_w->type;
+    const u32 vout_len = ranks == 1 ? dim : tp_shape(Wt, dim, dim, tp_split::columns, rank, ranks).cols;
+    const u32 ff_len = ranks == 1 ? ff : tp_shape(Wt, dim, ff, tp_split::columns, rank, ranks).cols;
     const auto F = ggml_value_type::f32;
     main_buffer_memory = new llava_device_memory(ctx);
     llava_device_memory* m = main_buffer_memory;
     current_thought = new llava_buffer(ctx, F, dim, B, m);
     current_thought_sublayer = new llava_buffer(ctx, F, dim, B, m);
     current_thought_middle_normd = new llava_buffer(ctx, F, dim, B, m);
-    main_ff_result = new llava_buffer(ctx, F, ff, B, m);
-    current_Q = new llava_buffer(ctx, F, dim, B, m);
-    current_K = new llava_buffer(ctx, F, dim, B, m);
-    current_V = new llava_buffer(ctx, F, dim, B, m);
-    current_Vout = new llava_buffer(ctx, F, dim, B, m);
+    main_ff_result = new llava_buffer(ctx, F, ff_len, B, m);
+    current_Q = new llava_buffer(ctx, F, local_dim, B, m);
+    current_K = new llava_buffer(ctx, F, local_dim, B, m);
+    current_V = new llava_buffer(ctx, F, local_dim, B, m);
+    current_Vout = new llava_buffer(ctx, F, vout_len, B, m);
+    if (ranks > 1) tp_partial = new llava_buffer(ctx, F, dim, B, m);
     if (is_tracing_enabled()) main_attn_result = new llava_buffer(ctx, F, backlog_size, h.n_heads * B, m);
     config_buffer = new llava_buffer(ctx, F, 4, 1, m);
     output_probs = new llava_buffer(ctx, F, h.vocab_size, 1, m);
     token_log = new llava_buffer(ctx, F, max_backlog_size + kPinnedExtra, 1, m);
     argmax_result = new llava_buffer(ctx, F, 4, 1, m);
-    const size_t scratch = lv_attention_scratch_bytes(h.n_heads, h.rot, max_backlog_size, B);
+    const size_t scratch = lv_attention_scratch_bytes(h.n_heads / ranks, h.rot, max_backlog_size, B);
     if (scratch == 0) return false;
     attn_scratch = new llava_buffer(ctx, F, u32((scratch + 3) / 4), 1, m);
     if (!m->freeze() || !m->zero(0, m->get_size())) return false;
@@ -91,7 +99,7 @@ bool llava_session::recreate_buffers() {
 void llava_session::reset_main_buffers() {
     for (llava_buffer** b : {&current_thought, &current_thought_sublayer, &current_thought_middle_normd, &current_Q, &current_K,
                              &current_V, &current_Vout, &main_attn_result, &config_buffer, &output_probs, &main_ff_result,
-                             &token_log, &argmax_result, &attn_scratch}) {
+                             &token_log, &argmax_result, &attn_scratch, &tp_partial}) {
         delete *b;
         *b = nullptr;
     }
@@ -313,6 +321,7 @@ bool llava_session::set_backlog_size(u32 new_size) {
 
 bool llava_session::set_max_batch(u32 n) {
     if (n < 1 || n > max_batch_limit) return false;
+    if (n > 1 && ctx->tp_size() > 1) return false;        // sharded sessions evaluate token by token
     if (n == max_batch) return true;
     lv_stream_sync(ctx->lv(), 0);
     drop_command_buffers();
@@ -336,6 +345,7 @@ void llava_session::rewind(u32 n) {
 
 ReturnCode llava_session::set_options(u32 new_options) {
     if (options == new_options) return ReturnCode::ok;
+    if (new_options != 0 && ctx->tp_size() > 1) return ReturnCode::nok;    // tracing records whole-model buffers
     lv_stream_sync(ctx->lv(), 0);
     options = new_options;
     drop_command_buffers();
@@ -360,6 +370,7 @@ ReturnCode llava_session::save_frame(const string& path) {
 // File layout (llava_session.cpp:447-495): u32 n; u32 tokens[n]; then per layer the first n
 // rows of the K cache followed by the first n rows of the V cache, f16 [n][dim] each.
 ReturnCode llava_session::snapshot(const string& path) {
+    if (ctx->tp_size() > 1) return ReturnCode::nok;        // each rank holds a head slice of the caches
     if (!ensure_buffers_created()) return ReturnCode::nok;
     if (last_command_buffer) last_command_buffer->wait_idle();
     const u32 n = current_tokens_in_gpu, dim = model->get_header().dim;
@@ -379,6 +390,7 @@ ReturnCode llava_session::snapshot(const string& path) {
 }
 
 ReturnCode llava_session::restore(const string& path) {
+    if (ctx->tp_size() > 1) return ReturnCode::nok;
     if (!ensure_buffers_created()) return ReturnCode::nok;
     const int fd = ::open(path.c_str(), O_RDONLY);
     if (fd < 0) {

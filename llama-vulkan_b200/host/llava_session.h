@@ -100,6 +100,7 @@ private:
     llava_buffer* token_log = nullptr;
     llava_buffer* argmax_result = nullptr;
     llava_buffer* attn_scratch = nullptr;
+    llava_buffer* tp_partial = nullptr;           // tensor-parallel only: this rank's partial wo / w2 product
     std::vector<llava_layer_session_data*> layer_data;
 
     u32 batch_size = 0;           // batch of the step recorded last

@@ -265,7 +265,7 @@ def test_qkv_fused_writes_cache_rows_and_query(gpu, pkg):
     dkc, dvc = gpu.zeros(ctx_rows * DIM * 2), gpu.zeros(ctx_rows * DIM * 2)
     dq = gpu.alloc(batch * DIM * 4)
     pkg.check(gpu.lib.lv_norm_qkv_kvappend(gpu.handle, dq, dkc, dvc, gpu.upload(wq), gpu.upload(wk), gpu.upload(wv), qn.Q4_0,
-                                           gpu.upload(x), gpu.upload(nw), u32_dev(gpu, pos), DIM, batch, ctx_rows))
+                                           gpu.upload(x), gpu.upload(nw), u32_dev(gpu, pos), DIM, DIM, batch, ctx_rows))
     gpu.sync()
     gq = gpu.download(dq, np.float32, batch * DIM).reshape(batch, DIM)
     gk = gpu.download(dkc, np.uint16, ctx_rows * DIM).reshape(ctx_rows, DIM).view(np.float16).astype(np.float32)

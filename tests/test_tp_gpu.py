@@ -1,0 +1,101 @@
+"""Tensor-parallel decoding on 2 GPUs (one process per GPU, NCCL all-reduce after
+wo and w2) against the single-GPU path on the same 2-layer model: logits within
+the end-to-end tolerance, greedy tokens identical.  Skipped on a 1-GPU box."""
+import ctypes as C
+import os
+import queue
+
+import numpy as np
+import pytest
+
+from conftest import load_pkg
+
+pytestmark = pytest.mark.gpu
+
+N_PROMPT, N_DECODE = 8, 12
+
+
+def _device_count():
+    pkg = load_pkg()
+    n = C.c_int(0)
+    pkg.load_kernels().lv_device_count(C.byref(n))
+    return n.value
+
+
+def _prompt():
+    return [int(t) for t in np.random.default_rng(4321).integers(3, 32000, N_PROMPT)]
+
+
+def _decode(ctx):
+    s = ctx.session()
+    s.set_deterministic(True)
+    for t in _prompt():
+        assert s.push_token(t)
+    toks, logits = [], []
+    for _ in range(N_DECODE):
+        tok = s.predict_next_token()
+        assert tok != 0xFFFFFFFF
+        toks.append(tok)
+        logits.append(s.logits(32000))
+        s.push_token(tok)
+    assert not s.set_max_batch(4) or ctx_is_single(ctx)
+    s.close()
+    return toks, logits
+
+
+def ctx_is_single(ctx):
+    return getattr(ctx, "n_ranks", 1) == 1
+
+
+def _worker(rank, world, path, id_q, out_q):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    pkg = load_pkg()
+    klib = pkg.load_kernels()
+    if rank == 0:
+        buf = (C.c_uint8 * 128)()
+        pkg.check(klib.lv_comm_unique_id(buf))
+        for _ in range(world - 1):
+            id_q.put(bytes(buf))
+        ident = bytes(buf)
+    else:
+        ident = id_q.get(timeout=120)
+    ctx = pkg.HostContext(path, rank, rank, world, ident)
+    ctx.n_ranks = world
+    toks, logits = _decode(ctx)
+    ctx.close()
+    out_q.put((rank, toks, [l.tobytes() for l in logits]))
+
+
+def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path):
+    if _device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    path = str(tmp_path / "tiny.bin")
+    pkg.write_synthetic_model(path, "7b", n_layers=2)
+    ctx = pkg.HostContext(path, 0)
+    want_toks, want_logits = _decode(ctx)
+    ctx.close()
+    mpc = mp.get_context("spawn")
+    id_q, out_q = mpc.Queue(), mpc.Queue()
+    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(2):
+        try:
+            r, toks, logits = out_q.get(timeout=300)
+        except queue.Empty:
+            for p in procs:
+                p.kill()
+            raise AssertionError("a rank did not finish")
+        results[r] = (toks, [np.frombuffer(b, np.float32) for b in logits])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results[0][0] == results[1][0] == want_toks
+    for step in range(N_DECODE):
+        for r in (0, 1):
+            got, want = results[r][1][step].astype(np.float64), want_logits[step].astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-2
+            assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+        assert np.array_equal(results[0][1][step], results[1][1][step])      # every rank holds the same logits
