@@ -84,6 +84,24 @@ uint32_t llava_session_get_tokens_in_gpu(void* session);
 /* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
 int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
 
+/* ---- lsrv::session_wrapper (server/session_wrapper.h:17-23): one thread and one session per
+ *      served session, driven by orders (opcodes of server/types.h:50-73).  The owner created
+ *      here plays the reference's llava_server: it collects the outbound packets. */
+void*    llava_wrapper_owner_create(void* ctx);
+void     llava_wrapper_owner_destroy(void* owner);
+uint32_t llava_wrapper_owner_dead_sessions(void* owner);
+/* next outbound item (kind 0: packet to client `who` answering `request`; 1: broadcast of session
+ * `who`); returns 0 when nothing arrived within timeout_ms */
+int      llava_wrapper_owner_pop(void* owner, int timeout_ms, uint32_t* kind, uint32_t* who, uint32_t* opcode,
+                                 uint32_t* request, uint8_t* payload, uint32_t cap, uint32_t* length);
+void*    llava_wrapper_create(void* owner, int deterministic);
+uint32_t llava_wrapper_session_id(void* wrapper);
+void     llava_wrapper_start(void* wrapper);
+void     llava_wrapper_push_order(void* wrapper, uint32_t client_id, uint32_t request_id, uint32_t opcode, uint32_t arg1,
+                                  const char* s, size_t len);
+void     llava_wrapper_join(void* wrapper);
+void     llava_wrapper_destroy(void* wrapper);
+
 #ifdef __cplusplus
 }
 #endif

@@ -234,6 +234,16 @@ HOST_API = {
     "llava_session_get_backlog_size": (_u32, [_p]),
     "llava_session_get_tokens_in_gpu": (_u32, [_p]),
     "llava_session_read_kv": (_int, [_p, _u32, _int, _u32, _u32, _p]),
+    "llava_wrapper_owner_create": (_p, [_p]),
+    "llava_wrapper_owner_destroy": (None, [_p]),
+    "llava_wrapper_owner_dead_sessions": (_u32, [_p]),
+    "llava_wrapper_owner_pop": (_int, [_p, _int, _u32p, _u32p, _u32p, _u32p, _p, _u32, _u32p]),
+    "llava_wrapper_create": (_p, [_p, _int]),
+    "llava_wrapper_session_id": (_u32, [_p]),
+    "llava_wrapper_start": (None, [_p]),
+    "llava_wrapper_push_order": (None, [_p, _u32, _u32, _u32, _u32, C.c_char_p, _sz]),
+    "llava_wrapper_join": (None, [_p]),
+    "llava_wrapper_destroy": (None, [_p]),
 }
 
 NO_TOKEN = 0xFFFFFFFF

@@ -60,10 +60,10 @@ def build_kernels(force=False, verbose_ptxas=False):
 def build_host(force=False):
     if not os.path.isdir(HOST):
         return None
-    cpp = [f for f in _glob(HOST, (".cpp",)) if not f.endswith("main.cpp")]
+    cpp = [f for f in _glob(HOST, (".cpp",)) if not f.endswith("main.cpp")] + _glob(os.path.join(HOST, "server"), (".cpp",))
     if not cpp:
         return None
-    deps = cpp + _glob(HOST, (".h",)) + [os.path.join(ROOT, "include", "lv_b200.h"), os.path.join(ROOT, "include", "llava_host.h")]
+    deps = cpp + _glob(HOST, (".h",)) + _glob(os.path.join(HOST, "server"), (".h",)) + [os.path.join(ROOT, "include", "lv_b200.h"), os.path.join(ROOT, "include", "llava_host.h")]
     deps = [d for d in deps if os.path.exists(d)]
     out = os.path.join(HERE, "libllava_host.so")
     cxx = shutil.which("g++") or "g++"

@@ -10,6 +10,12 @@
 #include "llava_context.h"
 #include "llava_layer_session_data.h"
 #include "llava_session.h"
+#include <chrono>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+
+#include "server/session_wrapper.h"
 #include "synth_ggjt.h"
 #include "tp_shard.h"
 
@@ -209,6 +215,67 @@ int llava_session_read_kv(void* s, uint32_t layer, int which, uint32_t row0, uin
     llava_buffer* b = which == 0 ? data[layer]->get_k_cache() : data[layer]->get_v_cache();
     const size_t row_bytes = size_t(b->shape.second) * 2;
     return b->read_raw(row0 * row_bytes, out, nrows * row_bytes) ? 1 : 0;
+}
+
+// ---- lsrv::session_wrapper behind a collecting owner (what a front end would implement) ----
+namespace {
+struct collected { int kind; uint32_t who, opcode, request; std::vector<uint8_t> payload; };
+class collecting_owner : public lsrv::session_owner {
+public:
+    explicit collecting_owner(llava_context* c) : ctx(c) {}
+    llava_context* context() override { return ctx; }
+    void receive_session_outbound_packets(std::list<lsrv::outbound_packet>& packets, std::list<lsrv::outbound_broadcast>& broadcasts) override {
+        std::lock_guard<std::mutex> g(m);
+        for (auto& p : packets) q.push_back({0, std::get<0>(p), uint32_t(std::get<1>(p)), std::get<2>(p), std::get<3>(p)});
+        for (auto& b : broadcasts) q.push_back({1, std::get<0>(b), uint32_t(std::get<1>(b)), 0, std::get<2>(b)});
+        packets.clear();
+        broadcasts.clear();
+        cv.notify_all();
+    }
+    void notify_session_death(uint32_t) override {
+        std::lock_guard<std::mutex> g(m);
+        ++dead;
+        cv.notify_all();
+    }
+    llava_context* ctx;
+    std::mutex m;
+    std::condition_variable cv;
+    std::deque<collected> q;
+    uint32_t dead = 0;
+};
+}  // namespace
+
+void* llava_wrapper_owner_create(void* ctx) { return new collecting_owner(static_cast<llava_context*>(ctx)); }
+void llava_wrapper_owner_destroy(void* owner) { delete static_cast<collecting_owner*>(owner); }
+uint32_t llava_wrapper_owner_dead_sessions(void* owner) {
+    auto* o = static_cast<collecting_owner*>(owner);
+    std::lock_guard<std::mutex> g(o->m);
+    return o->dead;
+}
+
+int llava_wrapper_owner_pop(void* owner, int timeout_ms, uint32_t* kind, uint32_t* who, uint32_t* opcode, uint32_t* request,
+                            uint8_t* payload, uint32_t cap, uint32_t* length) {
+    auto* o = static_cast<collecting_owner*>(owner);
+    std::unique_lock<std::mutex> g(o->m);
+    if (!o->cv.wait_for(g, std::chrono::milliseconds(timeout_ms), [o]() { return !o->q.empty(); })) return 0;
+    collected c = o->q.front();
+    o->q.pop_front();
+    *kind = uint32_t(c.kind); *who = c.who; *opcode = c.opcode; *request = c.request;
+    *length = uint32_t(c.payload.size());
+    std::memcpy(payload, c.payload.data(), c.payload.size() < cap ? c.payload.size() : cap);
+    return 1;
+}
+
+void* llava_wrapper_create(void* owner, int deterministic) {
+    lsrv::session_wrapper::set_deterministic_sessions(deterministic != 0);
+    return new lsrv::session_wrapper(static_cast<collecting_owner*>(owner));
+}
+uint32_t llava_wrapper_session_id(void* w) { return static_cast<lsrv::session_wrapper*>(w)->session_id; }
+void llava_wrapper_start(void* w) { static_cast<lsrv::session_wrapper*>(w)->start(); }
+void llava_wrapper_join(void* w) { static_cast<lsrv::session_wrapper*>(w)->join(); }
+void llava_wrapper_destroy(void* w) { delete static_cast<lsrv::session_wrapper*>(w); }
+void llava_wrapper_push_order(void* w, uint32_t client_id, uint32_t request_id, uint32_t opcode, uint32_t arg1, const char* s, size_t len) {
+    static_cast<lsrv::session_wrapper*>(w)->push_order(client_id, request_id, opcode, arg1, s ? std::string(s, len) : std::string());
 }
 
 }  // extern "C"

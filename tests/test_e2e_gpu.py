@@ -260,3 +260,65 @@ def test_trace_frames_match_oracle_layer_outputs(run, tmp_path):
         orc.push(t)
         if orc.lib.orc_session_token_count(orc.s) >= N_PROMPT + N_DECODE:
             break
+
+
+def test_sampler_draws_from_the_reference_candidate_set(run):
+    """Non-greedy mode is the reference's sampler (llava_session.cpp:154-194): the drawn token must be one of
+    the candidates the oracle's restatement keeps for the same logits, token history and mu = 2 * tau."""
+    s = run["ctx"].session()
+    s.set_seed(7)
+    for t in run["prompt"]:
+        s.push_token(t)
+    tok = s.predict_next_token()
+    logits = s.logits(run["vocab"])
+    lib = run["orc"].lib
+    toks = np.array(run["prompt"], np.uint32)
+    probs, ids, kept = np.empty(run["vocab"], np.float32), np.empty(run["vocab"], np.uint32), C.c_float()
+    k = lib.orc_sampler_candidates(ob.ptr(logits), run["vocab"], ob.ptr(toks), toks.size, 10.0, ob.ptr(probs), ob.ptr(ids), kept)
+    assert k >= 1 and tok in set(int(i) for i in ids[:k])
+    s.close()
+
+
+def test_session_wrapper_orders(run, pkg):
+    """lsrv::session_wrapper: addToken / tick / getSessionTokens / start / stop / kill through the order queue."""
+    if run["wtype"] != qn.Q4_0:
+        pytest.skip("one quantisation is enough")
+    lib = pkg.load_host()
+    owner = lib.llava_wrapper_owner_create(run["ctx"].handle)
+    w = lib.llava_wrapper_create(owner, 1)
+    sid = lib.llava_wrapper_session_id(w)
+    lib.llava_wrapper_start(w)
+
+    def pop(timeout=20000):
+        kind, who, op, req, n = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        buf = (C.c_uint8 * 65536)()
+        assert lib.llava_wrapper_owner_pop(owner, timeout, C.byref(kind), C.byref(who), C.byref(op), C.byref(req), buf, 65536, C.byref(n))
+        return kind.value, who.value, op.value, req.value, bytes(buf[:n.value])
+
+    CLIENT = 9
+    for i, t in enumerate(run["prompt"]):
+        lib.llava_wrapper_push_order(w, CLIENT, 100 + i, 33, t, None, 0)           # cmdAddToken
+        assert pop() == (0, CLIENT, 6, 100 + i, (0).to_bytes(4, "little"))           # ack(ok)
+    lib.llava_wrapper_push_order(w, CLIENT, 200, 33, 32000, None, 0)                  # bad token id
+    assert pop() == (0, CLIENT, 6, 200, (1).to_bytes(4, "little"))                   # ack(nok)
+    lib.llava_wrapper_push_order(w, CLIENT, 300, 22, 0, None, 0)                      # cmdTick: one token
+    seen = [pop(), pop()]
+    payload = sid.to_bytes(4, "little") + run["greedy"][0].to_bytes(4, "little") + (N_PROMPT).to_bytes(4, "little")
+    assert (1, sid, 0, 0, payload) in seen and (0, CLIENT, 0, 300, payload) in seen  # broadcast + reply to the ticker
+    lib.llava_wrapper_push_order(w, CLIENT, 400, 16, 0, None, 0)                      # cmdGetSessionTokens
+    k, who, op, req, data = pop()
+    assert (k, who, op, req) == (0, CLIENT, 1, 400)
+    assert list(np.frombuffer(data, np.uint32)) == run["prompt"] + run["greedy"][:1]
+    lib.llava_wrapper_push_order(w, CLIENT, 500, 20, 0, None, 0)                      # cmdStartSessionGeneration
+    got = []
+    while len(got) < 4:
+        k, who, op, req, data = pop()
+        if k == 1 and op == 0:
+            got.append(int.from_bytes(data[4:8], "little"))
+    assert got == run["greedy"][1:5]
+    lib.llava_wrapper_push_order(w, CLIENT, 600, 21, 0, None, 0)                      # cmdStopSessionGeneration
+    lib.llava_wrapper_push_order(w, CLIENT, 700, 19, 0, None, 0)                      # cmdKillSession
+    lib.llava_wrapper_join(w)
+    assert lib.llava_wrapper_owner_dead_sessions(owner) == 1
+    lib.llava_wrapper_destroy(w)
+    lib.llava_wrapper_owner_destroy(owner)
