@@ -383,6 +383,7 @@ def main():
     if rank != 0:
         ctx.close()
         barrier()
+        dist.destroy_process_group()
         return
     if not args.no_cpu_baseline and world == 1:
         ctx.close()
@@ -408,6 +409,8 @@ def main():
     }
     print(json.dumps(line), flush=True)
     barrier()
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -25,6 +25,8 @@ SHAPES = {                      # rows, cols, kind
     "w2": (4096, 11008, "add"),
     "w2_13b": (5120, 13824, "add"),
     "head": (32000, 4096, "plain"),
+    "qkv": (4096, 4096, "qkv"),          # norm + wk, wq, wv (3 x 4096 rows) + cache append
+    "attn": (4096, 4096, "attn"),        # fused attention, 32 heads, --pos rows in the cache
 }
 
 
@@ -45,6 +47,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--ring-mb", type=int, default=400)
+    ap.add_argument("--pos", type=int, default=200, help="cache rows already filled, for the attn shape")
     ap.add_argument("--copies", type=int, default=0,
                     help="override the ring length; 1 keeps the matrix resident in L2 and shows the kernel's compute ceiling")
     args = ap.parse_args()
@@ -64,7 +67,7 @@ def main():
         rng = np.random.default_rng(99)
         for name in args.shape:
             rows, cols, kind = SHAPES[name]
-            nmat = 2 if kind == "silu" else 1
+            nmat = {"silu": 2, "qkv": 3}.get(kind, 1)
             rb = qn.row_bytes(wtype, cols)
             slab_rows = 256
             slab = qn.quantize((rng.standard_normal((slab_rows, cols)) * 0.02).astype(np.float32), wtype)
@@ -77,9 +80,30 @@ def main():
             x = gpu.upload(rng.standard_normal((args.batch, cols)).astype(np.float32))
             out = gpu.zeros(args.batch * rows * 4)
 
+            if kind in ("qkv", "attn"):
+                ctx_rows = 2048
+                kc, vc = gpu.zeros(ctx_rows * rows * 2), gpu.zeros(ctx_rows * rows * 2)
+                if kind == "attn":
+                    fill = (rng.standard_normal((args.pos + 1, rows)) * 0.5).astype(np.float16)
+                    for c in (kc, vc):
+                        pkg.check(lib.lv_upload(h, c, fill.ctypes.data_as(C.c_void_p), fill.nbytes))
+                nw = gpu.upload((1 + 0.01 * rng.standard_normal(cols)).astype(np.float32))
+                dpos = gpu.upload(np.array([args.pos] * 4, np.uint32))
+                table = gpu.alloc(ctx_rows * 128 * 4)
+                pkg.check(lib.lv_rope_table_build(h, table, ctx_rows, 128))
+                backlog = 128
+                while backlog <= args.pos:
+                    backlog *= 2
+                scratch = gpu.zeros(lib.lv_attention_scratch_bytes(rows // 128, 128, ctx_rows, 1))
+
             def launch(i):
                 w = pkg.offset(ring, (i % copies) * nmat * mat_bytes)
-                if kind == "silu":
+                if kind == "qkv":
+                    pkg.check(lib.lv_norm_qkv_kvappend(h, out, kc, vc, w, pkg.offset(w, mat_bytes), pkg.offset(w, 2 * mat_bytes), wtype,
+                                                       x, nw, dpos, rows, cols, 1, ctx_rows))
+                elif kind == "attn":
+                    pkg.check(lib.lv_attention_fused(h, out, x, kc, vc, dpos, table, scratch, rows // 128, 128, backlog, 1))
+                elif kind == "silu":
                     pkg.check(lib.lv_gemv_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, x, rows, cols, args.batch))
                 else:
                     pkg.check(lib.lv_gemv(h, out, w, wtype, x, rows, cols, args.batch, 1 if kind == "add" else 0))
@@ -103,9 +127,10 @@ def main():
             gpu.sync()
             pkg.check(lib.lv_graph_destroy(graph))
             sec = e0.elapsed_time(e1) * 1e-3 / args.iters
-            gbs = nmat * mat_bytes / sec / 1e9
+            nbytes = nmat * mat_bytes if kind != "attn" else 2 * (args.pos + 1) * rows * 2
+            gbs = nbytes / sec / 1e9
             print(json.dumps({"shape": name, "rows": rows, "cols": cols, "kind": kind, "wtype": args.wtype, "batch": args.batch,
-                              "us_per_launch": sec * 1e6, "bytes": nmat * mat_bytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / peak,
+                              "us_per_launch": sec * 1e6, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / peak,
                               "ring_copies": copies}), flush=True)
             for d in (ring, x, out):
                 gpu.free(d)
