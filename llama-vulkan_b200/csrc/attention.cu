@@ -17,8 +17,10 @@
 
 namespace lv {
 
-constexpr int kAttnThreads = 256;
-constexpr int kAttnChunk = 64;   // cache rows per CTA of the fused kernel
+constexpr int kAttnThreads = 256;  // the three separate ops
+constexpr int kFusedThreads = 1024;
+constexpr int kAttnChunk = 256;    // cache rows per CTA of the fused kernel (8 per warp)
+constexpr int kRowGroups = kFusedThreads / 16;   // 16 threads x 8 dims cover a row of one head
 constexpr int kRot = 128;        // head size; the reference supports only 128 (dim 4096/5120)
 
 // Score of one (query head, cache row) pair, computed by a full warp: each
@@ -119,17 +121,24 @@ __host__ __device__ inline size_t attn_partial_floats(uint32_t heads, uint32_t n
     return size_t(batch) * heads * nchunks * (kRot + 2);
 }
 
-// grid (heads, nchunks, batch).  CTA (h, c, z) covers cache rows [c*64, c*64+64)
-// up to P; the last CTA of a (z, h) to finish combines the chunks.
-__global__ void __launch_bounds__(kAttnThreads) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
-                                                                      const __half* __restrict__ kc, const __half* __restrict__ vc,
-                                                                      const uint32_t* __restrict__ pos, const float* __restrict__ table,
-                                                                      float* __restrict__ partial, uint32_t* __restrict__ counters,
-                                                                      uint32_t heads, uint32_t nchunks, float scale) {
+// grid (heads, nchunks, batch).  CTA (h, c, z) covers cache rows [c*256, c*256+256)
+// up to P; contexts of up to 256 rows need one CTA per head and no combine, longer
+// ones end with the last CTA of a (z, h) combining the chunks.
+//
+// The kernel is a short chain of dependent steps on little data, so each step
+// issues all of its global loads before using any of them (one trip to L2 per
+// step): scores with 8 lanes per cache row (16 elements each, both of a warp's
+// row batches in flight together), values with 16 threads per row (8 dims each)
+// and four rows per thread in flight.
+__global__ void __launch_bounds__(kFusedThreads) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
+                                                                       const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                                       const uint32_t* __restrict__ pos, const float* __restrict__ table,
+                                                                       float* __restrict__ partial, uint32_t* __restrict__ counters,
+                                                                       uint32_t heads, uint32_t nchunks, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_e[kAttnChunk];
-    __shared__ float s_part[kRot];
+    __shared__ __align__(16) float s_v[kRowGroups][kRot];
     __shared__ float s_red[2];
     __shared__ uint32_t s_last;
 
@@ -142,47 +151,106 @@ __global__ void __launch_bounds__(kAttnThreads) attention_fused_kernel(float* __
     const uint32_t p0 = c * kAttnChunk;
     const uint32_t n = min(uint32_t(kAttnChunk), P + 1 - p0);
 
-    // scores of this chunk: 8 warps x 8 rows
-    const float4 q4 = *reinterpret_cast<const float4*>(q + size_t(z) * dim + h * kRot + 4 * lane);
-    for (uint32_t i = warp; i < uint32_t(kAttnChunk); i += kAttnThreads / 32) {
-        float s = -INFINITY;
-        if (i < n) {
-            const uint32_t p = p0 + i;
-            s = rope_score(q4, kc + size_t(p) * dim + h * kRot, table + size_t(P - p) * kRot, lane) * scale;
+    // ---- scores: warp w owns rows 8w .. 8w+7, lane group g = lane / 8 one row per pass -------
+    {
+        const int sub = lane & 7, g = lane >> 3;
+        const float* qh = q + size_t(z) * dim + h * kRot + sub * 16;
+        float4 qv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) qv[j] = *reinterpret_cast<const float4*>(qh + 4 * j);
+        uint4 kraw[2][2];
+        float4 cs[2][4];
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const uint32_t i = warp * 8 + it * 4 + g;
+            const uint32_t p = p0 + min(i, n - 1);                 // clamped: rows past n are computed and discarded
+            const __half* krow = kc + size_t(p) * dim + h * kRot + sub * 16;
+            kraw[it][0] = *reinterpret_cast<const uint4*>(krow);
+            kraw[it][1] = *reinterpret_cast<const uint4*>(krow + 8);
+            const float* t = table + size_t(P - p) * kRot + sub * 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cs[it][j] = *reinterpret_cast<const float4*>(t + 4 * j);
         }
-        if (lane == 0) s_e[i] = s;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const uint32_t i = warp * 8 + it * 4 + g;
+            const __half2* k2 = reinterpret_cast<const __half2*>(&kraw[it][0]);      // 8 (even, odd) pairs
+            float sacc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // pairs 2j and 2j+1 of this lane: q (x, y, z, w), cos/sin (x, y, z, w) -- mhsa.comp:42-57
+                const float2 ka = __half22float2(k2[2 * j]), kb = __half22float2(k2[2 * j + 1]);
+                const float4 t = cs[it][j], qq = qv[j];
+                const float rx0 = t.x * ka.x + t.y * ka.y, ry0 = -t.y * ka.x + t.x * ka.y;
+                const float rx1 = t.z * kb.x + t.w * kb.y, ry1 = -t.w * kb.x + t.z * kb.y;
+                sacc += qq.x * rx0 + qq.y * ry0;
+                sacc += qq.z * rx1 + qq.w * ry1;
+            }
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 4);
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 1);
+            if (sub == 0) s_e[i] = i < n ? sacc * scale : -INFINITY;
+        }
     }
     __syncthreads();
-    // chunk maximum and exponentials
+    // ---- chunk maximum and exponentials -------------------------------------------------------
     if (warp == 0) {
-        const float a = s_e[lane], b = s_e[lane + 32];
-        const float m = warp_max(fmaxf(a, b));
-        const float ea = (lane < n) ? expf(a - m) : 0.f;
-        const float eb = (lane + 32 < n) ? expf(b - m) : 0.f;
-        s_e[lane] = ea;
-        s_e[lane + 32] = eb;
-        const float l = warp_sum(ea + eb);
+        float sc[kAttnChunk / 32];
+        float m = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < kAttnChunk / 32; ++k) {
+            sc[k] = s_e[lane + 32 * k];
+            m = fmaxf(m, sc[k]);
+        }
+        m = warp_max(m);
+        float l = 0.f;
+#pragma unroll
+        for (int k = 0; k < kAttnChunk / 32; ++k) {
+            const float e = (uint32_t(lane) + 32 * k < n) ? expf(sc[k] - m) : 0.f;
+            s_e[lane + 32 * k] = e;
+            l += e;
+        }
+        l = warp_sum(l);
         if (lane == 0) { s_red[0] = m; s_red[1] = l; }
     }
-    __syncthreads();
-    // weighted values: thread = (d, half of the rows)
-    const int d = threadIdx.x & (kRot - 1), half = threadIdx.x >> 7;
-    float acc = 0.f;
-    for (uint32_t i = half; i < n; i += 2) acc = fmaf(__half2float(vc[size_t(p0 + i) * dim + h * kRot + d]), s_e[i], acc);
-    if (half == 1) s_part[d] = acc;
+    // ---- weighted values: thread = (8 dims, one of 64 row groups), rows rg, rg+64, rg+128, rg+192 --
+    const int d8 = (threadIdx.x & 15) * 8, rg = threadIdx.x >> 4;
+    uint4 vraw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t i = min(uint32_t(rg + kRowGroups * j), n - 1);
+        vraw[j] = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * dim + h * kRot + d8);
+    }
+    __syncthreads();                                       // s_e now holds the exponentials
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t i = rg + kRowGroups * j;
+        const float e = i < n ? s_e[i] : 0.f;
+        const __half2* v2 = reinterpret_cast<const __half2*>(&vraw[j]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(v2[k]);
+            acc[2 * k] = fmaf(f.x, e, acc[2 * k]);
+            acc[2 * k + 1] = fmaf(f.y, e, acc[2 * k + 1]);
+        }
+    }
+    *reinterpret_cast<float4*>(&s_v[rg][d8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(&s_v[rg][d8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     __syncthreads();
     float* my = partial + ((size_t(z) * heads + h) * nchunks + c) * (kRot + 2);
-    if (half == 0) {
-        acc += s_part[d];
+    if (threadIdx.x < kRot) {
+        float o = 0.f;
+#pragma unroll 16
+        for (int r = 0; r < kRowGroups; ++r) o += s_v[r][threadIdx.x];
         if (active == 1) {
-            out[size_t(z) * dim + h * kRot + d] = acc / s_red[1];
-            return;
+            out[size_t(z) * dim + h * kRot + threadIdx.x] = o / s_red[1];
+        } else {
+            my[threadIdx.x] = o;
+            if (threadIdx.x == 0) { my[kRot] = s_red[0]; my[kRot + 1] = s_red[1]; }
         }
-        my[d] = acc;
-        if (d == 0) { my[kRot] = s_red[0]; my[kRot + 1] = s_red[1]; }
-    } else if (active == 1) {
-        return;
     }
+    if (active == 1) return;
     // publish, then find out whether this CTA is the last of its (z, h)
     __threadfence();
     __syncthreads();
@@ -196,14 +264,20 @@ __global__ void __launch_bounds__(kAttnThreads) attention_fused_kernel(float* __
     __threadfence();
     if (threadIdx.x < kRot) {
         const float* base = partial + (size_t(z) * heads + h) * nchunks * (kRot + 2);
-        float M = -INFINITY;
-        for (uint32_t j = 0; j < active; ++j) M = fmaxf(M, __ldcg(base + size_t(j) * (kRot + 2) + kRot));
-        float num = 0.f, den = 0.f;
-        for (uint32_t j = 0; j < active; ++j) {
-            const float* pj = base + size_t(j) * (kRot + 2);
-            const float w = expf(__ldcg(pj + kRot) - M);
-            num = fmaf(__ldcg(pj + threadIdx.x), w, num);
-            den = fmaf(__ldcg(pj + kRot + 1), w, den);
+        // lane j of every warp fetches chunk j's (max, sum): at most 32 chunks
+        const bool mine = uint32_t(lane) < active;
+        const float mj = mine ? __ldcg(base + size_t(lane) * (kRot + 2) + kRot) : -INFINITY;
+        const float lj = mine ? __ldcg(base + size_t(lane) * (kRot + 2) + kRot + 1) : 0.f;
+        const float M = warp_max(mj);
+        const float wj = mine ? expf(mj - M) : 0.f;
+        const float den = warp_sum(lj * wj);
+        float num = 0.f;
+        for (uint32_t j0 = 0; j0 < active; j0 += 8) {
+            float oj[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) oj[u] = (j0 + u < active) ? __ldcg(base + size_t(j0 + u) * (kRot + 2) + threadIdx.x) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) num = fmaf(oj[u], __shfl_sync(0xffffffffu, wj, (j0 + u) & 31), num);
         }
         out[size_t(z) * dim + h * kRot + threadIdx.x] = num / den;
     }
@@ -310,7 +384,7 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
     dim3 grid(heads, nchunks, batch);
-    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kAttnThreads), 0, out, q, static_cast<const __half*>(k_cache),
+    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
                        static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
                        1.0f / sqrtf(static_cast<float>(rot))));
     return LV_OK;
@@ -337,7 +411,7 @@ extern "C" int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q
     // the buffer keeps whatever the last call left; only the arrival counters must start at zero
     LV_CUDA(cudaMemsetAsync(counters, 0, size_t(batch) * heads * sizeof(uint32_t), ctx->stream));
     dim3 grid(heads, nchunks, batch);
-    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kAttnThreads), 0, out, q, static_cast<const __half*>(k_cache),
+    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
                        static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
                        1.0f / sqrtf(static_cast<float>(rot))));
     return LV_OK;
