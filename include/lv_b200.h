@@ -186,7 +186,7 @@ int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const void* k_ca
  * the call performs no cudaMalloc/cudaFree and calls nothing that allocates.
  * Shapes whose scratch (lv_attention_scratch_bytes) exceeds that limit are
  * rejected with LV_ERR_BAD_ARGUMENTS: 7B and 13B geometry at 2048 rows fit
- * with batch 1.  The first call on a device looks up the buffer's device
+ * with a batch of up to 6.  The first call on a device looks up the buffer's device
  * address; make that call before any stream capture.  All calls on a device
  * share the one buffer: calls that overlap on the GPU (different streams or
  * contexts) race; calls on one stream are safe.  Stale contents of earlier

@@ -7,20 +7,28 @@
 namespace lv {
 
 // Shared memory map of one CTA:
-//   [ring: warps x stages x stage bytes][mbarriers][reduction scratch][activation records]
+//   [ring: warps x stages x stage bytes][mbarriers][reduction scratch][item partials][activation records]
 constexpr size_t kBarBytes = 256;
 constexpr size_t kScratchBytes = 256;
+constexpr int kPartialFloats = 2048;          // per-round row-segment partial sums
+constexpr size_t kPartialBytes = kPartialFloats * sizeof(float);
 
 template <int QT, int NS>
 __host__ __device__ constexpr size_t stage_bytes() { return size_t(NS) * kSegBlocks * QTraits<QT>::kBlockBytes; }
 
 template <int QT, int NS>
 static size_t gemv_smem_bytes(uint32_t K) {
-    return size_t(QTraits<QT>::kWarps) * kStages * stage_bytes<QT, NS>() + kBarBytes + kScratchBytes + size_t(K / 64) * kPairBytes;
+    return size_t(QTraits<QT>::kWarps) * kStages * stage_bytes<QT, NS>() + kBarBytes + kScratchBytes + kPartialBytes +
+           size_t(K / 64) * kPairBytes;
 }
 
 // NS row streams per work item: NS consecutive rows, or NS/2 rows of each of the
 // two matrices of the SiLU-gated pair (streams ordered w3 r0, w1 r0, w3 r1, w1 r1).
+//
+// A CTA takes a contiguous share of the row groups.  Its work items are (row group, segment of
+// 64 blocks) pairs dealt to the warps round robin, which balances the warps to within one
+// item; an item's NS partial sums go to shared memory and, once all items of a round are done,
+// one thread per row adds the segments in order and applies the epilogue (deterministic).
 template <int QT, int NS, bool SILU>
 __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const GemvParams p) {
     using Q = QTraits<QT>;
@@ -34,21 +42,23 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRing);
     float* scratch = reinterpret_cast<float*>(smem + kRing + kBarBytes);
-    uint8_t* xrec = smem + kRing + kBarBytes + kScratchBytes;
+    float* part = reinterpret_cast<float*>(smem + kRing + kBarBytes + kScratchBytes);
+    uint8_t* xrec = smem + kRing + kBarBytes + kScratchBytes + kPartialBytes;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t z = blockIdx.y;
     const uint32_t nb = p.K / 32;
     const uint32_t nseg = (nb + kSegBlocks - 1) / kSegBlocks;
 
-    // groups of kRowsPerItem rows, numbered across the (up to three) matrices; every CTA
-    // takes a contiguous share, its warps take the groups of that share round robin
+    // groups of kRowsPerItem rows, numbered across the (up to three) matrices
     const uint32_t g0 = p.m[0].rows / kRowsPerItem;
     const uint32_t g1 = g0 + (p.n_mat > 1 ? p.m[1].rows / kRowsPerItem : 0);
     const uint32_t g2 = g1 + (p.n_mat > 2 ? p.m[2].rows / kRowsPerItem : 0);
     const uint32_t cta_first = uint32_t(uint64_t(g2) * blockIdx.x / gridDim.x);
-    const uint32_t cta_end = uint32_t(uint64_t(g2) * (blockIdx.x + 1) / gridDim.x);
-    const uint32_t first = cta_first + warp;
+    const uint32_t cta_groups = uint32_t(uint64_t(g2) * (blockIdx.x + 1) / gridDim.x) - cta_first;
+    const uint32_t n_items = cta_groups * nseg;
+    // a round = as many whole groups as the partial buffer holds
+    const uint32_t groups_per_round = max(1u, uint32_t(kPartialFloats) / (nseg * NS));
 
     uint8_t* my_ring = smem + size_t(warp) * kStages * kStage;
     uint64_t* my_bars = bars + warp * kStages;
@@ -69,10 +79,11 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
         return p.m[2];
     };
 
-    // lanes 0..NS-1: each starts the copy of one stream of (group gg, segment seg) into ring slot `slot`
-    auto issue = [&](uint32_t gg, uint32_t seg, int slot) {
+    // lanes 0..NS-1: each starts the copy of one stream of item j into ring slot `slot`
+    auto issue = [&](uint32_t j, int slot) {
+        const uint32_t gl = j / nseg, seg = j - gl * nseg;
         uint32_t lg;
-        const GemvMatrix& M = locate(gg, lg);
+        const GemvMatrix& M = locate(cta_first + gl, lg);
         const uint32_t segblocks = min(uint32_t(kSegBlocks), nb - seg * kSegBlocks);
         const uint32_t bytes = segblocks * Q::kBlockBytes;
         if (lane == 0) mbar_expect_tx(&my_bars[slot], NS * bytes);
@@ -92,13 +103,13 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
         }
     };
 
-    // issue cursor (ig, is) runs kStages work items ahead of the consume cursor (cg, cs)
-    uint32_t ig = first, is = 0;
+    // the issue cursor runs kStages items ahead of the consume cursor
+    uint32_t ij = warp;
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
-        if (ig < cta_end) {
-            issue(ig, is, s);
-            if (++is == nseg) { is = 0; ig += kWarps; }
+        if (ij < n_items) {
+            issue(ij, s);
+            ij += kWarps;
         }
     }
 
@@ -108,83 +119,78 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) gemv_kernel(const
     stage_activations<Q::kFracBits>(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
     __syncthreads();
 
-    float acc[NS];
-#pragma unroll
-    for (int i = 0; i < NS; ++i) acc[i] = 0.f;
-
     int slot = 0;
     uint32_t parity = 0;
-    for (uint32_t cg = first, cs = 0; cg < cta_end;) {
-        if (!mbar_wait(&my_bars[slot], parity, p.err)) break;
-
-        const uint32_t segblocks = min(uint32_t(kSegBlocks), nb - cs * kSegBlocks);
-        const uint8_t* stage = my_ring + slot * kStage;
-        if (uint32_t(lane) * 2 < segblocks) {
-            PairX px;
-            load_pair_x(px, xrec + size_t(cs * (kSegBlocks / 2) + lane) * kPairBytes);
-#pragma unroll
-            for (int i = 0; i < NS; ++i) {
-                const uint32_t* sw = reinterpret_cast<const uint32_t*>(stage + i * kStreamStride) + lane * Q::kPairWords;
-                acc[i] += dot_pair<QT>(sw, px);
-            }
-        }
-        __syncwarp();
-        if (ig < cta_end) {
-            issue(ig, is, slot);
-            if (++is == nseg) { is = 0; ig += kWarps; }
-        }
-        slot ^= 1;
-        parity ^= uint32_t(slot == 0);
-
-        if (cs == nseg - 1) {
-            uint32_t lg;
-            const GemvMatrix& M = locate(cg, lg);
-            float v;
-            uint32_t row;
-            bool writer;
-            if constexpr (NS == 4) {
-                const float u = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
-                if constexpr (SILU) {
-                    const float gate = __shfl_xor_sync(0xffffffffu, u, 8);
-                    v = u * gate / (expf(-gate) + 1.0f);                 // matmul_silu_ff.comp:95
-                    row = lg * 2 + (lane >> 4);
-                    writer = (lane & 15) == 0;
-                } else {
-                    v = u;
-                    row = lg * 4 + (lane >> 3);
-                    writer = (lane & 7) == 0;
-                }
-            } else {
-                const float u = warp_sum2(acc[0], acc[1], lane);
-                if constexpr (SILU) {
-                    const float gate = __shfl_xor_sync(0xffffffffu, u, 16);
-                    v = u * gate / (expf(-gate) + 1.0f);
-                    row = lg;
-                    writer = lane == 0;
-                } else {
-                    v = u;
-                    row = lg * 2 + (lane >> 4);
-                    writer = (lane & 15) == 0;
-                }
-            }
-            if (writer) {
-                if (M.epilogue == EPI_STORE_F16_AT_POS) {
-                    __half* cache = static_cast<__half*>(M.out);
-                    const uint32_t slot_row = *p.pos + z;
-                    if (slot_row < p.ctx_rows) cache[size_t(slot_row) * M.rows + row] = __float2half_rn(v);   // copy_to_cache.comp:35
-                    else atomicOr(p.err, ERR_BAD_INDEX);
-                } else {
-                    float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
-                    *o = (M.epilogue == EPI_ADD) ? (*o + v) : v;                       // matmul.glsl:68-72
-                }
-            }
+    uint32_t cj = warp;
+    bool ok = true;
+    for (uint32_t round_first = 0; round_first < cta_groups; round_first += groups_per_round) {
+        const uint32_t round_groups = min(groups_per_round, cta_groups - round_first);
+        const uint32_t item_base = round_first * nseg, item_end = (round_first + round_groups) * nseg;
+        while (ok && cj < item_end) {
+            if (!mbar_wait(&my_bars[slot], parity, p.err)) { ok = false; break; }
+            const uint32_t gl = cj / nseg, seg = cj - gl * nseg;
+            const uint32_t segblocks = min(uint32_t(kSegBlocks), nb - seg * kSegBlocks);
+            const uint8_t* stage = my_ring + slot * kStage;
+            float acc[NS];
 #pragma unroll
             for (int i = 0; i < NS; ++i) acc[i] = 0.f;
-            cs = 0;
-            cg += kWarps;
-        } else {
-            ++cs;
+            if (uint32_t(lane) * 2 < segblocks) {
+                PairX px;
+                load_pair_x(px, xrec + size_t(seg * (kSegBlocks / 2) + lane) * kPairBytes);
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    const uint32_t* sw = reinterpret_cast<const uint32_t*>(stage + i * kStreamStride) + lane * Q::kPairWords;
+                    acc[i] = dot_pair<QT>(sw, px);
+                }
+            }
+            __syncwarp();
+            if (ij < n_items) {
+                issue(ij, slot);
+                ij += kWarps;
+            }
+            slot ^= 1;
+            parity ^= uint32_t(slot == 0);
+            float* dst = part + size_t(cj - item_base) * NS;
+            if constexpr (NS == 4) {
+                const float u = warp_sum4(acc[0], acc[1], acc[2], acc[3], lane);
+                if ((lane & 7) == 0) dst[lane >> 3] = u;
+            } else {
+                const float u = warp_sum2(acc[0], acc[1], lane);
+                if ((lane & 15) == 0) dst[lane >> 4] = u;
+            }
+            cj += kWarps;
         }
+        __syncthreads();
+        // one thread per row of the round: add its segments in order, then the epilogue
+        for (uint32_t t = threadIdx.x; t < round_groups * kRowsPerItem; t += blockDim.x) {
+            const uint32_t gl = t / kRowsPerItem, rr = t - gl * kRowsPerItem;
+            const float* src = part + size_t(gl) * nseg * NS;
+            float v;
+            if constexpr (SILU) {
+                float up = 0.f, gate = 0.f;
+                for (uint32_t sg = 0; sg < nseg; ++sg) {
+                    up += src[sg * NS + 2 * rr];
+                    gate += src[sg * NS + 2 * rr + 1];
+                }
+                v = up * gate / (expf(-gate) + 1.0f);                   // matmul_silu_ff.comp:95
+            } else {
+                v = 0.f;
+                for (uint32_t sg = 0; sg < nseg; ++sg) v += src[sg * NS + rr];
+            }
+            uint32_t lg;
+            const GemvMatrix& M = locate(cta_first + round_first + gl, lg);
+            const uint32_t row = lg * kRowsPerItem + rr;
+            if (M.epilogue == EPI_STORE_F16_AT_POS) {
+                __half* cache = static_cast<__half*>(M.out);
+                const uint32_t slot_row = *p.pos + z;
+                if (slot_row < p.ctx_rows) cache[size_t(slot_row) * M.rows + row] = __float2half_rn(v);   // copy_to_cache.comp:35
+                else atomicOr(p.err, ERR_BAD_INDEX);
+            } else {
+                float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
+                *o = (M.epilogue == EPI_ADD) ? (*o + v) : v;                       // matmul.glsl:68-72
+            }
+        }
+        if (round_first + groups_per_round < cta_groups) __syncthreads();        // partials are reused by the next round
     }
 }
 

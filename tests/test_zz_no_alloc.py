@@ -53,8 +53,9 @@ def test_static_scratch_variant_matches_caller_scratch_variant_twice_in_a_row(gp
 def test_shapes_beyond_the_built_in_buffer_are_refused(gpu, pkg):
     lib, h = gpu.lib, gpu.handle
     d = gpu.alloc(4096)
-    assert lib.lv_attention_scratch_bytes(HEADS, ROT, 2048, 2) > lib.lv_attention_static_scratch_limit()
-    rc = lib.lv_attention_fused_static(h, d, d, d, d, d, d, HEADS, ROT, 2048, 2)
+    assert lib.lv_attention_scratch_bytes(HEADS, ROT, 2048, 6) <= lib.lv_attention_static_scratch_limit()
+    assert lib.lv_attention_scratch_bytes(HEADS, ROT, 2048, 16) > lib.lv_attention_static_scratch_limit()
+    rc = lib.lv_attention_fused_static(h, d, d, d, d, d, d, HEADS, ROT, 2048, 16)
     assert rc == pkg.LV_ERR_BAD_ARGUMENTS
     assert b"built-in buffer" in lib.lv_last_error_string()
     gpu.sync()
