@@ -259,6 +259,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-q4_0", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: one-kernel all-reduce over NVLink peer memory (default) or NCCL + add")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -310,6 +312,12 @@ def main():
     t0 = time.time()
     ctx = pkg.HostContext(path, local_rank, rank, world, nccl_id)
     print(f"[bench] rank {rank}: model on device in {time.time() - t0:.1f} s", file=sys.stderr)
+    if world > 1 and args.allreduce == "peer":
+        mine = torch.tensor(list(ctx.peer_window_handle()), dtype=torch.uint8, device="cuda")
+        gathered = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        ctx.peer_connect([bytes(g.cpu().tolist()) for g in gathered])
+        barrier()
     lv = C.c_void_p(ctx.lib.llava_context_lv(ctx.handle))
     stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=local_rank)
 
@@ -402,7 +410,7 @@ def main():
         "config": {"workload": f"LLaMA-{w['geometry'].upper()} {'q4_0' if w['wtype'] == 2 else 'q8_0'} single-stream greedy decode, "
                                f"{n_layers} layers, {n_prompt}-token seeded prompt, f16 KV cache, context {first_pos}..{first_pos + args.steps}",
                    "baseline_config_index": w["config"], "cache": "weights per token (GBs) exceed the 126 MB L2; no flush needed",
-                   "parallelism": f"tp{world}"},
+                   "parallelism": f"tp{world}" + (f" ({args.allreduce} all-reduce)" if world > 1 else "")},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": args.steps / sec_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": launches_per_token * args.steps, "clocks": clocks,

@@ -46,6 +46,10 @@ void*    llava_context_open(const char* model_path, int device);   /* NULL on fa
  * of lv_comm_unique_id made by rank 0 (ignored when n_ranks == 1) */
 void*    llava_context_open_sharded(const char* model_path, int device, uint32_t rank, uint32_t n_ranks,
                                     const uint8_t* nccl_id);
+/* peer-memory all-reduce between the ranks (see lv_peer_window_create in lv_b200.h): make this
+ * rank's window and 64-byte handle, exchange the handles of all ranks, connect (rank order) */
+int      llava_context_peer_window_create(void* ctx, uint8_t* handle64);
+int      llava_context_peer_connect(void* ctx, const uint8_t* handles);
 /* shard geometry and packing (host/tp_shard.h): how = 1 rows, 2 columns */
 int      llava_tp_shape(int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank, uint32_t n_ranks,
                         uint32_t* out_rows, uint32_t* out_cols, uint32_t* out_cols_used, uint64_t* out_bytes);

@@ -216,6 +216,19 @@ int lv_comm_unique_id(uint8_t* out128);
 int lv_comm_init_rank(lv_ctx* ctx, const uint8_t* id128, int n_ranks, int rank);
 /* in place, on the context's stream (capturable); a no-op without a communicator */
 int lv_allreduce_f32(lv_ctx* ctx, float* buf, size_t count);
+/* residual += sum over ranks of partial: the tensor-parallel form of the residual add that
+ * matmul_add_inplace fuses (llava_layer.cpp:67,73).  With a connected peer window (below) this is
+ * ONE kernel: peer stores of the partial vector into every rank's window over NVLink, arrival
+ * flags, a bounded wait, and the sum in rank order from local memory (bit-identical on all
+ * ranks).  Without one it is lv_allreduce_f32 followed by lv_add_f32.  partial is clobbered. */
+int lv_allreduce_add_f32(lv_ctx* ctx, float* residual, float* partial, size_t count);
+/* Peer windows: every rank creates one (capacity_floats >= the longest vector, multiple of 4),
+ * hands the 64-byte CUDA IPC handle to all ranks by any means, and connects with the handles
+ * of all ranks in rank order (its own entry is ignored).  One process per GPU, same node. */
+size_t lv_peer_window_bytes(int n_ranks, uint32_t capacity_floats);
+int lv_peer_window_create(lv_ctx* ctx, int n_ranks, uint32_t capacity_floats, uint8_t* handle64);
+int lv_peer_connect(lv_ctx* ctx, int rank, const uint8_t* handles);
+int lv_peer_destroy(lv_ctx* ctx);
 int lv_comm_status(lv_ctx* ctx);     /* LV_ERR_COMM if NCCL reported an asynchronous error */
 int lv_comm_abort(lv_ctx* ctx);
 int lv_comm_destroy(lv_ctx* ctx);

@@ -69,6 +69,11 @@ KERNEL_API = {
     "lv_comm_unique_id": (_int, [_p]),
     "lv_comm_init_rank": (_int, [_p, _p, _int, _int]),
     "lv_allreduce_f32": (_int, [_p, _p, _sz]),
+    "lv_allreduce_add_f32": (_int, [_p, _p, _p, _sz]),
+    "lv_peer_window_bytes": (_sz, [_int, _u32]),
+    "lv_peer_window_create": (_int, [_p, _int, _u32, _p]),
+    "lv_peer_connect": (_int, [_p, _int, _p]),
+    "lv_peer_destroy": (_int, [_p]),
     "lv_comm_status": (_int, [_p]),
     "lv_comm_abort": (_int, [_p]),
     "lv_comm_destroy": (_int, [_p]),
@@ -204,6 +209,8 @@ HOST_API = {
     "llava_dequantize": (_int, [_p, _int, _u32, _p, _u32]),
     "llava_context_open": (_p, [C.c_char_p, _int]),
     "llava_context_open_sharded": (_p, [C.c_char_p, _int, _u32, _u32, _p]),
+    "llava_context_peer_window_create": (_int, [_p, _p]),
+    "llava_context_peer_connect": (_int, [_p, _p]),
     "llava_tp_shape": (_int, [_int, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _u32p, C.POINTER(_u64)]),
     "llava_tp_pack": (_int, [_p, _int, _u32, _u32, _u32, _u32, _u32, _p]),
     "llava_context_close": (None, [_p]),
@@ -343,6 +350,20 @@ class HostContext:
         if self.handle:
             self.lib.llava_context_close(self.handle)
             self.handle = None
+
+    def peer_window_handle(self):
+        """Creates this rank's peer window; returns its 64-byte CUDA IPC handle."""
+        buf = (C.c_uint8 * 64)()
+        if not self.lib.llava_context_peer_window_create(self.handle, buf):
+            raise RuntimeError("peer window creation failed")
+        return bytes(buf)
+
+    def peer_connect(self, handles):
+        """handles: the 64-byte handles of all ranks, in rank order."""
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        if not self.lib.llava_context_peer_connect(self.handle, buf):
+            raise RuntimeError("peer connect failed: " + (load_kernels().lv_last_error_string() or b"").decode("utf-8", "replace"))
 
     def session(self):
         return Session(self)

@@ -75,6 +75,7 @@ extern "C" int lv_ctx_create(int device, lv_ctx** out) {
 extern "C" int lv_ctx_destroy(lv_ctx* ctx) {
     if (!ctx) return LV_OK;
     cudaSetDevice(ctx->device);
+    if (ctx->peer) lv_peer_destroy(ctx);
     if (ctx->comm) lv_comm_destroy(ctx);
     if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
     if (ctx->d_err) cudaFree(ctx->d_err);

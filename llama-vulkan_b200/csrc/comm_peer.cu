@@ -1,0 +1,208 @@
+// One-shot all-reduce over NVLink peer memory, fused with the residual add of the
+// tensor-parallel decoder: residual += sum over ranks of partial.
+//
+// Every rank owns a receive window (cudaMalloc'd, exported with CUDA IPC) of
+// 2 x n_ranks slots of `capacity` floats plus arrival flags.  A launch pushes the rank's
+// partial vector into its slot of every rank's window with ordinary peer stores, publishes a
+// flag per (rank, CTA), waits -- bounded -- for the flags of all ranks in its own window, and
+// adds the slots from its own memory in rank order, so every rank computes bit-identical
+// sums.  Slots and flags alternate between two halves by launch parity, which is enough
+// because a rank cannot start launch k + 2 before every rank has finished reading launch k.
+// The reference is single-device; this replaces the NCCL all-reduce + add pair of the
+// baseline path (lv_allreduce_f32 + lv_add_f32) with one kernel.
+#include <string>
+
+#include "common.cuh"
+#include "ctx.h"
+
+namespace lv {
+
+constexpr int kPeerMaxRanks = 8;
+constexpr int kPeerCtas = 4;
+constexpr int kPeerThreads = 256;
+
+struct PeerWindowLayout {
+    uint32_t capacity;        // floats per slot
+    __host__ __device__ size_t slot_floats(int n_ranks) const { return size_t(2) * n_ranks * capacity; }
+    __host__ __device__ size_t bytes(int n_ranks) const { return slot_floats(n_ranks) * sizeof(float) + size_t(2) * kPeerMaxRanks * kPeerCtas * sizeof(uint32_t) + 256; }
+};
+
+struct PeerParams {
+    float* window[kPeerMaxRanks];     // window[r]: rank r's receive window as seen from this GPU
+    int rank, n_ranks;
+    uint32_t capacity;
+    uint32_t* epoch;                  // device word of this rank: launches completed so far
+    uint32_t* err;
+};
+
+__device__ __forceinline__ uint32_t* window_flags(float* window, int n_ranks, uint32_t capacity) {
+    return reinterpret_cast<uint32_t*>(window + size_t(2) * n_ranks * capacity);
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// grid = kPeerCtas; CTA c owns the float4 indices c, c + kPeerCtas, ... of the vector
+__global__ void __launch_bounds__(kPeerThreads) allreduce_add_peer_kernel(float* __restrict__ residual, const float* __restrict__ partial,
+                                                                         uint32_t count, const PeerParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t epoch = *p.epoch + 1;                 // this launch's number, the same on every rank
+    const uint32_t half = epoch & 1u;
+    const uint32_t n4 = count / 4;
+    const size_t my_slot = (size_t(half) * p.n_ranks + p.rank) * p.capacity;
+
+    // push this rank's slice into its slot of every window (its own included)
+    for (uint32_t i = blockIdx.x * kPeerThreads + threadIdx.x; i < n4; i += kPeerCtas * kPeerThreads) {
+        const float4 v = reinterpret_cast<const float4*>(partial)[i];
+        for (int r = 0; r < p.n_ranks; ++r) reinterpret_cast<float4*>(p.window[r] + my_slot)[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < uint32_t(p.n_ranks)) {
+        uint32_t* flags = window_flags(p.window[threadIdx.x], p.n_ranks, p.capacity);
+        st_release_sys(&flags[(half * kPeerMaxRanks + p.rank) * kPeerCtas + blockIdx.x], epoch);
+    }
+    // wait for every rank's slice of this CTA to land in this rank's window
+    __shared__ uint32_t s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < uint32_t(p.n_ranks)) {
+        const uint32_t* flag = &window_flags(p.window[p.rank], p.n_ranks, p.capacity)[(half * kPeerMaxRanks + threadIdx.x) * kPeerCtas + blockIdx.x];
+        const long long t0 = clock64();
+        while (ld_acquire_sys(flag) != epoch) {
+            if (*reinterpret_cast<volatile uint32_t*>(p.err) != 0 || clock64() - t0 > kWaitCycleLimit) {
+                atomicOr(p.err, ERR_PEER_TIMEOUT);
+                s_ok = 0;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_ok) {
+        const float* base = p.window[p.rank] + size_t(half) * p.n_ranks * p.capacity;
+        for (uint32_t i = blockIdx.x * kPeerThreads + threadIdx.x; i < n4; i += kPeerCtas * kPeerThreads) {
+            float4 acc = reinterpret_cast<float4*>(residual)[i];
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < p.n_ranks; ++r) {              // fixed order: identical on every rank
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(base + size_t(r) * p.capacity) + i);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            acc.x += sum.x; acc.y += sum.y; acc.z += sum.z; acc.w += sum.w;
+            reinterpret_cast<float4*>(residual)[i] = acc;
+        }
+    }
+    // the last CTA to finish advances the launch counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t done = atomicAdd(p.epoch + 1, 1u);
+        if (done == kPeerCtas - 1) {
+            p.epoch[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(p.epoch) = epoch;
+        }
+    }
+}
+
+struct PeerState {
+    PeerParams params{};
+    void* own_window = nullptr;
+    void* opened[kPeerMaxRanks] = {nullptr};
+    uint32_t* d_epoch = nullptr;
+};
+
+}  // namespace lv
+
+using namespace lv;
+
+extern "C" size_t lv_peer_window_bytes(int n_ranks, uint32_t capacity_floats) {
+    if (n_ranks < 1 || n_ranks > kPeerMaxRanks || capacity_floats == 0 || capacity_floats % 4) return 0;
+    return PeerWindowLayout{capacity_floats}.bytes(n_ranks);
+}
+
+extern "C" int lv_peer_window_create(lv_ctx* ctx, int n_ranks, uint32_t capacity_floats, uint8_t* handle64) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(handle64 && ctx->peer == nullptr, "bad peer window arguments");
+    const size_t bytes = lv_peer_window_bytes(n_ranks, capacity_floats);
+    LV_REQUIRE(bytes != 0, "n_ranks must be 1..8 and the capacity a multiple of 4 floats");
+    auto* st = new PeerState();
+    cudaError_t e = cudaMalloc(&st->own_window, bytes);
+    if (e == cudaSuccess) e = cudaMemset(st->own_window, 0, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&st->d_epoch, 256);
+    if (e == cudaSuccess) e = cudaMemset(st->d_epoch, 0, 256);
+    cudaIpcMemHandle_t h{};
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, st->own_window);
+    if (e != cudaSuccess) {
+        cudaFree(st->own_window);
+        cudaFree(st->d_epoch);
+        delete st;
+        return cuda_fail(e, "lv_peer_window_create");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    st->params.capacity = capacity_floats;
+    st->params.n_ranks = n_ranks;
+    st->params.epoch = st->d_epoch;
+    st->params.err = ctx->d_err;
+    ctx->peer = st;
+    return LV_OK;
+}
+
+extern "C" int lv_peer_connect(lv_ctx* ctx, int rank, const uint8_t* handles /* n_ranks x 64 */) {
+    LV_ENTER(ctx);
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    LV_REQUIRE(st && handles && rank >= 0 && rank < st->params.n_ranks, "bad peer connect arguments");
+    st->params.rank = rank;
+    for (int r = 0; r < st->params.n_ranks; ++r) {
+        if (r == rank) {
+            st->params.window[r] = static_cast<float*>(st->own_window);
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + size_t(r) * 64, 64);
+        void* ptr = nullptr;
+        LV_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        st->opened[r] = ptr;
+        st->params.window[r] = static_cast<float*>(ptr);
+    }
+    ctx->peer_ready = true;
+    return LV_OK;
+}
+
+extern "C" int lv_allreduce_add_f32(lv_ctx* ctx, float* residual, float* partial, size_t count) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(residual && partial && count, "bad all-reduce arguments");
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    if (st != nullptr && ctx->peer_ready) {
+        LV_REQUIRE(count % 4 == 0 && count <= st->params.capacity, "vector longer than the peer window's slots or not a multiple of 4");
+        LV_REQUIRE((reinterpret_cast<uintptr_t>(residual) & 15u) == 0 && (reinterpret_cast<uintptr_t>(partial) & 15u) == 0, "vectors must be 16-byte aligned");
+        LV_CUDA(launch_pdl(ctx, allreduce_add_peer_kernel, dim3(kPeerCtas), dim3(kPeerThreads), 0, residual,
+                           static_cast<const float*>(partial), uint32_t(count), st->params));
+        return LV_OK;
+    }
+    // baseline: NCCL (or nothing, on one rank), then the add
+    if (int rc = lv_allreduce_f32(ctx, partial, count)) return rc;
+    return lv_add_f32(ctx, residual, partial, count);
+}
+
+extern "C" int lv_peer_destroy(lv_ctx* ctx) {
+    LV_ENTER(ctx);
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    if (!st) return LV_OK;
+    cudaStreamSynchronize(ctx->stream);
+    for (void* p : st->opened) if (p) cudaIpcCloseMemHandle(p);
+    cudaFree(st->own_window);
+    cudaFree(st->d_epoch);
+    delete st;
+    ctx->peer = nullptr;
+    ctx->peer_ready = false;
+    return LV_OK;
+}

@@ -18,6 +18,8 @@ struct lv_ctx {
     bool capturing = false;
     void* comm = nullptr;             // ncclComm_t when a communicator is attached
     int comm_rank = 0, comm_size = 1;
+    void* peer = nullptr;             // lv::PeerState of the peer-memory all-reduce
+    bool peer_ready = false;
 };
 
 namespace lv {

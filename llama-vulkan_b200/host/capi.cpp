@@ -137,6 +137,14 @@ void* llava_context_open_sharded(const char* model_path, int device, uint32_t ra
     return c;
 }
 
+int llava_context_peer_window_create(void* ctx, uint8_t* handle64) {
+    return static_cast<llava_context*>(ctx)->peer_window_create(handle64) ? 1 : 0;
+}
+
+int llava_context_peer_connect(void* ctx, const uint8_t* handles) {
+    return static_cast<llava_context*>(ctx)->peer_connect(handles) ? 1 : 0;
+}
+
 int llava_tp_shape(int type, uint32_t rows, uint32_t cols, uint32_t how, uint32_t rank, uint32_t n_ranks, uint32_t* out_rows,
                    uint32_t* out_cols, uint32_t* out_cols_used, uint64_t* out_bytes) {
     const tp_shard_shape s = tp_shape(static_cast<ggml_value_type>(type), rows, cols, static_cast<tp_split>(how), rank, n_ranks);

@@ -179,8 +179,8 @@ void llava_command_buffer::attention_fused(llava_buffer* v_out, llava_buffer* qu
 void llava_command_buffer::allreduce_add(llava_buffer* residual, llava_buffer* partial) {
     const u32 dim = session->model->get_header().dim;
     if (!expect(residual->shape.first == dim && partial->shape.first == dim, "allreduce shapes")) return;
-    note(lv_allreduce_f32(lv(), f32(partial), size_t(dim) * batch_size));
-    note(lv_add_f32(lv(), f32(residual), f32(partial), size_t(dim) * batch_size));
+    // one kernel over NVLink peer memory when the ranks have connected their windows, else NCCL + add
+    note(lv_allreduce_add_f32(lv(), f32(residual), f32(partial), size_t(dim) * batch_size));
 }
 
 void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf,

@@ -60,6 +60,15 @@ bool llava_context::open_sharded(const string& model_path, int device, u32 rank,
     return true;
 }
 
+bool llava_context::peer_window_create(u8* handle64) {
+    if (lv_context == nullptr || model == nullptr) return false;
+    return lv_peer_window_create(lv_context, int(n_ranks_), model->get_header().dim * llava_session::max_batch_limit, handle64) == LV_OK;
+}
+
+bool llava_context::peer_connect(const u8* handles) {
+    return lv_context != nullptr && lv_peer_connect(lv_context, int(rank_), handles) == LV_OK;
+}
+
 bool llava_context::open(const string& model_path, int device) {
     const u32 keep_rank = rank_, keep_ranks = n_ranks_;
     close_all();

@@ -27,6 +27,10 @@ public:
     // Tensor-parallel open: this process is rank `rank` of `n_ranks` (one GPU each) and uploads
     // only its shard of every layer.  nccl_id: the 128 bytes of lv_comm_unique_id made by rank 0.
     bool open_sharded(const std::string& model_path, int device, u32 rank, u32 n_ranks, const u8* nccl_id);
+    // Peer-memory all-reduce (lv_allreduce_add_f32 as one kernel): every rank makes a window and
+    // its 64-byte IPC handle, the handles of all ranks are exchanged by the caller, then connected.
+    bool peer_window_create(u8* handle64);
+    bool peer_connect(const u8* handles);
     u32 tp_rank() const { return rank_; }
     u32 tp_size() const { return n_ranks_; }
 

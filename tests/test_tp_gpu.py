@@ -47,7 +47,7 @@ def ctx_is_single(ctx):
     return getattr(ctx, "n_ranks", 1) == 1
 
 
-def _worker(rank, world, path, id_q, out_q):
+def _worker(rank, world, path, id_q, out_q, peer_q=None):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     pkg = load_pkg()
     klib = pkg.load_kernels()
@@ -61,12 +61,19 @@ def _worker(rank, world, path, id_q, out_q):
         ident = id_q.get(timeout=120)
     ctx = pkg.HostContext(path, rank, rank, world, ident)
     ctx.n_ranks = world
+    if peer_q is not None:                      # one-kernel all-reduce over peer memory instead of NCCL + add
+        mine = ctx.peer_window_handle()
+        for r in range(world):
+            peer_q[r].put((rank, mine))
+        got = dict(peer_q[rank].get(timeout=120) for _ in range(world))
+        ctx.peer_connect([got[r] for r in range(world)])
     toks, logits = _decode(ctx)
     ctx.close()
     out_q.put((rank, toks, [l.tobytes() for l in logits]))
 
 
-def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path):
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path, exchange):
     if _device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -77,7 +84,8 @@ def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path):
     ctx.close()
     mpc = mp.get_context("spawn")
     id_q, out_q = mpc.Queue(), mpc.Queue()
-    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q)) for r in range(2)]
+    peer_q = [mpc.Queue() for _ in range(2)] if exchange == "peer" else None
+    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q, peer_q)) for r in range(2)]
     for p in procs:
         p.start()
     results = {}
