@@ -94,6 +94,16 @@ __device__ __forceinline__ void bulk_g2s_stream(void* smem_dst, const void* gsrc
         : "memory");
 }
 
+// 2-D tiled TMA load: one instruction fetches a box of rows x bytes described by a tensor
+// map (tile coordinates x = inner element index, y = row) and counts the box on `bar`.
+// The inner coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(smem_u32(smem_dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));

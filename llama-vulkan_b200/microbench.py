@@ -25,6 +25,9 @@ SHAPES = {                      # rows, cols, kind
     "w2": (4096, 11008, "add"),
     "w2_13b": (5120, 13824, "add"),
     "head": (32000, 4096, "plain"),
+    "tiny": (592, 4096, "plain"),        # one row group per SM: the fixed cost of a launch
+    "tiny_ff": (592, 11008, "plain"),
+    "tiny_norm": (592, 4096, "norm"),
     "qkv": (4096, 4096, "qkv"),          # norm + wk, wq, wv (3 x 4096 rows) + cache append
     "attn": (4096, 4096, "attn"),        # fused attention, 32 heads, --pos rows in the cache
 }
@@ -80,6 +83,8 @@ def main():
             x = gpu.upload(rng.standard_normal((args.batch, cols)).astype(np.float32))
             out = gpu.zeros(args.batch * rows * 4)
 
+            if kind == "norm":
+                nw = gpu.upload((1 + 0.01 * rng.standard_normal(cols)).astype(np.float32))
             if kind in ("qkv", "attn"):
                 ctx_rows = 2048
                 kc, vc = gpu.zeros(ctx_rows * rows * 2), gpu.zeros(ctx_rows * rows * 2)
@@ -103,6 +108,8 @@ def main():
                                                        x, nw, dpos, rows, cols, 1, ctx_rows))
                 elif kind == "attn":
                     pkg.check(lib.lv_attention_fused(h, out, x, kc, vc, dpos, table, scratch, rows // 128, 128, backlog, 1))
+                elif kind == "norm":
+                    pkg.check(lib.lv_norm_gemv(h, out, w, wtype, x, nw, rows, cols, args.batch))
                 elif kind == "silu":
                     pkg.check(lib.lv_gemv_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, x, rows, cols, args.batch))
                 else:
