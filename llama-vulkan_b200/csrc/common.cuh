@@ -129,21 +129,32 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Block-wide sum over up to 32 warps; `scratch` holds 33 floats of shared
-// memory.  Every thread gets the total.  Deterministic (fixed order).
+// Block-wide sums over up to 32 warps with a single barrier; `scratch` holds 64 floats of
+// shared memory that must not be in use by another reduction.  Every thread adds the warp
+// totals itself in warp order, so every thread gets the same, reproducible result.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     v = warp_sum(v);
-    __syncthreads();
+    __syncthreads();                      // the previous use of scratch is over
     if (lane == 0) scratch[warp] = v;
     __syncthreads();
-    if (warp == 0) {
-        float t = lane < nwarps ? scratch[lane] : 0.f;
-        t = warp_sum(t);
-        if (lane == 0) scratch[32] = t;
-    }
+    float t = 0.f;
+    for (int w = 0; w < nwarps; ++w) t += scratch[w];
+    return t;
+}
+
+// Two sums at once (same rules; uses scratch[0..63]).
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
     __syncthreads();
-    return scratch[32];
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+    __syncthreads();
+    float ta = 0.f, tb = 0.f;
+    for (int w = 0; w < nwarps; ++w) { ta += scratch[w]; tb += scratch[32 + w]; }
+    a = ta;
+    b = tb;
 }
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {

@@ -11,12 +11,12 @@
 // Arithmetic.  B200 has about three issue slots per weight at the HBM
 // roofline, so widening every nibble to fp32 cannot keep up.  Instead each
 // block of 32 activations is turned, once per CTA, into fixed point
-// X_e = rint(x_e * S / max|x|), S = 126 * 2^14, split into three base-128
-// digits (X = a*2^14 + b*2^7 + c; a in [-126, 126], b and c in [-64, 63]), and the inner sums
+// X_e = rint(x_e * S / max|x|), S = 63 * 2^14, split into three base-128
+// digits (X = a*2^14 + b*2^7 + c, every digit in [-64, 63]), and the inner sums
 // sum_e q_e * X_e are formed exactly in int32 with dp4a.  The block result is
 // converted to fp32 once and multiplied by d * max|x| / S; rows are
 // accumulated in fp32 and lanes combined by shuffles in a fixed order.  The
-// only rounding beyond fp32 is that of x_e to about 22 bits relative to its block
+// only rounding beyond fp32 is that of x_e to about 21 bits relative to its block
 // maximum, of the order of the reordering noise of an fp32 accumulation.
 #pragma once
 
@@ -206,26 +206,45 @@ __device__ __forceinline__ float warp_sum2(float a0, float a1, int lane) {
 // reference's normalisation is applied first (shaders/normalize.comp:39-63):
 // m = mean(x), v = mean((x-m)^2), x * w * rsqrt(v); no epsilon, numerator not
 // centred.  `scratch` holds 33 floats.
-constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
-__device__ __forceinline__ void digits_of(int X, int& a, int& b, int& c) {
-    c = ((X + 64) & 127) - 64;
-    const int X1 = (X - c) >> 7;
-    b = ((X1 + 64) & 127) - 64;
-    a = (X1 - b) >> 7;
-}
-
-__device__ __forceinline__ uint32_t pack4(int b0, int b1, int b2, int b3) {
+// Three balanced base-128 digits of four fixed-point values, packed as int8x4 words.
+// Adding 64 * (2^14 + 2^7 + 1) makes every digit of the sum non-negative, so the digits are
+// plain bit fields; subtracting 64 from each again (done on the packed bytes: flip bit 6, then
+// copy it into bit 7) gives digits in [-64, 63] whose weighted sum is the original value.
+__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
     return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
 }
+
+__device__ __forceinline__ uint32_t unbias4(uint32_t w) {
+    const uint32_t v = w ^ 0x40404040u;
+    return v | ((v & 0x40404040u) << 1);
+}
+
+__device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint32_t& wa, uint32_t& wb, uint32_t& wc) {
+    constexpr int kBias = 64 * (16384 + 128 + 1);
+    const uint32_t Y0 = uint32_t(X0 + kBias), Y1 = uint32_t(X1 + kBias), Y2 = uint32_t(X2 + kBias), Y3 = uint32_t(X3 + kBias);
+    wc = unbias4(pack4(Y0 & 127u, Y1 & 127u, Y2 & 127u, Y3 & 127u));
+    wb = unbias4(pack4((Y0 >> 7) & 127u, (Y1 >> 7) & 127u, (Y2 >> 7) & 127u, (Y3 >> 7) & 127u));
+    wa = unbias4(pack4(Y0 >> 14, Y1 >> 14, Y2 >> 14, Y3 >> 14));
+}
+
+// Builds the activation records of all K/64 block pairs in shared memory.
+// A thread owns four consecutive elements (one 16-byte load), eight adjacent
+// lanes own a block.  Everything a thread needs is fetched before anything
+// depends on it, so the vector costs one trip to L2.  With norm_w the
+// reference's normalisation is applied first (shaders/normalize.comp:39-63):
+// m = mean(x), v = mean((x-m)^2), x * w * rsqrt(v); no epsilon, numerator not
+// centred.  Mean and variance come from one pass over values shifted by x[0]
+// (sum d, sum d^2 with d = x - x[0]), which is the same quantity without the
+// cancellation of sum x^2 - n*mean^2.  `scratch` holds 64 floats.
+constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
 template <int FRAC_BITS>
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
                                                   const float* __restrict__ norm_w, uint32_t K, float* scratch) {
     const int lane = threadIdx.x & 31;
-    // largest fixed-point magnitude: 126 * 2^14, which keeps the top digit within int8 after the
-    // two lower digits have been balanced around zero
-    constexpr float kTwoF = static_cast<float>((126u << FRAC_BITS) >> 6);
+    // largest fixed-point magnitude: 63 * 2^14, so that the biased value keeps its top digit in [1, 127]
+    constexpr float kTwoF = static_cast<float>((63u << FRAC_BITS) >> 6);
     const uint32_t stride = blockDim.x * 4;
 
     for (uint32_t chunk = 0; chunk < K; chunk += stride * kActIters) {
@@ -237,24 +256,25 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
         }
         if (norm_w != nullptr) {
             // normalised inputs have length dim, which always fits one chunk
+            const float x0 = x[0];
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
                 const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
                 w[i] = e < K ? *reinterpret_cast<const float4*>(norm_w + e) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            float part = 0.f;
-#pragma unroll
-            for (int i = 0; i < kActIters; ++i) part += (v[i].x + v[i].y) + (v[i].z + v[i].w);      // absent elements hold 0
-            const float mean = block_sum(part, scratch) / static_cast<float>(K);
-            part = 0.f;
+            float s1 = 0.f, s2 = 0.f;
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
                 if (chunk + uint32_t(i) * stride + threadIdx.x * 4 < K) {
-                    const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
-                    part += (a * a + b * b) + (c * c + d * d);
+                    const float a = v[i].x - x0, b = v[i].y - x0, c = v[i].z - x0, d = v[i].w - x0;
+                    s1 += (a + b) + (c + d);
+                    s2 += (a * a + b * b) + (c * c + d * d);
                 }
             }
-            const float factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(K));
+            block_sum2(s1, s2, scratch);
+            const float md = s1 / static_cast<float>(K);                          // mean - x0
+            const float var = s2 / static_cast<float>(K) - md * md;
+            const float factor = 1.0f / sqrtf(var);
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
                 v[i].x = (v[i].x * w[i].x) * factor; v[i].y = (v[i].y * w[i].y) * factor;
@@ -270,10 +290,10 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
             const float inv = m > 0.f ? kTwoF / m : 0.f;
-            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 126 * 2^14
+            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 63 * 2^14
             const int X2 = __float2int_rn(v[i].z * inv), X3 = __float2int_rn(v[i].w * inv);
-            int a0, b0, c0, a1, b1, c1, a2, b2, c2, a3, b3, c3;
-            digits_of(X0, a0, b0, c0); digits_of(X1, a1, b1, c1); digits_of(X2, a2, b2, c2); digits_of(X3, a3, b3, c3);
+            uint32_t wa, wb, wc;
+            digit_words(X0, X1, X2, X3, wa, wb, wc);
             int T = (X0 + X1) + (X2 + X3);
             T += __shfl_xor_sync(0xffffffffu, T, 1);
             T += __shfl_xor_sync(0xffffffffu, T, 2);
@@ -281,9 +301,9 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             const uint32_t blk = e >> 5;
             uint8_t* rec = xrec + size_t(blk >> 1) * kPairBytes;
             const uint32_t at = (blk & 1) * 32 + (lane & 7) * 4;
-            *reinterpret_cast<uint32_t*>(rec + at) = pack4(a0, a1, a2, a3);
-            *reinterpret_cast<uint32_t*>(rec + 64 + at) = pack4(b0, b1, b2, b3);
-            *reinterpret_cast<uint32_t*>(rec + 128 + at) = pack4(c0, c1, c2, c3);
+            *reinterpret_cast<uint32_t*>(rec + at) = wa;
+            *reinterpret_cast<uint32_t*>(rec + 64 + at) = wb;
+            *reinterpret_cast<uint32_t*>(rec + 128 + at) = wc;
             if ((lane & 7) == 0) {
                 reinterpret_cast<int*>(rec + 192)[blk & 1] = 8 * T;
                 reinterpret_cast<float*>(rec + 200)[blk & 1] = m / kTwoF;

@@ -12,7 +12,7 @@ __global__ void __launch_bounds__(1024) norm_kernel(float* __restrict__ out, con
                                                     const float* __restrict__ w, uint32_t dim) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float scratch[33];
+    __shared__ float scratch[64];
     const float* xr = x + size_t(blockIdx.x) * dim;
     float* orow = out + size_t(blockIdx.x) * dim;
     float part = 0.f;
