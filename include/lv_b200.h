@@ -155,6 +155,18 @@ int lv_argmax_f32(lv_ctx* ctx, uint32_t* out_index, const float* v, uint32_t n);
 int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
                       uint32_t log_capacity);
 
+/* lv_argmax_f32 followed by lv_decode_advance in one launch, for the recorded
+ * greedy step: token = first index of the maximum of v[0..n) (same rules as
+ * lv_argmax_f32); token_log[old token_count + batch] = token; the four words
+ * of config grow by batch.  The token is also stored to *argmax_out (device,
+ * may be null) and to *host_token (may be null): a word of pinned host memory
+ * from lv_host_alloc, written by the kernel itself so that the step needs no
+ * separate device-to-host copy; it is valid after the stream has been
+ * synchronised.  Replaces the host-side scan and bookkeeping of
+ * llava_session.cpp:145-151,224-228. */
+int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config, uint32_t* token_log, uint32_t batch,
+                      uint32_t log_capacity, uint32_t* argmax_out, uint32_t* host_token);
+
 /* ---- fused forms used by the decode graph -------------------------------- */
 
 /* normalize + matmul wk, wq, wv + two kv_copy (llava_layer.cpp:53-58) in one

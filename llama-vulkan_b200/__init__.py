@@ -65,6 +65,7 @@ KERNEL_API = {
     "lv_dequant_rows": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_argmax_f32": (_int, [_p, _p, _p, _u32]),
     "lv_decode_advance": (_int, [_p, _p, _p, _p, _u32, _u32]),
+    "lv_argmax_advance": (_int, [_p, _p, _u32, _p, _p, _u32, _u32, _p, _p]),
     "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_comm_unique_id": (_int, [_p]),
     "lv_comm_init_rank": (_int, [_p, _p, _int, _int]),

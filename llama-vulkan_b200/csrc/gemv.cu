@@ -147,8 +147,18 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
 
     // weights never depend on the previous kernel; everything below does
     pdl_wait();
+    // a CTA that finishes in one round knows its output rows now: fetch what an add-in-place
+    // epilogue adds to before the long part instead of after it
+    const bool early_rows = cta_groups <= groups_per_round && cta_groups * kRowsPerItem <= blockDim.x;
+    float resid = 0.f;
+    if (early_rows && threadIdx.x < cta_groups * kRowsPerItem) {
+        const uint32_t gl = threadIdx.x / kRowsPerItem, rr = threadIdx.x - gl * kRowsPerItem;
+        uint32_t lg;
+        const GemvMatrix& M = locate(cta_first + gl, lg);
+        if (M.epilogue == EPI_ADD) resid = static_cast<const float*>(M.out)[size_t(z) * M.rows + lg * kRowsPerItem + rr];
+    }
     // activation records (optionally normalised) while the first weight bytes are in flight
-    stage_activations<Q::kFracBits>(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
+    stage_activations(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
     __syncthreads();
 
     int slot = 0;
@@ -220,7 +230,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
                 else atomicOr(p.err, ERR_BAD_INDEX);
             } else {
                 float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
-                *o = (M.epilogue == EPI_ADD) ? (*o + v) : v;                       // matmul.glsl:68-72
+                *o = (M.epilogue == EPI_ADD) ? ((early_rows ? resid : *o) + v) : v;   // matmul.glsl:68-72
             }
         }
         if (round_first + groups_per_round < cta_groups) __syncthreads();        // partials are reused by the next round

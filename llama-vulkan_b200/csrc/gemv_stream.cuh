@@ -11,13 +11,14 @@
 // Arithmetic.  B200 has about three issue slots per weight at the HBM
 // roofline, so widening every nibble to fp32 cannot keep up.  Instead each
 // block of 32 activations is turned, once per CTA, into fixed point
-// X_e = rint(x_e * S / max|x|), S = 63 * 2^14, split into three base-128
-// digits (X = a*2^14 + b*2^7 + c, every digit in [-64, 63]), and the inner sums
-// sum_e q_e * X_e are formed exactly in int32 with dp4a.  The block result is
-// converted to fp32 once and multiplied by d * max|x| / S; rows are
-// accumulated in fp32 and lanes combined by shuffles in a fixed order.  The
-// only rounding beyond fp32 is that of x_e to about 21 bits relative to its block
-// maximum, of the order of the reordering noise of an fp32 accumulation.
+// X_e = rint(x_e * S / max|x|), S = 31 * 2^16, split into three balanced
+// base-256 digits (X = a*2^16 + b*2^8 + c, every digit an int8, |a| <= 32), and
+// the inner sums sum_e q_e * X_e are formed exactly in int32 with dp4a (the
+// bound on a keeps 15 * 32 * |X| below 2^31).  The block result is converted
+// to fp32 once and multiplied by d * max|x| / S; rows are accumulated in fp32
+// and lanes combined by shuffles in a fixed order.  The only rounding beyond
+// fp32 is that of x_e to about 22 bits relative to its block maximum, of the
+// order of the reordering noise of an fp32 accumulation.
 #pragma once
 
 #include "common.cuh"
@@ -35,14 +36,16 @@ template <> struct QTraits<T_Q4_0> {
     static constexpr int kBlockBytes = kQ4BlockBytes;
     static constexpr int kPairWords = 9;
     static constexpr int kWarps = 16;                 // consumer warps per CTA
-    static constexpr int kFracBits = 20;              // activations are scaled to +-1.99 * 2^kFracBits
 };
 template <> struct QTraits<T_Q8_0> {
     static constexpr int kBlockBytes = kQ8BlockBytes;
     static constexpr int kPairWords = 17;
     static constexpr int kWarps = 8;
-    static constexpr int kFracBits = 20;
 };
+
+// largest fixed-point magnitude of an activation: top digit at most 31 (32 after the rounding
+// slack of the approximate reciprocal)
+constexpr float kFixedOne = 31.0f * 65536.0f;
 
 // What to do with a finished row.
 enum : int { EPI_STORE = 0, EPI_ADD = 1, EPI_STORE_F16_AT_POS = 2 };
@@ -113,11 +116,11 @@ __device__ __forceinline__ int block_sum_q4(const uint32_t (&q)[4], const uint32
         ah = dp4a_us(hi, a[4 + k], ah); bh = dp4a_us(hi, b[4 + k], bh); ch = dp4a_us(hi, c[4 + k], ch);
     }
     // the high-nibble sums are exact multiples of 16
-    const int hi_ab = (ah * 128 + bh) >> 4;
-    return ((al * 128 + bl + hi_ab) * 128 + cl + (ch >> 4)) - t8;
+    const int hi_ab = (ah * 256 + bh) >> 4;
+    return ((al * 256 + bl + hi_ab) * 256 + cl + (ch >> 4)) - t8;
 }
 
-// sum_e int8_e * X_e of one q8_0 block.  The exact integer can reach 2^32, so the two upper
+// sum_e int8_e * X_e of one q8_0 block.  The exact integer can exceed 2^31, so the two upper
 // digits and the lowest one are converted separately (the first conversion rounds to 24 bits,
 // like any fp32 accumulation would).
 __device__ __forceinline__ float block_sum_q8(const uint32_t (&q)[8], const uint32_t* __restrict__ a,
@@ -127,7 +130,7 @@ __device__ __forceinline__ float block_sum_q8(const uint32_t (&q)[8], const uint
     for (int k = 0; k < 8; ++k) {
         sa = dp4a_ss(q[k], a[k], sa); sb = dp4a_ss(q[k], b[k], sb); sc = dp4a_ss(q[k], c[k], sc);
     }
-    return fmaf(static_cast<float>(sa * 128 + sb), 128.0f, static_cast<float>(sc));
+    return fmaf(static_cast<float>(sa * 256 + sb), 256.0f, static_cast<float>(sc));
 }
 
 // Contribution of one lane's block pair to one row stream.
@@ -199,33 +202,18 @@ __device__ __forceinline__ float warp_sum2(float a0, float a1, int lane) {
     return u;
 }
 
-// Builds the activation records of all K/64 block pairs in shared memory.
-// A thread owns four consecutive elements (one 16-byte load), eight adjacent
-// lanes own a block.  Everything a thread needs is fetched before anything
-// depends on it, so the vector costs one trip to L2.  With norm_w the
-// reference's normalisation is applied first (shaders/normalize.comp:39-63):
-// m = mean(x), v = mean((x-m)^2), x * w * rsqrt(v); no epsilon, numerator not
-// centred.  `scratch` holds 33 floats.
-
-// Three balanced base-128 digits of four fixed-point values, packed as int8x4 words.
-// Adding 64 * (2^14 + 2^7 + 1) makes every digit of the sum non-negative, so the digits are
-// plain bit fields; subtracting 64 from each again (done on the packed bytes: flip bit 6, then
-// copy it into bit 7) gives digits in [-64, 63] whose weighted sum is the original value.
-__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
-    return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
-}
-
-__device__ __forceinline__ uint32_t unbias4(uint32_t w) {
-    const uint32_t v = w ^ 0x40404040u;
-    return v | ((v & 0x40404040u) << 1);
-}
-
+// Three balanced base-256 digits of four fixed-point values, packed as int8x4 words.
+// Adding 128 * (2^16 + 2^8 + 1) makes every digit of the sum non-negative, so the digits are
+// the bytes of the sum; flipping bit 7 of each byte subtracts the 128 again and leaves int8
+// digits whose weighted sum is the original value.
 __device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint32_t& wa, uint32_t& wb, uint32_t& wc) {
-    constexpr int kBias = 64 * (16384 + 128 + 1);
+    constexpr int kBias = 128 * (65536 + 256 + 1);
     const uint32_t Y0 = uint32_t(X0 + kBias), Y1 = uint32_t(X1 + kBias), Y2 = uint32_t(X2 + kBias), Y3 = uint32_t(X3 + kBias);
-    wc = unbias4(pack4(Y0 & 127u, Y1 & 127u, Y2 & 127u, Y3 & 127u));
-    wb = unbias4(pack4((Y0 >> 7) & 127u, (Y1 >> 7) & 127u, (Y2 >> 7) & 127u, (Y3 >> 7) & 127u));
-    wa = unbias4(pack4(Y0 >> 14, Y1 >> 14, Y2 >> 14, Y3 >> 14));
+    const uint32_t p01 = __byte_perm(Y0, Y1, 0x5140), p23 = __byte_perm(Y2, Y3, 0x5140);   // (c0 c1 b0 b1), (c2 c3 b2 b3)
+    const uint32_t q01 = __byte_perm(Y0, Y1, 0x0062), q23 = __byte_perm(Y2, Y3, 0x0062);   // (a0 a1 . .), (a2 a3 . .)
+    wc = __byte_perm(p01, p23, 0x5410) ^ 0x80808080u;
+    wb = __byte_perm(p01, p23, 0x7632) ^ 0x80808080u;
+    wa = __byte_perm(q01, q23, 0x5410) ^ 0x80808080u;
 }
 
 // Builds the activation records of all K/64 block pairs in shared memory.
@@ -239,12 +227,9 @@ __device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint
 // cancellation of sum x^2 - n*mean^2.  `scratch` holds 64 floats.
 constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
-template <int FRAC_BITS>
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
                                                   const float* __restrict__ norm_w, uint32_t K, float* scratch) {
     const int lane = threadIdx.x & 31;
-    // largest fixed-point magnitude: 63 * 2^14, so that the biased value keeps its top digit in [1, 127]
-    constexpr float kTwoF = static_cast<float>((63u << FRAC_BITS) >> 6);
     const uint32_t stride = blockDim.x * 4;
 
     for (uint32_t chunk = 0; chunk < K; chunk += stride * kActIters) {
@@ -289,8 +274,10 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-            const float inv = m > 0.f ? kTwoF / m : 0.f;
-            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 63 * 2^14
+            // an approximate quotient is enough: the record keeps whatever integers come out, and
+            // their scale is off by an fp32 rounding or two at most
+            const float inv = m > 1e-30f ? __fdividef(kFixedOne, m) : 0.f;     // smaller blocks count as zero
+            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 31 * 2^16 (+ slack)
             const int X2 = __float2int_rn(v[i].z * inv), X3 = __float2int_rn(v[i].w * inv);
             uint32_t wa, wb, wc;
             digit_words(X0, X1, X2, X3, wa, wb, wc);
@@ -306,7 +293,7 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             *reinterpret_cast<uint32_t*>(rec + 128 + at) = wc;
             if ((lane & 7) == 0) {
                 reinterpret_cast<int*>(rec + 192)[blk & 1] = 8 * T;
-                reinterpret_cast<float*>(rec + 200)[blk & 1] = m / kTwoF;
+                reinterpret_cast<float*>(rec + 200)[blk & 1] = m * (1.0f / kFixedOne);
             }
         }
     }

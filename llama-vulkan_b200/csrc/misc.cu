@@ -102,16 +102,38 @@ __device__ __forceinline__ void argmax_merge(float& best, uint32_t& bi, float ov
     if (bi == kNoIndex || ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out, const float* __restrict__ v, uint32_t n) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ float s_val[32];
-    __shared__ uint32_t s_idx[32];
+// First index of the maximum of v[0..n) over a 1024-thread CTA; the result is valid in thread 0.
+// Elements that are NaN never win; kNoIndex if every element is NaN.  A thread looks at its
+// elements in ascending order and keeps a candidate only on a strict improvement, and the merges
+// prefer the lower index among equals, so the lowest index of the maximum comes out
+// (llava_session.cpp:145-151).  All loads of a thread are issued before the first compare.
+__device__ __forceinline__ uint32_t block_argmax(const float* __restrict__ v, uint32_t n, float* s_val, uint32_t* s_idx) {
+    constexpr int kVec = 8;                                   // float4 loads in flight per thread
     float best = 0.f;
     uint32_t bi = kNoIndex;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(v) & 15u) == 0;
+    const uint32_t n4 = vec_ok ? n / 4 : 0;
+    for (uint32_t base = 0; base < n4; base += blockDim.x * kVec) {
+        float4 q[kVec];
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) {
+            const uint32_t i = base + k * blockDim.x + threadIdx.x;
+            q[k] = i < n4 ? __ldcg(reinterpret_cast<const float4*>(v) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) {
+            const uint32_t i = base + k * blockDim.x + threadIdx.x;
+            if (i < n4) {
+                const float e[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (e[j] == e[j] && (bi == kNoIndex || e[j] > best)) { best = e[j]; bi = 4 * i + j; }
+            }
+        }
+    }
+    for (uint32_t i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
         const float x = v[i];
-        if (x == x && (bi == kNoIndex || x > best)) { best = x; bi = i; }
+        if (x == x && (bi == kNoIndex || x > best || (x == best && i < bi))) { best = x; bi = i; }
     }
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -130,9 +152,47 @@ __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out
             const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
             argmax_merge(best, bi, ov, oi);
         }
-        if (lane == 0) {
-            const float first = v[0];
-            *out = (bi == kNoIndex || first != first) ? 0u : bi;
+    }
+    return bi;
+}
+
+// The reference returns index 0 when the scan never improves on element 0, which includes a NaN
+// in element 0 (every comparison with it is false).
+__device__ __forceinline__ uint32_t argmax_result(uint32_t bi, const float* v) {
+    const float first = v[0];
+    return (bi == kNoIndex || first != first) ? 0u : bi;
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out, const float* __restrict__ v, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ uint32_t s_idx[32];
+    const uint32_t bi = block_argmax(v, n, s_val, s_idx);
+    if (threadIdx.x == 0) *out = argmax_result(bi, v);
+}
+
+// argmax and the step's bookkeeping in one launch: the winner goes to token_log[old count + batch]
+// (input of the next step), to *argmax_out and, when given, to a word of mapped host memory.
+__global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __restrict__ v, uint32_t n, uint32_t* config,
+                                                              uint32_t* token_log, uint32_t batch, uint32_t log_capacity,
+                                                              uint32_t* argmax_out, volatile uint32_t* host_token, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ uint32_t s_idx[32];
+    const uint32_t count = threadIdx.x == 0 ? config[0] : 0u;           // in flight together with the logits
+    const uint32_t bi = block_argmax(v, n, s_val, s_idx);
+    if (threadIdx.x == 0) {
+        const uint32_t token = argmax_result(bi, v);
+        const uint32_t at = count + batch;
+        if (at < log_capacity) token_log[at] = token;
+        else atomicOr(err, ERR_BAD_INDEX);
+        if (argmax_out != nullptr) *argmax_out = token;
+        for (int i = 0; i < 4; ++i) config[i] = count + batch;
+        if (host_token != nullptr) {
+            *host_token = token;
+            __threadfence_system();
         }
     }
 }
@@ -158,6 +218,15 @@ extern "C" int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* 
     LV_ENTER(ctx);
     LV_REQUIRE(config && batch, "bad advance arguments");
     LV_CUDA(launch_pdl(ctx, decode_advance_kernel, dim3(1), dim3(1), 0, config, argmax, token_log, batch, log_capacity, ctx->d_err));
+    return LV_OK;
+}
+
+extern "C" int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config, uint32_t* token_log,
+                                 uint32_t batch, uint32_t log_capacity, uint32_t* argmax_out, uint32_t* host_token) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(v && n && config && token_log && batch, "bad argmax_advance arguments");
+    LV_CUDA(launch_pdl(ctx, argmax_advance_kernel, dim3(1), dim3(1024), 0, v, n, config, token_log, batch, log_capacity,
+                       argmax_out, static_cast<volatile uint32_t*>(host_token), ctx->d_err));
     return LV_OK;
 }
 

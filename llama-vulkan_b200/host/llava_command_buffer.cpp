@@ -74,10 +74,11 @@ bool llava_command_buffer::record_execution() {
         float* logits = static_cast<float*>(s->output_probs->device_ptr());
         note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), int(c->output_w->type), last,
                           static_cast<const float*>(c->norm_w->device_ptr()), h.vocab_size, h.dim, 1));
+        // greedy choice, token log and position word in one launch; the kernel stores the token
+        // into the pinned staging word itself
         u32* am = static_cast<u32*>(s->argmax_result->device_ptr());
-        note(lv_argmax_f32(lv(), am, logits, h.vocab_size));
-        note(lv_decode_advance(lv(), config, am, log, batch_size, max_backlog_size + 1));
-        note(lv_download_async(lv(), s->pinned + max_backlog_size + 4, am, 4));
+        note(lv_argmax_advance(lv(), logits, h.vocab_size, config, log, batch_size, max_backlog_size + 1, am,
+                               s->pinned + max_backlog_size + 4));
     } else {
         // leading chunk of a prompt: only the position advances
         note(lv_decode_advance(lv(), config, nullptr, nullptr, batch_size, 0));

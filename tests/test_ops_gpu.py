@@ -303,6 +303,53 @@ def test_argmax_copy_add(gpu, pkg):
     assert np.array_equal(gpu.download(da, np.float32, a.size), a + b)
 
 
+def test_argmax_odd_sizes_and_unaligned_start(gpu, pkg):
+    rng = np.random.default_rng(35)
+    lib, h = gpu.lib, gpu.handle
+    d_idx = gpu.alloc(16)
+    big = rng.standard_normal(40000).astype(np.float32)
+    big[[3, 20001, 39999]] = 9.0                        # equal maxima at both ends of the vector paths
+    d_big = gpu.upload(big)
+    for first, n in ((0, 1), (0, 3), (1, 4097), (0, 32769), (2, 39998), (3, 37), (4, 36001)):
+        pkg.check(lib.lv_argmax_f32(h, d_idx, C.c_void_p(d_big.value + 4 * first), n))
+        gpu.sync()
+        v = np.ascontiguousarray(big[first:first + n])
+        assert gpu.download(d_idx, np.uint32, 1)[0] == ob.load().orc_argmax(ob.ptr(v), n), (first, n)
+
+
+def test_argmax_advance_logs_the_token_and_moves_the_position(gpu, pkg):
+    """One launch = lv_argmax_f32 + lv_decode_advance, plus the token in mapped host memory."""
+    rng = np.random.default_rng(36)
+    lib, h = gpu.lib, gpu.handle
+    host = C.c_void_p()
+    pkg.check(lib.lv_host_alloc(h, 64, C.byref(host)))
+    word = (C.c_uint32 * 16).from_address(host.value)
+    try:
+        for case, batch in ((0, 1), (1, 3), (2, 1)):
+            v = rng.standard_normal(32000).astype(np.float32)
+            if case == 1:
+                v[[31000, 42]] = v.max() + 2
+            if case == 2:
+                v[0] = np.nan
+            want = ob.load().orc_argmax(ob.ptr(v), v.size)
+            cfg, log, am = u32_dev(gpu, 7), gpu.upload(np.full(32, 0xFFFFFFFF, np.uint32)), gpu.zeros(4)
+            word[5] = 0xDEADBEEF
+            pkg.check(lib.lv_argmax_advance(h, gpu.upload(v), v.size, cfg, log, batch, 32, am, C.c_void_p(host.value + 20)))
+            gpu.sync()
+            assert word[5] == want
+            assert gpu.download(am, np.uint32, 1)[0] == want
+            got_log = gpu.download(log, np.uint32, 32)
+            assert got_log[7 + batch] == want and (np.delete(got_log, 7 + batch) == 0xFFFFFFFF).all()
+            assert (gpu.download(cfg, np.uint32, 4) == 7 + batch).all()
+        # a log index outside the log is reported, not written
+        cfg, log = u32_dev(gpu, 31), gpu.upload(np.full(32, 0xFFFFFFFF, np.uint32))
+        pkg.check(lib.lv_argmax_advance(h, gpu.upload(np.ones(64, np.float32)), 64, cfg, log, 1, 32, None, None))
+        assert lib.lv_stream_sync(h, 10000) == pkg.LV_ERR_DEVICE_WAIT
+        assert (gpu.download(log, np.uint32, 32) == 0xFFFFFFFF).all()
+    finally:
+        pkg.check(lib.lv_host_free(h, host))
+
+
 def test_graph_capture_replays_with_a_new_position(gpu, pkg, rope_table):
     """The recorded step reads the position from device memory, so one graph serves every token."""
     rng = np.random.default_rng(34)
