@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
         }
         __syncthreads();
         // one thread per row of the round: add its segments in order, then the epilogue
+        const bool finishing = threadIdx.x < round_groups * kRowsPerItem;
+        const float factor = (p.norm_w != nullptr && finishing) ? norm_factor(scratch, p.K) : 1.0f;
         for (uint32_t t = threadIdx.x; t < round_groups * kRowsPerItem; t += blockDim.x) {
             const uint32_t gl = t / kRowsPerItem, rr = t - gl * kRowsPerItem;
             const float* src = part + size_t(gl) * nseg * NS;
@@ -215,10 +217,13 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
                     up += src[sg * NS + kUp * rr];
                     gate += src[sg * NS + kUp * rr + kGateOff];
                 }
+                up *= factor;
+                gate *= factor;
                 v = up * gate / (expf(-gate) + 1.0f);                   // matmul_silu_ff.comp:95
             } else {
                 v = 0.f;
                 for (uint32_t sg = 0; sg < nseg; ++sg) v += src[sg * NS + rr];
+                v *= factor;
             }
             uint32_t lg;
             const GemvMatrix& M = locate(cta_first + round_first + gl, lg);

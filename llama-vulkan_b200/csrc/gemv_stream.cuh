@@ -219,12 +219,18 @@ __device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint
 // Builds the activation records of all K/64 block pairs in shared memory.
 // A thread owns four consecutive elements (one 16-byte load), eight adjacent
 // lanes own a block.  Everything a thread needs is fetched before anything
-// depends on it, so the vector costs one trip to L2.  With norm_w the
-// reference's normalisation is applied first (shaders/normalize.comp:39-63):
-// m = mean(x), v = mean((x-m)^2), x * w * rsqrt(v); no epsilon, numerator not
-// centred.  Mean and variance come from one pass over values shifted by x[0]
-// (sum d, sum d^2 with d = x - x[0]), which is the same quantity without the
-// cancellation of sum x^2 - n*mean^2.  `scratch` holds 64 floats.
+// depends on it, so the vector costs one trip to L2.
+//
+// With norm_w the reference's normalisation (shaders/normalize.comp:39-63:
+// m = mean(x), v = mean((x-m)^2), out = x * w * rsqrt(v); no epsilon, numerator
+// not centred) is split in two.  The records hold x * w: the fixed-point digits
+// of a block do not change when the whole vector is multiplied by a constant,
+// only the block scales do.  The constant rsqrt(v) multiplies the finished row
+// sums instead (norm_factor below), which takes the block-wide reduction and
+// the square root off the path to the first weight.  Mean and variance come
+// from one pass over values shifted by x[0] (sum d, sum d^2 with d = x - x[0]),
+// which is the same quantity without the cancellation of sum x^2 - n*mean^2.
+// `scratch` holds 64 floats: the per-warp partial sums.
 constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
@@ -256,14 +262,13 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
                     s2 += (a * a + b * b) + (c * c + d * d);
                 }
             }
-            block_sum2(s1, s2, scratch);
-            const float md = s1 / static_cast<float>(K);                          // mean - x0
-            const float var = s2 / static_cast<float>(K) - md * md;
-            const float factor = 1.0f / sqrtf(var);
+            // per-warp sums go to scratch; norm_factor() adds them up after the caller's barrier
+            s1 = warp_sum(s1);
+            s2 = warp_sum(s2);
+            if (lane == 0) { scratch[threadIdx.x >> 5] = s1; scratch[32 + (threadIdx.x >> 5)] = s2; }
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
-                v[i].x = (v[i].x * w[i].x) * factor; v[i].y = (v[i].y * w[i].y) * factor;
-                v[i].z = (v[i].z * w[i].z) * factor; v[i].w = (v[i].w * w[i].w) * factor;
+                v[i].x *= w[i].x; v[i].y *= w[i].y; v[i].z *= w[i].z; v[i].w *= w[i].w;
             }
         }
 #pragma unroll
@@ -297,6 +302,17 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             }
         }
     }
+}
+
+// rsqrt of the variance from the partial sums stage_activations left in scratch; call after a
+// CTA barrier.  The warps' sums are added in warp order, so every thread gets the same bits.
+__device__ __forceinline__ float norm_factor(const float* scratch, uint32_t K) {
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float s1 = 0.f, s2 = 0.f;
+    for (int w = 0; w < nwarps; ++w) { s1 += scratch[w]; s2 += scratch[32 + w]; }
+    const float md = s1 / static_cast<float>(K);                          // mean - x[0]
+    const float var = s2 / static_cast<float>(K) - md * md;
+    return 1.0f / sqrtf(var);
 }
 
 }  // namespace lv
