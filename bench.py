@@ -160,17 +160,20 @@ def time_dominant_kernel(pkg, ctx_handle_lv, dim, ff, wtype, stream, torch):
     host = np.tile(slab, reps)[:mat_bytes]
     copies = max(3, int(400e6 // (2 * mat_bytes)) + 1)  # > 400 MB in the ring, well over the 126 MB L2
     d = C.c_void_p()
-    pkg.check(lib.lv_arena_create(ctx_handle_lv, copies * 2 * mat_bytes + ff * 4 + dim * 4, C.byref(d)))
+    pkg.check(lib.lv_arena_create(ctx_handle_lv, copies * 2 * mat_bytes + ff * 4 + 2 * dim * 4, C.byref(d)))
     for i in range(copies * 2):
         pkg.check(lib.lv_upload(ctx_handle_lv, C.c_void_p(d.value + i * mat_bytes), host.ctypes.data_as(C.c_void_p), mat_bytes))
     x = rng.standard_normal(dim).astype(np.float32)
     dx = C.c_void_p(d.value + copies * 2 * mat_bytes)
-    dout = C.c_void_p(dx.value + dim * 4)
+    dnorm = C.c_void_p(dx.value + dim * 4)
+    dout = C.c_void_p(dnorm.value + dim * 4)
+    norm_w = (1.0 + 0.01 * rng.standard_normal(dim)).astype(np.float32)
     pkg.check(lib.lv_upload(ctx_handle_lv, dx, x.ctypes.data_as(C.c_void_p), dim * 4))
+    pkg.check(lib.lv_upload(ctx_handle_lv, dnorm, norm_w.ctypes.data_as(C.c_void_p), dim * 4))
     def launch(i):
         w3 = C.c_void_p(d.value + (2 * (i % copies)) * mat_bytes)
         w1 = C.c_void_p(w3.value + mat_bytes)
-        pkg.check(lib.lv_gemv_silu(ctx_handle_lv, dout, w3, w1, wtype, dx, ff, dim, 1))
+        pkg.check(lib.lv_norm_gate_up_silu(ctx_handle_lv, dout, w3, w1, wtype, dx, dnorm, ff, dim, 1))   # as the decode step calls it
     for i in range(copies):
         launch(i)
     pkg.check(lib.lv_stream_sync(ctx_handle_lv, 0))
@@ -377,8 +380,8 @@ def main():
     tps = args.steps / sec_dev
     achieved = k_bytes / k_sec / 1e9
     peak_all = peak * world                               # aggregate bandwidth of the N GPUs for the whole step
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<q4_0, SILU> (norm + gate/up + SiLU, 11008x4096 pair)" if w["wtype"] == 2
-                else "gemv_kernel<q8_0, SILU>", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+    roofline = {"bound": "hbm", "kernel": f"gemv_kernel<{'q4_0' if w['wtype'] == 2 else 'q8_0'}, SILU> (norm + gate/up + SiLU, "
+                                          f"{ff // world}x{dim} pair)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}",
                 # dram__bytes_read + dram__bytes_write of one launch of this kernel at this shape (ncu capture summarised
                 # in profiles/gemv_silu_q4_0_11008x4096.md); no capture exists for the other shapes
