@@ -167,6 +167,39 @@ int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uin
 int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config, uint32_t* token_log, uint32_t batch,
                       uint32_t log_capacity, uint32_t* argmax_out, uint32_t* host_token);
 
+/* ---- batched products on the tensor cores (prompt evaluation) -------------- */
+
+/* When 16 or more tokens are evaluated together the reference dispatches its
+ * matmul shaders with the batch in gl_WorkGroupID.z (llava_command_buffer.cpp:
+ * 61-132), streaming every matrix once per token.  These entry points read the
+ * matrix once for up to 64 tokens: q4_0 blocks are dequantised in the kernel
+ * into exact fp16 (hi, lo) tiles and multiplied on the tcgen05 tensor cores
+ * with fp32 accumulation.  The activations enter as the two fp16 planes that
+ * lv_act_split_f16 writes.  rows: multiple of 128 (64 for the SiLU pair);
+ * cols: multiple of 256; batch 1..64; wtype must be q4_0 (2). */
+
+/* Bytes of the split-activation buffer for [batch][cols] inputs. */
+size_t lv_act_split_bytes(uint32_t cols, uint32_t batch);
+
+/* xh = (hi, lo) fp16 planes of x [batch][cols], hi + lo = x to 22 bits; with
+ * norm_w the reference's normalisation (shaders/normalize.comp:39-63) is
+ * applied first.  Rows up to the next multiple of 16 are zero-filled. */
+int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch);
+
+/* out[z][r] (+)= sum_k W[r][k] x[z][k]: matmul / matmul_add_inplace for a batch. */
+int lv_gemm_tc(lv_ctx* ctx, float* out, const void* W, int wtype, const void* xh, uint32_t rows, uint32_t cols,
+               uint32_t batch, int add);
+
+/* matmul_silu_ff for a batch (shaders/matmul_silu_ff.comp:49-97). */
+int lv_gemm_tc_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const void* xh, uint32_t ff,
+                    uint32_t dim, uint32_t batch);
+
+/* wk, wq, wv products of a batch with the K and V rows written as f16 into the
+ * caches at rows *pos + z (llava_layer.cpp:53-58); xh holds the normalised input. */
+int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq, const void* wk,
+                            const void* wv, int wtype, const void* xh, const uint32_t* pos, uint32_t rows_each,
+                            uint32_t dim, uint32_t batch, uint32_t ctx_rows);
+
 /* ---- fused forms used by the decode graph -------------------------------- */
 
 /* normalize + matmul wk, wq, wv + two kv_copy (llava_layer.cpp:53-58) in one

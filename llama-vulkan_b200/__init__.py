@@ -82,6 +82,11 @@ KERNEL_API = {
     "lv_attention_fused": (_int, [_p, _p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_attention_static_scratch_limit": (_sz, []),
     "lv_attention_fused_static": (_int, [_p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
+    "lv_act_split_bytes": (_sz, [_u32, _u32]),
+    "lv_act_split_f16": (_int, [_p, _p, _p, _p, _u32, _u32]),
+    "lv_gemm_tc": (_int, [_p, _p, _p, _int, _p, _u32, _u32, _u32, _int]),
+    "lv_gemm_tc_silu": (_int, [_p, _p, _p, _p, _int, _p, _u32, _u32, _u32]),
+    "lv_gemm_tc_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_norm_gate_up_silu": (_int, [_p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_norm_gemv": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
 }

@@ -64,6 +64,7 @@ extern "C" int lv_ctx_create(int device, lv_ctx** out) {
     *ctx->h_err = 0;
     int rc = gemv_configure(ctx);
     if (rc == LV_OK) rc = attention_configure(ctx);
+    if (rc == LV_OK) rc = gemm_tc_configure(ctx);
     if (rc != LV_OK) {
         lv_ctx_destroy(ctx);
         return rc;

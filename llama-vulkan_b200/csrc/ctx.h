@@ -29,6 +29,7 @@ int fail(int code, const std::string& msg);
 int cuda_fail(cudaError_t e, const char* what);
 int gemv_configure(lv_ctx* ctx);
 int attention_configure(lv_ctx* ctx);
+int gemm_tc_configure(lv_ctx* ctx);
 
 #define LV_CUDA(call)                                          \
     do {                                                       \

@@ -1,0 +1,541 @@
+// Batched (multi-token) matrix products on the tcgen05 tensor cores.
+//
+// The decode step multiplies every matrix by one activation vector (gemv.cu).  When a prompt
+// is evaluated, 16 or more tokens share each matrix, the contraction becomes dense and the
+// reference's per-token shader dispatches (matmul.glsl with a batch in gl_WorkGroupID.z,
+// llava_command_buffer.cpp:61-132) are replaced by one pass over the weights:
+//
+//   out[z][r] = sum_k W[r][k] * x[z][k]        r: 128 rows per CTA, z < Z <= 64
+//
+// A operand: the q4_0 blocks of 128 rows, fetched by 2-D tensor-map TMA loads into a raw
+// ring, dequantised by sixteen warps into K-major fp16 tiles with the 128-byte swizzle.  A
+// weight (q - 8) * d needs up to 14 significant bits, so it is written as an exact pair
+// hi = fp16(w), lo = w - hi.  B operand: the activations as an exact-to-22-bits pair of fp16
+// planes (lv_act_split_f16), fetched by swizzled TMA loads (the lo plane's rows follow the hi
+// plane's, so one B tile of 2Z rows serves both).  One thread issues, per 64 columns of K,
+// four K=16 steps of two tcgen05.mma: W_hi x [x_hi; x_lo] (N = 2Z) and W_lo x x_hi (N = Z)
+// into three 128 x Z fp32 accumulators in tensor memory (lo*lo is below fp32 resolution).
+// Four warps read the accumulators back with tcgen05.ld, add them and apply the epilogue
+// (store / add to the residual / f16 cache rows at the position / SiLU gate of a row pair).
+//
+// Every wait is bounded (common.cuh); a lost wait sets the context's error word, the CTA
+// drains and frees its tensor memory.
+#include <cuda.h>
+
+#include <string>
+
+#include "common.cuh"
+#include "ctx.h"
+#include "gemv_stream.cuh"
+#include "tmap.h"
+
+namespace lv {
+
+constexpr int kTcRows = 128;                   // rows of W per CTA = M of the MMA
+constexpr int kTcMaxZ = 64;                    // tokens per launch = N of the MMA (padded to 16)
+constexpr int kTcChunkK = 64;                  // K per A/B tile: 64 fp16 = one 128-byte swizzle row
+constexpr int kTcRawBlocks = 8;                // q-blocks of a row per raw stage (4 tiles of K)
+constexpr int kTcRawRowBytes = kTcRawBlocks * kQ4BlockBytes;          // 144
+constexpr int kTcRawStage = kTcRows * kTcRawRowBytes;                 // 18432
+constexpr int kTcRawStages = 2;
+constexpr int kTcSlots = 3;
+constexpr int kTcTileBytes = kTcRows * kTcChunkK * 2;                 // 16384: one fp16 plane of A
+constexpr int kTcSlotBytes = 2 * kTcTileBytes;                        // 32768: hi and lo planes of A
+constexpr int kTcBRingBytes = 65536;           // ring of B tiles (hi and lo planes, 2 zpad rows of 128 bytes each)
+constexpr int kTcMaxBStages = 16;
+constexpr int kTcBanks = 2;                    // accumulator sets used in turn, to halve the length of each fp32 chain
+constexpr int kTcProducerWarps = 16;           // two groups of 8: even and odd tiles of K
+constexpr int kTcGroupWarps = 8;
+constexpr int kTcThreads = (kTcProducerWarps + 2) * 32;               // + TMA warp + MMA warp
+constexpr size_t kTcSmemBytes = 1024 /* alignment slack */ + size_t(kTcSlots) * kTcSlotBytes + kTcBRingBytes +
+                                size_t(kTcRawStages) * kTcRawStage + 512;
+
+struct GemmTcParams {
+    GemvMatrix m[3];         // same meaning as in the GEMV; w_gate set = SiLU pair (64 + 64 rows per CTA)
+    int n_mat;
+    const uint32_t* pos;     // device word for EPI_STORE_F16_AT_POS
+    uint32_t K;
+    uint32_t Z;              // tokens (columns actually written)
+    uint32_t zpad;           // Z rounded up to 16 = N of the MMA
+    uint32_t ctx_rows;
+    uint32_t* err;
+};
+
+struct GemmTcMaps {
+    CUtensorMap w[3];
+    CUtensorMap gate;
+    CUtensorMap x;           // [2 * zpad][K] fp16: hi plane rows, then lo plane rows
+};
+
+__device__ __forceinline__ void tma_load_2d_plain(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], fp16 inputs, fp32 accumulation; issued by one thread.
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16) with the
+// 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+    return uint64_t((smem_addr >> 4) & 0x3fffu) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+           (uint64_t(2) << 61);
+}
+
+// Where the 16-byte chunk `c` (0..7) of row `r` lives inside a swizzled tile.
+__device__ __forceinline__ uint32_t tc_swizzled(uint32_t r, uint32_t c) {
+    return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4);
+}
+
+// Eight nibbles of one word -> exact (hi, lo) fp16 pairs of (q - 8) * d.
+// Output order: e[0] = elements (4k, 4k+1), e[1] = (4k+2, 4k+3), e[2] = (16+4k, 17+4k), e[3] = (18+4k, 19+4k).
+__device__ __forceinline__ void dequant_word(uint32_t w, __half2 d2, __half2 (&hi)[4], __half2 (&lo)[4]) {
+    const uint32_t v01 = __byte_perm(w, 0u, 0x4140), v23 = __byte_perm(w, 0u, 0x4342);       // (b0, b1), (b2, b3) in 16-bit lanes
+    const uint32_t raw[4] = {(v01 & 0x000f000fu) | 0x64006400u, (v23 & 0x000f000fu) | 0x64006400u,
+                             ((v01 >> 4) & 0x000f000fu) | 0x64006400u, ((v23 >> 4) & 0x000f000fu) | 0x64006400u};   // 1024 + q
+    const __half2 off = __floats2half2_rn(1032.0f, 1032.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&raw[i]), off);      // q - 8, exact
+        hi[i] = __hmul2(q, d2);
+        lo[i] = __hfma2(q, d2, __hneg2(hi[i]));                                            // exact remainder
+    }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcParams p, const __grid_constant__ GemmTcMaps maps) {
+    pdl_launch_dependents();
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    uint8_t* slots = smem;
+    uint8_t* bring = smem + kTcSlots * kTcSlotBytes;
+    uint8_t* rawring = bring + kTcBRingBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rawring + kTcRawStages * kTcRawStage);
+    uint64_t* raw_full = bars;                       // [2]
+    uint64_t* raw_empty = bars + 2;                  // [2]
+    uint64_t* slot_full = bars + 4;                  // [3]
+    uint64_t* slot_empty = bars + 7;                 // [3]
+    uint64_t* acc_full = bars + 10;
+    uint64_t* b_full = bars + 12;                    // [16]
+    uint64_t* b_empty = bars + 28;                   // [16]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 44);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool pair = p.m[0].w_gate != nullptr;
+    const uint32_t rows_per_cta = pair ? kTcRows / 2 : kTcRows;
+
+    // which matrix this CTA works on, and its first row there
+    uint32_t t0 = p.m[0].rows / rows_per_cta;
+    uint32_t t1 = t0 + (p.n_mat > 1 ? p.m[1].rows / rows_per_cta : 0);
+    int mi = 0;
+    uint32_t tile = blockIdx.x;
+    if (tile >= t1) { mi = 2; tile -= t1; }
+    else if (tile >= t0) { mi = 1; tile -= t0; }
+    const GemvMatrix& M = p.m[mi];
+    const uint32_t row0 = tile * rows_per_cta;
+
+    const uint32_t n_chunks = p.K / kTcChunkK;
+    const uint32_t b_bytes = 2u * p.zpad * kTcChunkK * 2u;
+    const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kTcBRingBytes) / b_bytes);      // B stages: 4 (zpad 64) .. 16
+    // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
+    // the allocation is a power of two >= 32
+    const uint32_t bank_cols = 3u * p.zpad;
+    const uint32_t tmem_cols = p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kTcRawStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kTcProducerWarps); }
+        for (int i = 0; i < kTcSlots; ++i) { mbar_init(&slot_full[i], kTcGroupWarps); mbar_init(&slot_empty[i], 1); }
+        for (int i = 0; i < kTcMaxBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+        mbar_init(acc_full, 1);
+        fence_mbar_init();
+    }
+    if (warp == kTcProducerWarps + 1) {
+        // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    auto issue_raw = [&](uint32_t g) {
+        const int rs = int(g % kTcRawStages);
+        uint8_t* dst = rawring + rs * kTcRawStage;
+        const int x = int(g * (kTcRawRowBytes / 8));
+        mbar_expect_tx(&raw_full[rs], kTcRawStage);
+        const CUtensorMap* wm = mi == 0 ? &maps.w[0] : (mi == 1 ? &maps.w[1] : &maps.w[2]);
+        if (pair) {
+            tma_load_2d_plain(dst, &maps.w[0], x, int(row0), &raw_full[rs]);                              // w3 rows -> tile rows 0..63
+            tma_load_2d_plain(dst + (kTcRows / 2) * kTcRawRowBytes, &maps.gate, x, int(row0), &raw_full[rs]);   // w1 rows -> 64..127
+        } else {
+            tma_load_2d_plain(dst, wm, x, int(row0), &raw_full[rs]);
+        }
+    };
+
+    const uint32_t n_groups = n_chunks / 4;
+    bool ok = true;
+
+    if (warp == kTcProducerWarps) {
+        // ---------------- TMA warp: one lane feeds the raw ring and the B tiles ----------------
+        if (lane == 0) {
+            issue_raw(0);
+            if (n_groups > 1) issue_raw(1);
+            pdl_wait();                                    // the activations come from the previous kernel
+            for (uint32_t c = 0; c < n_chunks && ok; ++c) {
+                if ((c & 3u) == 0) {
+                    const uint32_t g = c >> 2;
+                    if (g >= kTcRawStages) {
+                        ok = mbar_wait(&raw_empty[g % kTcRawStages], ((g / kTcRawStages) - 1) & 1u, p.err);
+                        if (!ok) break;
+                        issue_raw(g);
+                    }
+                }
+                const uint32_t bs = c % nb;
+                if (c >= nb) {
+                    ok = mbar_wait(&b_empty[bs], ((c / nb) - 1) & 1u, p.err);
+                    if (!ok) break;
+                }
+                mbar_expect_tx(&b_full[bs], b_bytes);
+                tma_load_2d_plain(bring + bs * b_bytes, &maps.x, int(c * kTcChunkK), 0, &b_full[bs]);
+            }
+        }
+    } else if (warp == kTcProducerWarps + 1) {
+        // ---------------- MMA warp: one lane issues the tensor-core work ------------------------
+        if (lane == 0) {
+            // instruction descriptors: fp32 accumulator, fp16 A and B, both K-major, M = 128, N = 2 zpad / zpad
+            const uint32_t idesc_common = (1u << 4) | ((uint32_t(kTcRows) >> 4) << 24);
+            const uint32_t idesc_wide = idesc_common | (((2u * p.zpad) >> 3) << 17);
+            const uint32_t idesc_narrow = idesc_common | ((p.zpad >> 3) << 17);
+            for (uint32_t c = 0; c < n_chunks && ok; ++c) {
+                const int s = int(c % kTcSlots);
+                const uint32_t bs = c % nb;
+                ok = mbar_wait(&b_full[bs], (c / nb) & 1u, p.err) && mbar_wait(&slot_full[s], (c / kTcSlots) & 1u, p.err);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t a_hi = smem_u32(slots + s * kTcSlotBytes), a_lo = a_hi + kTcTileBytes;
+                const uint32_t b_all = smem_u32(bring + bs * b_bytes);        // rows 0..zpad-1: x_hi, zpad..2 zpad-1: x_lo
+                const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
+#pragma unroll
+                for (int k = 0; k < kTcChunkK / 16; ++k) {
+                    const uint32_t off = uint32_t(k) * 32u;                  // 16 fp16 along K inside the swizzled row
+                    const uint32_t acc = (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u;
+                    tc_mma_f16(bank, tc_smem_desc(a_hi + off), tc_smem_desc(b_all + off), idesc_wide, acc);
+                    tc_mma_f16(bank + 2u * p.zpad, tc_smem_desc(a_lo + off), tc_smem_desc(b_all + off), idesc_narrow, acc);
+                }
+                tc_commit(&slot_empty[s]);                                   // arrive when these MMAs have read the tiles
+                tc_commit(&b_empty[bs]);
+            }
+            if (ok) tc_commit(acc_full);
+        }
+    } else {
+        // ---------------- producer warps: q4_0 blocks -> swizzled fp16 hi/lo tiles ---------------
+        const uint32_t r = threadIdx.x & (kTcRows - 1);       // tile row of this thread
+        const uint32_t khalf = (threadIdx.x >> 7) & 1u;       // which block of a 64-column tile
+        const uint32_t jpar = threadIdx.x >> 8;               // producer group: even or odd tiles of K
+        for (uint32_t g = 0; g < n_groups && ok; ++g) {
+            const int rs = int(g % kTcRawStages);
+            ok = mbar_wait(&raw_full[rs], (g / kTcRawStages) & 1u, p.err);
+            if (!ok) break;
+            // the two tiles of this group that the thread's producer group owns: 18 words (4 blocks) each
+            uint32_t w[2][9];
+            const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kTcRawStage + r * kTcRawRowBytes);
+            {
+                // tile jpar: bytes 36 jpar .. +36; tile jpar + 2: bytes 72 + 36 jpar .. +36
+                uint32_t all[36];
+#pragma unroll
+                for (int i = 0; i < 9; ++i) {
+                    const uint4 v = src[i];
+                    all[4 * i] = v.x; all[4 * i + 1] = v.y; all[4 * i + 2] = v.z; all[4 * i + 3] = v.w;
+                }
+#pragma unroll
+                for (int i = 0; i < 9; ++i) {
+                    w[0][i] = jpar ? all[9 + i] : all[i];
+                    w[1][i] = jpar ? all[27 + i] : all[18 + i];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[rs]);       // the row is in registers
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+                const uint32_t c = g * 4 + jpar + 2 * jj;
+                const int s = int(c % kTcSlots);
+                if (c >= kTcSlots) {
+                    ok = mbar_wait(&slot_empty[s], ((c / kTcSlots) - 1) & 1u, p.err);
+                    if (!ok) break;
+                }
+                // even block: scale in the low half of word 0, nibbles shifted by two bytes;
+                // odd block: scale in the high half of word 4, nibbles aligned
+                uint32_t q[4];
+                uint32_t dbits;
+                if (khalf == 0) {
+                    dbits = w[jj][0] & 0xffffu;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k] = __funnelshift_r(w[jj][k], w[jj][k + 1], 16);
+                } else {
+                    dbits = w[jj][4] >> 16;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k] = w[jj][5 + k];
+                }
+                const __half dh = __ushort_as_half(static_cast<unsigned short>(dbits));
+                const __half2 d2 = __half2half2(dh);
+                __half2 hi[4][4], lo[4][4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) dequant_word(q[k], d2, hi[k], lo[k]);
+                // 16-byte chunks of the block: elements 0-7 (words 0,1 low nibbles), 8-15, 16-23 (high nibbles), 24-31
+                uint8_t* a_hi = slots + s * kTcSlotBytes;
+                uint8_t* a_lo = a_hi + kTcTileBytes;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int k0 = (cc & 1) * 2, part = (cc >> 1) * 2;     // words k0, k0+1; low (0) or high (2) nibbles
+                    const uint32_t at = tc_swizzled(r, khalf * 4 + cc);
+                    uint4 vh, vl;
+                    vh.x = *reinterpret_cast<uint32_t*>(&hi[k0][part]); vh.y = *reinterpret_cast<uint32_t*>(&hi[k0][part + 1]);
+                    vh.z = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part]); vh.w = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part + 1]);
+                    vl.x = *reinterpret_cast<uint32_t*>(&lo[k0][part]); vl.y = *reinterpret_cast<uint32_t*>(&lo[k0][part + 1]);
+                    vl.z = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part]); vl.w = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part + 1]);
+                    *reinterpret_cast<uint4*>(a_hi + at) = vh;
+                    *reinterpret_cast<uint4*>(a_lo + at) = vl;
+                }
+                fence_proxy_async();                           // make the tile visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&slot_full[s]);
+            }
+        }
+        // ---------------- epilogue: warps 0-3 own accumulator rows 32w .. 32w+31 -----------------
+        if (warp < 4) {
+            pdl_wait();
+            if (ok) ok = mbar_wait(acc_full, 0u, p.err);
+            tc_fence_after_sync();
+            float* gate_s = reinterpret_cast<float*>(slots);      // [64][17] floats, free once the accumulator is complete
+            for (uint32_t z0 = 0; z0 < p.zpad; z0 += 16) {
+                uint32_t v[16];
+                if (ok) {
+                    const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + z0;
+                    float sum[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+                    const uint32_t banks_used = min(uint32_t(kTcBanks), n_chunks);
+                    for (uint32_t b = 0; b < banks_used; ++b) {
+                        uint32_t u[3][16];
+#pragma unroll
+                        for (int a = 0; a < 3; ++a) {
+                            asm volatile(
+                                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                                : "=r"(u[a][0]), "=r"(u[a][1]), "=r"(u[a][2]), "=r"(u[a][3]), "=r"(u[a][4]), "=r"(u[a][5]), "=r"(u[a][6]),
+                                  "=r"(u[a][7]), "=r"(u[a][8]), "=r"(u[a][9]), "=r"(u[a][10]), "=r"(u[a][11]), "=r"(u[a][12]), "=r"(u[a][13]),
+                                  "=r"(u[a][14]), "=r"(u[a][15])
+                                : "r"(taddr + b * bank_cols + uint32_t(a) * p.zpad));
+                        }
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)      // the two small cross terms first, then the main one
+                            sum[i] += (__uint_as_float(u[1][i]) + __uint_as_float(u[2][i])) + __uint_as_float(u[0][i]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(sum[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0u;
+                }
+                const uint32_t tr = uint32_t(warp * 32 + lane);      // tile row
+                if (pair) {
+                    // rows 64..127 carry the gate (w1) of rows 0..63
+                    if (tr >= 64) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) gate_s[(tr - 64) * 17 + i] = __uint_as_float(v[i]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (tr < 64 && ok) {
+                        const uint32_t row = row0 + tr;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t z = z0 + i;
+                            if (z < p.Z) {
+                                const float up = __uint_as_float(v[i]), gate = gate_s[tr * 17 + i];
+                                static_cast<float*>(M.out)[size_t(z) * M.rows + row] = up * gate / (expf(-gate) + 1.0f);   // matmul_silu_ff.comp:95
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                } else if (ok) {
+                    const uint32_t row = row0 + tr;
+                    if (M.epilogue == EPI_STORE_F16_AT_POS) {
+                        __half* cache = static_cast<__half*>(M.out);
+                        const uint32_t first = *p.pos;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t z = z0 + i;
+                            if (z < p.Z) {
+                                if (first + z < p.ctx_rows) cache[size_t(first + z) * M.rows + row] = __float2half_rn(__uint_as_float(v[i]));
+                                else atomicOr(p.err, ERR_BAD_INDEX);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t z = z0 + i;
+                            if (z < p.Z) {
+                                float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
+                                const float r32 = __uint_as_float(v[i]);
+                                *o = (M.epilogue == EPI_ADD) ? (*o + r32) : r32;                   // matmul.glsl:68-72
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kTcProducerWarps + 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// x (optionally normalised, normalize.comp:39-63) as two fp16 planes: hi = fp16(v), lo = fp16(v - hi).
+// Grid: zpad CTAs; rows z >= Z are zero so that the padded columns of the product are defined.
+__global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh, const float* __restrict__ x,
+                                                        const float* __restrict__ norm_w, uint32_t K, uint32_t Z, uint32_t zpad) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[64];
+    const uint32_t z = blockIdx.x;
+    __half* hi = xh + size_t(z) * K;
+    __half* lo = xh + size_t(zpad + z) * K;
+    if (z >= Z) {
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) { hi[i] = __float2half_rn(0.f); lo[i] = __float2half_rn(0.f); }
+        return;
+    }
+    const float* xr = x + size_t(z) * K;
+    float factor = 1.0f;
+    if (norm_w != nullptr) {
+        float part = 0.f;
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) part += xr[i];
+        const float mean = block_sum(part, scratch) / static_cast<float>(K);
+        part = 0.f;
+        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
+            const float c = xr[i] - mean;
+            part = fmaf(c, c, part);
+        }
+        factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(K));        // no epsilon
+    }
+    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
+        const float v = norm_w != nullptr ? (xr[i] * norm_w[i]) * factor : xr[i];
+        const __half h = __float2half_rn(v);
+        hi[i] = h;
+        lo[i] = __float2half_rn(v - __half2float(h));
+    }
+}
+
+int gemm_tc_configure(lv_ctx* ctx) {
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kTcSmemBytes, "device has too little shared memory for the batched product");
+    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTcSmemBytes)));
+    return LV_OK;
+}
+
+static int launch_gemm_tc(lv_ctx* ctx, GemmTcParams& p, const __half* xh) {
+    LV_REQUIRE(p.K != 0 && p.K % 256 == 0, "cols must be a non-zero multiple of 256");
+    LV_REQUIRE(p.Z >= 1 && p.Z <= uint32_t(kTcMaxZ), "batch of the tensor-core product must be 1..64");
+    LV_REQUIRE(xh != nullptr && (reinterpret_cast<uintptr_t>(xh) & 15u) == 0, "split activations null or not 16-byte aligned");
+    p.zpad = (p.Z + 15u) & ~15u;
+    const bool pair = p.m[0].w_gate != nullptr;
+    const uint32_t rows_per_cta = pair ? kTcRows / 2 : kTcRows;
+    const uint32_t row_bytes = p.K / 32 * kQ4BlockBytes;
+    GemmTcMaps maps{};
+    uint32_t tiles = 0;
+    for (int i = 0; i < p.n_mat; ++i) {
+        LV_REQUIRE(p.m[i].w != nullptr && (reinterpret_cast<uintptr_t>(p.m[i].w) & 15u) == 0, "matrix pointer null or not 16-byte aligned");
+        LV_REQUIRE(p.m[i].rows != 0 && p.m[i].rows % rows_per_cta == 0, "rows must be a multiple of 128 (64 for the SiLU pair)");
+        if (int rc = make_weight_map(&maps.w[i], p.m[i].w, p.m[i].rows, row_bytes, rows_per_cta, kTcRawRowBytes)) return rc;
+        tiles += p.m[i].rows / rows_per_cta;
+    }
+    if (pair) {
+        LV_REQUIRE((reinterpret_cast<uintptr_t>(p.m[0].w_gate) & 15u) == 0, "matrix pointer not 16-byte aligned");
+        if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, kTcRawRowBytes)) return rc;
+    }
+    if (int rc = make_act_map(&maps.x, xh, 2 * p.zpad, p.K, 2 * p.zpad, kTcChunkK)) return rc;
+    LV_CUDA(launch_pdl(ctx, gemm_tc_kernel, dim3(tiles), dim3(kTcThreads), kTcSmemBytes, p, maps));
+    return LV_OK;
+}
+
+}  // namespace lv
+
+using namespace lv;
+
+extern "C" size_t lv_act_split_bytes(uint32_t cols, uint32_t batch) {
+    return size_t(2) * ((batch + 15u) & ~15u) * cols * sizeof(__half);
+}
+
+extern "C" int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(xh && x && cols && batch >= 1 && batch <= uint32_t(kTcMaxZ), "bad act_split arguments");
+    const uint32_t zpad = (batch + 15u) & ~15u;
+    LV_CUDA(launch_pdl(ctx, act_split_kernel, dim3(zpad), dim3(512), 0, static_cast<__half*>(xh), x, norm_w, cols, batch, zpad));
+    return LV_OK;
+}
+
+extern "C" int lv_gemm_tc(lv_ctx* ctx, float* out, const void* W, int wtype, const void* xh, uint32_t rows, uint32_t cols,
+                          uint32_t batch, int add) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && W, "null argument");
+    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
+    GemmTcParams p{};
+    p.m[0] = {static_cast<const uint8_t*>(W), nullptr, out, rows, add ? EPI_ADD : EPI_STORE};
+    p.n_mat = 1;
+    p.K = cols;
+    p.Z = batch;
+    p.err = ctx->d_err;
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+}
+
+extern "C" int lv_gemm_tc_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const void* xh, uint32_t ff,
+                               uint32_t dim, uint32_t batch) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && w3 && w1, "null argument");
+    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
+    GemmTcParams p{};
+    p.m[0] = {static_cast<const uint8_t*>(w3), static_cast<const uint8_t*>(w1), out, ff, EPI_STORE};
+    p.n_mat = 1;
+    p.K = dim;
+    p.Z = batch;
+    p.err = ctx->d_err;
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+}
+
+extern "C" int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq, const void* wk,
+                                       const void* wv, int wtype, const void* xh, const uint32_t* pos, uint32_t rows_each,
+                                       uint32_t dim, uint32_t batch, uint32_t ctx_rows) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(q_out && k_cache && v_cache && wq && wk && wv && pos, "null argument");
+    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
+    LV_REQUIRE(ctx_rows >= batch, "cache smaller than the batch");
+    GemmTcParams p{};
+    p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, k_cache, rows_each, EPI_STORE_F16_AT_POS};
+    p.m[1] = {static_cast<const uint8_t*>(wq), nullptr, q_out, rows_each, EPI_STORE};
+    p.m[2] = {static_cast<const uint8_t*>(wv), nullptr, v_cache, rows_each, EPI_STORE_F16_AT_POS};
+    p.n_mat = 3;
+    p.pos = pos;
+    p.ctx_rows = ctx_rows;
+    p.K = dim;
+    p.Z = batch;
+    p.err = ctx->d_err;
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+}

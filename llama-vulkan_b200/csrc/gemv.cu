@@ -8,6 +8,7 @@
 
 #include "ctx.h"
 #include "gemv_stream.cuh"
+#include "tmap.h"
 
 namespace lv {
 
@@ -257,8 +258,7 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// [rows][row_bytes / 8] view of 8-byte elements, box = box_rows x seg_bytes / 8
-static int make_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t row_bytes, uint32_t box_rows, uint32_t seg_bytes) {
+int make_weight_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t row_bytes, uint32_t box_rows, uint32_t seg_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {row_bytes / 8, rows};
@@ -267,6 +267,20 @@ static int make_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t 
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, elem,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return LV_OK;
+}
+
+int make_act_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t cols, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
     return LV_OK;
@@ -286,9 +300,9 @@ static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_
     if (tmap) {
         constexpr uint32_t box_rows = SILU ? NS / 2 : NS;
         for (int i = 0; i < p.n_mat; ++i)
-            if (int rc = make_map(&maps.m[i], p.m[i].w, p.m[i].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
+            if (int rc = make_weight_map(&maps.m[i], p.m[i].w, p.m[i].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
         if (SILU)
-            if (int rc = make_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
+            if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
         LV_CUDA(launch_pdl(ctx, gemv_kernel<QT, NS, SILU, W, true>, grid, dim3(W * 32), smem, p, maps));
     } else {
         LV_CUDA(launch_pdl(ctx, gemv_kernel<QT, NS, SILU, W, false>, grid, dim3(W * 32), smem, p, maps));

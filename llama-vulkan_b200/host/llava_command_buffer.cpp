@@ -184,6 +184,40 @@ void llava_command_buffer::allreduce_add(llava_buffer* residual, llava_buffer* p
     note(lv_allreduce_add_f32(lv(), f32(residual), f32(partial), size_t(dim) * batch_size));
 }
 
+bool llava_command_buffer::use_tensor_cores(const llava_buffer* matrix) const {
+    return batch_size >= 16 && batch_size <= 64 && matrix->type == ggml_value_type::q4_0 && session->act_split != nullptr &&
+           session->ctx->tp_size() == 1;
+}
+
+void llava_command_buffer::act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights) {
+    const u32 cols = inbuf->shape.first;
+    if (!expect(size_t(split->shape.first) * 4 >= lv_act_split_bytes(cols, batch_size), "act_split shapes")) return;
+    note(lv_act_split_f16(lv(), split->device_ptr(), f32(inbuf), norm_weights ? f32(norm_weights) : nullptr, cols, batch_size));
+}
+
+void llava_command_buffer::gemm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq,
+                                             llava_buffer* wk, llava_buffer* wv, llava_buffer* split) {
+    const u32 dim = session->model->get_header().dim;
+    if (!expect(wq->shape == wk->shape && wq->shape == wv->shape && wq->shape.second == dim && q_out->shape.first == wq->shape.first &&
+                k_cache->shape.second == wq->shape.first && v_cache->shape.second == wq->shape.first, "qkv shapes")) return;
+    note(lv_gemm_tc_qkv_kvappend(lv(), f32(q_out), k_cache->device_ptr(), v_cache->device_ptr(), wq->device_ptr(), wk->device_ptr(),
+                                 wv->device_ptr(), int(wq->type), split->device_ptr(),
+                                 static_cast<u32*>(session->config_buffer->device_ptr()), wq->shape.first, dim, batch_size,
+                                 k_cache->shape.first));
+}
+
+void llava_command_buffer::gemm_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split) {
+    if (!expect(outbuf->shape.first == matrix->shape.first, "gemm_add_inplace shapes")) return;
+    note(lv_gemm_tc(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), split->device_ptr(), matrix->shape.first,
+                    matrix->shape.second, batch_size, 1));
+}
+
+void llava_command_buffer::gemm_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* split) {
+    if (!expect(w3->shape == w1->shape && w3->type == w1->type && outbuf->shape.first >= w3->shape.first, "gemm_silu_ff shapes")) return;
+    note(lv_gemm_tc_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), split->device_ptr(), w3->shape.first,
+                         w3->shape.second, batch_size));
+}
+
 void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf,
                                                llava_buffer* norm_weights) {
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&

@@ -41,6 +41,14 @@ public:
 
     // tensor-parallel: partial <- sum over ranks of partial; residual += partial
     void allreduce_add(llava_buffer* residual, llava_buffer* partial);
+    // batched forms on the tensor cores (16..64 tokens per step, q4_0): the activations are first
+    // split into two fp16 planes (optionally normalised), then every matrix is read once
+    bool use_tensor_cores(const llava_buffer* matrix) const;
+    void act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights);
+    void gemm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq, llava_buffer* wk,
+                           llava_buffer* wv, llava_buffer* split);
+    void gemm_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split);
+    void gemm_silu_ff(llava_buffer* outbuf, llava_buffer* w3_matrix, llava_buffer* w1_matrix, llava_buffer* split);
 
     int status() const { return first_error; }
 

@@ -78,6 +78,21 @@ llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_se
         // five launches: the residual stream is updated in place, as the reference does when
         // it is not tracing (llava_layer.cpp:45-51)
         llava_buffer* x = session->current_thought;
+        if (cmd_buf->use_tensor_cores(attention_wq)) {
+            // 16 or more tokens: every matrix is read once for the whole batch (tcgen05), nine launches
+            llava_buffer* split = session->act_split;
+            cmd_buf->act_split(split, x, attention_norm);
+            cmd_buf->gemm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
+                                       attention_wv, split);
+            cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);
+            cmd_buf->act_split(split, session->current_Vout, nullptr);
+            cmd_buf->gemm_add_inplace(x, attention_wo, split);
+            cmd_buf->act_split(split, x, ffn_norm);
+            cmd_buf->gemm_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, split);
+            cmd_buf->act_split(split, session->main_ff_result, nullptr);
+            cmd_buf->gemm_add_inplace(x, feed_forward_w2, split);
+            return x;
+        }
         cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
                                    attention_wv, x, attention_norm);
         cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);

@@ -91,6 +91,7 @@ bool llava_session::recreate_buffers() {
     const size_t scratch = lv_attention_scratch_bytes(h.n_heads / ranks, h.rot, max_backlog_size, B);
     if (scratch == 0) return false;
     attn_scratch = new llava_buffer(ctx, F, u32((scratch + 3) / 4), 1, m);
+    if (B >= 16 && ranks == 1) act_split = new llava_buffer(ctx, F, u32(lv_act_split_bytes(max(dim, ff), B) / 4), 1, m);
     if (!m->freeze() || !m->zero(0, m->get_size())) return false;
     device_pos = ~0U;
     return true;
@@ -99,7 +100,7 @@ bool llava_session::recreate_buffers() {
 void llava_session::reset_main_buffers() {
     for (llava_buffer** b : {&current_thought, &current_thought_sublayer, &current_thought_middle_normd, &current_Q, &current_K,
                              &current_V, &current_Vout, &main_attn_result, &config_buffer, &output_probs, &main_ff_result,
-                             &token_log, &argmax_result, &attn_scratch, &tp_partial}) {
+                             &token_log, &argmax_result, &attn_scratch, &tp_partial, &act_split}) {
         delete *b;
         *b = nullptr;
     }

@@ -65,7 +65,7 @@ public:
     u32 get_backlog_size() const { return backlog_size; }
     u32 get_tokens_in_gpu() const { return current_tokens_in_gpu; }
 
-    static constexpr u32 max_batch_limit = 16;
+    static constexpr u32 max_batch_limit = 64;
 
     llava_context* const ctx;
     ggml_file const* const model;
@@ -100,6 +100,7 @@ private:
     llava_buffer* token_log = nullptr;
     llava_buffer* argmax_result = nullptr;
     llava_buffer* attn_scratch = nullptr;
+    llava_buffer* act_split = nullptr;            // max_batch >= 16: fp16 (hi, lo) planes of a batch of activations
     llava_buffer* tp_partial = nullptr;           // tensor-parallel only: this rank's partial wo / w2 product
     std::vector<llava_layer_session_data*> layer_data;
 

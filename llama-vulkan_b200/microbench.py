@@ -2,7 +2,11 @@
 """Kernel microbenchmark of the quantised GEMV family (seeded N(0, 0.02)
 weights, N(0, 1) activations), one line of JSON per shape:
 
-    python llama-vulkan_b200/microbench.py [--shape NAME ...] [--wtype q4_0|q8_0] [--batch Z] [--iters N]
+    python llama-vulkan_b200/microbench.py [--shape NAME ...] [--wtype q4_0|q8_0] [--batch Z] [--tc] [--iters N]
+
+With --tc the plain / add / silu shapes run on the tensor cores (lv_gemm_tc*, batch 1..64,
+q4_0), otherwise the GEMV reads the matrix once per token of the batch; TFLOP/s =
+2 * rows * cols * batch / time is reported beside GB/s.
 
 Every timed launch reads a different copy of the matrix from a ring of copies
 larger than the 126 MB L2, so the figure is HBM bandwidth, not L2 bandwidth.
@@ -48,6 +52,7 @@ def main():
     ap.add_argument("--shape", nargs="*", default=sorted(SHAPES))
     ap.add_argument("--wtype", default="q4_0", choices=["q4_0", "q8_0"])
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--tc", action="store_true", help="batched product on the tensor cores instead of one GEMV per token")
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--ring-mb", type=int, default=400)
     ap.add_argument("--pos", type=int, default=200, help="cache rows already filled, for the attn shape")
@@ -101,9 +106,17 @@ def main():
                     backlog *= 2
                 scratch = gpu.zeros(lib.lv_attention_scratch_bytes(rows // 128, 128, ctx_rows, 1))
 
+            if args.tc:
+                xh = gpu.alloc(lib.lv_act_split_bytes(cols, args.batch))
+                pkg.check(lib.lv_act_split_f16(h, xh, x, None, cols, args.batch))
+
             def launch(i):
                 w = pkg.offset(ring, (i % copies) * nmat * mat_bytes)
-                if kind == "qkv":
+                if args.tc and kind in ("plain", "add", "norm"):
+                    pkg.check(lib.lv_gemm_tc(h, out, w, wtype, xh, rows, cols, args.batch, 1 if kind == "add" else 0))
+                elif args.tc and kind == "silu":
+                    pkg.check(lib.lv_gemm_tc_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, xh, rows, cols, args.batch))
+                elif kind == "qkv":
                     pkg.check(lib.lv_norm_qkv_kvappend(h, out, kc, vc, w, pkg.offset(w, mat_bytes), pkg.offset(w, 2 * mat_bytes), wtype,
                                                        x, nw, dpos, rows, cols, 1, ctx_rows))
                 elif kind == "attn":
@@ -137,7 +150,8 @@ def main():
             nbytes = nmat * mat_bytes if kind != "attn" else 2 * (args.pos + 1) * rows * 2
             gbs = nbytes / sec / 1e9
             print(json.dumps({"shape": name, "rows": rows, "cols": cols, "kind": kind, "wtype": args.wtype, "batch": args.batch,
-                              "us_per_launch": sec * 1e6, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / peak,
+                              "path": "tcgen05" if args.tc else "gemv", "us_per_launch": sec * 1e6, "bytes": nbytes, "GB/s": gbs,
+                              "frac_of_measured_hbm": gbs / peak, "TFLOP/s": 2.0 * nmat * rows * cols * args.batch / sec / 1e12,
                               "ring_copies": copies}), flush=True)
             for d in (ring, x, out):
                 gpu.free(d)

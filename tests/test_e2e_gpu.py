@@ -149,7 +149,37 @@ def test_prompt_in_batches_matches_token_by_token(run):
     tok = s.predict_next_token()
     assert_logits_close(s.logits(run["vocab"]), run["logits"][0])
     assert tok == run["greedy"][0]
-    assert not s.set_max_batch(0) and not s.set_max_batch(17)
+    assert not s.set_max_batch(0) and not s.set_max_batch(65)
+    s.close()
+
+
+def test_prompt_as_one_batch_on_the_tensor_cores(run):
+    """16 prompt tokens in one recorded step: q4_0 models take the tcgen05 path (lv_gemm_tc*), q8_0
+    models the per-token GEMV; either way the logits, the greedy token and the cache rows agree
+    with the oracle's token-by-token evaluation."""
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    assert s.set_max_batch(16)
+    for t in run["prompt"]:
+        assert s.push_token(t)
+    tok = s.predict_next_token()
+    m, r = assert_logits_close(s.logits(run["vocab"]), run["logits"][0])
+    assert tok == run["greedy"][0]
+    for layer in range(2):
+        for which in (0, 1):
+            got = s.read_kv(layer, which, 0, N_PROMPT, run["dim"]).view(np.float16).astype(np.float32)
+            want = run["orc"].cache(which, layer, N_PROMPT).view(np.float16).astype(np.float32)
+            assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    # decoding continues from the batched prompt with the per-token kernels
+    for step in range(1, 6):
+        assert s.push_token(tok)
+        tok = s.predict_next_token()
+        assert_logits_close(s.logits(run["vocab"]), run["logits"][step])
+        assert tok == run["greedy"][step]
+    report = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(report):
+        with open(os.path.join(report, "parity_report.txt"), "a") as f:
+            f.write(f"config0 wtype={run['wtype']} prompt as one batch of 16: logits after the prompt max-abs {m:.3e} rel-L2 {r:.3e}\n")
     s.close()
 
 

@@ -1,0 +1,148 @@
+"""Batched products on the tensor cores (lv_gemm_tc*) against the CPU oracle's per-token GEMV.
+
+The oracle (matmul.glsl restated) is evaluated token by token.  The products that enter the tensor
+cores are exact; their fp32 accumulator truncates instead of rounding, which over K = 4096..11008
+leaves a relative error of about 1e-5, so the tolerances here are rel-L2 <= 3e-5 and max-abs <=
+1e-4 of the largest output (the GEMV tests hold 1e-5), the f16 cache rows up to a neighbouring half.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle_bind as ob
+import quant_np as qn
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, rel_l2=3e-5, max_abs_frac=1e-4):
+    got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64).ravel()
+    assert got.shape == want.shape
+    assert np.all(np.isfinite(got))
+    l2 = np.linalg.norm(got - want) / (np.linalg.norm(want) or 1.0)
+    mx = np.abs(got - want).max()
+    assert l2 <= rel_l2, f"rel-L2 {l2:.3e}"
+    assert mx <= max_abs_frac * (np.abs(want).max() or 1.0), f"max-abs {mx:.3e}"
+
+
+def workers_for(cols):
+    return 32 if cols == 5120 else 128
+
+
+def split(gpu, pkg, x, norm_w=None):
+    batch, cols = x.shape
+    xh = gpu.alloc(gpu.lib.lv_act_split_bytes(cols, batch))
+    pkg.check(gpu.lib.lv_act_split_f16(gpu.handle, xh, gpu.upload(x), None if norm_w is None else gpu.upload(norm_w), cols, batch))
+    return xh
+
+
+def matrix(rng, rows, cols, scale=0.02):
+    return qn.quantize_q4_0((rng.standard_normal((rows, cols)) * scale).astype(np.float32))
+
+
+def test_act_split_planes_add_up_to_the_input(gpu, pkg):
+    rng = np.random.default_rng(50)
+    batch, cols = 5, 512
+    x = (rng.standard_normal((batch, cols)) * np.exp(rng.uniform(-6, 6, (batch, cols)))).astype(np.float32)
+    x = np.clip(x, -6e4, 6e4)
+    xh = split(gpu, pkg, x)
+    gpu.sync()
+    planes = gpu.download(xh, np.float16, 2 * 16 * cols).reshape(2, 16, cols).astype(np.float64)
+    assert not planes[:, batch:].any()                                   # padding rows are zero
+    got = planes[0, :batch] + planes[1, :batch]
+    err = np.abs(got - x)
+    assert (err <= np.maximum(np.abs(x) * 2.0 ** -21, 2.0 ** -24)).all()
+    # with a norm: same as the oracle's normalisation
+    w = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    xs = rng.standard_normal((batch, cols)).astype(np.float32)
+    xh = split(gpu, pkg, xs, w)
+    gpu.sync()
+    planes = gpu.download(xh, np.float16, 2 * 16 * cols).reshape(2, 16, cols).astype(np.float64)
+    for z in range(batch):
+        close(planes[0, z] + planes[1, z], ob.norm(xs[z], w), rel_l2=2e-6, max_abs_frac=2e-6)
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(128, 256, 16), (256, 4096, 5), (4096, 4096, 64), (384, 11008, 33), (640, 5120, 17)])
+def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch):
+    rng = np.random.default_rng(51)
+    W = matrix(rng, rows, cols)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    xh = split(gpu, pkg, x)
+    want = np.stack([ob.gemv(W, qn.Q4_0, x[z], rows, cols, workers_for(cols)) for z in range(batch)])
+    dW = gpu.upload(W)
+    out = gpu.upload(np.full((batch + 1, rows), 7.0, np.float32))
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, qn.Q4_0, xh, rows, cols, batch, 0))
+    gpu.sync()
+    got = gpu.download(out, np.float32, (batch + 1) * rows).reshape(batch + 1, rows)
+    close(got[:batch], want)
+    assert (got[batch] == 7.0).all()                                     # nothing written past the batch
+    base = rng.standard_normal((batch, rows)).astype(np.float32)
+    out = gpu.upload(base)
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, qn.Q4_0, xh, rows, cols, batch, 1))
+    gpu.sync()
+    close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), base + want)
+
+
+def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg):
+    """Blocks whose scale is tiny, huge or negative: hi + lo reproduces (q - 8) * d exactly."""
+    rng = np.random.default_rng(52)
+    rows, cols, batch = 128, 256, 16
+    W = matrix(rng, rows, cols).reshape(rows, cols // 32, 18).copy()
+    scales = np.array([6.1e-5, 3.0e-6, 1.0, -0.37, 1000.0, 0.0999, 2.0 ** -20, 7.77], np.float16).view(np.uint8).reshape(8, 2)
+    W[:, :, 0:2] = scales[None, :, :]
+    W = W.reshape(-1)
+    x = (rng.integers(-8, 9, (batch, cols)) / 8.0).astype(np.float32)    # exactly representable inputs: the result is exact in fp32 order-free
+    xh = split(gpu, pkg, x)
+    out = gpu.zeros(batch * rows * 4)
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, gpu.upload(W), qn.Q4_0, xh, rows, cols, batch, 0))
+    gpu.sync()
+    want = x.astype(np.float64) @ qn.dequantize_np(W, qn.Q4_0).reshape(rows, cols).astype(np.float64).T
+    close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), want, rel_l2=2e-6, max_abs_frac=2e-6)
+
+
+@pytest.mark.parametrize("ff,dim,batch", [(192, 512, 16), (11008, 4096, 20)])
+def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch):
+    rng = np.random.default_rng(53)
+    w3, w1 = matrix(rng, ff, dim), matrix(rng, ff, dim)
+    x = rng.standard_normal((batch, dim)).astype(np.float32)
+    nw = (1 + 0.05 * rng.standard_normal(dim)).astype(np.float32)
+    xh = split(gpu, pkg, x, nw)
+    out = gpu.zeros(batch * ff * 4)
+    pkg.check(gpu.lib.lv_gemm_tc_silu(gpu.handle, out, gpu.upload(w3), gpu.upload(w1), qn.Q4_0, xh, ff, dim, batch))
+    gpu.sync()
+    got = gpu.download(out, np.float32, batch * ff).reshape(batch, ff)
+    for z in range(0, batch, 7):
+        close(got[z], ob.gemv_silu(w3, w1, qn.Q4_0, ob.norm(x[z], nw), ff, dim, workers_for(dim)), rel_l2=3e-5, max_abs_frac=1e-4)
+
+
+def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg):
+    rng = np.random.default_rng(54)
+    dim, batch, ctx_rows, pos = 512, 18, 64, 9
+    wq, wk, wv = (matrix(rng, dim, dim, 0.05) for _ in range(3))
+    x = rng.standard_normal((batch, dim)).astype(np.float32)
+    xh = split(gpu, pkg, x)
+    q = gpu.zeros(batch * dim * 4)
+    kc, vc = gpu.zeros(ctx_rows * dim * 2), gpu.zeros(ctx_rows * dim * 2)
+    dpos = gpu.upload(np.array([pos] * 4, np.uint32))
+    pkg.check(gpu.lib.lv_gemm_tc_qkv_kvappend(gpu.handle, q, kc, vc, gpu.upload(wq), gpu.upload(wk), gpu.upload(wv), qn.Q4_0, xh,
+                                              dpos, dim, dim, batch, ctx_rows))
+    gpu.sync()
+    gq = gpu.download(q, np.float32, batch * dim).reshape(batch, dim)
+    gk = gpu.download(kc, np.float16, ctx_rows * dim).reshape(ctx_rows, dim)
+    gv = gpu.download(vc, np.float16, ctx_rows * dim).reshape(ctx_rows, dim)
+    for z in range(batch):
+        close(gq[z], ob.gemv(wq, qn.Q4_0, x[z], dim, dim, 128), rel_l2=1e-5)
+        close(gk[pos + z], ob.gemv(wk, qn.Q4_0, x[z], dim, dim, 128), rel_l2=6e-4, max_abs_frac=1e-3)
+        close(gv[pos + z], ob.gemv(wv, qn.Q4_0, x[z], dim, dim, 128), rel_l2=6e-4, max_abs_frac=1e-3)
+    assert not gk[:pos].any() and not gk[pos + batch:].any()
+
+
+def test_gemm_tc_refuses_what_it_cannot_do(gpu, pkg):
+    lib, h = gpu.lib, gpu.handle
+    d = gpu.zeros(1 << 16)
+    assert lib.lv_gemm_tc(h, d, d, qn.Q8_0, d, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # q4_0 only
+    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 100, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # rows not a multiple of 128
+    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 96, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS       # cols not a multiple of 256
+    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 256, 65, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # batch above 64
+    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, None, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS
