@@ -324,12 +324,18 @@ def main():
     lv = C.c_void_p(ctx.lib.llava_context_lv(ctx.handle))
     stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=local_rank)
 
+    prompt_eval = {}
+
     def fresh_session():
         s = ctx.session()
         s.set_deterministic(True)
+        if world == 1:
+            assert s.set_max_batch(64)          # prompt in steps of up to 64 tokens (tensor-core path for q4_0)
         for t in prompt_tokens(n_prompt):
             assert s.push_token(t)
-        first = s.predict_next_token()          # ingests the prompt
+        t0 = time.perf_counter()
+        first = s.predict_next_token()          # ingests the prompt (records its steps on first use)
+        prompt_eval.update(tokens=n_prompt, seconds=time.perf_counter() - t0, max_batch=64 if world == 1 else 1)
         assert first != pkg.NO_TOKEN
         assert s.push_token(first)
         return s
@@ -405,7 +411,8 @@ def main():
     if ctx is not None:
         ctx.close()
 
-    launches_per_token = 1 + (5 if world == 1 else 7) * n_layers + 3    # TP adds two residual adds per layer (NCCL's kernels not counted)
+    # embedding row, 5 kernels per layer (7 with the two all-reduce + residual kernels of a sharded layer), norm + head, argmax + advance
+    launches_per_token = 1 + (5 if world == 1 else 7) * n_layers + 2
     line = {
         "metric": "decode tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec_dev * 1e3 / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -417,6 +424,8 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": args.steps / sec_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": launches_per_token * args.steps, "clocks": clocks,
+        # not part of the metric: wall time of the prompt's evaluation, first use (records the steps) included
+        "prompt_eval": dict(prompt_eval, tokens_per_s=prompt_eval["tokens"] / prompt_eval["seconds"]) if prompt_eval else None,
     }
     print(json.dumps(line), flush=True)
     barrier()

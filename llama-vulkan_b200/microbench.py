@@ -88,7 +88,7 @@ def main():
             x = gpu.upload(rng.standard_normal((args.batch, cols)).astype(np.float32))
             out = gpu.zeros(args.batch * rows * 4)
 
-            if kind == "norm":
+            if kind in ("norm", "silu"):
                 nw = gpu.upload((1 + 0.01 * rng.standard_normal(cols)).astype(np.float32))
             if kind in ("qkv", "attn"):
                 ctx_rows = 2048
@@ -124,7 +124,7 @@ def main():
                 elif kind == "norm":
                     pkg.check(lib.lv_norm_gemv(h, out, w, wtype, x, nw, rows, cols, args.batch))
                 elif kind == "silu":
-                    pkg.check(lib.lv_gemv_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, x, rows, cols, args.batch))
+                    pkg.check(lib.lv_norm_gate_up_silu(h, out, w, pkg.offset(w, mat_bytes), wtype, x, nw, rows, cols, args.batch))   # as the decode step calls it
                 else:
                     pkg.check(lib.lv_gemv(h, out, w, wtype, x, rows, cols, args.batch, 1 if kind == "add" else 0))
 
