@@ -267,6 +267,25 @@ int lv_allreduce_f32(lv_ctx* ctx, float* buf, size_t count);
  * flags, a bounded wait, and the sum in rank order from local memory (bit-identical on all
  * ranks).  Without one it is lv_allreduce_f32 followed by lv_add_f32.  partial is clobbered. */
 int lv_allreduce_add_f32(lv_ctx* ctx, float* residual, float* partial, size_t count);
+
+/* The same exchange without a kernel of its own: the all-reduce is split between the GEMV that
+ * produces the partial vector and the GEMV that consumes the sum.
+ *   lv_tp_arm_push: the next lv_gemv on this context (one matrix, batch 1) sends its finished rows
+ *     into its slot of every rank's window with peer stores and publishes one flag per CTA,
+ *     instead of writing `out` (which is ignored).
+ *   lv_tp_arm_pull: the next lv_norm_gemv / lv_norm_gate_up_silu / lv_norm_qkv_kvappend (batch 1)
+ *     waits, bounded, for the flags of all ranks' producer launches (producer_rows = rows of the
+ *     pushed matrix, which fixes the number of producer CTAs), takes x + sum over ranks of the
+ *     slots (rank order) as its input, and stores that sum -- the new residual stream -- to x_out
+ *     (a buffer other than x).
+ * exchange: index of the exchange inside one evaluation step, 0 .. epochs_per_step-1, the same on
+ * every rank; consecutive exchanges must alternate in parity (two slot sets are used in turn) and
+ * every pushed exchange must be pulled before the second next one is pushed.  Flags carry
+ * step * epochs_per_step + exchange + 1, where step counts the lv_decode_advance /
+ * lv_argmax_advance launches of the context, so every step must end with one of them on every
+ * rank.  No counterpart in the reference (single device). */
+int lv_tp_arm_push(lv_ctx* ctx, int exchange, uint32_t epochs_per_step);
+int lv_tp_arm_pull(lv_ctx* ctx, int exchange, uint32_t epochs_per_step, uint32_t producer_rows, float* x_out);
 /* Peer windows: every rank creates one (capacity_floats >= the longest vector, multiple of 4),
  * hands the 64-byte CUDA IPC handle to all ranks by any means, and connects with the handles
  * of all ranks in rank order (its own entry is ignored).  One process per GPU, same node. */

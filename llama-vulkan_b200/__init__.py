@@ -65,6 +65,8 @@ KERNEL_API = {
     "lv_dequant_rows": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_argmax_f32": (_int, [_p, _p, _p, _u32]),
     "lv_decode_advance": (_int, [_p, _p, _p, _p, _u32, _u32]),
+    "lv_tp_arm_push": (_int, [_p, _int, _u32]),
+    "lv_tp_arm_pull": (_int, [_p, _int, _u32, _u32, _p]),
     "lv_argmax_advance": (_int, [_p, _p, _u32, _p, _p, _u32, _u32, _p, _p]),
     "lv_norm_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_comm_unique_id": (_int, [_p]),

@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "ctx.h"
+#include "gemv_stream.cuh"
 
 namespace lv {
 
@@ -24,7 +25,11 @@ constexpr int kPeerThreads = 256;
 struct PeerWindowLayout {
     uint32_t capacity;        // floats per slot
     __host__ __device__ size_t slot_floats(int n_ranks) const { return size_t(2) * n_ranks * capacity; }
-    __host__ __device__ size_t bytes(int n_ranks) const { return slot_floats(n_ranks) * sizeof(float) + size_t(2) * kPeerMaxRanks * kPeerCtas * sizeof(uint32_t) + 256; }
+    // slots, the flags of the stand-alone kernel (2 x 8 x 4 words), the flags of the exchanges fused into the GEMV
+    __host__ __device__ size_t bytes(int n_ranks) const {
+        return slot_floats(n_ranks) * sizeof(float) + size_t(kTpLegacyFlagWords) * sizeof(uint32_t) +
+               size_t(2) * kTpMaxRanks * kTpFlagCtas * sizeof(uint32_t) + 256;
+    }
 };
 
 struct PeerParams {
@@ -37,16 +42,6 @@ struct PeerParams {
 
 __device__ __forceinline__ uint32_t* window_flags(float* window, int n_ranks, uint32_t capacity) {
     return reinterpret_cast<uint32_t*>(window + size_t(2) * n_ranks * capacity);
-}
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
 }
 
 // grid = kPeerCtas; CTA c owns the float4 indices c, c + kPeerCtas, ... of the vector
@@ -64,7 +59,8 @@ __global__ void __launch_bounds__(kPeerThreads) allreduce_add_peer_kernel(float*
         const float4 v = reinterpret_cast<const float4*>(partial)[i];
         for (int r = 0; r < p.n_ranks; ++r) reinterpret_cast<float4*>(p.window[r] + my_slot)[i] = v;
     }
-    __threadfence_system();
+    // the barrier orders the CTA's stores before the release stores of the flags, whose system-scope
+    // release covers them (a system fence in every thread is far more expensive)
     __syncthreads();
     if (threadIdx.x < uint32_t(p.n_ranks)) {
         uint32_t* flags = window_flags(p.window[threadIdx.x], p.n_ranks, p.capacity);
@@ -111,6 +107,8 @@ __global__ void __launch_bounds__(kPeerThreads) allreduce_add_peer_kernel(float*
         }
     }
 }
+
+static_assert(kTpLegacyFlagWords == 2 * kPeerMaxRanks * kPeerCtas && kTpMaxRanks == kPeerMaxRanks, "window layout");
 
 struct PeerState {
     PeerParams params{};
@@ -191,6 +189,63 @@ extern "C" int lv_allreduce_add_f32(lv_ctx* ctx, float* residual, float* partial
     // baseline: NCCL (or nothing, on one rank), then the add
     if (int rc = lv_allreduce_f32(ctx, partial, count)) return rc;
     return lv_add_f32(ctx, residual, partial, count);
+}
+
+namespace lv {
+
+uint32_t* peer_step_counter(lv_ctx* ctx) {
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    return (st != nullptr && ctx->peer_ready) ? st->d_epoch + 2 : nullptr;
+}
+
+// Fills the exchange part of a GEMV launch from the roles armed on the context and disarms them.
+int peer_take_armed(lv_ctx* ctx, TpParams* tp, uint32_t pull_ctas) {
+    *tp = TpParams{};
+    tp->push_exchange = tp->pull_exchange = -1;
+    auto& arm = ctx->tp_arm;
+    if (arm.push < 0 && arm.pull < 0) return LV_OK;
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    const bool ready = st != nullptr && ctx->peer_ready;
+    if (ready) {
+        for (int r = 0; r < st->params.n_ranks; ++r) tp->window[r] = st->params.window[r];
+        tp->rank = st->params.rank;
+        tp->n_ranks = st->params.n_ranks;
+        tp->capacity = st->params.capacity;
+        tp->step = st->d_epoch + 2;
+        tp->epochs_per_step = arm.epochs_per_step;
+        tp->push_exchange = arm.push;
+        tp->pull_exchange = arm.pull;
+        tp->pull_ctas = pull_ctas;
+        tp->x_out = arm.x_out;
+    }
+    arm.push = arm.pull = -1;
+    arm.x_out = nullptr;
+    if (!ready) return fail(LV_ERR_BAD_ARGUMENTS, "an exchange was armed but the peer windows are not connected");
+    return LV_OK;
+}
+
+}  // namespace lv
+
+extern "C" int lv_tp_arm_push(lv_ctx* ctx, int exchange, uint32_t epochs_per_step) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(ctx->peer_ready, "peer windows are not connected");
+    LV_REQUIRE(exchange >= 0 && uint32_t(exchange) < epochs_per_step, "exchange index out of range");
+    ctx->tp_arm.push = exchange;
+    ctx->tp_arm.epochs_per_step = epochs_per_step;
+    return LV_OK;
+}
+
+extern "C" int lv_tp_arm_pull(lv_ctx* ctx, int exchange, uint32_t epochs_per_step, uint32_t producer_rows, float* x_out) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(ctx->peer_ready, "peer windows are not connected");
+    LV_REQUIRE(exchange >= 0 && uint32_t(exchange) < epochs_per_step, "exchange index out of range");
+    LV_REQUIRE(producer_rows != 0 && producer_rows % 4 == 0, "producer rows must be a non-zero multiple of 4");
+    LV_REQUIRE(x_out != nullptr && (reinterpret_cast<uintptr_t>(x_out) & 15u) == 0, "x_out null or not 16-byte aligned");
+    ctx->tp_arm.pull = exchange;
+    ctx->tp_arm.epochs_per_step = epochs_per_step;
+    ctx->tp_arm.pull_rows = producer_rows;
+    ctx->tp_arm.x_out = x_out;
+    return LV_OK;
 }
 
 extern "C" int lv_peer_destroy(lv_ctx* ctx) {

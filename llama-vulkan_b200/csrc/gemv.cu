@@ -158,14 +158,34 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
         const GemvMatrix& M = locate(cta_first + gl, lg);
         if (M.epilogue == EPI_ADD) resid = static_cast<const float*>(M.out)[size_t(z) * M.rows + lg * kRowsPerItem + rr];
     }
+    const bool tp_pull = p.tp.n_ranks > 0 && p.tp.pull_exchange >= 0;
+    const bool tp_push = p.tp.n_ranks > 0 && p.tp.push_exchange >= 0;
+    bool ok = true;
+    if (tp_pull) {
+        // wait until every CTA of every rank's producer launch has delivered its rows to this rank's window
+        const uint32_t epoch = tp_epoch(p.tp, p.tp.pull_exchange);
+        const uint32_t total = uint32_t(p.tp.n_ranks) * p.tp.pull_ctas;
+        for (uint32_t idx = threadIdx.x; idx < total && ok; idx += blockDim.x) {
+            const uint32_t src = idx / p.tp.pull_ctas, cta = idx - src * p.tp.pull_ctas;
+            const uint32_t* flag = tp_flag(p.tp, p.tp.rank, p.tp.pull_exchange, int(src), cta);
+            const long long t0 = clock64();
+            while (ld_acquire_sys(flag) != epoch) {
+                if (*reinterpret_cast<volatile uint32_t*>(p.err) != 0 || clock64() - t0 > kWaitCycleLimit) {
+                    atomicOr(p.err, ERR_PEER_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        ok = __syncthreads_and(ok);
+    }
     // activation records (optionally normalised) while the first weight bytes are in flight
-    stage_activations(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch);
+    stage_activations(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch, p.tp);
     __syncthreads();
 
     int slot = 0;
     uint32_t parity = 0;
     uint32_t cj = warp;
-    bool ok = true;
     for (uint32_t round_first = 0; round_first < cta_groups; round_first += groups_per_round) {
         const uint32_t round_groups = min(groups_per_round, cta_groups - round_first);
         const uint32_t item_base = round_first * nseg, item_end = (round_first + round_groups) * nseg;
@@ -229,7 +249,10 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
             uint32_t lg;
             const GemvMatrix& M = locate(cta_first + round_first + gl, lg);
             const uint32_t row = lg * kRowsPerItem + rr;
-            if (M.epilogue == EPI_STORE_F16_AT_POS) {
+            if (tp_push) {
+                // this rank's partial product of the row goes to its slot of every rank's window
+                for (int r = 0; r < p.tp.n_ranks; ++r) tp_slot(p.tp, r, p.tp.push_exchange, p.tp.rank)[row] = v;
+            } else if (M.epilogue == EPI_STORE_F16_AT_POS) {
                 __half* cache = static_cast<__half*>(M.out);
                 const uint32_t slot_row = *p.pos + z;
                 if (slot_row < p.ctx_rows) cache[size_t(slot_row) * M.rows + row] = __float2half_rn(v);   // copy_to_cache.comp:35
@@ -240,6 +263,14 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
             }
         }
         if (round_first + groups_per_round < cta_groups) __syncthreads();        // partials are reused by the next round
+    }
+    if (tp_push) {
+        // the rows are out: one flag per CTA in every rank's window.  The barrier orders the CTA's row
+        // stores before the few release stores below, whose system-scope release covers them all (a
+        // system fence in every thread costs ~10 us here)
+        __syncthreads();
+        if (threadIdx.x < uint32_t(p.tp.n_ranks))
+            st_release_sys(tp_flag(p.tp, int(threadIdx.x), p.tp.push_exchange, p.tp.rank, blockIdx.x), tp_epoch(p.tp, p.tp.push_exchange));
     }
 }
 
@@ -354,7 +385,25 @@ static int check_matrix_args(const void* const* ws, int nw, int wtype, uint32_t 
     return LV_OK;
 }
 
-static int gemv_dispatch(lv_ctx* ctx, const GemvParams& p, int wtype, bool silu, uint32_t batch) {
+int peer_take_armed(lv_ctx* ctx, TpParams* tp, uint32_t pull_ctas);
+
+// CTAs of a plain (one matrix, no SiLU pair) GEMV launch over `rows` rows; mirrors launch_gemv_pick_streams.
+static uint32_t plain_gemv_ctas(const lv_ctx* ctx, uint32_t rows) {
+    const uint32_t groups4 = rows / 4;
+    return groups4 >= uint32_t(ctx->sm_count) ? uint32_t(ctx->sm_count) : min(uint32_t(ctx->sm_count), groups4 * 2);
+}
+
+static int gemv_dispatch(lv_ctx* ctx, GemvParams& p, int wtype, bool silu, uint32_t batch) {
+    if (int rc = peer_take_armed(ctx, &p.tp, plain_gemv_ctas(ctx, ctx->tp_arm.pull_rows))) return rc;
+    if (p.tp.n_ranks > 0) {
+        LV_REQUIRE(batch == 1, "an exchange fused into a GEMV needs batch 1");
+        LV_REQUIRE(p.tp.pull_ctas <= uint32_t(kTpFlagCtas), "too many producer CTAs for the flag area");
+        if (p.tp.push_exchange >= 0) {
+            LV_REQUIRE(p.n_mat == 1 && !silu && p.m[0].rows <= p.tp.capacity, "a pushing GEMV has one matrix whose rows fit a window slot");
+            LV_REQUIRE(plain_gemv_ctas(ctx, p.m[0].rows) <= uint32_t(kTpFlagCtas), "too many CTAs for the flag area");
+        }
+        if (p.tp.pull_exchange >= 0) LV_REQUIRE(p.K <= p.tp.capacity, "input longer than a window slot");
+    }
     if (wtype == T_Q4_0) return silu ? launch_gemv_pick_streams<T_Q4_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q4_0, false>(ctx, p, batch);
     return silu ? launch_gemv_pick_streams<T_Q8_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q8_0, false>(ctx, p, batch);
 }

@@ -58,7 +58,42 @@ struct GemvMatrix {
     int epilogue;
 };
 
+// Tensor-parallel exchange fused into the GEMV (see comm_peer.cu for the window layout).
+// A producer launch (push_exchange >= 0) sends its finished row sums -- this rank's partial
+// products -- into its slot of every rank's receive window instead of storing them, and
+// publishes one flag per CTA.  A consumer launch (pull_exchange >= 0) waits for the flags of
+// all ranks in its own window and builds its input as x + sum over ranks of the slots.
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpFlagCtas = 256;       // flags per (exchange parity, source rank)
+constexpr int kTpLegacyFlagWords = 64; // flag words of the stand-alone all-reduce kernel that precede these
+
+struct TpParams {
+    float* window[kTpMaxRanks];   // window[r]: rank r's receive window as seen from this GPU
+    int rank, n_ranks;            // n_ranks == 0: no exchange in this launch
+    uint32_t capacity;            // floats per slot
+    const uint32_t* step;         // device word: evaluation steps completed by this context
+    uint32_t epochs_per_step;     // exchanges in one step; epoch = step * epochs_per_step + exchange + 1
+    int push_exchange;            // producer side, -1 = none
+    int pull_exchange;            // consumer side, -1 = none
+    uint32_t pull_ctas;           // CTAs of the producer launch of the consumed exchange
+    float* x_out;                 // consumer: CTA 0 stores the summed input here (the new residual stream)
+};
+
+__device__ __forceinline__ float* tp_slot(const TpParams& t, int r_window, int exchange, int src) {
+    return t.window[r_window] + (size_t(exchange & 1) * t.n_ranks + src) * t.capacity;
+}
+
+__device__ __forceinline__ uint32_t* tp_flag(const TpParams& t, int r_window, int exchange, int src, uint32_t cta) {
+    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[r_window] + size_t(2) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
+    return flags + (size_t(exchange & 1) * kTpMaxRanks + src) * kTpFlagCtas + cta;
+}
+
+__device__ __forceinline__ uint32_t tp_epoch(const TpParams& t, int exchange) {
+    return *t.step * t.epochs_per_step + uint32_t(exchange) + 1u;
+}
+
 struct GemvParams {
+    TpParams tp;
     GemvMatrix m[3];
     int n_mat;
     const float* x;          // [batch][K]
@@ -234,9 +269,11 @@ __device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint
 constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
-                                                  const float* __restrict__ norm_w, uint32_t K, float* scratch) {
+                                                  const float* __restrict__ norm_w, uint32_t K, float* scratch,
+                                                  const TpParams& tp) {
     const int lane = threadIdx.x & 31;
     const uint32_t stride = blockDim.x * 4;
+    const bool pull = tp.n_ranks > 0 && tp.pull_exchange >= 0;
 
     for (uint32_t chunk = 0; chunk < K; chunk += stride * kActIters) {
         float4 v[kActIters], w[kActIters];
@@ -244,6 +281,30 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
         for (int i = 0; i < kActIters; ++i) {
             const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
             v[i] = e < K ? *reinterpret_cast<const float4*>(x + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (pull) {
+            // input = x + the partial products of all ranks, added in rank order (the same bits on every
+            // rank); the slots are read from L2, where the peers' stores land
+            float4 sum[kActIters];
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < tp.n_ranks; ++r) {
+                const float* slot = tp_slot(tp, tp.rank, tp.pull_exchange, r);
+#pragma unroll
+                for (int i = 0; i < kActIters; ++i) {
+                    const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
+                    if (e < K) {
+                        const float4 t = __ldcg(reinterpret_cast<const float4*>(slot + e));
+                        sum[i].x += t.x; sum[i].y += t.y; sum[i].z += t.z; sum[i].w += t.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kActIters; ++i) {
+                const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
+                v[i].x += sum[i].x; v[i].y += sum[i].y; v[i].z += sum[i].z; v[i].w += sum[i].w;
+                if (e < K && blockIdx.x == 0 && blockIdx.y == 0 && tp.x_out != nullptr) *reinterpret_cast<float4*>(tp.x_out + e) = v[i];
+            }
         }
         if (norm_w != nullptr) {
             // normalised inputs have length dim, which always fits one chunk

@@ -176,7 +176,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(uint32_t* __restrict__ out
 // (input of the next step), to *argmax_out and, when given, to a word of mapped host memory.
 __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __restrict__ v, uint32_t n, uint32_t* config,
                                                               uint32_t* token_log, uint32_t batch, uint32_t log_capacity,
-                                                              uint32_t* argmax_out, volatile uint32_t* host_token, uint32_t* err) {
+                                                              uint32_t* argmax_out, volatile uint32_t* host_token, uint32_t* tp_step,
+                                                              uint32_t* err) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_val[32];
@@ -190,6 +191,7 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
         else atomicOr(err, ERR_BAD_INDEX);
         if (argmax_out != nullptr) *argmax_out = token;
         for (int i = 0; i < 4; ++i) config[i] = count + batch;
+        if (tp_step != nullptr) *tp_step += 1;          // numbers the exchanges of the next step (sharded contexts)
         if (host_token != nullptr) {
             *host_token = token;
             __threadfence_system();
@@ -198,7 +200,7 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
 }
 
 __global__ void decode_advance_kernel(uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
-                                      uint32_t log_capacity, uint32_t* err) {
+                                      uint32_t log_capacity, uint32_t* tp_step, uint32_t* err) {
     pdl_launch_dependents();
     pdl_wait();
     if (argmax != nullptr && token_log != nullptr) {
@@ -207,6 +209,7 @@ __global__ void decode_advance_kernel(uint32_t* config, const uint32_t* argmax, 
         else atomicOr(err, ERR_BAD_INDEX);
     }
     for (int i = 0; i < 4; ++i) config[i] += batch;
+    if (tp_step != nullptr) *tp_step += 1;
 }
 
 }  // namespace lv
@@ -217,7 +220,8 @@ extern "C" int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* 
                                  uint32_t batch, uint32_t log_capacity) {
     LV_ENTER(ctx);
     LV_REQUIRE(config && batch, "bad advance arguments");
-    LV_CUDA(launch_pdl(ctx, decode_advance_kernel, dim3(1), dim3(1), 0, config, argmax, token_log, batch, log_capacity, ctx->d_err));
+    LV_CUDA(launch_pdl(ctx, decode_advance_kernel, dim3(1), dim3(1), 0, config, argmax, token_log, batch, log_capacity,
+                       peer_step_counter(ctx), ctx->d_err));
     return LV_OK;
 }
 
@@ -226,7 +230,7 @@ extern "C" int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32
     LV_ENTER(ctx);
     LV_REQUIRE(v && n && config && token_log && batch, "bad argmax_advance arguments");
     LV_CUDA(launch_pdl(ctx, argmax_advance_kernel, dim3(1), dim3(1024), 0, v, n, config, token_log, batch, log_capacity,
-                       argmax_out, static_cast<volatile uint32_t*>(host_token), ctx->d_err));
+                       argmax_out, static_cast<volatile uint32_t*>(host_token), peer_step_counter(ctx), ctx->d_err));
     return LV_OK;
 }
 

@@ -72,6 +72,10 @@ bool llava_command_buffer::record_execution() {
         // reference computes every row and reads the last, llava_session.cpp:129-135)
         const float* last = static_cast<const float*>(current->device_ptr()) + size_t(batch_size - 1) * h.dim;
         float* logits = static_cast<float*>(s->output_probs->device_ptr());
+        // sharded with fused exchanges: the last layer's w2 pushed its partial rows; the head's
+        // normalisation takes residual + the ranks' sum
+        if (c->tp_size() > 1 && c->fused_exchange())
+            tp_arm_pull(2 * u32(c->get_layers().size()) - 1, h.dim, current == s->current_thought ? s->current_thought_sublayer : s->current_thought);
         note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), int(c->output_w->type), last,
                           static_cast<const float*>(c->norm_w->device_ptr()), h.vocab_size, h.dim, 1));
         // greedy choice, token log and position word in one launch; the kernel stores the token
@@ -216,6 +220,14 @@ void llava_command_buffer::gemm_silu_ff(llava_buffer* outbuf, llava_buffer* w3, 
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && outbuf->shape.first >= w3->shape.first, "gemm_silu_ff shapes")) return;
     note(lv_gemm_tc_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), split->device_ptr(), w3->shape.first,
                          w3->shape.second, batch_size));
+}
+
+void llava_command_buffer::tp_arm_push(u32 exchange) {
+    note(lv_tp_arm_push(lv(), int(exchange), 2 * u32(session->ctx->get_layers().size())));
+}
+
+void llava_command_buffer::tp_arm_pull(u32 exchange, u32 producer_rows, llava_buffer* x_out) {
+    note(lv_tp_arm_pull(lv(), int(exchange), 2 * u32(session->ctx->get_layers().size()), producer_rows, f32(x_out)));
 }
 
 void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf,

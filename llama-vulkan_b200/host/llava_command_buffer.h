@@ -41,6 +41,11 @@ public:
 
     // tensor-parallel: partial <- sum over ranks of partial; residual += partial
     void allreduce_add(llava_buffer* residual, llava_buffer* partial);
+    // exchange fused into the neighbouring GEMVs (lv_tp_arm_push / lv_tp_arm_pull): the next matmul
+    // pushes its rows to all ranks; the next normalising matmul takes inbuf + the ranks' sum as its
+    // input and leaves that sum in x_out
+    void tp_arm_push(u32 exchange);
+    void tp_arm_pull(u32 exchange, u32 producer_rows, llava_buffer* x_out);
     // batched forms on the tensor cores (16..64 tokens per step, q4_0): the activations are first
     // split into two fp16 planes (optionally normalised), then every matrix is read once
     bool use_tensor_cores(const llava_buffer* matrix) const;

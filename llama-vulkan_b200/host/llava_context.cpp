@@ -66,7 +66,8 @@ bool llava_context::peer_window_create(u8* handle64) {
 }
 
 bool llava_context::peer_connect(const u8* handles) {
-    return lv_context != nullptr && lv_peer_connect(lv_context, int(rank_), handles) == LV_OK;
+    peers_connected = lv_context != nullptr && lv_peer_connect(lv_context, int(rank_), handles) == LV_OK;
+    return peers_connected;
 }
 
 bool llava_context::open(const string& model_path, int device) {

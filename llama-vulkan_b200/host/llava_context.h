@@ -31,6 +31,10 @@ public:
     // its 64-byte IPC handle, the handles of all ranks are exchanged by the caller, then connected.
     bool peer_window_create(u8* handle64);
     bool peer_connect(const u8* handles);
+    // true once the ranks' windows are connected: the all-reduces are then split between the
+    // producing and the consuming GEMV instead of running as kernels of their own
+    bool fused_exchange() const { return peers_connected && fused_exchange_enabled; }
+    void set_fused_exchange(bool on) { fused_exchange_enabled = on; }
     u32 tp_rank() const { return rank_; }
     u32 tp_size() const { return n_ranks_; }
 
@@ -54,6 +58,8 @@ public:
     std::mutex queue_mutex;          // serialises sessions that share the stream
 
 private:
+    bool peers_connected = false;
+    bool fused_exchange_enabled = true;
     bool setup_signal_handling();
     void close_all();
     ggml_file* model = nullptr;

@@ -93,13 +93,44 @@ llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_se
             cmd_buf->gemm_add_inplace(x, feed_forward_w2, split);
             return x;
         }
-        cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
-                                   attention_wv, x, attention_norm);
+        if (context->tp_size() > 1 && context->fused_exchange() && layer_id > 0) {
+            // the previous layer's w2 pushed exchange 2l-1: input = xb + the ranks' rows, sum kept in xa
+            cmd_buf->tp_arm_pull(2 * layer_id - 1, context->get_model()->get_header().dim, session->current_thought);
+            cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
+                                       attention_wv, session->current_thought_sublayer, attention_norm);
+        } else {
+            cmd_buf->norm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
+                                       attention_wv, x, attention_norm);
+        }
         cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);
         if (context->tp_size() == 1) {
             cmd_buf->matmul_add_inplace(x, attention_wo, session->current_Vout);
             cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, x, ffn_norm);
             cmd_buf->matmul_add_inplace(x, feed_forward_w2, session->main_ff_result);
+        } else if (context->fused_exchange()) {
+            // every rank holds a column shard of wo and w2.  Their partial products travel inside the
+            // GEMVs: wo / w2 push their rows into every rank's window, the next normalising GEMV adds
+            // the ranks' rows to the residual stream on its way in and leaves the sum in the other of
+            // the two residual buffers (xa = current_thought, xb = current_thought_sublayer).
+            // Exchange 2l follows wo of layer l, exchange 2l+1 follows w2.
+            llava_buffer* xa = session->current_thought;
+            llava_buffer* xb = session->current_thought_sublayer;
+            const u32 dim = context->get_model()->get_header().dim;
+            const bool last = layer_id + 1 == context->get_layers().size();
+            // (the QKV launch above already consumed exchange 2l-1 when l > 0: see below)
+            cmd_buf->tp_arm_push(2 * layer_id);
+            cmd_buf->matmul(session->tp_partial, attention_wo, session->current_Vout);
+            cmd_buf->tp_arm_pull(2 * layer_id, dim, xb);
+            cmd_buf->norm_matmul_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, xa, ffn_norm);
+            if (last && !cmd_buf->with_head) {
+                // nothing consumes the last exchange of a step without a head: use the stand-alone kernel
+                cmd_buf->matmul(session->tp_partial, feed_forward_w2, session->main_ff_result);
+                cmd_buf->allreduce_add(xb, session->tp_partial);
+            } else {
+                cmd_buf->tp_arm_push(2 * layer_id + 1);
+                cmd_buf->matmul(session->tp_partial, feed_forward_w2, session->main_ff_result);
+            }
+            return xb;
         } else {
             // every rank holds a column shard of wo and w2: partial products, summed over the
             // ranks, then added to the (replicated) residual stream
