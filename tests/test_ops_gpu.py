@@ -371,3 +371,38 @@ def test_graph_capture_replays_with_a_new_position(gpu, pkg, rope_table):
     assert np.array_equal(got[2], want) and np.array_equal(got[9], want)
     assert not got[[0, 1, 3, 8, 10]].any()
     pkg.check(gpu.lib.lv_graph_destroy(g))
+
+
+def test_exchange_fused_into_the_gemvs_on_one_rank(pkg):
+    """lv_tp_arm_push / lv_tp_arm_pull with a single-rank window: the pushed rows of one GEMV come
+    back as `x + rows` in the input of the next normalising GEMV, which also stores that sum."""
+    rng = np.random.default_rng(60)
+    K, rows_out, steps = 1024, 512, 3
+    Wa = qn.quantize_q4_0((rng.standard_normal((K, 512)) * 0.05).astype(np.float32))      # K rows of 512 columns
+    Wb = qn.quantize_q4_0((rng.standard_normal((rows_out, K)) * 0.05).astype(np.float32))
+    nw = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    with pkg.Context(0) as g:
+        lib, h = g.lib, g.handle
+        handle = (C.c_uint8 * 64)()
+        pkg.check(lib.lv_peer_window_create(h, 1, K, handle))
+        pkg.check(lib.lv_peer_connect(h, 0, handle))
+        cfg, dWa, dWb, dnw = u32_dev(g, 0), g.upload(Wa), g.upload(Wb), g.upload(nw)
+        for step in range(steps):                       # a new step number (flag epoch) every round
+            v = rng.standard_normal(512).astype(np.float32)
+            x = rng.standard_normal(K).astype(np.float32)
+            dx, dxo, dout, dummy = g.upload(x), g.zeros(K * 4), g.zeros(rows_out * 4), g.zeros(K * 4)
+            for exchange in (0, 1):                     # both slot sets
+                pkg.check(lib.lv_tp_arm_push(h, exchange, 2))
+                pkg.check(lib.lv_gemv(h, dummy, dWa, qn.Q4_0, g.upload(v), K, 512, 1, 0))
+                pkg.check(lib.lv_tp_arm_pull(h, exchange, 2, K, dxo))
+                pkg.check(lib.lv_norm_gemv(h, dout, dWb, qn.Q4_0, dx, dnw, rows_out, K, 1))
+                g.sync()
+                partial = ob.gemv(Wa, qn.Q4_0, v, K, 512, 128)
+                close(g.download(dxo, np.float32, K), x + partial, rel_l2=2e-6, max_abs_frac=2e-6)
+                close(g.download(dout, np.float32, rows_out), ob.gemv(Wb, qn.Q4_0, ob.norm(x + partial, nw), rows_out, K, 128))
+                assert not g.download(dummy, np.float32, K).any()          # a pushing GEMV does not write its `out`
+            pkg.check(lib.lv_decode_advance(h, cfg, None, None, 1, 0))      # ends the step: the next epochs differ
+        # an armed role without connected windows is refused, as is an exchange index outside the step
+        assert lib.lv_tp_arm_push(h, 2, 2) == pkg.LV_ERR_BAD_ARGUMENTS
+        pkg.check(lib.lv_peer_destroy(h))
+        assert lib.lv_tp_arm_push(h, 0, 2) == pkg.LV_ERR_BAD_ARGUMENTS
