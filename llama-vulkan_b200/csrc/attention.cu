@@ -18,8 +18,10 @@
 namespace lv {
 
 constexpr int kAttnThreads = 256;  // the three separate ops
-constexpr int kFusedThreads = 1024;
-constexpr int kAttnChunk = 256;    // cache rows per CTA of the fused kernel (8 per warp)
+constexpr int kFusedThreads = 512;  // 128 registers per thread: room to keep every load of a step in flight
+constexpr int kAttnChunk = 256;    // cache rows per CTA of the fused kernel (16 per warp)
+constexpr int kScoreIters = kAttnChunk / (kFusedThreads / 32) / 4;   // row batches per warp: four rows at a time, 8 lanes each
+constexpr int kValueRows = kAttnChunk / (kFusedThreads / 16);        // rows per thread in the value pass
 constexpr int kRowGroups = kFusedThreads / 16;   // 16 threads x 8 dims cover a row of one head
 constexpr int kRot = 128;        // head size; the reference supports only 128 (dim 4096/5120)
 
@@ -130,7 +132,7 @@ __host__ __device__ inline size_t attn_partial_floats(uint32_t heads, uint32_t n
 // step): scores with 8 lanes per cache row (16 elements each, both of a warp's
 // row batches in flight together), values with 16 threads per row (8 dims each)
 // and four rows per thread in flight.
-__global__ void __launch_bounds__(kFusedThreads) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
+__global__ void __launch_bounds__(kFusedThreads, 1) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
                                                                        const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                        float* __restrict__ partial, uint32_t* __restrict__ counters,
@@ -151,18 +153,18 @@ __global__ void __launch_bounds__(kFusedThreads) attention_fused_kernel(float* _
     const uint32_t p0 = c * kAttnChunk;
     const uint32_t n = min(uint32_t(kAttnChunk), P + 1 - p0);
 
-    // ---- scores: warp w owns rows 8w .. 8w+7, lane group g = lane / 8 one row per pass -------
+    // ---- scores: warp w owns rows 16w .. 16w+15, lane group g = lane / 8 one row per pass -----
     {
         const int sub = lane & 7, g = lane >> 3;
         const float* qh = q + size_t(z) * dim + h * kRot + sub * 16;
         float4 qv[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) qv[j] = *reinterpret_cast<const float4*>(qh + 4 * j);
-        uint4 kraw[2][2];
-        float4 cs[2][4];
+        uint4 kraw[kScoreIters][2];
+        float4 cs[kScoreIters][4];
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const uint32_t i = warp * 8 + it * 4 + g;
+        for (int it = 0; it < kScoreIters; ++it) {
+            const uint32_t i = warp * (4 * kScoreIters) + it * 4 + g;
             const uint32_t p = p0 + min(i, n - 1);                 // clamped: rows past n are computed and discarded
             const __half* krow = kc + size_t(p) * dim + h * kRot + sub * 16;
             kraw[it][0] = *reinterpret_cast<const uint4*>(krow);
@@ -172,8 +174,8 @@ __global__ void __launch_bounds__(kFusedThreads) attention_fused_kernel(float* _
             for (int j = 0; j < 4; ++j) cs[it][j] = *reinterpret_cast<const float4*>(t + 4 * j);
         }
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const uint32_t i = warp * 8 + it * 4 + g;
+        for (int it = 0; it < kScoreIters; ++it) {
+            const uint32_t i = warp * (4 * kScoreIters) + it * 4 + g;
             const __half2* k2 = reinterpret_cast<const __half2*>(&kraw[it][0]);      // 8 (even, odd) pairs
             float sacc = 0.f;
 #pragma unroll
@@ -213,18 +215,18 @@ __global__ void __launch_bounds__(kFusedThreads) attention_fused_kernel(float* _
         l = warp_sum(l);
         if (lane == 0) { s_red[0] = m; s_red[1] = l; }
     }
-    // ---- weighted values: thread = (8 dims, one of 64 row groups), rows rg, rg+64, rg+128, rg+192 --
+    // ---- weighted values: thread = (8 dims, one of 32 row groups), rows rg, rg+32, ... -----------
     const int d8 = (threadIdx.x & 15) * 8, rg = threadIdx.x >> 4;
-    uint4 vraw[4];
+    uint4 vraw[kValueRows];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kValueRows; ++j) {
         const uint32_t i = min(uint32_t(rg + kRowGroups * j), n - 1);
         vraw[j] = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * dim + h * kRot + d8);
     }
     __syncthreads();                                       // s_e now holds the exponentials
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kValueRows; ++j) {
         const uint32_t i = rg + kRowGroups * j;
         const float e = i < n ? s_e[i] : 0.f;
         const __half2* v2 = reinterpret_cast<const __half2*>(&vraw[j]);
