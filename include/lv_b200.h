@@ -172,11 +172,11 @@ int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config,
 /* When 16 or more tokens are evaluated together the reference dispatches its
  * matmul shaders with the batch in gl_WorkGroupID.z (llava_command_buffer.cpp:
  * 61-132), streaming every matrix once per token.  These entry points read the
- * matrix once for up to 64 tokens: q4_0 blocks are dequantised in the kernel
- * into exact fp16 (hi, lo) tiles and multiplied on the tcgen05 tensor cores
- * with fp32 accumulation.  The activations enter as the two fp16 planes that
+ * matrix once for up to 64 tokens: q4_0 / q8_0 blocks are dequantised in the
+ * kernel into exact fp16 (hi, lo) tiles and multiplied on the tcgen05 tensor
+ * cores with fp32 accumulation.  The activations enter as the two fp16 planes that
  * lv_act_split_f16 writes.  rows: multiple of 128 (64 for the SiLU pair);
- * cols: multiple of 256; batch 1..64; wtype must be q4_0 (2). */
+ * cols: multiple of 256; batch 1..64; wtype q4_0 (2) or q8_0 (8). */
 
 /* Bytes of the split-activation buffer for [batch][cols] inputs. */
 size_t lv_act_split_bytes(uint32_t cols, uint32_t batch);

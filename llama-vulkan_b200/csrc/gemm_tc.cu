@@ -7,10 +7,10 @@
 //
 //   out[z][r] = sum_k W[r][k] * x[z][k]        r: 128 rows per CTA, z < Z <= 64
 //
-// A operand: the q4_0 blocks of 128 rows, fetched by 2-D tensor-map TMA loads into a raw
-// ring, dequantised by sixteen warps into K-major fp16 tiles with the 128-byte swizzle.  A
-// weight (q - 8) * d needs up to 14 significant bits, so it is written as an exact pair
-// hi = fp16(w), lo = w - hi.  B operand: the activations as an exact-to-22-bits pair of fp16
+// A operand: the q4_0 / q8_0 blocks of 128 rows, fetched by 2-D tensor-map TMA loads into a
+// raw ring, dequantised by sixteen warps into K-major fp16 tiles with the 128-byte swizzle.
+// A weight (q - 8) * d (q4_0) or q * d (q8_0) needs up to 14 / 19 significant bits, so it is
+// written as an exact pair hi = fp16(w), lo = w - hi.  B operand: the activations as an exact-to-22-bits pair of fp16
 // planes (lv_act_split_f16), fetched by swizzled TMA loads (the lo plane's rows follow the hi
 // plane's, so one B tile of 2Z rows serves both).  One thread issues, per 64 columns of K,
 // four K=16 steps of two tcgen05.mma: W_hi x [x_hi; x_lo] (N = 2Z) and W_lo x x_hi (N = Z)
@@ -35,20 +35,30 @@ constexpr int kTcRows = 128;                   // rows of W per CTA = M of the M
 constexpr int kTcMaxZ = 64;                    // tokens per launch = N of the MMA (padded to 16)
 constexpr int kTcChunkK = 64;                  // K per A/B tile: 64 fp16 = one 128-byte swizzle row
 constexpr int kTcRawBlocks = 8;                // q-blocks of a row per raw stage (4 tiles of K)
-constexpr int kTcRawRowBytes = kTcRawBlocks * kQ4BlockBytes;          // 144
-constexpr int kTcRawStage = kTcRows * kTcRawRowBytes;                 // 18432
 constexpr int kTcRawStages = 2;
 constexpr int kTcSlots = 3;
 constexpr int kTcTileBytes = kTcRows * kTcChunkK * 2;                 // 16384: one fp16 plane of A
 constexpr int kTcSlotBytes = 2 * kTcTileBytes;                        // 32768: hi and lo planes of A
-constexpr int kTcBRingBytes = 65536;           // ring of B tiles (hi and lo planes, 2 zpad rows of 128 bytes each)
 constexpr int kTcMaxBStages = 16;
 constexpr int kTcBanks = 2;                    // accumulator sets used in turn, to halve the length of each fp32 chain
 constexpr int kTcProducerWarps = 16;           // two groups of 8: even and odd tiles of K
 constexpr int kTcGroupWarps = 8;
 constexpr int kTcThreads = (kTcProducerWarps + 2) * 32;               // + TMA warp + MMA warp
-constexpr size_t kTcSmemBytes = 1024 /* alignment slack */ + size_t(kTcSlots) * kTcSlotBytes + kTcBRingBytes +
-                                size_t(kTcRawStages) * kTcRawStage + 512;
+
+template <int QT> struct TcTraits;
+template <> struct TcTraits<T_Q4_0> {
+    static constexpr int kBlockBytes = kQ4BlockBytes;
+    static constexpr int kBRingBytes = 65536;  // ring of B tiles (hi and lo planes, 2 zpad rows of 128 bytes each)
+};
+template <> struct TcTraits<T_Q8_0> {
+    static constexpr int kBlockBytes = kQ8BlockBytes;
+    static constexpr int kBRingBytes = 49152;  // the raw ring is larger, the B ring shorter
+};
+template <int QT> __host__ __device__ constexpr int tc_raw_row_bytes() { return kTcRawBlocks * TcTraits<QT>::kBlockBytes; }       // 144 / 272
+template <int QT> __host__ __device__ constexpr int tc_raw_stage() { return kTcRows * tc_raw_row_bytes<QT>(); }                   // 18432 / 34816
+template <int QT> __host__ __device__ constexpr size_t tc_smem_bytes() {
+    return 1024 /* alignment slack */ + size_t(kTcSlots) * kTcSlotBytes + TcTraits<QT>::kBRingBytes + size_t(kTcRawStages) * tc_raw_stage<QT>() + 512;
+}
 
 struct GemmTcParams {
     GemvMatrix m[3];         // same meaning as in the GEMV; w_gate set = SiLU pair (64 + 64 rows per CTA)
@@ -118,15 +128,31 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 d2, __half2 (&h
     }
 }
 
+// Four int8 of one word -> exact (hi, lo) fp16 pairs of q * d: e[0] = elements (4k, 4k+1), e[1] = (4k+2, 4k+3).
+__device__ __forceinline__ void dequant_word_q8(uint32_t w, __half2 d2, __half2 (&hi)[2], __half2 (&lo)[2]) {
+    const uint32_t u = w ^ 0x80808080u;                                       // q + 128 as unsigned bytes
+    const uint32_t raw[2] = {__byte_perm(u, 0x64646464u, 0x4140), __byte_perm(u, 0x64646464u, 0x4342)};   // 1024 + 128 + q
+    const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&raw[i]), off);      // q, exact
+        hi[i] = __hmul2(q, d2);
+        lo[i] = __hfma2(q, d2, __hneg2(hi[i]));                                            // exact remainder (q * d has <= 19 bits)
+    }
+}
+
+template <int QT>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcParams p, const __grid_constant__ GemmTcMaps maps) {
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     uint8_t* slots = smem;
+    constexpr int kRawRowBytes = tc_raw_row_bytes<QT>(), kRawStage = tc_raw_stage<QT>(), kBRingBytes = TcTraits<QT>::kBRingBytes;
+    constexpr int kTileWords = kRawRowBytes / 16;                    // 32-bit words of one 64-column tile of a row: 9 / 17
     uint8_t* bring = smem + kTcSlots * kTcSlotBytes;
-    uint8_t* rawring = bring + kTcBRingBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(rawring + kTcRawStages * kTcRawStage);
+    uint8_t* rawring = bring + kBRingBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rawring + kTcRawStages * kRawStage);
     uint64_t* raw_full = bars;                       // [2]
     uint64_t* raw_empty = bars + 2;                  // [2]
     uint64_t* slot_full = bars + 4;                  // [3]
@@ -152,7 +178,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
 
     const uint32_t n_chunks = p.K / kTcChunkK;
     const uint32_t b_bytes = 2u * p.zpad * kTcChunkK * 2u;
-    const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kTcBRingBytes) / b_bytes);      // B stages: 4 (zpad 64) .. 16
+    const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kBRingBytes) / b_bytes);         // B stages: 3-4 (zpad 64) .. 16
     // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
     // the allocation is a power of two >= 32
     const uint32_t bank_cols = 3u * p.zpad;
@@ -177,13 +203,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
 
     auto issue_raw = [&](uint32_t g) {
         const int rs = int(g % kTcRawStages);
-        uint8_t* dst = rawring + rs * kTcRawStage;
-        const int x = int(g * (kTcRawRowBytes / 8));
-        mbar_expect_tx(&raw_full[rs], kTcRawStage);
+        uint8_t* dst = rawring + rs * kRawStage;
+        const int x = int(g * (kRawRowBytes / 8));
+        mbar_expect_tx(&raw_full[rs], kRawStage);
         const CUtensorMap* wm = mi == 0 ? &maps.w[0] : (mi == 1 ? &maps.w[1] : &maps.w[2]);
         if (pair) {
             tma_load_2d_plain(dst, &maps.w[0], x, int(row0), &raw_full[rs]);                              // w3 rows -> tile rows 0..63
-            tma_load_2d_plain(dst + (kTcRows / 2) * kTcRawRowBytes, &maps.gate, x, int(row0), &raw_full[rs]);   // w1 rows -> 64..127
+            tma_load_2d_plain(dst + (kTcRows / 2) * kRawRowBytes, &maps.gate, x, int(row0), &raw_full[rs]);      // w1 rows -> 64..127
         } else {
             tma_load_2d_plain(dst, wm, x, int(row0), &raw_full[rs]);
         }
@@ -253,21 +279,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             const int rs = int(g % kTcRawStages);
             ok = mbar_wait(&raw_full[rs], (g / kTcRawStages) & 1u, p.err);
             if (!ok) break;
-            // the two tiles of this group that the thread's producer group owns: 18 words (4 blocks) each
-            uint32_t w[2][9];
-            const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kTcRawStage + r * kTcRawRowBytes);
+            // the two tiles of this group that the thread's producer group owns (tiles jpar and jpar + 2 of the
+            // four): kTileWords words each, taken out of the row with 16-byte loads
+            uint32_t w[2][kTileWords];
+            const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kRawStage + r * kRawRowBytes);
             {
-                // tile jpar: bytes 36 jpar .. +36; tile jpar + 2: bytes 72 + 36 jpar .. +36
-                uint32_t all[36];
+                uint32_t all[4 * kTileWords];
 #pragma unroll
-                for (int i = 0; i < 9; ++i) {
+                for (int i = 0; i < kTileWords; ++i) {
                     const uint4 v = src[i];
                     all[4 * i] = v.x; all[4 * i + 1] = v.y; all[4 * i + 2] = v.z; all[4 * i + 3] = v.w;
                 }
 #pragma unroll
-                for (int i = 0; i < 9; ++i) {
-                    w[0][i] = jpar ? all[9 + i] : all[i];
-                    w[1][i] = jpar ? all[27 + i] : all[18 + i];
+                for (int i = 0; i < kTileWords; ++i) {
+                    w[0][i] = jpar ? all[kTileWords + i] : all[i];
+                    w[1][i] = jpar ? all[3 * kTileWords + i] : all[2 * kTileWords + i];
                 }
             }
             __syncwarp();
@@ -280,38 +306,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     ok = mbar_wait(&slot_empty[s], ((c / kTcSlots) - 1) & 1u, p.err);
                     if (!ok) break;
                 }
-                // even block: scale in the low half of word 0, nibbles shifted by two bytes;
-                // odd block: scale in the high half of word 4, nibbles aligned
-                uint32_t q[4];
+                // even block of the tile: scale in the low half of word 0, payload shifted by two bytes;
+                // odd block: scale in the high half of the middle word, payload word-aligned
+                constexpr int kQWords = (kTileWords - 1) / 2;         // payload words of a block: 4 (nibbles) / 8 (int8)
+                uint32_t q[kQWords];
                 uint32_t dbits;
                 if (khalf == 0) {
                     dbits = w[jj][0] & 0xffffu;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) q[k] = __funnelshift_r(w[jj][k], w[jj][k + 1], 16);
+                    for (int k = 0; k < kQWords; ++k) q[k] = __funnelshift_r(w[jj][k], w[jj][k + 1], 16);
                 } else {
-                    dbits = w[jj][4] >> 16;
+                    dbits = w[jj][kQWords] >> 16;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) q[k] = w[jj][5 + k];
+                    for (int k = 0; k < kQWords; ++k) q[k] = w[jj][kQWords + 1 + k];
                 }
                 const __half dh = __ushort_as_half(static_cast<unsigned short>(dbits));
                 const __half2 d2 = __half2half2(dh);
-                __half2 hi[4][4], lo[4][4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) dequant_word(q[k], d2, hi[k], lo[k]);
-                // 16-byte chunks of the block: elements 0-7 (words 0,1 low nibbles), 8-15, 16-23 (high nibbles), 24-31
                 uint8_t* a_hi = slots + s * kTcSlotBytes;
                 uint8_t* a_lo = a_hi + kTcTileBytes;
+                if constexpr (QT == T_Q4_0) {
+                    __half2 hi[4][4], lo[4][4];
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int k0 = (cc & 1) * 2, part = (cc >> 1) * 2;     // words k0, k0+1; low (0) or high (2) nibbles
-                    const uint32_t at = tc_swizzled(r, khalf * 4 + cc);
-                    uint4 vh, vl;
-                    vh.x = *reinterpret_cast<uint32_t*>(&hi[k0][part]); vh.y = *reinterpret_cast<uint32_t*>(&hi[k0][part + 1]);
-                    vh.z = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part]); vh.w = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part + 1]);
-                    vl.x = *reinterpret_cast<uint32_t*>(&lo[k0][part]); vl.y = *reinterpret_cast<uint32_t*>(&lo[k0][part + 1]);
-                    vl.z = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part]); vl.w = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part + 1]);
-                    *reinterpret_cast<uint4*>(a_hi + at) = vh;
-                    *reinterpret_cast<uint4*>(a_lo + at) = vl;
+                    for (int k = 0; k < 4; ++k) dequant_word(q[k], d2, hi[k], lo[k]);
+                    // 16-byte chunks of the block: elements 0-7 (words 0,1 low nibbles), 8-15, 16-23 (high nibbles), 24-31
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int k0 = (cc & 1) * 2, part = (cc >> 1) * 2;     // words k0, k0+1; low (0) or high (2) nibbles
+                        const uint32_t at = tc_swizzled(r, khalf * 4 + cc);
+                        uint4 vh, vl;
+                        vh.x = *reinterpret_cast<uint32_t*>(&hi[k0][part]); vh.y = *reinterpret_cast<uint32_t*>(&hi[k0][part + 1]);
+                        vh.z = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part]); vh.w = *reinterpret_cast<uint32_t*>(&hi[k0 + 1][part + 1]);
+                        vl.x = *reinterpret_cast<uint32_t*>(&lo[k0][part]); vl.y = *reinterpret_cast<uint32_t*>(&lo[k0][part + 1]);
+                        vl.z = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part]); vl.w = *reinterpret_cast<uint32_t*>(&lo[k0 + 1][part + 1]);
+                        *reinterpret_cast<uint4*>(a_hi + at) = vh;
+                        *reinterpret_cast<uint4*>(a_lo + at) = vl;
+                    }
+                } else {
+                    // int8 payload in element order: chunk cc = elements 8cc .. 8cc+7 = words 2cc, 2cc+1
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        __half2 hi0[2], lo0[2], hi1[2], lo1[2];
+                        dequant_word_q8(q[2 * cc], d2, hi0, lo0);
+                        dequant_word_q8(q[2 * cc + 1], d2, hi1, lo1);
+                        const uint32_t at = tc_swizzled(r, khalf * 4 + cc);
+                        uint4 vh, vl;
+                        vh.x = *reinterpret_cast<uint32_t*>(&hi0[0]); vh.y = *reinterpret_cast<uint32_t*>(&hi0[1]);
+                        vh.z = *reinterpret_cast<uint32_t*>(&hi1[0]); vh.w = *reinterpret_cast<uint32_t*>(&hi1[1]);
+                        vl.x = *reinterpret_cast<uint32_t*>(&lo0[0]); vl.y = *reinterpret_cast<uint32_t*>(&lo0[1]);
+                        vl.z = *reinterpret_cast<uint32_t*>(&lo1[0]); vl.w = *reinterpret_cast<uint32_t*>(&lo1[1]);
+                        *reinterpret_cast<uint4*>(a_hi + at) = vh;
+                        *reinterpret_cast<uint4*>(a_lo + at) = vl;
+                    }
                 }
                 fence_proxy_async();                           // make the tile visible to the tensor core's reads
                 __syncwarp();
@@ -446,34 +491,42 @@ __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh,
 }
 
 int gemm_tc_configure(lv_ctx* ctx) {
-    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kTcSmemBytes, "device has too little shared memory for the batched product");
-    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTcSmemBytes)));
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q4_0>() && size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q8_0>(),
+               "device has too little shared memory for the batched product");
+    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>())));
+    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>())));
     return LV_OK;
 }
 
-static int launch_gemm_tc(lv_ctx* ctx, GemmTcParams& p, const __half* xh) {
+template <int QT>
+static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) {
     LV_REQUIRE(p.K != 0 && p.K % 256 == 0, "cols must be a non-zero multiple of 256");
     LV_REQUIRE(p.Z >= 1 && p.Z <= uint32_t(kTcMaxZ), "batch of the tensor-core product must be 1..64");
     LV_REQUIRE(xh != nullptr && (reinterpret_cast<uintptr_t>(xh) & 15u) == 0, "split activations null or not 16-byte aligned");
     p.zpad = (p.Z + 15u) & ~15u;
     const bool pair = p.m[0].w_gate != nullptr;
     const uint32_t rows_per_cta = pair ? kTcRows / 2 : kTcRows;
-    const uint32_t row_bytes = p.K / 32 * kQ4BlockBytes;
+    const uint32_t row_bytes = p.K / 32 * TcTraits<QT>::kBlockBytes;
     GemmTcMaps maps{};
     uint32_t tiles = 0;
     for (int i = 0; i < p.n_mat; ++i) {
         LV_REQUIRE(p.m[i].w != nullptr && (reinterpret_cast<uintptr_t>(p.m[i].w) & 15u) == 0, "matrix pointer null or not 16-byte aligned");
         LV_REQUIRE(p.m[i].rows != 0 && p.m[i].rows % rows_per_cta == 0, "rows must be a multiple of 128 (64 for the SiLU pair)");
-        if (int rc = make_weight_map(&maps.w[i], p.m[i].w, p.m[i].rows, row_bytes, rows_per_cta, kTcRawRowBytes)) return rc;
+        if (int rc = make_weight_map(&maps.w[i], p.m[i].w, p.m[i].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
         tiles += p.m[i].rows / rows_per_cta;
     }
     if (pair) {
         LV_REQUIRE((reinterpret_cast<uintptr_t>(p.m[0].w_gate) & 15u) == 0, "matrix pointer not 16-byte aligned");
-        if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, kTcRawRowBytes)) return rc;
+        if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
     }
     if (int rc = make_act_map(&maps.x, xh, 2 * p.zpad, p.K, 2 * p.zpad, kTcChunkK)) return rc;
-    LV_CUDA(launch_pdl(ctx, gemm_tc_kernel, dim3(tiles), dim3(kTcThreads), kTcSmemBytes, p, maps));
+    LV_CUDA(launch_pdl(ctx, gemm_tc_kernel<QT>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps));
     return LV_OK;
+}
+
+static int launch_gemm_tc(lv_ctx* ctx, GemmTcParams& p, const __half* xh, int wtype) {
+    LV_REQUIRE(wtype == T_Q4_0 || wtype == T_Q8_0, "matrix type must be q4_0 (2) or q8_0 (8)");
+    return wtype == T_Q4_0 ? launch_gemm_tc_typed<T_Q4_0>(ctx, p, xh) : launch_gemm_tc_typed<T_Q8_0>(ctx, p, xh);
 }
 
 }  // namespace lv
@@ -496,28 +549,26 @@ extern "C" int lv_gemm_tc(lv_ctx* ctx, float* out, const void* W, int wtype, con
                           uint32_t batch, int add) {
     LV_ENTER(ctx);
     LV_REQUIRE(out && W, "null argument");
-    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
     GemmTcParams p{};
     p.m[0] = {static_cast<const uint8_t*>(W), nullptr, out, rows, add ? EPI_ADD : EPI_STORE};
     p.n_mat = 1;
     p.K = cols;
     p.Z = batch;
     p.err = ctx->d_err;
-    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh), wtype);
 }
 
 extern "C" int lv_gemm_tc_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1, int wtype, const void* xh, uint32_t ff,
                                uint32_t dim, uint32_t batch) {
     LV_ENTER(ctx);
     LV_REQUIRE(out && w3 && w1, "null argument");
-    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
     GemmTcParams p{};
     p.m[0] = {static_cast<const uint8_t*>(w3), static_cast<const uint8_t*>(w1), out, ff, EPI_STORE};
     p.n_mat = 1;
     p.K = dim;
     p.Z = batch;
     p.err = ctx->d_err;
-    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh), wtype);
 }
 
 extern "C" int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache, void* v_cache, const void* wq, const void* wk,
@@ -525,7 +576,6 @@ extern "C" int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache,
                                        uint32_t dim, uint32_t batch, uint32_t ctx_rows) {
     LV_ENTER(ctx);
     LV_REQUIRE(q_out && k_cache && v_cache && wq && wk && wv && pos, "null argument");
-    LV_REQUIRE(wtype == T_Q4_0, "the tensor-core product takes q4_0 (2) matrices");
     LV_REQUIRE(ctx_rows >= batch, "cache smaller than the batch");
     GemmTcParams p{};
     p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, k_cache, rows_each, EPI_STORE_F16_AT_POS};
@@ -537,5 +587,5 @@ extern "C" int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache,
     p.K = dim;
     p.Z = batch;
     p.err = ctx->d_err;
-    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh));
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh), wtype);
 }

@@ -37,8 +37,8 @@ def split(gpu, pkg, x, norm_w=None):
     return xh
 
 
-def matrix(rng, rows, cols, scale=0.02):
-    return qn.quantize_q4_0((rng.standard_normal((rows, cols)) * scale).astype(np.float32))
+def matrix(rng, rows, cols, scale=0.02, wtype=qn.Q4_0):
+    return qn.quantize((rng.standard_normal((rows, cols)) * scale).astype(np.float32), wtype)
 
 
 def test_act_split_planes_add_up_to_the_input(gpu, pkg):
@@ -63,23 +63,24 @@ def test_act_split_planes_add_up_to_the_input(gpu, pkg):
         close(planes[0, z] + planes[1, z], ob.norm(xs[z], w), rel_l2=2e-6, max_abs_frac=2e-6)
 
 
+@pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
 @pytest.mark.parametrize("rows,cols,batch", [(128, 256, 16), (256, 4096, 5), (4096, 4096, 64), (384, 11008, 33), (640, 5120, 17)])
-def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch):
+def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch, wtype):
     rng = np.random.default_rng(51)
-    W = matrix(rng, rows, cols)
+    W = matrix(rng, rows, cols, wtype=wtype)
     x = rng.standard_normal((batch, cols)).astype(np.float32)
     xh = split(gpu, pkg, x)
-    want = np.stack([ob.gemv(W, qn.Q4_0, x[z], rows, cols, workers_for(cols)) for z in range(batch)])
+    want = np.stack([ob.gemv(W, wtype, x[z], rows, cols, workers_for(cols)) for z in range(batch)])
     dW = gpu.upload(W)
     out = gpu.upload(np.full((batch + 1, rows), 7.0, np.float32))
-    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, qn.Q4_0, xh, rows, cols, batch, 0))
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, wtype, xh, rows, cols, batch, 0))
     gpu.sync()
     got = gpu.download(out, np.float32, (batch + 1) * rows).reshape(batch + 1, rows)
     close(got[:batch], want)
     assert (got[batch] == 7.0).all()                                     # nothing written past the batch
     base = rng.standard_normal((batch, rows)).astype(np.float32)
     out = gpu.upload(base)
-    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, qn.Q4_0, xh, rows, cols, batch, 1))
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, wtype, xh, rows, cols, batch, 1))
     gpu.sync()
     close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), base + want)
 
@@ -101,19 +102,20 @@ def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg):
     close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), want, rel_l2=2e-6, max_abs_frac=2e-6)
 
 
+@pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
 @pytest.mark.parametrize("ff,dim,batch", [(192, 512, 16), (11008, 4096, 20)])
-def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch):
+def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype):
     rng = np.random.default_rng(53)
-    w3, w1 = matrix(rng, ff, dim), matrix(rng, ff, dim)
+    w3, w1 = matrix(rng, ff, dim, wtype=wtype), matrix(rng, ff, dim, wtype=wtype)
     x = rng.standard_normal((batch, dim)).astype(np.float32)
     nw = (1 + 0.05 * rng.standard_normal(dim)).astype(np.float32)
     xh = split(gpu, pkg, x, nw)
     out = gpu.zeros(batch * ff * 4)
-    pkg.check(gpu.lib.lv_gemm_tc_silu(gpu.handle, out, gpu.upload(w3), gpu.upload(w1), qn.Q4_0, xh, ff, dim, batch))
+    pkg.check(gpu.lib.lv_gemm_tc_silu(gpu.handle, out, gpu.upload(w3), gpu.upload(w1), wtype, xh, ff, dim, batch))
     gpu.sync()
     got = gpu.download(out, np.float32, batch * ff).reshape(batch, ff)
     for z in range(0, batch, 7):
-        close(got[z], ob.gemv_silu(w3, w1, qn.Q4_0, ob.norm(x[z], nw), ff, dim, workers_for(dim)), rel_l2=3e-5, max_abs_frac=1e-4)
+        close(got[z], ob.gemv_silu(w3, w1, wtype, ob.norm(x[z], nw), ff, dim, workers_for(dim)), rel_l2=3e-5, max_abs_frac=1e-4)
 
 
 def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg):
@@ -141,7 +143,7 @@ def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg):
 def test_gemm_tc_refuses_what_it_cannot_do(gpu, pkg):
     lib, h = gpu.lib, gpu.handle
     d = gpu.zeros(1 << 16)
-    assert lib.lv_gemm_tc(h, d, d, qn.Q8_0, d, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # q4_0 only
+    assert lib.lv_gemm_tc(h, d, d, 0, d, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS            # f32 matrices are not taken
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 100, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # rows not a multiple of 128
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 96, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS       # cols not a multiple of 256
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 256, 65, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # batch above 64
