@@ -10,6 +10,7 @@
 // because a rank cannot start launch k + 2 before every rank has finished reading launch k.
 // The reference is single-device; this replaces the NCCL all-reduce + add pair of the
 // baseline path (lv_allreduce_f32 + lv_add_f32) with one kernel.
+#include <cstdlib>
 #include <string>
 
 #include "common.cuh"
@@ -28,7 +29,7 @@ struct PeerWindowLayout {
     // slots, the flags of the stand-alone kernel (2 x 8 x 4 words), the flags of the exchanges fused into the GEMV
     __host__ __device__ size_t bytes(int n_ranks) const {
         return slot_floats(n_ranks) * sizeof(float) + size_t(kTpLegacyFlagWords) * sizeof(uint32_t) +
-               size_t(2) * kTpMaxRanks * kTpFlagCtas * sizeof(uint32_t) + 256;
+               size_t(2) * kTpMaxRanks * kTpFlagCtas * sizeof(uint32_t) + size_t(kTpFlagCtas) * sizeof(uint32_t) /* local flags */ + 256;
     }
 };
 
@@ -217,6 +218,10 @@ int peer_take_armed(lv_ctx* ctx, TpParams* tp, uint32_t pull_ctas) {
         tp->pull_exchange = arm.pull;
         tp->pull_ctas = pull_ctas;
         tp->x_out = arm.x_out;
+        // summing once per GPU pays from four ranks on (LV_TP_TWO_PHASE=0/1 overrides, for tests)
+        const char* force = getenv("LV_TP_TWO_PHASE");
+        tp->two_phase = force != nullptr && (force[0] == '0' || force[0] == '1') ? uint32_t(force[0] - '0')
+                                                                                  : uint32_t(st->params.n_ranks >= kTpTwoPhaseRanks);
     }
     arm.push = arm.pull = -1;
     arm.x_out = nullptr;

@@ -179,8 +179,45 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, con
         }
         ok = __syncthreads_and(ok);
     }
+    const float* x_in = p.x + size_t(z) * p.K;
+    bool sum_slots = true;
+    if (tp_pull && p.tp.two_phase != 0) {
+        // many ranks: summing all slots in every CTA would read (ranks + 1) vectors 148 times from L2.
+        // Instead every CTA sums one slice of the vector into x_out, publishes a flag, and all CTAs then
+        // stage the finished sum.  (All CTAs of the grid become resident: the kernel before this one
+        // waits for nothing, and a successor cannot start before every CTA of this grid has.)
+        const uint32_t epoch = tp_epoch(p.tp, p.tp.pull_exchange);
+        const uint32_t n4 = p.K / 4, per = (n4 + gridDim.x - 1) / gridDim.x;
+        const uint32_t begin = min(n4, blockIdx.x * per), end = min(n4, begin + per);
+        for (uint32_t i = begin + threadIdx.x; i < end && ok; i += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(x_in)[i];
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < p.tp.n_ranks; ++r) {                     // rank order: the same bits on every rank
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(tp_slot(p.tp, p.tp.rank, p.tp.pull_exchange, r)) + i);
+                sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+            }
+            v.x += sum.x; v.y += sum.y; v.z += sum.z; v.w += sum.w;
+            reinterpret_cast<float4*>(p.tp.x_out)[i] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_gpu(tp_local_flag(p.tp, blockIdx.x), epoch);
+        for (uint32_t idx = threadIdx.x; idx < gridDim.x && ok; idx += blockDim.x) {
+            const uint32_t* flag = tp_local_flag(p.tp, idx);
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(flag) != epoch) {
+                if (*reinterpret_cast<volatile uint32_t*>(p.err) != 0 || clock64() - t0 > kWaitCycleLimit) {
+                    atomicOr(p.err, ERR_PEER_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        ok = __syncthreads_and(ok);
+        x_in = p.tp.x_out;
+        sum_slots = false;
+    }
     // activation records (optionally normalised) while the first weight bytes are in flight
-    stage_activations(xrec, p.x + size_t(z) * p.K, p.norm_w, p.K, scratch, p.tp);
+    stage_activations(xrec, x_in, p.norm_w, p.K, scratch, p.tp, sum_slots);
     __syncthreads();
 
     int slot = 0;
@@ -345,13 +382,21 @@ template <int QT, bool SILU>
 static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t batch) {
     uint32_t rows = 0;
     for (int i = 0; i < p.n_mat; ++i) rows += p.m[i].rows;
-    // four streams per item reuse each activation record twice as often as two; measured on B200
-    // this wins for every decoder shape (gate/up 12.1 vs 14.5 us, wq 4.7 vs 5.6 us), so the
-    // two-stream form is kept only for matrices with fewer row groups than SMs
+    // four streams per item reuse each activation record twice as often as two and win whenever a
+    // CTA has enough items to keep its warps equally busy (gate/up 12.1 vs 14.5 us, wq 4.7 vs 5.6 us).
+    // What counts is the longest warp: items are dealt round-robin, so a CTA takes
+    // ceil(items / warps) item-times, and a two-stream item costs about 0.56 of a four-stream one.
     const uint32_t groups4 = SILU ? rows / 2 : rows / 4;
     constexpr int W = QTraits<QT>::kWarps;      // 20 warps instead of 16 measured no faster
-    if (groups4 >= uint32_t(ctx->sm_count)) return launch_gemv<QT, 4, SILU, W>(ctx, p, batch, groups4);
-    return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
+    if (groups4 < uint32_t(ctx->sm_count)) return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
+    static const char* no_model = getenv("LV_GEMV_NO_STREAM_MODEL");
+    if (!(no_model != nullptr && no_model[0] == '1')) {
+        const uint32_t ctas = uint32_t(ctx->sm_count), nseg = (p.K / 32 + kSegBlocks - 1) / kSegBlocks;
+        const uint32_t items4 = ((groups4 + ctas - 1) / ctas) * nseg, items2 = ((2 * groups4 + ctas - 1) / ctas) * nseg;
+        const float t4 = float((items4 + W - 1) / W), t2 = 0.56f * float((items2 + W - 1) / W);
+        if (t2 < t4) return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
+    }
+    return launch_gemv<QT, 4, SILU, W>(ctx, p, batch, groups4);
 }
 
 // Raises the dynamic shared-memory limit of every instantiation; called once
@@ -402,7 +447,10 @@ static int gemv_dispatch(lv_ctx* ctx, GemvParams& p, int wtype, bool silu, uint3
             LV_REQUIRE(p.n_mat == 1 && !silu && p.m[0].rows <= p.tp.capacity, "a pushing GEMV has one matrix whose rows fit a window slot");
             LV_REQUIRE(plain_gemv_ctas(ctx, p.m[0].rows) <= uint32_t(kTpFlagCtas), "too many CTAs for the flag area");
         }
-        if (p.tp.pull_exchange >= 0) LV_REQUIRE(p.K <= p.tp.capacity, "input longer than a window slot");
+        if (p.tp.pull_exchange >= 0) {
+            LV_REQUIRE(p.K <= p.tp.capacity, "input longer than a window slot");
+            LV_REQUIRE(ctx->sm_count <= kTpFlagCtas, "too many CTAs for the flag area");
+        }
     }
     if (wtype == T_Q4_0) return silu ? launch_gemv_pick_streams<T_Q4_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q4_0, false>(ctx, p, batch);
     return silu ? launch_gemv_pick_streams<T_Q8_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q8_0, false>(ctx, p, batch);

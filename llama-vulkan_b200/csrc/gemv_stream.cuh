@@ -66,6 +66,7 @@ struct GemvMatrix {
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpFlagCtas = 256;       // flags per (exchange parity, source rank)
 constexpr int kTpLegacyFlagWords = 64; // flag words of the stand-alone all-reduce kernel that precede these
+constexpr int kTpTwoPhaseRanks = 4;    // from this many ranks on, a consumer launch sums the slots once per GPU, not once per CTA
 
 struct TpParams {
     float* window[kTpMaxRanks];   // window[r]: rank r's receive window as seen from this GPU
@@ -76,7 +77,8 @@ struct TpParams {
     int push_exchange;            // producer side, -1 = none
     int pull_exchange;            // consumer side, -1 = none
     uint32_t pull_ctas;           // CTAs of the producer launch of the consumed exchange
-    float* x_out;                 // consumer: CTA 0 stores the summed input here (the new residual stream)
+    float* x_out;                 // consumer: the summed input is stored here (the new residual stream)
+    uint32_t two_phase;           // consumer: sum the slots once per GPU (slice per CTA + local flags) instead of in every CTA
 };
 
 __device__ __forceinline__ float* tp_slot(const TpParams& t, int r_window, int exchange, int src) {
@@ -86,6 +88,12 @@ __device__ __forceinline__ float* tp_slot(const TpParams& t, int r_window, int e
 __device__ __forceinline__ uint32_t* tp_flag(const TpParams& t, int r_window, int exchange, int src, uint32_t cta) {
     uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[r_window] + size_t(2) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
     return flags + (size_t(exchange & 1) * kTpMaxRanks + src) * kTpFlagCtas + cta;
+}
+
+// Flag of CTA `cta` of a consumer launch on this GPU: its slice of the summed input is in x_out.
+__device__ __forceinline__ uint32_t* tp_local_flag(const TpParams& t, uint32_t cta) {
+    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[t.rank] + size_t(2) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
+    return flags + size_t(2) * kTpMaxRanks * kTpFlagCtas + cta;
 }
 
 __device__ __forceinline__ uint32_t tp_epoch(const TpParams& t, int exchange) {
@@ -270,10 +278,10 @@ constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >=
 
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
                                                   const float* __restrict__ norm_w, uint32_t K, float* scratch,
-                                                  const TpParams& tp) {
+                                                  const TpParams& tp, bool sum_slots) {
     const int lane = threadIdx.x & 31;
     const uint32_t stride = blockDim.x * 4;
-    const bool pull = tp.n_ranks > 0 && tp.pull_exchange >= 0;
+    const bool pull = sum_slots && tp.n_ranks > 0 && tp.pull_exchange >= 0;
 
     for (uint32_t chunk = 0; chunk < K; chunk += stride * kActIters) {
         float4 v[kActIters], w[kActIters];

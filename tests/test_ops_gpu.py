@@ -373,9 +373,12 @@ def test_graph_capture_replays_with_a_new_position(gpu, pkg, rope_table):
     pkg.check(gpu.lib.lv_graph_destroy(g))
 
 
-def test_exchange_fused_into_the_gemvs_on_one_rank(pkg):
+@pytest.mark.parametrize("two_phase", ["0", "1"], ids=["sum-per-cta", "sum-per-gpu"])
+def test_exchange_fused_into_the_gemvs_on_one_rank(pkg, two_phase, monkeypatch):
     """lv_tp_arm_push / lv_tp_arm_pull with a single-rank window: the pushed rows of one GEMV come
-    back as `x + rows` in the input of the next normalising GEMV, which also stores that sum."""
+    back as `x + rows` in the input of the next normalising GEMV, which also stores that sum.  Both
+    ways of forming the sum (in every CTA; one slice per CTA, then shared through local flags)."""
+    monkeypatch.setenv("LV_TP_TWO_PHASE", two_phase)
     rng = np.random.default_rng(60)
     K, rows_out, steps = 1024, 512, 3
     Wa = qn.quantize_q4_0((rng.standard_normal((K, 512)) * 0.05).astype(np.float32))      # K rows of 512 columns
