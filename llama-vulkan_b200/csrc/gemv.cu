@@ -382,21 +382,14 @@ template <int QT, bool SILU>
 static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t batch) {
     uint32_t rows = 0;
     for (int i = 0; i < p.n_mat; ++i) rows += p.m[i].rows;
-    // four streams per item reuse each activation record twice as often as two and win whenever a
-    // CTA has enough items to keep its warps equally busy (gate/up 12.1 vs 14.5 us, wq 4.7 vs 5.6 us).
-    // What counts is the longest warp: items are dealt round-robin, so a CTA takes
-    // ceil(items / warps) item-times, and a two-stream item costs about 0.56 of a four-stream one.
+    // four streams per item reuse each activation record twice as often as two; measured on B200
+    // this wins for every decoder shape (gate/up 12.1 vs 14.5 us, wq 4.7 vs 5.6 us; 4096x11008, where
+    // two streams would balance the warps better, is a tie), so the two-stream form is kept only for
+    // matrices with fewer row groups than SMs
     const uint32_t groups4 = SILU ? rows / 2 : rows / 4;
     constexpr int W = QTraits<QT>::kWarps;      // 20 warps instead of 16 measured no faster
-    if (groups4 < uint32_t(ctx->sm_count)) return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
-    static const char* no_model = getenv("LV_GEMV_NO_STREAM_MODEL");
-    if (!(no_model != nullptr && no_model[0] == '1')) {
-        const uint32_t ctas = uint32_t(ctx->sm_count), nseg = (p.K / 32 + kSegBlocks - 1) / kSegBlocks;
-        const uint32_t items4 = ((groups4 + ctas - 1) / ctas) * nseg, items2 = ((2 * groups4 + ctas - 1) / ctas) * nseg;
-        const float t4 = float((items4 + W - 1) / W), t2 = 0.56f * float((items2 + W - 1) / W);
-        if (t2 < t4) return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
-    }
-    return launch_gemv<QT, 4, SILU, W>(ctx, p, batch, groups4);
+    if (groups4 >= uint32_t(ctx->sm_count)) return launch_gemv<QT, 4, SILU, W>(ctx, p, batch, groups4);
+    return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
 }
 
 // Raises the dynamic shared-memory limit of every instantiation; called once
