@@ -218,7 +218,7 @@ int peer_take_armed(lv_ctx* ctx, TpParams* tp, uint32_t pull_ctas) {
         tp->pull_exchange = arm.pull;
         tp->pull_ctas = pull_ctas;
         tp->x_out = arm.x_out;
-        // summing once per GPU pays from four ranks on (LV_TP_TWO_PHASE=0/1 overrides, for tests)
+        // summing once per GPU instead of in every CTA is off unless LV_TP_TWO_PHASE=1 asks for it
         const char* force = getenv("LV_TP_TWO_PHASE");
         tp->two_phase = force != nullptr && (force[0] == '0' || force[0] == '1') ? uint32_t(force[0] - '0')
                                                                                   : uint32_t(st->params.n_ranks >= kTpTwoPhaseRanks);

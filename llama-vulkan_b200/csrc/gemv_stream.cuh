@@ -66,7 +66,8 @@ struct GemvMatrix {
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpFlagCtas = 256;       // flags per (exchange parity, source rank)
 constexpr int kTpLegacyFlagWords = 64; // flag words of the stand-alone all-reduce kernel that precede these
-constexpr int kTpTwoPhaseRanks = 4;    // from this many ranks on, a consumer launch sums the slots once per GPU, not once per CTA
+constexpr int kTpTwoPhaseRanks = 64;   // ranks from which a consumer launch would sum the slots once per GPU instead of once per CTA:
+                                       // never by default -- on 2 GPUs the extra intra-GPU flag round costs 5 us per exchange
 
 struct TpParams {
     float* window[kTpMaxRanks];   // window[r]: rank r's receive window as seen from this GPU
