@@ -183,7 +183,10 @@ size_t lv_act_split_bytes(uint32_t cols, uint32_t batch);
 
 /* xh = (hi, lo) fp16 planes of x [batch][cols], hi + lo = x to 22 bits; with
  * norm_w the reference's normalisation (shaders/normalize.comp:39-63) is
- * applied first.  Rows up to the next multiple of 16 are zero-filled. */
+ * applied first.  The buffer is private to the lv_gemm_tc* calls: it holds,
+ * per 64 columns, one ready-to-copy operand tile of 2 * zpad rows of 128 bytes
+ * (zpad = batch rounded up to 16; rows < zpad: hi of a token, then lo; a
+ * row's 16-byte units at unit ^ (row & 7)); tokens >= batch are zero. */
 int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch);
 
 /* out[z][r] (+)= sum_k W[r][k] x[z][k]: matmul / matmul_add_inplace for a batch. */

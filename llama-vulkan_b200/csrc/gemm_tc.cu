@@ -68,13 +68,13 @@ struct GemmTcParams {
     uint32_t Z;              // tokens (columns actually written)
     uint32_t zpad;           // Z rounded up to 16 = N of the MMA
     uint32_t ctx_rows;
+    const __half* xh;        // split activations, one contiguous pre-swizzled B tile per 64 columns of K (act_split_kernel)
     uint32_t* err;
 };
 
 struct GemmTcMaps {
     CUtensorMap w[3];
     CUtensorMap gate;
-    CUtensorMap x;           // [2 * zpad][K] fp16: hi plane rows, then lo plane rows
 };
 
 __device__ __forceinline__ void tma_load_2d_plain(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     if (!ok) break;
                 }
                 mbar_expect_tx(&b_full[bs], b_bytes);
-                tma_load_2d_plain(bring + bs * b_bytes, &maps.x, int(c * kTcChunkK), 0, &b_full[bs]);
+                bulk_g2s(bring + bs * b_bytes, reinterpret_cast<const uint8_t*>(p.xh) + size_t(c) * b_bytes, b_bytes, &b_full[bs]);
             }
         }
     } else if (warp == kTcProducerWarps + 1) {
@@ -455,23 +455,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     }
 }
 
-// x (optionally normalised, normalize.comp:39-63) as two fp16 planes: hi = fp16(v), lo = fp16(v - hi).
-// Grid: zpad CTAs; rows z >= Z are zero so that the padded columns of the product are defined.
+// x (optionally normalised, normalize.comp:39-63) as two fp16 planes, hi = fp16(v), lo = fp16(v - hi), laid out
+// as the B tiles the product kernel copies verbatim into shared memory: for every 64 columns of K one
+// contiguous tile of 2 zpad rows x 128 bytes (rows 0..zpad-1: hi of token z, rows zpad..: lo), each row's eight
+// 16-byte units stored at unit ^ (row & 7) -- the 128-byte swizzle the tensor core's descriptors expect.
+// (A strided tensor-map load of 128-byte rows out of a [tokens][K] array kept the tensor pipe waiting for
+// B about three quarters of the time.)  Grid: zpad CTAs; tokens z >= Z are zero so that the padded columns
+// of the product are defined.  A thread converts one unit of eight values.
 __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh, const float* __restrict__ x,
                                                         const float* __restrict__ norm_w, uint32_t K, uint32_t Z, uint32_t zpad) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[64];
     const uint32_t z = blockIdx.x;
-    __half* hi = xh + size_t(z) * K;
-    __half* lo = xh + size_t(zpad + z) * K;
-    if (z >= Z) {
-        for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) { hi[i] = __float2half_rn(0.f); lo[i] = __float2half_rn(0.f); }
-        return;
-    }
     const float* xr = x + size_t(z) * K;
     float factor = 1.0f;
-    if (norm_w != nullptr) {
+    if (z < Z && norm_w != nullptr) {
         float part = 0.f;
         for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) part += xr[i];
         const float mean = block_sum(part, scratch) / static_cast<float>(K);
@@ -482,11 +481,34 @@ __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh,
         }
         factor = 1.0f / sqrtf(block_sum(part, scratch) / static_cast<float>(K));        // no epsilon
     }
-    for (uint32_t i = threadIdx.x; i < K; i += blockDim.x) {
-        const float v = norm_w != nullptr ? (xr[i] * norm_w[i]) * factor : xr[i];
-        const __half h = __float2half_rn(v);
-        hi[i] = h;
-        lo[i] = __float2half_rn(v - __half2float(h));
+    for (uint32_t unit = threadIdx.x; unit < K / 8; unit += blockDim.x) {
+        float v[8];
+        if (z < Z) {
+            const float4 a = *reinterpret_cast<const float4*>(xr + 8 * unit), b = *reinterpret_cast<const float4*>(xr + 8 * unit + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            if (norm_w != nullptr) {
+                const float4 wa = *reinterpret_cast<const float4*>(norm_w + 8 * unit), wb = *reinterpret_cast<const float4*>(norm_w + 8 * unit + 4);
+                const float w8[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (v[i] * w8[i]) * factor;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+        __half2 hi[4], lo[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half h0 = __float2half_rn(v[2 * i]), h1 = __float2half_rn(v[2 * i + 1]);
+            hi[i] = __halves2half2(h0, h1);
+            lo[i] = __halves2half2(__float2half_rn(v[2 * i] - __half2float(h0)), __float2half_rn(v[2 * i + 1] - __half2float(h1)));
+        }
+        const uint32_t chunk = unit >> 3, u = unit & 7u;
+        const size_t tile = size_t(chunk) * 2 * zpad * 64;                   // halves
+        const size_t at_hi = tile + size_t(z) * 64 + ((u ^ (z & 7u)) << 3);
+        const size_t at_lo = at_hi + size_t(zpad) * 64;                      // zpad is a multiple of 8: same swizzle key
+        *reinterpret_cast<uint4*>(xh + at_hi) = *reinterpret_cast<const uint4*>(hi);
+        *reinterpret_cast<uint4*>(xh + at_lo) = *reinterpret_cast<const uint4*>(lo);
     }
 }
 
@@ -519,7 +541,7 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
         LV_REQUIRE((reinterpret_cast<uintptr_t>(p.m[0].w_gate) & 15u) == 0, "matrix pointer not 16-byte aligned");
         if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
     }
-    if (int rc = make_act_map(&maps.x, xh, 2 * p.zpad, p.K, 2 * p.zpad, kTcChunkK)) return rc;
+    p.xh = xh;
     LV_CUDA(launch_pdl(ctx, gemm_tc_kernel<QT>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps));
     return LV_OK;
 }

@@ -340,20 +340,6 @@ int make_weight_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t 
     return LV_OK;
 }
 
-int make_act_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t cols, uint32_t box_rows, uint32_t box_cols) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
-    return LV_OK;
-}
-
 template <int QT, int NS, bool SILU, int W>
 static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_t groups) {
     const size_t smem = gemv_smem_bytes<QT, NS, W>(p.K);

@@ -11,8 +11,4 @@ namespace lv {
 // of seg_bytes bytes.  row_bytes and seg_bytes must be multiples of 16.
 int make_weight_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t row_bytes, uint32_t box_rows, uint32_t seg_bytes);
 
-// [rows][cols] fp16, box = box_rows x box_cols with the 128-byte shared-memory swizzle
-// (box_cols * 2 must be 128).
-int make_act_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t cols, uint32_t box_rows, uint32_t box_cols);
-
 }  // namespace lv

@@ -41,6 +41,17 @@ def matrix(rng, rows, cols, scale=0.02, wtype=qn.Q4_0):
     return qn.quantize((rng.standard_normal((rows, cols)) * scale).astype(np.float32), wtype)
 
 
+def planes_of(raw, zpad, cols):
+    """Undo the tile layout of lv_act_split_f16: [cols/64][2 zpad rows][8 units ^ (row & 7)][8] -> (hi, lo) as [zpad][cols]."""
+    t = raw.reshape(cols // 64, 2 * zpad, 8, 8)
+    out = np.empty_like(t)
+    for r in range(2 * zpad):
+        for u in range(8):
+            out[:, r, u] = t[:, r, u ^ (r & 7)]
+    rows = out.reshape(cols // 64, 2 * zpad, 64).transpose(1, 0, 2).reshape(2 * zpad, cols)
+    return rows[:zpad].astype(np.float64), rows[zpad:].astype(np.float64)
+
+
 def test_act_split_planes_add_up_to_the_input(gpu, pkg):
     rng = np.random.default_rng(50)
     batch, cols = 5, 512
@@ -48,19 +59,19 @@ def test_act_split_planes_add_up_to_the_input(gpu, pkg):
     x = np.clip(x, -6e4, 6e4)
     xh = split(gpu, pkg, x)
     gpu.sync()
-    planes = gpu.download(xh, np.float16, 2 * 16 * cols).reshape(2, 16, cols).astype(np.float64)
-    assert not planes[:, batch:].any()                                   # padding rows are zero
-    got = planes[0, :batch] + planes[1, :batch]
-    err = np.abs(got - x)
+    hi, lo = planes_of(gpu.download(xh, np.float16, 2 * 16 * cols), 16, cols)
+    assert not hi[batch:].any() and not lo[batch:].any()                  # padding tokens are zero
+    err = np.abs(hi[:batch] + lo[:batch] - x)
     assert (err <= np.maximum(np.abs(x) * 2.0 ** -21, 2.0 ** -24)).all()
+    assert np.array_equal(hi[:batch].astype(np.float16), x.astype(np.float16))
     # with a norm: same as the oracle's normalisation
     w = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
     xs = rng.standard_normal((batch, cols)).astype(np.float32)
     xh = split(gpu, pkg, xs, w)
     gpu.sync()
-    planes = gpu.download(xh, np.float16, 2 * 16 * cols).reshape(2, 16, cols).astype(np.float64)
+    hi, lo = planes_of(gpu.download(xh, np.float16, 2 * 16 * cols), 16, cols)
     for z in range(batch):
-        close(planes[0, z] + planes[1, z], ob.norm(xs[z], w), rel_l2=2e-6, max_abs_frac=2e-6)
+        close(hi[z] + lo[z], ob.norm(xs[z], w), rel_l2=2e-6, max_abs_frac=2e-6)
 
 
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
