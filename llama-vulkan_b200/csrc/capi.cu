@@ -79,6 +79,7 @@ extern "C" int lv_ctx_destroy(lv_ctx* ctx) {
     if (ctx->peer) lv_peer_destroy(ctx);
     if (ctx->comm) lv_comm_destroy(ctx);
     if (ctx->stream) { cudaStreamSynchronize(ctx->stream); cudaStreamDestroy(ctx->stream); }
+    gemm_tc_release(ctx);
     if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     delete ctx;

@@ -20,6 +20,8 @@ struct lv_ctx {
     int comm_rank = 0, comm_size = 1;
     void* peer = nullptr;             // lv::PeerState of the peer-memory all-reduce
     bool peer_ready = false;
+    void* tc_scratch = nullptr;       // partial accumulators of the K-split tensor-core products
+    void* tc_counters = nullptr;
     // exchange roles that lv_tp_arm_push / lv_tp_arm_pull set for the next GEMV-family launch
     struct {
         int push = -1, pull = -1;
@@ -36,6 +38,7 @@ int cuda_fail(cudaError_t e, const char* what);
 int gemv_configure(lv_ctx* ctx);
 int attention_configure(lv_ctx* ctx);
 int gemm_tc_configure(lv_ctx* ctx);
+void gemm_tc_release(lv_ctx* ctx);
 uint32_t* peer_step_counter(lv_ctx* ctx);          // device word counting evaluation steps, or null without a peer window
 
 #define LV_CUDA(call)                                          \

@@ -18,10 +18,17 @@
 // Four warps read the accumulators back with tcgen05.ld, add them and apply the epilogue
 // (store / add to the residual / f16 cache rows at the position / SiLU gate of a row pair).
 //
+// A matrix with few row tiles (wo, w2: 32-40) is also split along K, up to four CTAs per tile:
+// the kernel is bound by shared-memory traffic (each weight is written once and read once as two
+// fp16 planes), which only more SMs relieve.  The CTAs of a tile leave their partial accumulators
+// in a scratch buffer; the last to arrive adds them in split order (deterministic) and applies
+// the epilogue.
+//
 // Every wait is bounded (common.cuh); a lost wait sets the context's error word, the CTA
 // drains and frees its tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "common.cuh"
@@ -69,6 +76,9 @@ struct GemmTcParams {
     uint32_t zpad;           // Z rounded up to 16 = N of the MMA
     uint32_t ctx_rows;
     const __half* xh;        // split activations, one contiguous pre-swizzled B tile per 64 columns of K (act_split_kernel)
+    uint32_t splits;         // CTAs that share one tile of rows, each taking a contiguous range of K
+    float* scratch;          // splits > 1: partial accumulators [tile][split][zpad][128]
+    uint32_t* counters;      // splits > 1: arrivals per tile (zero between launches)
     uint32_t* err;
 };
 
@@ -170,13 +180,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     uint32_t t0 = p.m[0].rows / rows_per_cta;
     uint32_t t1 = t0 + (p.n_mat > 1 ? p.m[1].rows / rows_per_cta : 0);
     int mi = 0;
-    uint32_t tile = blockIdx.x;
+    const uint32_t tile_all = blockIdx.x / p.splits, split = blockIdx.x - tile_all * p.splits;
+    uint32_t tile = tile_all;
     if (tile >= t1) { mi = 2; tile -= t1; }
     else if (tile >= t0) { mi = 1; tile -= t0; }
     const GemvMatrix& M = p.m[mi];
     const uint32_t row0 = tile * rows_per_cta;
 
-    const uint32_t n_chunks = p.K / kTcChunkK;
+    // this CTA's share of K, in groups of four 64-column tiles (one raw stage each)
+    const uint32_t groups_all = p.K / (4 * kTcChunkK);
+    const uint32_t g_begin = groups_all * split / p.splits, n_groups = groups_all * (split + 1) / p.splits - g_begin;
+    const uint32_t n_chunks = 4 * n_groups;
     const uint32_t b_bytes = 2u * p.zpad * kTcChunkK * 2u;
     const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kBRingBytes) / b_bytes);         // B stages: 3-4 (zpad 64) .. 16
     // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
@@ -204,7 +218,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     auto issue_raw = [&](uint32_t g) {
         const int rs = int(g % kTcRawStages);
         uint8_t* dst = rawring + rs * kRawStage;
-        const int x = int(g * (kRawRowBytes / 8));
+        const int x = int((g_begin + g) * (kRawRowBytes / 8));
         mbar_expect_tx(&raw_full[rs], kRawStage);
         const CUtensorMap* wm = mi == 0 ? &maps.w[0] : (mi == 1 ? &maps.w[1] : &maps.w[2]);
         if (pair) {
@@ -215,7 +229,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         }
     };
 
-    const uint32_t n_groups = n_chunks / 4;
     bool ok = true;
 
     if (warp == kTcProducerWarps) {
@@ -239,7 +252,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     if (!ok) break;
                 }
                 mbar_expect_tx(&b_full[bs], b_bytes);
-                bulk_g2s(bring + bs * b_bytes, reinterpret_cast<const uint8_t*>(p.xh) + size_t(c) * b_bytes, b_bytes, &b_full[bs]);
+                bulk_g2s(bring + bs * b_bytes, reinterpret_cast<const uint8_t*>(p.xh) + size_t(4 * g_begin + c) * b_bytes, b_bytes, &b_full[bs]);
             }
         }
     } else if (warp == kTcProducerWarps + 1) {
@@ -369,13 +382,47 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             if (ok) ok = mbar_wait(acc_full, 0u, p.err);
             tc_fence_after_sync();
             float* gate_s = reinterpret_cast<float*>(slots);      // [64][17] floats, free once the accumulator is complete
+            const uint32_t tr = uint32_t(warp * 32 + lane);       // tile row
+            // 16 tokens z0 .. z0+15 of one output row
+            auto store_plain = [&](uint32_t z0, const float (&r32)[16]) {
+                const uint32_t row = row0 + tr;
+                if (M.epilogue == EPI_STORE_F16_AT_POS) {
+                    __half* cache = static_cast<__half*>(M.out);
+                    const uint32_t first = *p.pos;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t z = z0 + i;
+                        if (z < p.Z) {
+                            if (first + z < p.ctx_rows) cache[size_t(first + z) * M.rows + row] = __float2half_rn(r32[i]);
+                            else atomicOr(p.err, ERR_BAD_INDEX);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t z = z0 + i;
+                        if (z < p.Z) {
+                            float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
+                            *o = (M.epilogue == EPI_ADD) ? (*o + r32[i]) : r32[i];                   // matmul.glsl:68-72
+                        }
+                    }
+                }
+            };
+            auto store_pair = [&](uint32_t z0, const float (&up)[16], const float (&gate)[16]) {
+                const uint32_t row = row0 + tr;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t z = z0 + i;
+                    if (z < p.Z) static_cast<float*>(M.out)[size_t(z) * M.rows + row] = up[i] * gate[i] / (expf(-gate[i]) + 1.0f);   // matmul_silu_ff.comp:95
+                }
+            };
+            float* my_partial = p.scratch + (size_t(tile_all) * p.splits + split) * p.zpad * kTcRows;
             for (uint32_t z0 = 0; z0 < p.zpad; z0 += 16) {
-                uint32_t v[16];
+                float v[16];
                 if (ok) {
                     const uint32_t taddr = tmem_base + (uint32_t(warp * 32) << 16) + z0;
-                    float sum[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) sum[i] = 0.f;
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
                     const uint32_t banks_used = min(uint32_t(kTcBanks), n_chunks);
                     for (uint32_t b = 0; b < banks_used; ++b) {
                         uint32_t u[3][16];
@@ -391,56 +438,71 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int i = 0; i < 16; ++i)      // the two small cross terms first, then the main one
-                            sum[i] += (__uint_as_float(u[1][i]) + __uint_as_float(u[2][i])) + __uint_as_float(u[0][i]);
+                            v[i] += (__uint_as_float(u[1][i]) + __uint_as_float(u[2][i])) + __uint_as_float(u[0][i]);
                     }
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(sum[i]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0u;
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
                 }
-                const uint32_t tr = uint32_t(warp * 32 + lane);      // tile row
-                if (pair) {
+                if (p.splits > 1) {
+                    // leave the partial sums for the last CTA of the tile
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) my_partial[size_t(z0 + i) * kTcRows + tr] = v[i];
+                } else if (pair) {
                     // rows 64..127 carry the gate (w1) of rows 0..63
                     if (tr >= 64) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) gate_s[(tr - 64) * 17 + i] = __uint_as_float(v[i]);
+                        for (int i = 0; i < 16; ++i) gate_s[(tr - 64) * 17 + i] = v[i];
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (tr < 64 && ok) {
-                        const uint32_t row = row0 + tr;
+                        float gate[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const uint32_t z = z0 + i;
-                            if (z < p.Z) {
-                                const float up = __uint_as_float(v[i]), gate = gate_s[tr * 17 + i];
-                                static_cast<float*>(M.out)[size_t(z) * M.rows + row] = up * gate / (expf(-gate) + 1.0f);   // matmul_silu_ff.comp:95
-                            }
-                        }
+                        for (int i = 0; i < 16; ++i) gate[i] = gate_s[tr * 17 + i];
+                        store_pair(z0, v, gate);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 } else if (ok) {
-                    const uint32_t row = row0 + tr;
-                    if (M.epilogue == EPI_STORE_F16_AT_POS) {
-                        __half* cache = static_cast<__half*>(M.out);
-                        const uint32_t first = *p.pos;
+                    store_plain(z0, v);
+                }
+            }
+            if (p.splits > 1) {
+                // the last of the tile's CTAs to get here adds the partial sums in split order and finishes the rows
+                uint32_t* s_last = tmem_slot + 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (tr == 0) {
+                    __threadfence();
+                    const uint32_t prev = atomicAdd(&p.counters[tile_all], 1u);
+                    *s_last = (prev + 1 == p.splits) ? 1u : 0u;
+                    if (prev + 1 == p.splits) p.counters[tile_all] = 0;         // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*reinterpret_cast<volatile uint32_t*>(s_last) != 0 && ok) {
+                    __threadfence();
+                    const float* base = p.scratch + size_t(tile_all) * p.splits * p.zpad * kTcRows;
+                    for (uint32_t z0 = 0; z0 < p.zpad; z0 += 16) {
+                        if (pair) {
+                            if (tr < 64) {
+                                float up[16], gate[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const uint32_t z = z0 + i;
-                            if (z < p.Z) {
-                                if (first + z < p.ctx_rows) cache[size_t(first + z) * M.rows + row] = __float2half_rn(__uint_as_float(v[i]));
-                                else atomicOr(p.err, ERR_BAD_INDEX);
-                            }
-                        }
-                    } else {
+                                for (int i = 0; i < 16; ++i) { up[i] = 0.f; gate[i] = 0.f; }
+                                for (uint32_t sp = 0; sp < p.splits; ++sp) {
+                                    const float* q = base + (size_t(sp) * p.zpad + z0) * kTcRows;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const uint32_t z = z0 + i;
-                            if (z < p.Z) {
-                                float* o = static_cast<float*>(M.out) + size_t(z) * M.rows + row;
-                                const float r32 = __uint_as_float(v[i]);
-                                *o = (M.epilogue == EPI_ADD) ? (*o + r32) : r32;                   // matmul.glsl:68-72
+                                    for (int i = 0; i < 16; ++i) { up[i] += __ldcg(q + size_t(i) * kTcRows + tr); gate[i] += __ldcg(q + size_t(i) * kTcRows + tr + 64); }
+                                }
+                                store_pair(z0, up, gate);
                             }
+                        } else {
+                            float v[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                            for (uint32_t sp = 0; sp < p.splits; ++sp) {
+                                const float* q = base + (size_t(sp) * p.zpad + z0) * kTcRows;
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) v[i] += __ldcg(q + size_t(i) * kTcRows + tr);
+                            }
+                            store_plain(z0, v);
                         }
                     }
                 }
@@ -459,8 +521,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
 // as the B tiles the product kernel copies verbatim into shared memory: for every 64 columns of K one
 // contiguous tile of 2 zpad rows x 128 bytes (rows 0..zpad-1: hi of token z, rows zpad..: lo), each row's eight
 // 16-byte units stored at unit ^ (row & 7) -- the 128-byte swizzle the tensor core's descriptors expect.
-// (A strided tensor-map load of 128-byte rows out of a [tokens][K] array kept the tensor pipe waiting for
-// B about three quarters of the time.)  Grid: zpad CTAs; tokens z >= Z are zero so that the padded columns
+// Grid: zpad CTAs; tokens z >= Z are zero so that the padded columns
 // of the product are defined.  A thread converts one unit of eight values.
 __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh, const float* __restrict__ x,
                                                         const float* __restrict__ norm_w, uint32_t K, uint32_t Z, uint32_t zpad) {
@@ -512,7 +573,20 @@ __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh,
     }
 }
 
+constexpr size_t kTcScratchBytes = size_t(8) << 20;
+constexpr uint32_t kTcMaxTiles = 1024;
+
+void gemm_tc_release(lv_ctx* ctx) {
+    cudaFree(ctx->tc_scratch);
+    cudaFree(ctx->tc_counters);
+    ctx->tc_scratch = nullptr;
+    ctx->tc_counters = nullptr;
+}
+
 int gemm_tc_configure(lv_ctx* ctx) {
+    LV_CUDA(cudaMalloc(&ctx->tc_scratch, kTcScratchBytes));
+    LV_CUDA(cudaMalloc(&ctx->tc_counters, kTcMaxTiles * sizeof(uint32_t)));
+    LV_CUDA(cudaMemset(ctx->tc_counters, 0, kTcMaxTiles * sizeof(uint32_t)));
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q4_0>() && size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q8_0>(),
                "device has too little shared memory for the batched product");
     LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>())));
@@ -542,6 +616,18 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
         if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
     }
     p.xh = xh;
+    // few row tiles: up to four CTAs per tile, each with at least two raw stages of K, as far as SMs and scratch allow
+    uint32_t splits = 1;
+    const uint32_t groups_all = p.K / (4 * kTcChunkK);
+    while (splits < 4 && tiles * (splits + 1) <= uint32_t(ctx->sm_count) && groups_all / (splits + 1) >= 2 &&
+           size_t(tiles) * (splits + 1) * p.zpad * kTcRows * sizeof(float) <= kTcScratchBytes && tiles <= kTcMaxTiles)
+        ++splits;
+    static const char* no_split = getenv("LV_GEMM_TC_NO_SPLIT");
+    if (no_split != nullptr && no_split[0] == '1') splits = 1;
+    p.splits = splits;
+    p.scratch = static_cast<float*>(ctx->tc_scratch);
+    p.counters = static_cast<uint32_t*>(ctx->tc_counters);
+    tiles *= splits;
     LV_CUDA(launch_pdl(ctx, gemm_tc_kernel<QT>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps));
     return LV_OK;
 }

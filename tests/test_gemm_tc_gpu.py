@@ -114,7 +114,7 @@ def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg):
 
 
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
-@pytest.mark.parametrize("ff,dim,batch", [(192, 512, 16), (11008, 4096, 20)])
+@pytest.mark.parametrize("ff,dim,batch", [(192, 512, 16), (256, 4096, 24), (11008, 4096, 20)])     # the middle one is split along K
 def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype):
     rng = np.random.default_rng(53)
     w3, w1 = matrix(rng, ff, dim, wtype=wtype), matrix(rng, ff, dim, wtype=wtype)
@@ -129,9 +129,10 @@ def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype):
         close(got[z], ob.gemv_silu(w3, w1, wtype, ob.norm(x[z], nw), ff, dim, workers_for(dim)), rel_l2=3e-5, max_abs_frac=1e-4)
 
 
-def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg):
+@pytest.mark.parametrize("dim", [512, 1024])             # 1024: two CTAs per row tile, each with half of K
+def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg, dim):
     rng = np.random.default_rng(54)
-    dim, batch, ctx_rows, pos = 512, 18, 64, 9
+    batch, ctx_rows, pos = 18, 64, 9
     wq, wk, wv = (matrix(rng, dim, dim, 0.05) for _ in range(3))
     x = rng.standard_normal((batch, dim)).astype(np.float32)
     xh = split(gpu, pkg, x)
@@ -159,3 +160,23 @@ def test_gemm_tc_refuses_what_it_cannot_do(gpu, pkg):
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 96, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS       # cols not a multiple of 256
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 256, 65, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # batch above 64
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, None, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS
+
+
+def test_gemm_tc_split_along_k_is_reproducible(gpu, pkg):
+    """Tiles shared by several CTAs are summed in a fixed order: two launches give the same bits, and a launch right
+    after another one (the arrival counters must be back at zero) is as good as the first."""
+    rng = np.random.default_rng(55)
+    rows, cols, batch = 512, 4096, 40
+    W = matrix(rng, rows, cols)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    xh, dW = split(gpu, pkg, x), gpu.upload(W)
+    outs = []
+    for _ in range(3):
+        out = gpu.zeros(batch * rows * 4)
+        pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, qn.Q4_0, xh, rows, cols, batch, 0))
+        outs.append(out)
+    gpu.sync()
+    got = [gpu.download(o, np.float32, batch * rows) for o in outs]
+    assert np.array_equal(got[0], got[1]) and np.array_equal(got[0], got[2])
+    want = np.stack([ob.gemv(W, qn.Q4_0, x[z], rows, cols, 128) for z in range(batch)])
+    close(got[0].reshape(batch, rows), want)
