@@ -165,20 +165,6 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return t;
 }
 
-// Two sums at once (same rules; uses scratch[0..63]).
-__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
-    a = warp_sum(a);
-    b = warp_sum(b);
-    __syncthreads();
-    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
-    __syncthreads();
-    float ta = 0.f, tb = 0.f;
-    for (int w = 0; w < nwarps; ++w) { ta += scratch[w]; tb += scratch[32 + w]; }
-    a = ta;
-    b = tb;
-}
-
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
 }

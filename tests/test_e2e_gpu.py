@@ -183,6 +183,32 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run):
     s.close()
 
 
+def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run):
+    """40 prompt tokens in recorded steps of 16, 16 (batched products, the second one attending over the
+    rows of the first) and 8 (per-token kernels with a batch): logits and cache rows against the
+    oracle's token-by-token evaluation."""
+    toks = prompt_tokens(40, seed=777)
+    orc = OracleSession(run["path"])
+    for t in toks:
+        orc.push(t)
+    want = orc.eval()
+    s = run["ctx"].session()
+    s.set_deterministic(True)
+    assert s.set_max_batch(16)
+    for t in toks:
+        assert s.push_token(t)
+    tok = s.predict_next_token()
+    assert_logits_close(s.logits(run["vocab"]), want)
+    assert tok == orc.argmax()
+    for layer in range(2):
+        for which in (0, 1):
+            got = s.read_kv(layer, which, 0, 40, run["dim"]).view(np.float16).astype(np.float32)
+            ref = orc.cache(which, layer, 40).view(np.float16).astype(np.float32)
+            assert np.abs(got - ref).max() <= 2e-3 * np.abs(ref).max()
+    s.close()
+    orc.close()
+
+
 def test_rewind_then_regenerate(run):
     s = run["ctx"].session()
     s.set_deterministic(True)
