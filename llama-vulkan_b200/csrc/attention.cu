@@ -253,17 +253,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1) attention_fused_kernel(float
         }
     }
     if (active == 1) return;
-    // publish, then find out whether this CTA is the last of its (z, h)
-    __threadfence();
+    // publish, then find out whether this CTA is the last of its (z, h).  The barrier orders the
+    // CTA's partial stores before thread 0's fence, which makes them visible before the count
+    // (one fence instead of one per thread).
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();
         const uint32_t prev = atomicAdd(&counters[z * heads + h], 1u);
         s_last = (prev + 1 == active) ? 1u : 0u;
-        if (s_last) counters[z * heads + h] = 0;          // ready for the next launch
+        if (s_last) {
+            counters[z * heads + h] = 0;                  // ready for the next launch
+            __threadfence();                              // the count was seen: order the reads below after it
+        }
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
+    // the other chunks' partials are read from L2 (__ldcg), where their stores are by now
     if (threadIdx.x < kRot) {
         const float* base = partial + (size_t(z) * heads + h) * nchunks * (kRot + 2);
         // lane j of every warp fetches chunk j's (max, sum): at most 32 chunks
