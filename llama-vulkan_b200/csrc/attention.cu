@@ -132,7 +132,8 @@ __host__ __device__ inline size_t attn_partial_floats(uint32_t heads, uint32_t n
 // step): scores with 8 lanes per cache row (16 elements each, both of a warp's
 // row batches in flight together), values with 16 threads per row (8 dims each)
 // and four rows per thread in flight.
-__global__ void __launch_bounds__(kFusedThreads, 1) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
+template <int MIN_CTAS_PER_SM>
+__global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
                                                                        const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                        float* __restrict__ partial, uint32_t* __restrict__ counters,
@@ -391,9 +392,15 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
     dim3 grid(heads, nchunks, batch);
-    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                       static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                       1.0f / sqrtf(static_cast<float>(rot))));
+    if (heads * nchunks * batch > uint32_t(ctx->sm_count)) {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                           1.0f / sqrtf(static_cast<float>(rot))));
+    } else {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                           1.0f / sqrtf(static_cast<float>(rot))));
+    }
     return LV_OK;
 }
 
@@ -418,8 +425,14 @@ extern "C" int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q
     // the buffer keeps whatever the last call left; only the arrival counters must start at zero
     LV_CUDA(cudaMemsetAsync(counters, 0, size_t(batch) * heads * sizeof(uint32_t), ctx->stream));
     dim3 grid(heads, nchunks, batch);
-    LV_CUDA(launch_pdl(ctx, attention_fused_kernel, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                       static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                       1.0f / sqrtf(static_cast<float>(rot))));
+    if (heads * nchunks * batch > uint32_t(ctx->sm_count)) {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                           1.0f / sqrtf(static_cast<float>(rot))));
+    } else {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
+                           1.0f / sqrtf(static_cast<float>(rot))));
+    }
     return LV_OK;
 }
