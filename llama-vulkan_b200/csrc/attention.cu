@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     pdl_wait();
     __shared__ float s_e[kAttnChunk];
     __shared__ __align__(16) float s_v[kRowGroups][kRot];
-    __shared__ float s_red[2];
+    __shared__ float s_l[kRowGroups];
     __shared__ uint32_t s_last;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -195,28 +195,8 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
             if (sub == 0) s_e[i] = i < n ? sacc * scale : -INFINITY;
         }
     }
-    __syncthreads();
-    // ---- chunk maximum and exponentials -------------------------------------------------------
-    if (warp == 0) {
-        float sc[kAttnChunk / 32];
-        float m = -INFINITY;
-#pragma unroll
-        for (int k = 0; k < kAttnChunk / 32; ++k) {
-            sc[k] = s_e[lane + 32 * k];
-            m = fmaxf(m, sc[k]);
-        }
-        m = warp_max(m);
-        float l = 0.f;
-#pragma unroll
-        for (int k = 0; k < kAttnChunk / 32; ++k) {
-            const float e = (uint32_t(lane) + 32 * k < n) ? expf(sc[k] - m) : 0.f;
-            s_e[lane + 32 * k] = e;
-            l += e;
-        }
-        l = warp_sum(l);
-        if (lane == 0) { s_red[0] = m; s_red[1] = l; }
-    }
     // ---- weighted values: thread = (8 dims, one of 32 row groups), rows rg, rg+32, ... -----------
+    // The value rows do not depend on the scores: their loads are issued before the barrier.
     const int d8 = (threadIdx.x & 15) * 8, rg = threadIdx.x >> 4;
     uint4 vraw[kValueRows];
 #pragma unroll
@@ -224,12 +204,19 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
         const uint32_t i = min(uint32_t(rg + kRowGroups * j), n - 1);
         vraw[j] = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * dim + h * kRot + d8);
     }
-    __syncthreads();                                       // s_e now holds the exponentials
+    __syncthreads();                                       // s_e holds the scaled scores
+    // ---- chunk maximum (every warp on its own) and the exponentials a thread needs ---------------
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kAttnChunk / 32; ++k) m = fmaxf(m, s_e[lane + 32 * k]);
+    m = warp_max(m);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float lsum = 0.f;
 #pragma unroll
     for (int j = 0; j < kValueRows; ++j) {
         const uint32_t i = rg + kRowGroups * j;
-        const float e = i < n ? s_e[i] : 0.f;
+        const float e = i < n ? expf(s_e[i] - m) : 0.f;
+        lsum += e;
         const __half2* v2 = reinterpret_cast<const __half2*>(&vraw[j]);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -240,17 +227,21 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     }
     *reinterpret_cast<float4*>(&s_v[rg][d8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     *reinterpret_cast<float4*>(&s_v[rg][d8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if ((threadIdx.x & 15) == 0) s_l[rg] = lsum;           // the exp-sum of this row group's rows
     __syncthreads();
     float* my = partial + ((size_t(z) * heads + h) * nchunks + c) * (kRot + 2);
     if (threadIdx.x < kRot) {
-        float o = 0.f;
+        float o = 0.f, l = 0.f;
 #pragma unroll 16
-        for (int r = 0; r < kRowGroups; ++r) o += s_v[r][threadIdx.x];
+        for (int r = 0; r < kRowGroups; ++r) {
+            o += s_v[r][threadIdx.x];
+            l += s_l[r];
+        }
         if (active == 1) {
-            out[size_t(z) * dim + h * kRot + threadIdx.x] = o / s_red[1];
+            out[size_t(z) * dim + h * kRot + threadIdx.x] = o / l;
         } else {
             my[threadIdx.x] = o;
-            if (threadIdx.x == 0) { my[kRot] = s_red[0]; my[kRot + 1] = s_red[1]; }
+            if (threadIdx.x == 0) { my[kRot] = m; my[kRot + 1] = l; }
         }
     }
     if (active == 1) return;
