@@ -169,7 +169,7 @@ int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config,
 
 /* ---- batched products on the tensor cores (prompt evaluation) -------------- */
 
-/* When 16 or more tokens are evaluated together the reference dispatches its
+/* When several tokens are evaluated together the reference dispatches its
  * matmul shaders with the batch in gl_WorkGroupID.z (llava_command_buffer.cpp:
  * 61-132), streaming every matrix once per token.  These entry points read the
  * matrix once for up to 64 tokens: q4_0 / q8_0 blocks are dequantised in the

@@ -46,7 +46,8 @@ public:
     // input and leaves that sum in x_out
     void tp_arm_push(u32 exchange);
     void tp_arm_pull(u32 exchange, u32 producer_rows, llava_buffer* x_out);
-    // batched forms on the tensor cores (16..64 tokens per step): the activations are first
+    static constexpr u32 kTensorCoreMinBatch = 6;
+    // batched forms on the tensor cores (6..64 tokens per step): the activations are first
     // split into two fp16 planes (optionally normalised), then every matrix is read once
     bool use_tensor_cores(const llava_buffer* matrix) const;
     void act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights);

@@ -79,7 +79,7 @@ llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_se
         // it is not tracing (llava_layer.cpp:45-51)
         llava_buffer* x = session->current_thought;
         if (cmd_buf->use_tensor_cores(attention_wq)) {
-            // 16 or more tokens: every matrix is read once for the whole batch (tcgen05), nine launches
+            // six or more tokens: every matrix is read once for the whole batch (tcgen05), nine launches
             llava_buffer* split = session->act_split;
             cmd_buf->act_split(split, x, attention_norm);
             cmd_buf->gemm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,

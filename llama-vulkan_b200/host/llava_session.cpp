@@ -91,7 +91,7 @@ bool llava_session::recreate_buffers() {
     const size_t scratch = lv_attention_scratch_bytes(h.n_heads / ranks, h.rot, max_backlog_size, B);
     if (scratch == 0) return false;
     attn_scratch = new llava_buffer(ctx, F, u32((scratch + 3) / 4), 1, m);
-    if (B >= 16 && ranks == 1) act_split = new llava_buffer(ctx, F, u32(lv_act_split_bytes(max(dim, ff), B) / 4), 1, m);
+    if (B >= llava_command_buffer::kTensorCoreMinBatch && ranks == 1) act_split = new llava_buffer(ctx, F, u32(lv_act_split_bytes(max(dim, ff), B) / 4), 1, m);
     if (!m->freeze() || !m->zero(0, m->get_size())) return false;
     device_pos = ~0U;
     return true;

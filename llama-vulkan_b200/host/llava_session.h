@@ -100,7 +100,7 @@ private:
     llava_buffer* token_log = nullptr;
     llava_buffer* argmax_result = nullptr;
     llava_buffer* attn_scratch = nullptr;
-    llava_buffer* act_split = nullptr;            // max_batch >= 16: fp16 (hi, lo) planes of a batch of activations
+    llava_buffer* act_split = nullptr;            // max_batch >= 6: fp16 (hi, lo) planes of a batch of activations
     llava_buffer* tp_partial = nullptr;           // tensor-parallel only: this rank's partial wo / w2 product
     std::vector<llava_layer_session_data*> layer_data;
 
