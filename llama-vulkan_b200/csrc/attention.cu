@@ -8,6 +8,7 @@
 // host builds once in double precision.
 #include <math.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -132,18 +133,30 @@ __host__ __device__ inline size_t attn_partial_floats(uint32_t heads, uint32_t n
 // step): scores with 8 lanes per cache row (16 elements each, both of a warp's
 // row batches in flight together), values with 16 threads per row (8 dims each)
 // and four rows per thread in flight.
-template <int MIN_CTAS_PER_SM>
+// Shared-memory staging of the score inputs (STAGED = true, one CTA per SM): the chunk's key rows and
+// the rows of the rotation table it needs (one contiguous range of distances) are brought in by bulk
+// (TMA) copies -- one per key row, one for the table -- and the scores are computed from shared
+// memory.  With plain loads the kernel spent a fifth of its samples throttled on the load/store
+// queue (28 16-byte loads per thread).  Key rows are padded to 320 bytes so that the two rows a
+// half-warp reads with 8-byte loads fall on different banks.
+constexpr int kStagedKeyStride = 320;
+constexpr size_t kStagedTableBytes = size_t(kAttnChunk) * kRot * sizeof(float);              // 131072
+constexpr size_t kStagedSmemBytes = kStagedTableBytes + size_t(kAttnChunk) * kStagedKeyStride;  // + 81920
+
+template <int MIN_CTAS_PER_SM, bool STAGED>
 __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
                                                                        const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                        float* __restrict__ partial, uint32_t* __restrict__ counters,
-                                                                       uint32_t heads, uint32_t nchunks, float scale) {
+                                                                       uint32_t heads, uint32_t nchunks, float scale, uint32_t* err) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_e[kAttnChunk];
     __shared__ __align__(16) float s_v[kRowGroups][kRot];
     __shared__ float s_l[kRowGroups];
     __shared__ uint32_t s_last;
+    __shared__ __align__(8) uint64_t s_bar;
+    extern __shared__ __align__(128) uint8_t staged[];       // STAGED: [table rows][key rows]
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t h = blockIdx.x, c = blockIdx.y, z = blockIdx.z;
@@ -155,7 +168,53 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     const uint32_t n = min(uint32_t(kAttnChunk), P + 1 - p0);
 
     // ---- scores: warp w owns rows 16w .. 16w+15, lane group g = lane / 8 one row per pass -----
-    {
+    if constexpr (STAGED) {
+        const int sub = lane & 7, g = lane >> 3;
+        float* ttile = reinterpret_cast<float*>(staged);
+        uint8_t* ktile = staged + kStagedTableBytes;
+        if (threadIdx.x == 0) {
+            mbar_init(&s_bar, 1);
+            fence_mbar_init();
+            mbar_expect_tx(&s_bar, n * (kRot * uint32_t(sizeof(__half)) + kRot * uint32_t(sizeof(float))));
+        }
+        __syncthreads();
+        // key row p0 + t -> ktile row t; table rows of the distances P - p0 - (n-1) .. P - p0 -> ttile rows 0 .. n-1
+        if (threadIdx.x < n)
+            bulk_g2s(ktile + threadIdx.x * kStagedKeyStride, kc + size_t(p0 + threadIdx.x) * dim + h * kRot, kRot * sizeof(__half), &s_bar);
+        if (threadIdx.x == 0)
+            bulk_g2s(ttile, table + size_t(P - p0 - (n - 1)) * kRot, n * kRot * uint32_t(sizeof(float)), &s_bar);
+        // this lane's part of q: float4 number sub + 8 m, i.e. pairs 2 (sub + 8 m) and 2 (sub + 8 m) + 1
+        float4 qv[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) qv[m] = *reinterpret_cast<const float4*>(q + size_t(z) * dim + h * kRot + (sub + 8 * m) * 4);
+        const bool ok = mbar_wait(&s_bar, 0u, err);
+#pragma unroll
+        for (int it = 0; it < kScoreIters; ++it) {
+            const uint32_t i = warp * (4 * kScoreIters) + it * 4 + g;
+            const uint32_t ic = min(i, n - 1);                        // rows past n are computed and discarded
+            const uint8_t* krow = ktile + ic * kStagedKeyStride;
+            const float* trow = ttile + size_t(n - 1 - ic) * kRot;
+            float sacc = 0.f;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int f = sub + 8 * m;
+                const uint2 kk = *reinterpret_cast<const uint2*>(krow + f * 8);           // 4 halves = 2 pairs
+                const float4 t = *reinterpret_cast<const float4*>(trow + f * 4);          // (cos, sin) of the two pairs
+                const float2 ka = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
+                const float2 kb = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
+                const float4 qq = qv[m];
+                // mhsa.comp:42-57
+                const float rx0 = t.x * ka.x + t.y * ka.y, ry0 = -t.y * ka.x + t.x * ka.y;
+                const float rx1 = t.z * kb.x + t.w * kb.y, ry1 = -t.w * kb.x + t.z * kb.y;
+                sacc += qq.x * rx0 + qq.y * ry0;
+                sacc += qq.z * rx1 + qq.w * ry1;
+            }
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 4);
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
+            sacc += __shfl_xor_sync(0xffffffffu, sacc, 1);
+            if (sub == 0) s_e[i] = (i < n && ok) ? sacc * scale : -INFINITY;
+        }
+    } else {
         const int sub = lane & 7, g = lane >> 3;
         const float* qh = q + size_t(z) * dim + h * kRot + sub * 16;
         float4 qv[4];
@@ -282,7 +341,33 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     }
 }
 
-int attention_configure(lv_ctx*) { return LV_OK; }
+int attention_configure(lv_ctx* ctx) {
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kStagedSmemBytes + 18 * 1024, "device has too little shared memory for the staged attention kernel");
+    LV_CUDA(cudaFuncSetAttribute(attention_fused_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kStagedSmemBytes)));
+    return LV_OK;
+}
+
+// Grids of at most one CTA per SM stage their inputs in shared memory; larger ones (context beyond
+// ~1280 rows, batches) use plain loads with two CTAs per SM.
+static int launch_attention_fused(lv_ctx* ctx, dim3 grid, float* out, const float* q, const void* k_cache, const void* v_cache,
+                                  const uint32_t* pos, const float* rope_table, float* partial, uint32_t* counters, uint32_t heads,
+                                  uint32_t nchunks, uint32_t rot) {
+    const float scale = 1.0f / sqrtf(static_cast<float>(rot));
+    static const char* no_stage = getenv("LV_ATTENTION_NO_STAGING");
+    const bool staged = !(no_stage != nullptr && no_stage[0] == '1');
+    if (grid.x * grid.y * grid.z > uint32_t(ctx->sm_count)) {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, false>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+    } else if (staged) {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, true>, grid, dim3(kFusedThreads), kStagedSmemBytes, out, q,
+                           static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
+                           heads, nchunks, scale, ctx->d_err));
+    } else {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, false>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+    }
+    return LV_OK;
+}
 
 // Scratch of lv_attention_fused_static.  It lives in the library image: every GPU that loads
 // the library holds these bytes until the process exits, whether or not the entry point is used.
@@ -383,15 +468,7 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
     dim3 grid(heads, nchunks, batch);
-    if (heads * nchunks * batch > uint32_t(ctx->sm_count)) {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                           1.0f / sqrtf(static_cast<float>(rot))));
-    } else {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                           1.0f / sqrtf(static_cast<float>(rot))));
-    }
+    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, rot)) return rc;
     return LV_OK;
 }
 
@@ -416,14 +493,6 @@ extern "C" int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q
     // the buffer keeps whatever the last call left; only the arrival counters must start at zero
     LV_CUDA(cudaMemsetAsync(counters, 0, size_t(batch) * heads * sizeof(uint32_t), ctx->stream));
     dim3 grid(heads, nchunks, batch);
-    if (heads * nchunks * batch > uint32_t(ctx->sm_count)) {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                           1.0f / sqrtf(static_cast<float>(rot))));
-    } else {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks,
-                           1.0f / sqrtf(static_cast<float>(rot))));
-    }
+    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, rot)) return rc;
     return LV_OK;
 }
