@@ -324,6 +324,10 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
         const float* base = partial + (size_t(z) * heads + h) * nchunks * (kRot + 2);
         // lane j of every warp fetches chunk j's (max, sum): at most 32 chunks
         const bool mine = uint32_t(lane) < active;
+        // the first eight chunks' outputs travel together with the (max, sum) pairs: one trip to L2
+        float oj[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) oj[u] = (uint32_t(u) < active) ? __ldcg(base + size_t(u) * (kRot + 2) + threadIdx.x) : 0.f;
         const float mj = mine ? __ldcg(base + size_t(lane) * (kRot + 2) + kRot) : -INFINITY;
         const float lj = mine ? __ldcg(base + size_t(lane) * (kRot + 2) + kRot + 1) : 0.f;
         const float M = warp_max(mj);
@@ -331,9 +335,10 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
         const float den = warp_sum(lj * wj);
         float num = 0.f;
         for (uint32_t j0 = 0; j0 < active; j0 += 8) {
-            float oj[8];
+            if (j0 != 0) {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) oj[u] = (j0 + u < active) ? __ldcg(base + size_t(j0 + u) * (kRot + 2) + threadIdx.x) : 0.f;
+                for (int u = 0; u < 8; ++u) oj[u] = (j0 + u < active) ? __ldcg(base + size_t(j0 + u) * (kRot + 2) + threadIdx.x) : 0.f;
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) num = fmaf(oj[u], __shfl_sync(0xffffffffu, wj, (j0 + u) & 31), num);
         }
