@@ -58,6 +58,14 @@ class OracleSession:
         self.lib.orc_model_close(self.model)
 
 
+def note_parity(line):
+    """Appends a line to the file named by LV_PARITY_REPORT, if set: the measured distances of a run, for the record."""
+    path = os.environ.get("LV_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(line + "\n")
+
+
 def assert_logits_close(got, want):
     diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
     rel = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
@@ -102,10 +110,7 @@ def test_greedy_tokens_identical_and_logits_within_tolerance(run):
         assert tok == run["greedy"][step], f"step {step}"
         assert s.push_token(tok)
     print(f"worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}")
-    report = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(report):
-        with open(os.path.join(report, "parity_report.txt"), "a") as f:
-            f.write(f"config0 wtype={run['wtype']} 32 greedy tokens identical; worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}\n")
+    note_parity(f"config0 wtype={run['wtype']} 32 greedy tokens identical; worst logits max-abs {worst[0]:.3e} rel-L2 {worst[1]:.3e}")
     assert s.tokens() == run["prompt"] + run["greedy"]
     # the caches hold un-rotated f16 K and V rows; a value that differs in its last fp32 bits may
     # round to the neighbouring half, so compare as numbers
@@ -176,10 +181,7 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run):
         tok = s.predict_next_token()
         assert_logits_close(s.logits(run["vocab"]), run["logits"][step])
         assert tok == run["greedy"][step]
-    report = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(report):
-        with open(os.path.join(report, "parity_report.txt"), "a") as f:
-            f.write(f"config0 wtype={run['wtype']} prompt as one batch of 16: logits after the prompt max-abs {m:.3e} rel-L2 {r:.3e}\n")
+    note_parity(f"config0 wtype={run['wtype']} prompt as one batch of 16: logits after the prompt max-abs {m:.3e} rel-L2 {r:.3e}")
     s.close()
 
 
