@@ -185,18 +185,19 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run):
     s.close()
 
 
-def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run):
-    """40 prompt tokens in recorded steps of 16, 16 (batched products, the second one attending over the
-    rows of the first) and 8 (per-token kernels with a batch): logits and cache rows against the
-    oracle's token-by-token evaluation."""
-    toks = prompt_tokens(40, seed=777)
+@pytest.mark.parametrize("n_tokens,max_batch", [(40, 16), (150, 64)])
+def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run, n_tokens, max_batch):
+    """A prompt evaluated in several recorded steps (16 + 16 + 8, or 64 + 64 + 22 tokens), each later step
+    attending over the rows of the earlier ones: logits and cache rows against the oracle's
+    token-by-token evaluation."""
+    toks = prompt_tokens(n_tokens, seed=777)
     orc = OracleSession(run["path"])
     for t in toks:
         orc.push(t)
     want = orc.eval()
     s = run["ctx"].session()
     s.set_deterministic(True)
-    assert s.set_max_batch(16)
+    assert s.set_max_batch(max_batch)
     for t in toks:
         assert s.push_token(t)
     tok = s.predict_next_token()
@@ -204,8 +205,8 @@ def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run):
     assert tok == orc.argmax()
     for layer in range(2):
         for which in (0, 1):
-            got = s.read_kv(layer, which, 0, 40, run["dim"]).view(np.float16).astype(np.float32)
-            ref = orc.cache(which, layer, 40).view(np.float16).astype(np.float32)
+            got = s.read_kv(layer, which, 0, n_tokens, run["dim"]).view(np.float16).astype(np.float32)
+            ref = orc.cache(which, layer, n_tokens).view(np.float16).astype(np.float32)
             assert np.abs(got - ref).max() <= 2e-3 * np.abs(ref).max()
     s.close()
     orc.close()
