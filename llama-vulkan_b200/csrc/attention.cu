@@ -133,17 +133,26 @@ __host__ __device__ inline size_t attn_partial_floats(uint32_t heads, uint32_t n
 // step): scores with 8 lanes per cache row (16 elements each, both of a warp's
 // row batches in flight together), values with 16 threads per row (8 dims each)
 // and four rows per thread in flight.
-// Shared-memory staging of the score inputs (STAGED = true, one CTA per SM): the chunk's key rows and
-// the rows of the rotation table it needs (one contiguous range of distances) are brought in by bulk
-// (TMA) copies -- one per key row, one for the table -- and the scores are computed from shared
-// memory.  With plain loads the kernel spent a fifth of its samples throttled on the load/store
-// queue (28 16-byte loads per thread).  Key rows are padded to 320 bytes so that the two rows a
-// half-warp reads with 8-byte loads fall on different banks.
+// Shared-memory staging of the score inputs: the chunk's key rows and the rows of the rotation table
+// it needs are brought in by bulk (TMA) copies and the scores are computed from shared memory.  With
+// plain loads the kernel spent a fifth of its samples throttled on the load/store queue (28 16-byte
+// loads per thread).
+//   STAGED = 2 (grids of at most one CTA per SM): the table rows of the chunk's distances, one
+//     contiguous range, in one copy of up to 128 KB; key rows padded to 320 bytes so that the two
+//     rows a half-warp reads with 8-byte loads fall on different banks.
+//   STAGED = 1 (larger grids: long contexts, batches; two CTAs per SM): only 41 table rows -- those
+//     of the distances 0..31 and of the up to nine multiples of 32 the chunk spans -- and
+//     cos/sin((32 A + B) theta) from the angle-addition formulas (exact for A = 0, else a few units
+//     in the last place beside the table's own rounding); key rows unpadded.
+//   STAGED = 0: plain loads.
 constexpr int kStagedKeyStride = 320;
 constexpr size_t kStagedTableBytes = size_t(kAttnChunk) * kRot * sizeof(float);              // 131072
 constexpr size_t kStagedSmemBytes = kStagedTableBytes + size_t(kAttnChunk) * kStagedKeyStride;  // + 81920
+constexpr int kCompactARows = kAttnChunk / 32 + 1;                                            // multiples of 32 a chunk can span
+constexpr size_t kCompactTableBytes = size_t(32 + kCompactARows) * kRot * sizeof(float);      // 20992
+constexpr size_t kCompactSmemBytes = kCompactTableBytes + size_t(kAttnChunk) * kRot * sizeof(__half);   // + 65536
 
-template <int MIN_CTAS_PER_SM, bool STAGED>
+template <int MIN_CTAS_PER_SM, int STAGED>
 __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
                                                                        const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
@@ -168,21 +177,34 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     const uint32_t n = min(uint32_t(kAttnChunk), P + 1 - p0);
 
     // ---- scores: warp w owns rows 16w .. 16w+15, lane group g = lane / 8 one row per pass -----
-    if constexpr (STAGED) {
+    if constexpr (STAGED != 0) {
         const int sub = lane & 7, g = lane >> 3;
+        constexpr bool kCompact = STAGED == 1;
+        constexpr int kKeyStride = kCompact ? kRot * int(sizeof(__half)) : kStagedKeyStride;
         float* ttile = reinterpret_cast<float*>(staged);
-        uint8_t* ktile = staged + kStagedTableBytes;
+        uint8_t* ktile = staged + (kCompact ? kCompactTableBytes : kStagedTableBytes);
+        // distances of the chunk's rows: d_min .. d_min + n - 1, row i at distance d_min + (n - 1 - i)
+        const uint32_t d_min = P - p0 - (n - 1);
+        const uint32_t a_first = d_min >> 5, a_count = ((d_min + n - 1) >> 5) - a_first + 1;      // compact: multiples of 32 spanned
         if (threadIdx.x == 0) {
             mbar_init(&s_bar, 1);
             fence_mbar_init();
-            mbar_expect_tx(&s_bar, n * (kRot * uint32_t(sizeof(__half)) + kRot * uint32_t(sizeof(float))));
+            const uint32_t table_bytes = kCompact ? (32u + a_count) * kRot * uint32_t(sizeof(float)) : n * kRot * uint32_t(sizeof(float));
+            mbar_expect_tx(&s_bar, n * kRot * uint32_t(sizeof(__half)) + table_bytes);
         }
         __syncthreads();
-        // key row p0 + t -> ktile row t; table rows of the distances P - p0 - (n-1) .. P - p0 -> ttile rows 0 .. n-1
+        // key row p0 + t -> ktile row t
         if (threadIdx.x < n)
-            bulk_g2s(ktile + threadIdx.x * kStagedKeyStride, kc + size_t(p0 + threadIdx.x) * dim + h * kRot, kRot * sizeof(__half), &s_bar);
-        if (threadIdx.x == 0)
-            bulk_g2s(ttile, table + size_t(P - p0 - (n - 1)) * kRot, n * kRot * uint32_t(sizeof(float)), &s_bar);
+            bulk_g2s(ktile + threadIdx.x * kKeyStride, kc + size_t(p0 + threadIdx.x) * dim + h * kRot, kRot * sizeof(__half), &s_bar);
+        if constexpr (kCompact) {
+            // table rows 0..31 -> ttile rows 0..31; rows 32 (a_first + t) -> ttile row 32 + t
+            if (threadIdx.x == 0) bulk_g2s(ttile, table, 32 * kRot * sizeof(float), &s_bar);
+            if (threadIdx.x >= 32 && threadIdx.x < 32 + a_count)
+                bulk_g2s(ttile + size_t(threadIdx.x) * kRot, table + size_t(32u * (a_first + threadIdx.x - 32)) * kRot, kRot * sizeof(float), &s_bar);
+        } else {
+            // table rows of the distances d_min .. d_min + n - 1 -> ttile rows 0 .. n-1
+            if (threadIdx.x == 0) bulk_g2s(ttile, table + size_t(d_min) * kRot, n * kRot * uint32_t(sizeof(float)), &s_bar);
+        }
         // this lane's part of q: float4 number sub + 8 m, i.e. pairs 2 (sub + 8 m) and 2 (sub + 8 m) + 1
         float4 qv[4];
 #pragma unroll
@@ -192,14 +214,23 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
         for (int it = 0; it < kScoreIters; ++it) {
             const uint32_t i = warp * (4 * kScoreIters) + it * 4 + g;
             const uint32_t ic = min(i, n - 1);                        // rows past n are computed and discarded
-            const uint8_t* krow = ktile + ic * kStagedKeyStride;
-            const float* trow = ttile + size_t(n - 1 - ic) * kRot;
+            const uint8_t* krow = ktile + ic * kKeyStride;
+            const uint32_t d = d_min + (n - 1 - ic);
+            const float* trow = kCompact ? ttile + size_t(d & 31u) * kRot : ttile + size_t(n - 1 - ic) * kRot;
+            const float* arow = ttile + size_t(32u + (d >> 5) - a_first) * kRot;          // compact only
             float sacc = 0.f;
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
                 const int f = sub + 8 * m;
                 const uint2 kk = *reinterpret_cast<const uint2*>(krow + f * 8);           // 4 halves = 2 pairs
-                const float4 t = *reinterpret_cast<const float4*>(trow + f * 4);          // (cos, sin) of the two pairs
+                float4 t = *reinterpret_cast<const float4*>(trow + f * 4);                // (cos, sin) of the two pairs
+                if constexpr (kCompact) {
+                    // (cos, sin)((32 A + B) theta) from the rows of 32 A and of B
+                    const float4 a = *reinterpret_cast<const float4*>(arow + f * 4);
+                    const float c0 = fmaf(a.x, t.x, -(a.y * t.y)), s0 = fmaf(a.y, t.x, a.x * t.y);
+                    const float c1 = fmaf(a.z, t.z, -(a.w * t.w)), s1 = fmaf(a.w, t.z, a.z * t.w);
+                    t = make_float4(c0, s0, c1, s1);
+                }
                 const float2 ka = __half22float2(*reinterpret_cast<const __half2*>(&kk.x));
                 const float2 kb = __half22float2(*reinterpret_cast<const __half2*>(&kk.y));
                 const float4 qq = qv[m];
@@ -348,28 +379,36 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
 
 int attention_configure(lv_ctx* ctx) {
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= kStagedSmemBytes + 18 * 1024, "device has too little shared memory for the staged attention kernel");
-    LV_CUDA(cudaFuncSetAttribute(attention_fused_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kStagedSmemBytes)));
+    LV_CUDA(cudaFuncSetAttribute(attention_fused_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kStagedSmemBytes)));
+    LV_CUDA(cudaFuncSetAttribute(attention_fused_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kCompactSmemBytes)));
     return LV_OK;
 }
 
-// Grids of at most one CTA per SM stage their inputs in shared memory; larger ones (context beyond
-// ~1280 rows, batches) use plain loads with two CTAs per SM.
+// Grids of at most one CTA per SM stage key rows and the exact table rows in shared memory; larger
+// ones (context beyond ~1280 rows, batches) stage key rows and the compact table, two CTAs per SM.
 static int launch_attention_fused(lv_ctx* ctx, dim3 grid, float* out, const float* q, const void* k_cache, const void* v_cache,
                                   const uint32_t* pos, const float* rope_table, float* partial, uint32_t* counters, uint32_t heads,
                                   uint32_t nchunks, uint32_t rot) {
     const float scale = 1.0f / sqrtf(static_cast<float>(rot));
     static const char* no_stage = getenv("LV_ATTENTION_NO_STAGING");
     const bool staged = !(no_stage != nullptr && no_stage[0] == '1');
-    if (grid.x * grid.y * grid.z > uint32_t(ctx->sm_count)) {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, false>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
-    } else if (staged) {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, true>, grid, dim3(kFusedThreads), kStagedSmemBytes, out, q,
+    const bool big = grid.x * grid.y * grid.z > uint32_t(ctx->sm_count);
+    if (!staged) {
+        if (big) {
+            LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+        } else {
+            LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+        }
+    } else if (big) {
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 1>, grid, dim3(kFusedThreads), kCompactSmemBytes, out, q,
                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
                            heads, nchunks, scale, ctx->d_err));
     } else {
-        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, false>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                           static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+        LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 2>, grid, dim3(kFusedThreads), kStagedSmemBytes, out, q,
+                           static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
+                           heads, nchunks, scale, ctx->d_err));
     }
     return LV_OK;
 }
