@@ -176,6 +176,20 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     const uint32_t p0 = c * kAttnChunk;
     const uint32_t n = min(uint32_t(kAttnChunk), P + 1 - p0);
 
+    // The value rows do not depend on the scores.  The staged variant with one CTA per SM has the
+    // registers to fetch them first, so that they arrive while the keys are staged and the scores
+    // computed; the others (64 registers, or plain loads) fetch them after the scores, before the barrier.
+    const int d8 = (threadIdx.x & 15) * 8, rg = threadIdx.x >> 4;
+    uint4 vraw[kValueRows];
+    auto load_values = [&]() {
+#pragma unroll
+        for (int j = 0; j < kValueRows; ++j) {
+            const uint32_t i = min(uint32_t(rg + kRowGroups * j), n - 1);
+            vraw[j] = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * dim + h * kRot + d8);
+        }
+    };
+    if constexpr (STAGED == 2) load_values();
+
     // ---- scores: warp w owns rows 16w .. 16w+15, lane group g = lane / 8 one row per pass -----
     if constexpr (STAGED != 0) {
         const int sub = lane & 7, g = lane >> 3;
@@ -286,14 +300,7 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
         }
     }
     // ---- weighted values: thread = (8 dims, one of 32 row groups), rows rg, rg+32, ... -----------
-    // The value rows do not depend on the scores: their loads are issued before the barrier.
-    const int d8 = (threadIdx.x & 15) * 8, rg = threadIdx.x >> 4;
-    uint4 vraw[kValueRows];
-#pragma unroll
-    for (int j = 0; j < kValueRows; ++j) {
-        const uint32_t i = min(uint32_t(rg + kRowGroups * j), n - 1);
-        vraw[j] = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * dim + h * kRot + d8);
-    }
+    if constexpr (STAGED != 2) load_values();              // (the one-CTA-per-SM staged variant issued these loads before the scores)
     __syncthreads();                                       // s_e holds the scaled scores
     // ---- chunk maximum (every warp on its own) and the exponentials a thread needs ---------------
     float m = -INFINITY;
