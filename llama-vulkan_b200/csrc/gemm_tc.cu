@@ -1,7 +1,7 @@
 // Batched (multi-token) matrix products on the tcgen05 tensor cores.
 //
 // The decode step multiplies every matrix by one activation vector (gemv.cu).  When a prompt
-// is evaluated, 16 or more tokens share each matrix, the contraction becomes dense and the
+// is evaluated, several tokens share each matrix, the contraction becomes dense and the
 // reference's per-token shader dispatches (matmul.glsl with a batch in gl_WorkGroupID.z,
 // llava_command_buffer.cpp:61-132) are replaced by one pass over the weights:
 //
@@ -10,13 +10,15 @@
 // A operand: the q4_0 / q8_0 blocks of 128 rows, fetched by 2-D tensor-map TMA loads into a
 // raw ring, dequantised by sixteen warps into K-major fp16 tiles with the 128-byte swizzle.
 // A weight (q - 8) * d (q4_0) or q * d (q8_0) needs up to 14 / 19 significant bits, so it is
-// written as an exact pair hi = fp16(w), lo = w - hi.  B operand: the activations as an exact-to-22-bits pair of fp16
-// planes (lv_act_split_f16), fetched by swizzled TMA loads (the lo plane's rows follow the hi
-// plane's, so one B tile of 2Z rows serves both).  One thread issues, per 64 columns of K,
-// four K=16 steps of two tcgen05.mma: W_hi x [x_hi; x_lo] (N = 2Z) and W_lo x x_hi (N = Z)
-// into three 128 x Z fp32 accumulators in tensor memory (lo*lo is below fp32 resolution).
-// Four warps read the accumulators back with tcgen05.ld, add them and apply the epilogue
-// (store / add to the residual / f16 cache rows at the position / SiLU gate of a row pair).
+// written as an exact pair hi = fp16(w), lo = w - hi.  B operand: the activations as an
+// exact-to-22-bits pair of fp16 planes that lv_act_split_f16 writes tile by tile in the
+// swizzled order, so that one bulk copy per 64 columns of K brings a ready B tile (the lo
+// plane's rows follow the hi plane's, so one tile of 2Z rows serves both).  One thread issues,
+// per 64 columns of K, four K=16 steps of two tcgen05.mma: W_hi x [x_hi; x_lo] (N = 2Z) and
+// W_lo x x_hi (N = Z) into three 128 x Z fp32 accumulators in tensor memory (lo*lo is below
+// fp32 resolution; two such banks are used in turn).  Four warps read the accumulators back
+// with tcgen05.ld, add them and apply the epilogue (store / add to the residual / f16 cache
+// rows at the position / SiLU gate of a row pair).
 //
 // A matrix with few row tiles (wo, w2: 32-40) is also split along K, up to four CTAs per tile:
 // the kernel is bound by shared-memory traffic (each weight is written once and read once as two
