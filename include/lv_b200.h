@@ -219,7 +219,10 @@ size_t lv_attention_scratch_bytes(uint32_t heads, uint32_t rot, uint32_t max_ctx
 /* mhsa + softmax + kqv_matching (llava_layer.cpp:59-62) in one launch, reading
  * only the P + 1 filled cache rows (the reference's masked slots contribute
  * exactly 0).  out: f32 [batch][heads*rot].  scratch: device memory of
- * lv_attention_scratch_bytes, zero-filled once before first use. */
+ * lv_attention_scratch_bytes, zero-filled once before first use.  Launches
+ * of at most one CTA per SM (heads * ceil(max_ctx / 256) * batch) rotate with
+ * the table rows themselves; larger ones form cos/sin of a distance 32A + B
+ * from the rows of 32A and of B (a few units in the last place). */
 int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const void* k_cache, const void* v_cache,
                        const uint32_t* pos, const float* rope_table, void* scratch, uint32_t heads, uint32_t rot,
                        uint32_t max_ctx, uint32_t batch);
