@@ -386,7 +386,7 @@ def main():
     tps = args.steps / sec_dev
     achieved = k_bytes / k_sec / 1e9
     peak_all = peak * world                               # aggregate bandwidth of the N GPUs for the whole step
-    roofline = {"bound": "hbm", "kernel": f"gemv_kernel<{'q4_0' if w['wtype'] == 2 else 'q8_0'}, SILU> (norm + gate/up + SiLU, "
+    roofline = {"bound": "hbm", "kernel": f"lv_qrow_stream_kernel<{'q4_0' if w['wtype'] == 2 else 'q8_0'}, SILU> (norm + gate/up + SiLU, "
                                           f"{ff // world}x{dim} pair)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}",
                 # dram__bytes_read + dram__bytes_write of one launch of this kernel at this shape (ncu capture summarised

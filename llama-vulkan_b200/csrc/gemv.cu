@@ -45,7 +45,7 @@ struct GemvMaps {
 };
 
 template <int QT, int NS, bool SILU, int W, bool TMAP>
-__global__ void __launch_bounds__(W * 32, 1) gemv_kernel(const GemvParams p, const __grid_constant__ GemvMaps maps) {
+__global__ void __launch_bounds__(W * 32, 1) lv_qrow_stream_kernel(const GemvParams p, const __grid_constant__ GemvMaps maps) {
     using Q = QTraits<QT>;
     constexpr int kWarps = W;
     static_assert(size_t(W) * kStages * sizeof(uint64_t) <= kBarBytes, "mbarrier area too small for this many warps");
@@ -357,9 +357,9 @@ static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_
             if (int rc = make_weight_map(&maps.m[i], p.m[i].w, p.m[i].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
         if (SILU)
             if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, p.row_bytes, box_rows, seg_bytes)) return rc;
-        LV_CUDA(launch_pdl(ctx, gemv_kernel<QT, NS, SILU, W, true>, grid, dim3(W * 32), smem, p, maps));
+        LV_CUDA(launch_pdl(ctx, lv_qrow_stream_kernel<QT, NS, SILU, W, true>, grid, dim3(W * 32), smem, p, maps));
     } else {
-        LV_CUDA(launch_pdl(ctx, gemv_kernel<QT, NS, SILU, W, false>, grid, dim3(W * 32), smem, p, maps));
+        LV_CUDA(launch_pdl(ctx, lv_qrow_stream_kernel<QT, NS, SILU, W, false>, grid, dim3(W * 32), smem, p, maps));
     }
     return LV_OK;
 }
@@ -383,8 +383,8 @@ static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t b
 int gemv_configure(lv_ctx* ctx) {
     const int lim = ctx->max_smem_optin;
 #define LV_CFG1(QT, NS, SILU, W)                                                                                              \
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, NS, SILU, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));         \
-    LV_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, NS, SILU, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim))
+    LV_CUDA(cudaFuncSetAttribute(lv_qrow_stream_kernel<QT, NS, SILU, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));         \
+    LV_CUDA(cudaFuncSetAttribute(lv_qrow_stream_kernel<QT, NS, SILU, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim))
 #define LV_CFG(QT, SILU)                       \
     LV_CFG1(QT, 4, SILU, QTraits<QT>::kWarps); \
     LV_CFG1(QT, 2, SILU, QTraits<QT>::kWarps)

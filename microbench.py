@@ -2,7 +2,7 @@
 """Kernel microbenchmark of the quantised GEMV family (seeded N(0, 0.02)
 weights, N(0, 1) activations), one line of JSON per shape:
 
-    python llama-vulkan_b200/microbench.py [--shape NAME ...] [--wtype q4_0|q8_0] [--batch Z] [--tc] [--iters N]
+    python microbench.py [--shape NAME ...] [--wtype q4_0|q8_0] [--batch Z] [--tc] [--iters N]
 
 With --tc the plain / add / silu shapes run on the tensor cores (lv_gemm_tc*, batch 1..64,
 q4_0), otherwise the GEMV reads the matrix once per token of the batch; TFLOP/s =
@@ -19,8 +19,8 @@ import json
 import os
 import sys
 
-HERE = os.path.dirname(os.path.abspath(__file__))
-ROOT = os.path.dirname(HERE)
+ROOT = os.path.dirname(os.path.abspath(__file__))
+HERE = os.path.join(ROOT, "llama-vulkan_b200")
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 SHAPES = {                      # rows, cols, kind

@@ -2,7 +2,7 @@
 
 Run in a checkout where the reference sources are available:
 
-    make -C oracle ref && python llama-vulkan_b200/build.py && python tests/golden/make_golden.py
+    make -C oracle ref REF=<reference checkout> && python llama-vulkan_b200/build.py && python tests/golden/make_golden.py
 
 The model file is produced by this repository's synthetic writer (small
 geometry, full 32000-entry vocabulary); the recorded answers -- tensor table
