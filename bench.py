@@ -196,26 +196,41 @@ def time_dominant_kernel(pkg, ctx_handle_lv, dim, ff, wtype, stream, torch):
     return sec, 2 * mat_bytes
 
 
-def cpu_oracle_tokens_per_s(path, n_tokens, budget_s, threads=0):
-    """Times the CPU oracle (full depth, all host threads) on the first tokens of
-    the prompt; stops early once budget_s is used.  Returns (tokens/s, tokens timed, threads)."""
+def oracle_threads():
+    """Host threads the CPU oracle may use: the cores this process is allowed on.  Set explicitly, because
+    launchers such as torch.distributed.run export OMP_NUM_THREADS=1 to their children."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_oracle_tokens_per_s(path, n_prompt, n_warmup, n_tokens, budget_s):
+    """Times the CPU oracle (full depth, all host threads): evaluates n_prompt prompt tokens and n_warmup greedy
+    tokens untimed, then times up to n_tokens greedy tokens, stopping early once budget_s is used.
+    Returns (tokens/s, tokens timed, threads, first timed context length)."""
     import numpy as np
     import oracle_bind as ob
     lib = ob.load()
-    if threads:
-        lib.orc_set_threads(threads)
+    lib.orc_set_threads(oracle_threads())
     model = lib.orc_model_open(os.fsencode(path))
-    sess = lib.orc_session_create(model, 1024)
+    sess = lib.orc_session_create(model, 2048)
     info = ob.ModelInfo()
     lib.orc_model_get_info(model, C.byref(info))
     logits = np.empty(info.vocab_size, np.float32)
-    toks = prompt_tokens(max(n_tokens, 1) + 1)
-    lib.orc_session_push_token(sess, toks[0])
-    lib.orc_session_eval(sess, ob.ptr(logits))         # warm the page cache / thread pool
+    for t in prompt_tokens(max(n_prompt, 1)):
+        lib.orc_session_push_token(sess, t)
+
+    def step():
+        lib.orc_session_eval(sess, ob.ptr(logits))          # evaluates every token pushed since the last call
+        lib.orc_session_push_token(sess, int(lib.orc_argmax(ob.ptr(logits), logits.size)))
+
+    for _ in range(1 + n_warmup):                           # the first call ingests the prompt
+        step()
+    first_ctx = lib.orc_session_token_count(sess)
     done, t0 = 0, time.perf_counter()
     while done < n_tokens:
-        lib.orc_session_push_token(sess, toks[done + 1])
-        lib.orc_session_eval(sess, ob.ptr(logits))
+        step()
         done += 1
         if time.perf_counter() - t0 > budget_s:
             break
@@ -223,35 +238,276 @@ def cpu_oracle_tokens_per_s(path, n_tokens, budget_s, threads=0):
     nthreads = lib.orc_get_threads()
     lib.orc_session_destroy(sess)
     lib.orc_model_close(model)
-    return done / dt, done, nthreads
+    return done / dt, done, nthreads, first_ctx
+
+
+def workload_config(pkg, name, args, world):
+    """The `config` object of the JSON line; both arms print the same one for the same arguments."""
+    w = WORKLOADS[name]
+    dim, heads, ff, n_layers = model_geometry(pkg, w)
+    first_pos = w["prompt"] + 1 + args.warmup               # cache rows already filled when the timed steps start
+    return {"workload": f"LLaMA-{w['geometry'].upper()} {'q4_0' if w['wtype'] == 2 else 'q8_0'} single-stream greedy decode, "
+                        f"{n_layers} layers, {w['prompt']}-token seeded prompt, f16 KV cache, context {first_pos}..{first_pos + args.steps}",
+            "baseline_config_index": w["config"], "cache": "weights per token (GBs) exceed the 126 MB L2; no flush needed",
+            "parallelism": f"tp{world}" + (f" ({args.allreduce} all-reduce)" if world > 1 else "")}
+
+
+def model_path_for(pkg, w):
+    dim, heads, ff, n_layers = model_geometry(pkg, w)
+    return os.path.join(MODEL_DIR, f"{w['geometry']}_L{n_layers}_t{w['wtype']}_seed1234.ggjt")
 
 
 def run_reference(args, rank, world):
-    """The reference arm: the reference's path restated for the CPU (oracle/),
-    since its own implementation needs Vulkan, which does not exist on this box."""
+    """The reference arm: the reference's path restated for the CPU (oracle/), since its own implementation
+    needs Vulkan, which does not exist on this box.  Same model file, prompt, warm-up and step count as the GPU
+    arm (the timed part stops early after ~150 s)."""
     if rank != 0:
         return
-    pkg = load_pkg()
+    pkg = load_pkg()                 # ctypes declarations only; the native product libraries are loaded on demand
     w = WORKLOADS[args.workload]
-    path = ensure_model(pkg, args.workload, w, 0, 1)
-    # bounded sample: whole-depth tokens, at most ~150 s in total
-    for _ in range(min(args.warmup, 1)):
-        cpu_oracle_tokens_per_s(path, 1, 30)
-    tps, timed, threads = cpu_oracle_tokens_per_s(path, args.steps, 150.0)
-    dim, heads, ff, n_layers = model_geometry(pkg, w)
+    path = model_path_for(pkg, w)
+    if not (os.path.exists(path + ".done") and os.path.exists(path)):
+        path = ensure_model(pkg, args.workload, w, 0, 1)       # first run on this box: the synthetic file has to be written
+    tps, timed, threads, first_ctx = cpu_oracle_tokens_per_s(path, w["prompt"], args.warmup, args.steps, 150.0)
     line = {
         "impl": "reference", "metric": "decode tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / tps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"LLaMA-{w['geometry'].upper()} {'q4_0' if w['wtype'] == 2 else 'q8_0'} decode, {n_layers} layers, "
-                               "seeded synthetic ggjt-v3 weights, host cores only", "baseline_config_index": w["config"]},
+        "config": workload_config(pkg, args.workload, args, args.gpus),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"{timed} whole-depth decode tokens at context 1..{timed + 1} (CPU restatement of the "
+                         "sample": f"{timed} whole-depth greedy decode tokens from context {first_ctx} on, after the same "
+                                   f"{w['prompt']}-token prompt and {args.warmup} warm-up tokens (CPU restatement of the "
                                    "reference shaders; the reference's own Vulkan path is unavailable on this box)"},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+PARITY_MODELS = (("7b", 2, 2), ("13b", 2, 2))        # geometry, layers, type: BASELINE config 0 and its 13B-geometry twin
+PARITY_PROMPT, PARITY_DECODE = 16, 32
+PARITY_MAX_ABS, PARITY_REL_L2 = 1e-2, 1e-3
+
+
+def oracle_trajectory(path, prompt, n_decode):
+    """Greedy decoding on the CPU oracle: the logits of every step and the tokens chosen."""
+    import numpy as np
+    import oracle_bind as ob
+    lib = ob.load()
+    lib.orc_set_threads(oracle_threads())
+    model = lib.orc_model_open(os.fsencode(path))
+    sess = lib.orc_session_create(model, 1024)
+    logits = np.empty(32000, np.float32)
+    for t in prompt:
+        lib.orc_session_push_token(sess, t)
+    all_logits, tokens = [], []
+    for _ in range(n_decode):
+        lib.orc_session_eval(sess, ob.ptr(logits))
+        all_logits.append(logits.copy())
+        tokens.append(int(lib.orc_argmax(ob.ptr(logits), logits.size)))
+        lib.orc_session_push_token(sess, tokens[-1])
+    lib.orc_session_destroy(sess)
+    lib.orc_model_close(model)
+    return all_logits, tokens
+
+
+class Rig:
+    """Process-wide plumbing: rank, torch.distributed, context creation with the peer windows connected."""
+
+    def __init__(self, args):
+        import torch
+        self.torch = torch
+        self.args = args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.pkg = load_pkg()
+        self.klib = self.pkg.load_kernels()
+        torch.cuda.set_device(self.local_rank)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, seconds):
+        if self.dist is None:
+            return seconds
+        t = self.torch.tensor([seconds], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def agree(self, ok):
+        """True only if every rank says ok."""
+        if self.dist is None:
+            return ok
+        t = self.torch.tensor([1 if ok else 0], dtype=self.torch.int32, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def open_context(self, path):
+        torch, dist, pkg = self.torch, self.dist, self.pkg
+        nccl_id = None
+        if self.world > 1:
+            ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+            if self.rank == 0:
+                buf = (C.c_uint8 * 128)()
+                pkg.check(self.klib.lv_comm_unique_id(buf))
+                ident = torch.tensor(list(buf), dtype=torch.uint8, device="cuda")
+            dist.broadcast(ident, 0)
+            nccl_id = bytes(ident.cpu().tolist())
+        ctx = pkg.HostContext(path, self.local_rank, self.rank, self.world, nccl_id)
+        if self.world > 1 and self.args.allreduce == "peer":
+            mine = torch.tensor(list(ctx.peer_window_handle()), dtype=torch.uint8, device="cuda")
+            gathered = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(self.world)]
+            dist.all_gather(gathered, mine)
+            ctx.peer_connect([bytes(g.cpu().tolist()) for g in gathered])
+            self.barrier()
+        return ctx
+
+
+def parity_check(rig):
+    """Before anything is timed: the two-layer 7B-geometry model of BASELINE config 0 and a two-layer
+    13B-geometry model, 16 seeded prompt tokens + 32 greedy tokens on the N ranks, every step's logits and
+    token compared on rank 0 with the CPU oracle.  Returns the worst distances; raises SystemExit on a miss."""
+    import numpy as np
+    pkg = rig.pkg
+    out = {"max_abs_tolerance": PARITY_MAX_ABS, "rel_l2_tolerance": PARITY_REL_L2, "tokens_per_model": PARITY_DECODE, "models": {}}
+    prompt = prompt_tokens(PARITY_PROMPT)
+    for geometry, n_layers, wtype in PARITY_MODELS:
+        w = dict(geometry=geometry, n_layers=n_layers, wtype=wtype, prompt=PARITY_PROMPT, config=0)
+        path = ensure_model(pkg, f"parity-{geometry}", w, rig.rank, rig.world)
+        rig.barrier()
+        want_logits, want_tokens = oracle_trajectory(path, prompt, PARITY_DECODE) if rig.rank == 0 else (None, None)
+        ctx = rig.open_context(path)
+        s = ctx.session()
+        s.set_deterministic(True)
+        for t in prompt:
+            assert s.push_token(t)
+        worst_abs = worst_rel = 0.0
+        ok, why = True, ""
+        for step in range(PARITY_DECODE):
+            tok = s.predict_next_token()
+            if tok == pkg.NO_TOKEN:
+                ok, why = False, f"step {step}: evaluation failed"
+                break
+            if rig.rank == 0:
+                got = s.logits(32000).astype(np.float64)
+                want = want_logits[step].astype(np.float64)
+                worst_abs = max(worst_abs, float(np.abs(got - want).max()))
+                worst_rel = max(worst_rel, float(np.linalg.norm(got - want) / np.linalg.norm(want)))
+                if tok != want_tokens[step]:
+                    ok, why = False, f"step {step}: token {tok}, oracle {want_tokens[step]}"
+                if not (worst_abs <= PARITY_MAX_ABS and worst_rel <= PARITY_REL_L2):
+                    ok, why = False, f"step {step}: logits max-abs {worst_abs:.3e} rel-L2 {worst_rel:.3e}"
+            if not rig.agree(ok):
+                ok = False
+                break
+            s.push_token(tok)
+        s.close()
+        ctx.close()
+        rig.barrier()
+        out["models"][f"{geometry}-geometry, {n_layers} layers, q4_0"] = {"logits_max_abs": worst_abs, "logits_rel_l2": worst_rel,
+                                                                        "greedy_tokens_identical": ok}
+        if not ok:
+            if rig.rank == 0:
+                print(json.dumps({"parity": out, "failed": why}), flush=True)
+            raise SystemExit(f"parity check against the CPU oracle failed on {rig.world} GPU(s): {why}")
+    out["against"] = "CPU oracle (oracle/llava_oracle.c), rank 0"
+    return out
+
+
+def median_spread(values):
+    v = sorted(values)
+    return v[len(v) // 2], {"min": v[0], "max": v[-1], "repeats": len(v)}
+
+
+def measure_decode(rig, ctx, name, args, repeats):
+    """Decode throughput of one workload on an open context: `repeats` timed regions of args.steps greedy tokens
+    each over the same context window (the session is rewound in between), device-resident and host-driven.
+    Returns a dict; tokens/s figures are medians over the repeats of the max over ranks."""
+    torch, pkg, klib = rig.torch, rig.pkg, rig.klib
+    w = WORKLOADS[name]
+    n_prompt, world = w["prompt"], rig.world
+    lv = C.c_void_p(ctx.lib.llava_context_lv(ctx.handle))
+    stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=rig.local_rank)
+    prompt_eval = {}
+
+    s = ctx.session()
+    s.set_deterministic(True)
+    if world == 1:
+        assert s.set_max_batch(64)          # prompt in steps of up to 64 tokens (tensor-core path)
+    for t in prompt_tokens(n_prompt):
+        assert s.push_token(t)
+    t0 = time.perf_counter()
+    first = s.predict_next_token()          # ingests the prompt (records its steps on first use)
+    prompt_eval.update(tokens=n_prompt, seconds=time.perf_counter() - t0, max_batch=64 if world == 1 else 1)
+    assert first != pkg.NO_TOKEN
+    assert s.push_token(first)
+    warm = s.generate_greedy_on_device(args.warmup)
+    base = s.tokens()                        # prompt, first token, warm-up tokens; the last one is not evaluated yet
+    assert len(base) == n_prompt + 1 + args.warmup and warm == base[-args.warmup:]
+
+    def restart():
+        """Back to the state right after the warm-up: every token but the last evaluated."""
+        s.rewind(len(base) - 1)
+        assert s.push_token(base[-1])
+
+    # ---- device-resident loop: inputs in HBM, no host round trip per token -------------------
+    dev_times, toks_dev = [], None
+    for r in range(repeats):
+        restart()
+        pkg.check(klib.lv_stream_sync(lv, 0))
+        rig.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        s.enqueue_greedy_on_device(args.steps)
+        e1.record(stream)
+        toks = s.collect_greedy_on_device()
+        pkg.check(klib.lv_stream_sync(lv, 0))
+        rig.barrier()
+        dev_times.append(rig.max_over_ranks(e0.elapsed_time(e1) * 1e-3))
+        if toks_dev is not None and toks != toks_dev:
+            raise SystemExit("two device-resident runs over the same context disagree on the greedy tokens")
+        toks_dev = toks
+    launches = s.step_kernel_launches()
+
+    # ---- end to end through the session API: token id in, argmax out, host in the loop -------
+    e2e_times = []
+    for r in range(repeats):
+        restart()
+        pkg.check(klib.lv_stream_sync(lv, 0))
+        rig.barrier()
+        toks_e2e = []
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            assert s.start_next_token_prediction()          # H2D: the pushed token id (pinned, 4 B)
+            tok = s.finish_next_token_prediction()          # D2H: the argmax (pinned, 4 B)
+            toks_e2e.append(tok)
+            s.push_token(tok)
+        e2e_times.append(rig.max_over_ranks(time.perf_counter() - t0))
+        rig.barrier()
+        if toks_e2e != toks_dev:
+            raise SystemExit("device-resident and host-driven decoding disagree on the greedy tokens")
+    s.close()
+    sec_dev, dev_spread = median_spread(dev_times)
+    sec_e2e, e2e_spread = median_spread(e2e_times)
+    dim, heads, ff, n_layers = model_geometry(pkg, w)
+    first_pos = n_prompt + 1 + args.warmup
+    mean_pos = first_pos + (args.steps - 1) / 2
+    bytes_per_token = weight_bytes_per_token(dim, ff, n_layers, 32000, w["wtype"]) + kv_bytes_per_token(dim, n_layers, mean_pos)
+    tps = args.steps / sec_dev
+    return {"tokens_per_s": tps, "ms_per_step": sec_dev * 1e3 / args.steps,
+            "spread_tokens_per_s": {"min": args.steps / dev_spread["max"], "max": args.steps / dev_spread["min"], "repeats": repeats},
+            "e2e_tokens_per_s": args.steps / sec_e2e,
+            "e2e_spread_tokens_per_s": {"min": args.steps / e2e_spread["max"], "max": args.steps / e2e_spread["min"], "repeats": repeats},
+            "bytes_per_token": bytes_per_token, "launches_per_token": launches, "tokens_digest": int(sum((i + 1) * t for i, t in enumerate(toks_dev)) % (1 << 31)),
+            "prompt_eval": dict(prompt_eval, tokens_per_s=prompt_eval["tokens"] / prompt_eval["seconds"])}
 
 
 def main():
@@ -261,20 +517,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="7b-q4_0", choices=sorted(WORKLOADS))
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions per figure; the median is reported")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison that precedes the timed runs")
+    ap.add_argument("--no-13b", action="store_true", help="skip the second measurement on LLaMA-13B q4_0 (BASELINE config 3)")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: one-kernel all-reduce over NVLink peer memory (default) or NCCL + add")
+                    help="N > 1: exchanges over NVLink peer memory (default) or NCCL + add")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     if args.impl == "reference":
         return run_reference(args, rank, world)
-    if args.warmup < 3:
-        args.warmup = 3
 
-    import numpy as np
-    import torch
     pkg = load_pkg()
     w = WORKLOADS[args.workload]
     dim, heads, ff, n_layers = model_geometry(pkg, w)
@@ -283,109 +539,30 @@ def main():
         raise SystemExit("prompt + warm-up + steps exceeds the 2048-token context of the reference")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run); got WORLD_SIZE={world}")
-    torch.cuda.set_device(local_rank)
-    dist = None
-    nccl_id = None
-    klib = pkg.load_kernels()
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            buf = (C.c_uint8 * 128)()
-            pkg.check(klib.lv_comm_unique_id(buf))
-            ident = torch.tensor(list(buf), dtype=torch.uint8, device="cuda")
-        dist.broadcast(ident, 0)
-        nccl_id = bytes(ident.cpu().tolist())
+    rig = Rig(args)
+    torch, klib = rig.torch, rig.klib
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(seconds):
-        if dist is None:
-            return seconds
-        t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    parity = None if args.no_parity else parity_check(rig)
 
     path = ensure_model(pkg, args.workload, w, rank, world)
-    barrier()
+    rig.barrier()
     t0 = time.time()
-    ctx = pkg.HostContext(path, local_rank, rank, world, nccl_id)
+    ctx = rig.open_context(path)
     print(f"[bench] rank {rank}: model on device in {time.time() - t0:.1f} s", file=sys.stderr)
-    if world > 1 and args.allreduce == "peer":
-        mine = torch.tensor(list(ctx.peer_window_handle()), dtype=torch.uint8, device="cuda")
-        gathered = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
-        dist.all_gather(gathered, mine)
-        ctx.peer_connect([bytes(g.cpu().tolist()) for g in gathered])
-        barrier()
     lv = C.c_void_p(ctx.lib.llava_context_lv(ctx.handle))
-    stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=local_rank)
+    stream = torch.cuda.ExternalStream(klib.lv_ctx_stream(lv), device=rig.local_rank)
 
-    prompt_eval = {}
-
-    def fresh_session():
-        s = ctx.session()
-        s.set_deterministic(True)
-        if world == 1:
-            assert s.set_max_batch(64)          # prompt in steps of up to 64 tokens (tensor-core path for q4_0)
-        for t in prompt_tokens(n_prompt):
-            assert s.push_token(t)
-        t0 = time.perf_counter()
-        first = s.predict_next_token()          # ingests the prompt (records its steps on first use)
-        prompt_eval.update(tokens=n_prompt, seconds=time.perf_counter() - t0, max_batch=64 if world == 1 else 1)
-        assert first != pkg.NO_TOKEN
-        assert s.push_token(first)
-        return s
-
-    # ---- device-resident loop: inputs in HBM, no host round trip per token -------------------
-    s = fresh_session()
-    s.generate_greedy_on_device(args.warmup)
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(rig.local_rank)
     sampler.start()
-    pkg.check(klib.lv_stream_sync(lv, 0))
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    s.enqueue_greedy_on_device(args.steps)
-    e1.record(stream)
-    toks_dev = s.collect_greedy_on_device()
-    pkg.check(klib.lv_stream_sync(lv, 0))
-    barrier()
-    sec_dev = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
-    s.close()
-
-    # ---- end to end through the session API: token id in, argmax out, host in the loop -------
-    s = fresh_session()
-    for _ in range(args.warmup):
-        s.push_token(s.predict_next_token())
-    pkg.check(klib.lv_stream_sync(lv, 0))
-    barrier()
-    toks_e2e = []
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        assert s.start_next_token_prediction()          # H2D: the pushed token id (pinned, 4 B)
-        tok = s.finish_next_token_prediction()          # D2H: the argmax (pinned, 4 B)
-        toks_e2e.append(tok)
-        s.push_token(tok)
-    sec_e2e = max_over_ranks(time.perf_counter() - t0)
-    barrier()
+    m = measure_decode(rig, ctx, args.workload, args, args.repeats)
     clocks = sampler.stop()
-    s.close()
-    if toks_e2e != toks_dev:
-        raise SystemExit("device-resident and host-driven decoding disagree on the greedy tokens")
 
     # ---- roofline of the dominant kernel ---------------------------------------------------
     peak, peak_kind = measured_peaks()
     k_sec, k_bytes = time_dominant_kernel(pkg, lv, dim, ff // world, w["wtype"], stream, torch)
-    first_pos = n_prompt + 1 + args.warmup               # cache rows already filled when the timed steps start
-    mean_pos = first_pos + (args.steps - 1) / 2
-    bytes_per_token = weight_bytes_per_token(dim, ff, n_layers, 32000, w["wtype"]) + kv_bytes_per_token(dim, n_layers, mean_pos)
-    tps = args.steps / sec_dev
     achieved = k_bytes / k_sec / 1e9
     peak_all = peak * world                               # aggregate bandwidth of the N GPUs for the whole step
+    tps = m["tokens_per_s"]
     roofline = {"bound": "hbm", "kernel": f"lv_qrow_stream_kernel<{'q4_0' if w['wtype'] == 2 else 'q8_0'}, SILU> (norm + gate/up + SiLU, "
                                           f"{ff // world}x{dim} pair)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}",
@@ -393,44 +570,54 @@ def main():
                 # in profiles/gemv_silu_q4_0_11008x4096.md); no capture exists for the other shapes
                 "traffic": 50810368 if (w["wtype"] == 2 and dim == 4096 and world == 1) else None,
                 "algorithmic_bytes_per_launch": k_bytes,
-                "whole_step": {"bytes_per_token": bytes_per_token, "achieved": bytes_per_token * tps / 1e9,
-                               "aggregate_peak": peak_all, "frac": bytes_per_token * tps / 1e9 / peak_all}}
+                "whole_step": {"bytes_per_token": m["bytes_per_token"], "achieved": m["bytes_per_token"] * tps / 1e9,
+                               "aggregate_peak": peak_all, "frac": m["bytes_per_token"] * tps / 1e9 / peak_all}}
+    ctx.close()
+    rig.barrier()
 
-    cpu = None
+    # ---- BASELINE config 3 (LLaMA-13B q4_0), the model the multi-GPU target is stated on -------
+    config3 = None
+    if not args.no_13b and args.workload != "13b-q4_0":
+        w13 = WORKLOADS["13b-q4_0"]
+        path13 = ensure_model(pkg, "13b-q4_0", w13, rank, world)
+        rig.barrier()
+        ctx13 = rig.open_context(path13)
+        m13 = measure_decode(rig, ctx13, "13b-q4_0", args, max(3, args.repeats // 2))
+        ctx13.close()
+        rig.barrier()
+        config3 = {"workload": workload_config(pkg, "13b-q4_0", args, world)["workload"], "tokens_per_s": m13["tokens_per_s"],
+                   "ms_per_step": m13["ms_per_step"], "spread_tokens_per_s": m13["spread_tokens_per_s"],
+                   "e2e_tokens_per_s": m13["e2e_tokens_per_s"], "bytes_per_token": m13["bytes_per_token"],
+                   "whole_step_frac": m13["bytes_per_token"] * m13["tokens_per_s"] / 1e9 / peak_all,
+                   "prompt_eval_tokens_per_s": m13["prompt_eval"]["tokens_per_s"]}
+
     if rank != 0:
-        ctx.close()
-        barrier()
-        dist.destroy_process_group()
+        rig.dist.destroy_process_group()
         return
+    cpu = None
     if not args.no_cpu_baseline and world == 1:
-        ctx.close()
-        ctx = None
-        v, timed, threads = cpu_oracle_tokens_per_s(path, 12, 20.0)
+        v, timed, threads, first_ctx = cpu_oracle_tokens_per_s(path, 1, 0, 12, 20.0)
         cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"{timed} whole-depth decode tokens at context 1..{timed + 1} of the same model file"}
-    if ctx is not None:
-        ctx.close()
+               "sample": f"{timed} whole-depth decode tokens from context {first_ctx} on, same model file"}
 
-    # embedding row, 5 kernels per layer (7 with the two all-reduce + residual kernels of a sharded layer), norm + head, argmax + advance
-    launches_per_token = 1 + (5 if world == 1 else 7) * n_layers + 2
     line = {
         "metric": "decode tokens/s", "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec_dev * 1e3 / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"LLaMA-{w['geometry'].upper()} {'q4_0' if w['wtype'] == 2 else 'q8_0'} single-stream greedy decode, "
-                               f"{n_layers} layers, {n_prompt}-token seeded prompt, f16 KV cache, context {first_pos}..{first_pos + args.steps}",
-                   "baseline_config_index": w["config"], "cache": "weights per token (GBs) exceed the 126 MB L2; no flush needed",
-                   "parallelism": f"tp{world}" + (f" ({args.allreduce} all-reduce)" if world > 1 else "")},
+        "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32 accumulate; weights q4_0/q8_0 blocks as stored; activations 22-bit fixed point per 32-block (exact int32 dot products)",
+        "data": "synthetic", "config": workload_config(pkg, args.workload, args, world),
+        "spread": dict(m["spread_tokens_per_s"], unit="tokens/s", value_is="median"),
         "roofline": roofline, "cpu_baseline": cpu,
-        "e2e": {"value": args.steps / sec_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
-        "gpu_launches": launches_per_token * args.steps, "clocks": clocks,
+        "e2e": {"value": m["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "spread": m["e2e_spread_tokens_per_s"]},
+        "gpu_launches": m["launches_per_token"] * args.steps, "clocks": clocks,
+        "parity": parity, "tokens_digest": m["tokens_digest"], "config3_13b": config3,
         # not part of the metric: wall time of the prompt's evaluation, first use (records the steps) included
-        "prompt_eval": dict(prompt_eval, tokens_per_s=prompt_eval["tokens"] / prompt_eval["seconds"]) if prompt_eval else None,
+        "prompt_eval": m["prompt_eval"],
     }
     print(json.dumps(line), flush=True)
-    barrier()
-    if dist is not None:
-        dist.destroy_process_group()
+    if rig.dist is not None:
+        rig.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

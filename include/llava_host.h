@@ -85,6 +85,8 @@ int      llava_session_collect_greedy_on_device(void* session, uint32_t* out, ui
 int      llava_session_get_logits(void* session, float* out, uint32_t cap);
 uint32_t llava_session_get_backlog_size(void* session);
 uint32_t llava_session_get_tokens_in_gpu(void* session);
+/* kernel launches of one replay of the step evaluated last (0 before the first step) */
+uint32_t llava_session_step_kernel_launches(void* session);
 /* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
 int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
 

@@ -75,6 +75,8 @@ int lv_copy_d2d(lv_ctx* ctx, void* dst, const void* src, size_t bytes);         
 int lv_graph_begin_capture(lv_ctx* ctx);
 int lv_graph_end_capture(lv_ctx* ctx, lv_graph** out);
 int lv_graph_launch(lv_ctx* ctx, lv_graph* g);
+/* number of kernel launches one replay of the graph performs */
+int lv_graph_kernel_nodes(lv_graph* g, uint32_t* out);
 int lv_graph_destroy(lv_graph* g);
 /* Waits until the stream is idle (timeout_ms <= 0: no limit), then reads the
  * device error word; LV_ERR_DEVICE_WAIT if a kernel recorded a lost wait. */

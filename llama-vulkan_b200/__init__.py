@@ -50,6 +50,7 @@ KERNEL_API = {
     "lv_graph_begin_capture": (_int, [_p]),
     "lv_graph_end_capture": (_int, [_p, C.POINTER(_p)]),
     "lv_graph_launch": (_int, [_p, _p]),
+    "lv_graph_kernel_nodes": (_int, [_p, _p]),
     "lv_graph_destroy": (_int, [_p]),
     "lv_stream_sync": (_int, [_p, _int]),
     "lv_norm_f32": (_int, [_p, _p, _p, _p, _u32, _u32]),
@@ -248,6 +249,7 @@ HOST_API = {
     "llava_session_get_logits": (_int, [_p, _p, _u32]),
     "llava_session_get_backlog_size": (_u32, [_p]),
     "llava_session_get_tokens_in_gpu": (_u32, [_p]),
+    "llava_session_step_kernel_launches": (_u32, [_p]),
     "llava_session_read_kv": (_int, [_p, _u32, _int, _u32, _u32, _p]),
     "llava_wrapper_owner_create": (_p, [_p]),
     "llava_wrapper_owner_destroy": (None, [_p]),
@@ -470,6 +472,10 @@ class Session:
 
     def tokens_in_gpu(self):
         return self.lib.llava_session_get_tokens_in_gpu(self.handle)
+
+    def step_kernel_launches(self):
+        """Kernel launches of one replay of the step evaluated last."""
+        return self.lib.llava_session_step_kernel_launches(self.handle)
 
     def read_kv(self, layer, which, row0, nrows, dim):
         import numpy as np

@@ -45,15 +45,26 @@ def _glob(d, exts):
 
 
 def build_kernels(force=False, verbose_ptxas=False):
+    """Compiles every .cu file to an object of its own (in parallel, only the stale ones) and links them."""
+    from concurrent.futures import ThreadPoolExecutor
     cu = _glob(CSRC, (".cu",))
-    deps = cu + _glob(CSRC, (".cuh", ".h")) + [os.path.join(ROOT, "include", "lv_b200.h")]
+    headers = _glob(CSRC, (".cuh", ".h")) + [os.path.join(ROOT, "include", "lv_b200.h")]
     out = os.path.join(HERE, "liblv_b200.so")
-    if not force and not _newer(out, deps):
-        return out
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
     flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
     if verbose_ptxas:
         flags += ["-Xptxas", "-v"]
-    _run([_nvcc(), "-shared", "-o", out] + flags + cu + ["-lcudart", "-ldl"])
+    objs, stale = [], []
+    for src in cu:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        if force or verbose_ptxas or _newer(obj, [src] + headers):
+            stale.append((src, obj))
+    with ThreadPoolExecutor(max_workers=max(1, min(len(stale), os.cpu_count() or 1))) as pool:
+        list(pool.map(lambda so: _run([_nvcc(), "-c", "-o", so[1]] + flags + [so[0]]), stale))
+    if stale or not os.path.exists(out):
+        _run([_nvcc(), "-shared", "-o", out, "-gencode", "arch=compute_100a,code=sm_100a"] + objs + ["-lcudart", "-ldl"])
     return out
 
 

@@ -157,7 +157,8 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
                                                                        const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                        float* __restrict__ partial, uint32_t* __restrict__ counters,
-                                                                       uint32_t heads, uint32_t nchunks, float scale, uint32_t* err) {
+                                                                       uint32_t heads, uint32_t nchunks, uint32_t max_ctx, float scale,
+                                                                       uint32_t* err) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_e[kAttnChunk];
@@ -170,6 +171,12 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t h = blockIdx.x, c = blockIdx.y, z = blockIdx.z;
     const uint32_t P = *pos + z;
+    if (P >= max_ctx) {
+        // the position lies outside the caches and the rotation table: report it and touch nothing
+        // (neither `out` nor the arrival counters), like the cache append does
+        if (threadIdx.x == 0 && h == 0 && c == 0) atomicOr(err, ERR_BAD_INDEX);
+        return;
+    }
     const uint32_t dim = heads * kRot;
     const uint32_t active = P / kAttnChunk + 1;          // chunks that hold at least one row <= P
     if (c >= active) return;
@@ -395,27 +402,28 @@ int attention_configure(lv_ctx* ctx) {
 // ones (context beyond ~1280 rows, batches) stage key rows and the compact table, two CTAs per SM.
 static int launch_attention_fused(lv_ctx* ctx, dim3 grid, float* out, const float* q, const void* k_cache, const void* v_cache,
                                   const uint32_t* pos, const float* rope_table, float* partial, uint32_t* counters, uint32_t heads,
-                                  uint32_t nchunks, uint32_t rot) {
+                                  uint32_t nchunks, uint32_t max_ctx, uint32_t rot) {
     const float scale = 1.0f / sqrtf(static_cast<float>(rot));
     static const char* no_stage = getenv("LV_ATTENTION_NO_STAGING");
-    const bool staged = !(no_stage != nullptr && no_stage[0] == '1');
+    // the compact table variant always copies the table rows of distances 0..31
+    const bool staged = !(no_stage != nullptr && no_stage[0] == '1') && max_ctx >= 32;
     const bool big = grid.x * grid.y * grid.z > uint32_t(ctx->sm_count);
     if (!staged) {
         if (big) {
             LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err));
         } else {
             LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, scale, ctx->d_err));
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err));
         }
     } else if (big) {
         LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 1>, grid, dim3(kFusedThreads), kCompactSmemBytes, out, q,
                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
-                           heads, nchunks, scale, ctx->d_err));
+                           heads, nchunks, max_ctx, scale, ctx->d_err));
     } else {
         LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 2>, grid, dim3(kFusedThreads), kStagedSmemBytes, out, q,
                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
-                           heads, nchunks, scale, ctx->d_err));
+                           heads, nchunks, max_ctx, scale, ctx->d_err));
     }
     return LV_OK;
 }
@@ -519,7 +527,7 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     float* partial = static_cast<float*>(scratch);
     uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, batch));
     dim3 grid(heads, nchunks, batch);
-    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, rot)) return rc;
+    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, max_ctx, rot)) return rc;
     return LV_OK;
 }
 
@@ -544,6 +552,6 @@ extern "C" int lv_attention_fused_static(lv_ctx* ctx, float* out, const float* q
     // the buffer keeps whatever the last call left; only the arrival counters must start at zero
     LV_CUDA(cudaMemsetAsync(counters, 0, size_t(batch) * heads * sizeof(uint32_t), ctx->stream));
     dim3 grid(heads, nchunks, batch);
-    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, rot)) return rc;
+    if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, max_ctx, rot)) return rc;
     return LV_OK;
 }

@@ -3,6 +3,7 @@
 #include <cstring>
 #include <string>
 #include <thread>
+#include <vector>
 
 #include "common.cuh"
 #include "ctx.h"
@@ -10,6 +11,7 @@
 struct lv_graph {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
+    uint32_t kernel_nodes = 0;
 };
 
 namespace lv {
@@ -186,6 +188,16 @@ extern "C" int lv_graph_end_capture(lv_ctx* ctx, lv_graph** out) {
     LV_CUDA(cudaStreamEndCapture(ctx->stream, &graph));
     auto* g = new lv_graph();
     g->graph = graph;
+    size_t n_nodes = 0;
+    if (cudaGraphGetNodes(graph, nullptr, &n_nodes) == cudaSuccess && n_nodes != 0) {
+        std::vector<cudaGraphNode_t> nodes(n_nodes);
+        if (cudaGraphGetNodes(graph, nodes.data(), &n_nodes) == cudaSuccess) {
+            for (size_t i = 0; i < n_nodes; ++i) {
+                cudaGraphNodeType t;
+                if (cudaGraphNodeGetType(nodes[i], &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) g->kernel_nodes++;
+            }
+        }
+    }
     cudaError_t e = cudaGraphInstantiate(&g->exec, graph, 0);
     if (e != cudaSuccess) {
         cudaGraphDestroy(graph);
@@ -200,6 +212,12 @@ extern "C" int lv_graph_launch(lv_ctx* ctx, lv_graph* g) {
     LV_ENTER(ctx);
     LV_REQUIRE(g && g->exec, "null graph");
     LV_CUDA(cudaGraphLaunch(g->exec, ctx->stream));
+    return LV_OK;
+}
+
+extern "C" int lv_graph_kernel_nodes(lv_graph* g, uint32_t* out) {
+    LV_REQUIRE(g && out, "null argument");
+    *out = g->kernel_nodes;
     return LV_OK;
 }
 

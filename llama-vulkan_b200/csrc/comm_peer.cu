@@ -2,11 +2,14 @@
 // tensor-parallel decoder: residual += sum over ranks of partial.
 //
 // Every rank owns a receive window (cudaMalloc'd, exported with CUDA IPC) of
-// 2 x n_ranks slots of `capacity` floats plus arrival flags.  A launch pushes the rank's
+// 4 x n_ranks slots of `capacity` floats plus arrival flags.  Slot sets 0 and 1 belong to the
+// exchanges fused into the GEMVs, sets 2 and 3 to the stand-alone kernel below: a step may mix the
+// two mechanisms (the last exchange of a step without an output head uses this kernel), and with
+// sets of its own this kernel can never overwrite a slot that a slower rank's GEMV is still reading.  A launch pushes the rank's
 // partial vector into its slot of every rank's window with ordinary peer stores, publishes a
 // flag per (rank, CTA), waits -- bounded -- for the flags of all ranks in its own window, and
 // adds the slots from its own memory in rank order, so every rank computes bit-identical
-// sums.  Slots and flags alternate between two halves by launch parity, which is enough
+// sums.  Its slots and flags alternate between two halves by launch parity, which is enough
 // because a rank cannot start launch k + 2 before every rank has finished reading launch k.
 // The reference is single-device; this replaces the NCCL all-reduce + add pair of the
 // baseline path (lv_allreduce_f32 + lv_add_f32) with one kernel.
@@ -25,7 +28,7 @@ constexpr int kPeerThreads = 256;
 
 struct PeerWindowLayout {
     uint32_t capacity;        // floats per slot
-    __host__ __device__ size_t slot_floats(int n_ranks) const { return size_t(2) * n_ranks * capacity; }
+    __host__ __device__ size_t slot_floats(int n_ranks) const { return size_t(kTpSlotSets) * n_ranks * capacity; }
     // slots, the flags of the stand-alone kernel (2 x 8 x 4 words), the flags of the exchanges fused into the GEMV
     __host__ __device__ size_t bytes(int n_ranks) const {
         return slot_floats(n_ranks) * sizeof(float) + size_t(kTpLegacyFlagWords) * sizeof(uint32_t) +
@@ -42,7 +45,7 @@ struct PeerParams {
 };
 
 __device__ __forceinline__ uint32_t* window_flags(float* window, int n_ranks, uint32_t capacity) {
-    return reinterpret_cast<uint32_t*>(window + size_t(2) * n_ranks * capacity);
+    return reinterpret_cast<uint32_t*>(window + size_t(kTpSlotSets) * n_ranks * capacity);
 }
 
 // grid = kPeerCtas; CTA c owns the float4 indices c, c + kPeerCtas, ... of the vector
@@ -53,7 +56,7 @@ __global__ void __launch_bounds__(kPeerThreads) allreduce_add_peer_kernel(float*
     const uint32_t epoch = *p.epoch + 1;                 // this launch's number, the same on every rank
     const uint32_t half = epoch & 1u;
     const uint32_t n4 = count / 4;
-    const size_t my_slot = (size_t(half) * p.n_ranks + p.rank) * p.capacity;
+    const size_t my_slot = (size_t(2 + half) * p.n_ranks + p.rank) * p.capacity;      // slot sets 2 and 3
 
     // push this rank's slice into its slot of every window (its own included)
     for (uint32_t i = blockIdx.x * kPeerThreads + threadIdx.x; i < n4; i += kPeerCtas * kPeerThreads) {
@@ -84,7 +87,7 @@ __global__ void __launch_bounds__(kPeerThreads) allreduce_add_peer_kernel(float*
     }
     __syncthreads();
     if (s_ok) {
-        const float* base = p.window[p.rank] + size_t(half) * p.n_ranks * p.capacity;
+        const float* base = p.window[p.rank] + size_t(2 + half) * p.n_ranks * p.capacity;
         for (uint32_t i = blockIdx.x * kPeerThreads + threadIdx.x; i < n4; i += kPeerCtas * kPeerThreads) {
             float4 acc = reinterpret_cast<float4*>(residual)[i];
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -64,6 +64,8 @@ struct GemvMatrix {
 // publishes one flag per CTA.  A consumer launch (pull_exchange >= 0) waits for the flags of
 // all ranks in its own window and builds its input as x + sum over ranks of the slots.
 constexpr int kTpMaxRanks = 8;
+constexpr int kTpSlotSets = 4;         // slot sets of a window: 0 and 1 alternate for the exchanges fused into the GEMVs,
+                                       // 2 and 3 for the stand-alone all-reduce kernel, so the two never share a slot
 constexpr int kTpFlagCtas = 256;       // flags per (exchange parity, source rank)
 constexpr int kTpLegacyFlagWords = 64; // flag words of the stand-alone all-reduce kernel that precede these
 constexpr int kTpTwoPhaseRanks = 64;   // ranks from which a consumer launch would sum the slots once per GPU instead of once per CTA:
@@ -87,13 +89,13 @@ __device__ __forceinline__ float* tp_slot(const TpParams& t, int r_window, int e
 }
 
 __device__ __forceinline__ uint32_t* tp_flag(const TpParams& t, int r_window, int exchange, int src, uint32_t cta) {
-    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[r_window] + size_t(2) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
+    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[r_window] + size_t(kTpSlotSets) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
     return flags + (size_t(exchange & 1) * kTpMaxRanks + src) * kTpFlagCtas + cta;
 }
 
 // Flag of CTA `cta` of a consumer launch on this GPU: its slice of the summed input is in x_out.
 __device__ __forceinline__ uint32_t* tp_local_flag(const TpParams& t, uint32_t cta) {
-    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[t.rank] + size_t(2) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
+    uint32_t* flags = reinterpret_cast<uint32_t*>(t.window[t.rank] + size_t(kTpSlotSets) * t.n_ranks * t.capacity) + kTpLegacyFlagWords;
     return flags + size_t(2) * kTpMaxRanks * kTpFlagCtas + cta;
 }
 

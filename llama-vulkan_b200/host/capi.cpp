@@ -216,6 +216,7 @@ int llava_session_get_logits(void* s, float* out, uint32_t cap) {
 
 uint32_t llava_session_get_backlog_size(void* s) { return S(s)->get_backlog_size(); }
 uint32_t llava_session_get_tokens_in_gpu(void* s) { return S(s)->get_tokens_in_gpu(); }
+uint32_t llava_session_step_kernel_launches(void* s) { return S(s)->step_kernel_launches(); }
 
 int llava_session_read_kv(void* s, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out) {
     const auto& data = S(s)->get_layer_data();

@@ -44,6 +44,11 @@ bool llava_command_buffer::wait_idle() const {
     return lv_stream_sync(lv(), 1000 * 1000) == LV_OK;
 }
 
+u32 llava_command_buffer::kernel_launches() const {
+    uint32_t n = 0;
+    return (graph && lv_graph_kernel_nodes(graph, &n) == LV_OK) ? n : 0;
+}
+
 bool llava_command_buffer::run() {
     if (!graph) return false;
     return lv_graph_launch(lv(), graph) == LV_OK;

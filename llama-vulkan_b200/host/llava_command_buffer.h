@@ -21,6 +21,7 @@ public:
     bool record_execution();
     bool run();
     bool wait_idle() const;
+    u32 kernel_launches() const;       // kernel nodes of the recorded graph
 
     // the reference's op set (llava_command_buffer.h:30-38)
     void normalize_logit(llava_buffer* outbuf, llava_buffer* inbuf, llava_buffer* weights);

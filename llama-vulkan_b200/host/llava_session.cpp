@@ -176,6 +176,10 @@ u32 llava_session::predict_next_token() {
     return finish_next_token_prediction();
 }
 
+u32 llava_session::step_kernel_launches() const {
+    return last_command_buffer ? last_command_buffer->kernel_launches() : 0;
+}
+
 bool llava_session::get_logits(vector<float>* out) {
     if (output_probs == nullptr) return false;
     out->resize(model->get_header().vocab_size);

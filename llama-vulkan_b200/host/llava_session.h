@@ -64,6 +64,7 @@ public:
     bool get_logits(std::vector<float>* out);
     u32 get_backlog_size() const { return backlog_size; }
     u32 get_tokens_in_gpu() const { return current_tokens_in_gpu; }
+    u32 step_kernel_launches() const;          // kernel launches of one replay of the step evaluated last
 
     static constexpr u32 max_batch_limit = 64;
 

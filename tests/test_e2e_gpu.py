@@ -17,6 +17,10 @@ pytestmark = pytest.mark.gpu
 
 N_PROMPT, N_DECODE = 16, 32
 LOGIT_MAX_ABS, LOGIT_REL_L2 = 1e-2, 1e-3
+# A cache value whose fp32 source differs from the oracle's in its last bits may round to the neighbouring half.
+# Observed on B200: at most 9 % of the halves of a cache (layer 1 of the 13B geometry, 47 rows) -- a relative
+# difference of ~4e-5 against a half spacing of 4.9e-4; the bound leaves a margin of a few points.
+CACHE_DIFFERING_HALVES = 0.13
 
 
 def prompt_tokens(n=N_PROMPT, seed=4321):
@@ -115,12 +119,15 @@ def test_greedy_tokens_identical_and_logits_within_tolerance(run):
     # the caches hold un-rotated f16 K and V rows; a value that differs in its last fp32 bits may
     # round to the neighbouring half, so compare as numbers
     n = N_PROMPT + N_DECODE - 1
+    differing = []
     for layer in range(2):
         for which in (0, 1):
             got = s.read_kv(layer, which, 0, n, run["dim"]).view(np.float16).astype(np.float32)
             want = run["orc"].cache(which, layer, n).view(np.float16).astype(np.float32)
-            assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
-            assert np.mean(got != want) < 0.2          # neighbouring halves only, and only a minority of them
+            assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()         # neighbouring halves only ...
+            differing.append(float(np.mean(got != want)))
+    note_parity(f"config0 wtype={run['wtype']}: fraction of cache halves that differ from the oracle's, per cache: {differing}")
+    assert max(differing) < CACHE_DIFFERING_HALVES                               # ... and only a small minority of them
     s.close()
 
 

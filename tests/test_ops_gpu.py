@@ -100,6 +100,50 @@ def test_gemv_and_residual_add(gpu, pkg, wtype, rows, cols):
         gpu.free(d)
 
 
+def _outlier_activations(rng, cols):
+    """Activations as a trained LLaMA's residual stream has them: a few channels two to three orders of
+    magnitude above the rest -- alone in a 32-block, several in one block, in many blocks -- plus an
+    all-zero block and a block of denormals.  The GEMV stores each block of activations as fixed point
+    relative to the block's largest magnitude, so these are the inputs that stress it most."""
+    x = rng.standard_normal(cols).astype(np.float32)
+    x[5] *= 1000.0                                   # one outlier alone in its block
+    x[64:96:7] *= 300.0                              # several in one block
+    x[3 * 32 + 1] = -850.0
+    x[np.arange(7, cols, 416)] *= 120.0              # spread over many blocks
+    x[10 * 32:11 * 32] = 0.0                         # an all-zero block
+    x[12 * 32:13 * 32] = (rng.standard_normal(32) * 1e-41).astype(np.float32)    # denormals only
+    x[14 * 32:15 * 32] = 0.0
+    x[14 * 32 + 9] = 512.0                           # a block that is one outlier and nothing else
+    return x
+
+
+@pytest.mark.parametrize("wtype,rows,cols", [(qn.Q4_0, 4096, 4096), (qn.Q4_0, 4096, 11008), (qn.Q8_0, 4096, 4096), (qn.Q8_0, 1024, 11008)])
+def test_gemv_with_outlier_activations(gpu, pkg, wtype, rows, cols):
+    rng = np.random.default_rng(77 + rows + cols + wtype)
+    W = qn.quantize((rng.standard_normal((rows, cols)) * 0.02).astype(np.float32), wtype)
+    x = _outlier_activations(rng, cols)
+    dW, dx = gpu.upload(W), gpu.upload(x)
+    d_out = gpu.alloc(rows * 4)
+    pkg.check(gpu.lib.lv_gemv(gpu.handle, d_out, dW, wtype, dx, rows, cols, 1, 0))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, rows), ob.gemv(W, wtype, x, rows, cols, workers_for(cols)))
+    for d in (dW, dx, d_out):
+        gpu.free(d)
+
+
+def test_norm_gate_up_silu_with_outlier_activations(gpu, pkg):
+    rng = np.random.default_rng(78)
+    ff, dim = 11008, 4096
+    w3 = qn.quantize_q4_0((rng.standard_normal((ff, dim)) * 0.02).astype(np.float32))
+    w1 = qn.quantize_q4_0((rng.standard_normal((ff, dim)) * 0.02).astype(np.float32))
+    x = _outlier_activations(rng, dim)
+    nw = (1 + 0.01 * rng.standard_normal(dim)).astype(np.float32)
+    d_out = gpu.alloc(ff * 4)
+    pkg.check(gpu.lib.lv_norm_gate_up_silu(gpu.handle, d_out, gpu.upload(w3), gpu.upload(w1), qn.Q4_0, gpu.upload(x), gpu.upload(nw), ff, dim, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, ff), ob.gemv_silu(w3, w1, qn.Q4_0, ob.norm(x, nw), ff, dim, 128))
+
+
 @pytest.mark.parametrize("wtype,ff,dim", [(qn.Q4_0, 11008, 4096), (qn.Q8_0, 11008, 4096), (qn.Q4_0, 13824, 5120)])
 def test_gemv_silu(gpu, pkg, wtype, ff, dim):
     rng = np.random.default_rng(ff)
@@ -244,6 +288,34 @@ def test_fused_attention(gpu, pkg, rope_table, pos, grid):
         close(gpu.download(d_out, np.float32, DIM), want, rel_l2=5e-6 if max_ctx < 2048 else 1e-5, max_abs_frac=2e-5)
     for d in (dk, dv, dq, d_out, scratch):
         gpu.free(d)
+
+
+def test_fused_attention_refuses_a_position_outside_the_cache(gpu, pkg, rope_table):
+    """A position word at or beyond max_ctx would index past the caches and the rotation table: the kernel
+    reports it through the error word and writes nothing (like lv_kv_append_f16), and the arrival counters
+    stay clear, so the next call with a valid position is unaffected."""
+    rng = np.random.default_rng(32)
+    for batch, max_ctx in ((1, 256), (6, 512)):         # one CTA per SM / the two-CTAs-per-SM variant
+        k, v = _caches(rng, max_ctx, max_ctx)
+        q = rng.standard_normal((batch, DIM)).astype(np.float32)
+        scratch = gpu.zeros(gpu.lib.lv_attention_scratch_bytes(HEADS, ROT, max_ctx, batch))
+        dk, dv, dq = gpu.upload(k), gpu.upload(v), gpu.upload(q)
+        d_out = gpu.alloc(batch * DIM * 4)
+        pkg.check(gpu.lib.lv_memset(gpu.handle, d_out, 0xA5, batch * DIM * 4))
+        pkg.check(gpu.lib.lv_attention_fused(gpu.handle, d_out, dq, dk, dv, u32_dev(gpu, max_ctx), rope_table, scratch, HEADS, ROT, max_ctx, batch))
+        with pytest.raises(pkg.LvError) as e:
+            gpu.sync()
+        assert e.value.code == pkg.LV_ERR_DEVICE_WAIT
+        assert np.all(gpu.download(d_out, np.uint8, batch * DIM * 4) == 0xA5)
+        # the refused call left no trace: the next one, with every row of the batch inside the cache, is correct
+        pos = max_ctx - batch
+        pkg.check(gpu.lib.lv_attention_fused(gpu.handle, d_out, dq, dk, dv, u32_dev(gpu, pos), rope_table, scratch, HEADS, ROT, max_ctx, batch))
+        gpu.sync()
+        got = gpu.download(d_out, np.float32, batch * DIM).reshape(batch, DIM)
+        for z in range(batch):
+            close(got[z], ob.attention(k, v, q[z], pos + z, max_ctx, HEADS, ROT), rel_l2=1e-5, max_abs_frac=2e-5)
+        for d in (dk, dv, dq, d_out, scratch):
+            gpu.free(d)
 
 
 def test_fused_attention_batch_is_causal(gpu, pkg, rope_table):
