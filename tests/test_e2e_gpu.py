@@ -18,9 +18,10 @@ pytestmark = pytest.mark.gpu
 N_PROMPT, N_DECODE = 16, 32
 LOGIT_MAX_ABS, LOGIT_REL_L2 = 1e-2, 1e-3
 # A cache value whose fp32 source differs from the oracle's in its last bits may round to the neighbouring half.
-# Observed on B200: at most 9 % of the halves of a cache (layer 1 of the 13B geometry, 47 rows) -- a relative
-# difference of ~4e-5 against a half spacing of 4.9e-4; the bound leaves a margin of a few points.
-CACHE_DIFFERING_HALVES = 0.13
+# Observed on B200: 0.3 % of the halves of a layer-0 cache and 9-11 % of a layer-1 cache (a layer-0 half that
+# rounds the other way moves the attention scores of every later row by ~3e-4, which reaches layer 1 as a
+# relative difference of a few 1e-5 against a half spacing of 4.9e-4); the bound leaves a margin of a few points.
+CACHE_DIFFERING_HALVES = 0.15
 
 
 def prompt_tokens(n=N_PROMPT, seed=4321):
