@@ -87,6 +87,10 @@ uint32_t llava_session_get_backlog_size(void* session);
 uint32_t llava_session_get_tokens_in_gpu(void* session);
 /* kernel launches of one replay of the step evaluated last (0 before the first step) */
 uint32_t llava_session_step_kernel_launches(void* session);
+/* timeline of the one-launch token step (lv_step_plan_set_trace / lv_step_plan_read_trace in lv_b200.h):
+ * returns the number of words copied, dims3 = {operations, CTAs, points}; 0 when unavailable */
+int      llava_session_set_step_trace(void* session, int on);
+uint64_t llava_session_read_step_trace(void* session, uint64_t* out, uint64_t cap, uint32_t* dims3);
 /* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
 int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
 

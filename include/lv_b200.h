@@ -258,6 +258,61 @@ int lv_norm_gate_up_silu(lv_ctx* ctx, float* out, const void* w3, const void* w1
 int lv_norm_gemv(lv_ctx* ctx, float* out, const void* W, int wtype, const float* x, const float* norm_w,
                  uint32_t rows, uint32_t cols, uint32_t batch);
 
+/* ---- one token in one launch ----------------------------------------------------------------
+ *
+ * The reference records, per evaluation step, the operations of every layer plus the final
+ * normalisation and output matrix into a list of command buffers and submits the list
+ * (llava_command_buffer::record_execution, llava_command_buffer.cpp:29-45, over
+ * llava_layer::execute, llava_layer.cpp:39-75).  lv_decode_step runs that whole list for ONE token
+ * as a single persistent kernel: embedding row (llava_session.cpp:219-223), every layer's
+ * normalize / matmul wk, wq, wv / copy_to_cache / mhsa / softmax / kqv_matching / matmul_add wo /
+ * normalize / matmul_silu_ff / matmul_add w2, final normalize and output matmul, then -- with_head --
+ * the greedy choice and the position bookkeeping of lv_argmax_advance (without the head only the
+ * position advances, as for the leading tokens of a prompt).  Arithmetic and results are those of
+ * the per-operation entry points above.
+ *
+ * A plan binds a model's weights and one session's caches and owns a small workspace; it must be
+ * created outside stream capture.  All quantised matrices (layers and output) must lie in ONE
+ * device allocation [weights_base, weights_base + weights_bytes), each at a multiple of its row
+ * size (cols / 32 * 18 or 34 bytes) from weights_base and 16-byte aligned -- they are then row
+ * ranges of one 2-D view of the arena per row size, which one TMA tensor map addresses.  Matrices
+ * that are not placed like this are still accepted (q4_0 falls back to 1-D bulk copies).
+ * ctx_rows: rows of the f16 caches.  tok_embeddings: [vocab][dim] of emb_type (q4_0, q8_0 or f32). */
+typedef struct lv_step_layer {
+    const void *wq, *wk, *wv, *wo, *w1, *w2, *w3;     /* quantised [rows][cols] in GGML block layout */
+    const float *attention_norm, *ffn_norm;         /* f32 [dim] */
+    void *k_cache, *v_cache;                        /* f16 [ctx_rows][dim] */
+} lv_step_layer;
+
+typedef struct lv_step_model {
+    uint32_t dim, ff, heads, n_layers, vocab, ctx_rows;
+    int wtype, emb_type;
+    const void* weights_base;
+    size_t weights_bytes;
+    const void* tok_embeddings;
+    const float* norm;
+    const void* output;
+    const float* rope_table;                        /* from lv_rope_table_build, at least ctx_rows rows */
+    const lv_step_layer* layers;                    /* host array of n_layers entries */
+} lv_step_model;
+
+typedef struct lv_step_plan lv_step_plan;
+int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* model, lv_step_plan** out);
+int lv_step_plan_destroy(lv_step_plan* plan);
+/* Timeline of the steps launched after the call (on != 0), for tuning: every CTA stamps the device's
+ * nanosecond clock at five points of every weight operation (begin, attention done, input records ready,
+ * work items done, rows handed over).  Steps recorded into a graph before the call are not traced.
+ * lv_step_plan_read_trace copies [operation][CTA][point] of the last traced step (4 * n_layers + 1
+ * operations: per layer QKV, wo, gate/up, w2; then the output head). */
+int lv_step_plan_set_trace(lv_step_plan* plan, int on);
+int lv_step_plan_read_trace(lv_step_plan* plan, uint64_t* out, size_t max_words, uint32_t* n_ops, uint32_t* n_ctas,
+                            uint32_t* n_points);
+/* config, token_log, logits, argmax_out: device memory as for lv_argmax_advance (config[0] = tokens
+ * already in the caches = position of the token to evaluate, read from token_log[config[0]]);
+ * host_token: pinned host word or null.  logits (f32 [vocab]) may be null without the head. */
+int lv_decode_step(lv_ctx* ctx, const lv_step_plan* plan, uint32_t* config, uint32_t* token_log, uint32_t log_capacity,
+                   float* logits, uint32_t* argmax_out, uint32_t* host_token, int with_head);
+
 /* ---- multi-GPU: one process per GPU, one communicator per context.  The
  *      reference is single-device (llava_context.cpp:264-279 takes one queue of
  *      one device); these entry points add the exchange step of the

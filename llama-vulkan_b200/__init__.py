@@ -92,6 +92,11 @@ KERNEL_API = {
     "lv_gemm_tc_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_norm_gate_up_silu": (_int, [_p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_norm_gemv": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
+    "lv_step_plan_create": (_int, [_p, _p, C.POINTER(_p)]),
+    "lv_step_plan_destroy": (_int, [_p]),
+    "lv_step_plan_set_trace": (_int, [_p, _int]),
+    "lv_step_plan_read_trace": (_int, [_p, _p, _sz, _p, _p, _p]),
+    "lv_decode_step": (_int, [_p, _p, _p, _p, _u32, _p, _p, _p, _int]),
 }
 
 _kernels = None
@@ -250,6 +255,8 @@ HOST_API = {
     "llava_session_get_backlog_size": (_u32, [_p]),
     "llava_session_get_tokens_in_gpu": (_u32, [_p]),
     "llava_session_step_kernel_launches": (_u32, [_p]),
+    "llava_session_set_step_trace": (_int, [_p, _int]),
+    "llava_session_read_step_trace": (_u64, [_p, _p, _u64, _p]),
     "llava_session_read_kv": (_int, [_p, _u32, _int, _u32, _u32, _p]),
     "llava_wrapper_owner_create": (_p, [_p]),
     "llava_wrapper_owner_destroy": (None, [_p]),
@@ -476,6 +483,17 @@ class Session:
     def step_kernel_launches(self):
         """Kernel launches of one replay of the step evaluated last."""
         return self.lib.llava_session_step_kernel_launches(self.handle)
+
+    def set_step_trace(self, on=True):
+        return bool(self.lib.llava_session_set_step_trace(self.handle, int(on)))
+
+    def read_step_trace(self):
+        """[operation][CTA][point] nanosecond stamps of the last traced one-launch step, or None."""
+        import numpy as np
+        buf = np.zeros(1 << 21, np.uint64)
+        dims = (_u32 * 3)()
+        n = self.lib.llava_session_read_step_trace(self.handle, buf.ctypes.data_as(_p), buf.size, dims)
+        return buf[:n].reshape(dims[0], dims[1], dims[2]).copy() if n else None
 
     def read_kv(self, layer, which, row0, nrows, dim):
         import numpy as np

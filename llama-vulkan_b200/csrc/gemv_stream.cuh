@@ -279,6 +279,52 @@ __device__ __forceinline__ void digit_words(int X0, int X1, int X2, int X3, uint
 // `scratch` holds 64 floats: the per-warp partial sums.
 constexpr int kActIters = 7;     // float4s per thread held at once (7 * 2048 >= 13824 with 16 warps)
 
+// Contribution of four consecutive elements to the sums from which norm_factor() forms the variance:
+// s1 += sum d, s2 += sum d^2 with d = x - x0 (any x0 gives the same variance; one near the data avoids
+// the cancellation of sum x^2 - n * mean^2).
+__device__ __forceinline__ void norm_accumulate(const float4& v, float x0, float& s1, float& s2) {
+    const float a = v.x - x0, b = v.y - x0, c = v.z - x0, d = v.w - x0;
+    s1 += (a + b) + (c + d);
+    s2 += (a * a + b * b) + (c * c + d * d);
+}
+
+// Per-warp sums go to scratch ([0..31] sum d, [32..63] sum d^2); norm_factor() adds them up after a CTA barrier.
+__device__ __forceinline__ void norm_publish(float s1, float s2, float* scratch) {
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if ((threadIdx.x & 31) == 0) { scratch[threadIdx.x >> 5] = s1; scratch[32 + (threadIdx.x >> 5)] = s2; }
+}
+
+// Writes this thread's part of the activation record of the block that holds elements e .. e+3 (e a multiple
+// of 4; the eight lanes that own a block call this together).
+__device__ __forceinline__ void emit_block_record(uint8_t* __restrict__ xrec, const float4& v, uint32_t e, int lane) {
+    float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    // an approximate quotient is enough: the record keeps whatever integers come out, and
+    // their scale is off by an fp32 rounding or two at most
+    const float inv = m > 1e-30f ? __fdividef(kFixedOne, m) : 0.f;     // smaller blocks count as zero
+    const int X0 = __float2int_rn(v.x * inv), X1 = __float2int_rn(v.y * inv);   // |X| <= 31 * 2^16 (+ slack)
+    const int X2 = __float2int_rn(v.z * inv), X3 = __float2int_rn(v.w * inv);
+    uint32_t wa, wb, wc;
+    digit_words(X0, X1, X2, X3, wa, wb, wc);
+    int T = (X0 + X1) + (X2 + X3);
+    T += __shfl_xor_sync(0xffffffffu, T, 1);
+    T += __shfl_xor_sync(0xffffffffu, T, 2);
+    T += __shfl_xor_sync(0xffffffffu, T, 4);
+    const uint32_t blk = e >> 5;
+    uint8_t* rec = xrec + size_t(blk >> 1) * kPairBytes;
+    const uint32_t at = (blk & 1) * 32 + (lane & 7) * 4;
+    *reinterpret_cast<uint32_t*>(rec + at) = wa;
+    *reinterpret_cast<uint32_t*>(rec + 64 + at) = wb;
+    *reinterpret_cast<uint32_t*>(rec + 128 + at) = wc;
+    if ((lane & 7) == 0) {
+        reinterpret_cast<int*>(rec + 192)[blk & 1] = 8 * T;
+        reinterpret_cast<float*>(rec + 200)[blk & 1] = m * (1.0f / kFixedOne);
+    }
+}
+
 __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, const float* __restrict__ x,
                                                   const float* __restrict__ norm_w, uint32_t K, float* scratch,
                                                   const TpParams& tp, bool sum_slots) {
@@ -328,16 +374,9 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
             float s1 = 0.f, s2 = 0.f;
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
-                if (chunk + uint32_t(i) * stride + threadIdx.x * 4 < K) {
-                    const float a = v[i].x - x0, b = v[i].y - x0, c = v[i].z - x0, d = v[i].w - x0;
-                    s1 += (a + b) + (c + d);
-                    s2 += (a * a + b * b) + (c * c + d * d);
-                }
+                if (chunk + uint32_t(i) * stride + threadIdx.x * 4 < K) norm_accumulate(v[i], x0, s1, s2);
             }
-            // per-warp sums go to scratch; norm_factor() adds them up after the caller's barrier
-            s1 = warp_sum(s1);
-            s2 = warp_sum(s2);
-            if (lane == 0) { scratch[threadIdx.x >> 5] = s1; scratch[32 + (threadIdx.x >> 5)] = s2; }
+            norm_publish(s1, s2, scratch);
 #pragma unroll
             for (int i = 0; i < kActIters; ++i) {
                 v[i].x *= w[i].x; v[i].y *= w[i].y; v[i].z *= w[i].z; v[i].w *= w[i].w;
@@ -347,31 +386,7 @@ __device__ __forceinline__ void stage_activations(uint8_t* __restrict__ xrec, co
         for (int i = 0; i < kActIters; ++i) {
             const uint32_t e = chunk + uint32_t(i) * stride + threadIdx.x * 4;
             if (e >= K) break;              // K is a multiple of 32: the eight lanes of a block leave together
-            float m = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-            // an approximate quotient is enough: the record keeps whatever integers come out, and
-            // their scale is off by an fp32 rounding or two at most
-            const float inv = m > 1e-30f ? __fdividef(kFixedOne, m) : 0.f;     // smaller blocks count as zero
-            const int X0 = __float2int_rn(v[i].x * inv), X1 = __float2int_rn(v[i].y * inv);   // |X| <= 31 * 2^16 (+ slack)
-            const int X2 = __float2int_rn(v[i].z * inv), X3 = __float2int_rn(v[i].w * inv);
-            uint32_t wa, wb, wc;
-            digit_words(X0, X1, X2, X3, wa, wb, wc);
-            int T = (X0 + X1) + (X2 + X3);
-            T += __shfl_xor_sync(0xffffffffu, T, 1);
-            T += __shfl_xor_sync(0xffffffffu, T, 2);
-            T += __shfl_xor_sync(0xffffffffu, T, 4);
-            const uint32_t blk = e >> 5;
-            uint8_t* rec = xrec + size_t(blk >> 1) * kPairBytes;
-            const uint32_t at = (blk & 1) * 32 + (lane & 7) * 4;
-            *reinterpret_cast<uint32_t*>(rec + at) = wa;
-            *reinterpret_cast<uint32_t*>(rec + 64 + at) = wb;
-            *reinterpret_cast<uint32_t*>(rec + 128 + at) = wc;
-            if ((lane & 7) == 0) {
-                reinterpret_cast<int*>(rec + 192)[blk & 1] = 8 * T;
-                reinterpret_cast<float*>(rec + 200)[blk & 1] = m * (1.0f / kFixedOne);
-            }
+            emit_block_record(xrec, v[i], e, lane);
         }
     }
 }

@@ -217,6 +217,15 @@ int llava_session_get_logits(void* s, float* out, uint32_t cap) {
 uint32_t llava_session_get_backlog_size(void* s) { return S(s)->get_backlog_size(); }
 uint32_t llava_session_get_tokens_in_gpu(void* s) { return S(s)->get_tokens_in_gpu(); }
 uint32_t llava_session_step_kernel_launches(void* s) { return S(s)->step_kernel_launches(); }
+int llava_session_set_step_trace(void* s, int on) { return S(s)->set_step_trace(on != 0); }
+uint64_t llava_session_read_step_trace(void* s, uint64_t* out, uint64_t cap, uint32_t* dims3) {
+    std::vector<u64> v;
+    if (!S(s)->read_step_trace(&v, &dims3[0], &dims3[1], &dims3[2])) return 0;
+    const uint64_t n = uint64_t(dims3[0]) * dims3[1] * dims3[2];
+    if (n > cap) return 0;
+    memcpy(out, v.data(), n * 8);
+    return n;
+}
 
 int llava_session_read_kv(void* s, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out) {
     const auto& data = S(s)->get_layer_data();

@@ -12,6 +12,18 @@ using namespace std;
 
 namespace {
 constexpr size_t kBufferAlignment = 256;      // keeps every tensor 16-byte aligned for bulk copies
+
+size_t gcd_sz(size_t a, size_t b) { return b == 0 ? a : gcd_sz(b, a % b); }
+
+// A quantised matrix starts at a multiple of its row size (and of 256 bytes) from the arena's base.  Every
+// matrix of one row size in an arena is then a row range of ONE 2-D view [arena bytes / row size][row size]
+// of the arena, so a single TMA tensor map per row size addresses them all (lv_step_plan_create).
+size_t matrix_alignment(ggml_value_type type, u32 cols) {
+    const size_t block = type == ggml_value_type::q4_0 ? 18 : type == ggml_value_type::q8_0 ? 34 : 0;
+    if (block == 0 || cols % 32 != 0) return kBufferAlignment;
+    const size_t row = size_t(cols / 32) * block;
+    return row / gcd_sz(row, kBufferAlignment) * kBufferAlignment;
+}
 }
 
 llava_buffer::llava_buffer(llava_context* _context, ggml_value_type _type, u32 shape1, u32 shape2,
@@ -33,7 +45,7 @@ llava_buffer::llava_buffer(llava_context* _context, const ggml_data_descriptor& 
       model_version(table.model_version), file_shape(table.shape1, table.shape2), used_cols(table.shape2) {
     device_memory->register_llava_buffer(this);
     bytes = table.size;
-    offset = device_memory->register_buffer(kBufferAlignment, bytes);
+    offset = device_memory->register_buffer(model_version == 3 ? matrix_alignment(type, shape.second) : kBufferAlignment, bytes);
     if (!device_memory_is_shared) device_memory->freeze();
 }
 
@@ -52,7 +64,7 @@ llava_buffer::llava_buffer(llava_context* _context, const ggml_data_descriptor& 
     const tp_shard_shape s = tp_shape(table.ftype, table.shape1, table.shape2, how, rank, n_ranks);
     bytes = s.bytes;
     used_cols = s.cols_used;
-    offset = device_memory->register_buffer(kBufferAlignment, bytes ? bytes : 16);
+    offset = device_memory->register_buffer(model_version == 3 ? matrix_alignment(type, shape.second) : kBufferAlignment, bytes ? bytes : 16);
     if (!device_memory_is_shared) device_memory->freeze();
 }
 

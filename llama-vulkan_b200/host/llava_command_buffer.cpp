@@ -66,6 +66,19 @@ bool llava_command_buffer::record_execution() {
     }
     u32* config = static_cast<u32*>(s->config_buffer->device_ptr());
     u32* log = static_cast<u32*>(s->token_log->device_ptr());
+    if (batch_size == 1 && s->step_plan != nullptr && !s->is_tracing_enabled()) {
+        // a single token: the whole list below as one persistent kernel
+        note(lv_decode_step(lv(), s->step_plan, config, log, max_backlog_size + 1, static_cast<float*>(s->output_probs->device_ptr()),
+                            static_cast<u32*>(s->argmax_result->device_ptr()), s->pinned + max_backlog_size + 4, with_head ? 1 : 0));
+        lv_graph* g1 = nullptr;
+        note(lv_graph_end_capture(lv(), &g1));
+        if (first_error != LV_OK) {
+            lv_graph_destroy(g1);
+            return false;
+        }
+        graph = g1;
+        return true;
+    }
     // embedding rows of the tokens at positions config.token_count .. + batch (the reference
     // dequantises them on the host, llava_session.cpp:219-223)
     note(lv_dequant_rows(lv(), static_cast<float*>(s->current_thought->device_ptr()), c->tok_embeddings->device_ptr(),

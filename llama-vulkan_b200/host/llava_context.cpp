@@ -109,7 +109,6 @@ bool llava_context::open(const string& model_path, int device) {
         cerr << "[!] unsupported tensor types for tok_embeddings / norm / output" << endl;
         return false;
     }
-    if (!shared_memory->freeze() || !tok_embeddings->load_to_gpu() || !norm_w->load_to_gpu() || !output_w->load_to_gpu()) return false;
 
     void* table = nullptr;
     if (lv_arena_create(lv_context, size_t(max_backlog_size) * h.rot * sizeof(float), &table) != LV_OK) return false;
@@ -121,6 +120,9 @@ bool llava_context::open(const string& model_path, int device) {
         layers.push_back(new llava_layer(this, i));
         if (!layers.back()->is_valid()) return false;
     }
+    // every tensor has registered its size: one allocation for the whole model
+    if (!shared_memory->freeze()) return false;
+    if (!tok_embeddings->load_to_gpu() || !norm_w->load_to_gpu() || !output_w->load_to_gpu()) return false;
     for (llava_layer* l : layers) {
         if (sigfd >= 0 && pop_signal()) return false;
         if (!l->freeze_storage() || !l->load_to_gpu()) {

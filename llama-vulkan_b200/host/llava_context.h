@@ -39,6 +39,8 @@ public:
     u32 tp_size() const { return n_ranks_; }
 
     lv_ctx* lv() const { return lv_context; }
+    // the one device arena that holds every weight tensor of the model
+    llava_device_memory* weights_memory() const { return shared_memory; }
     const ggml_file* get_model() const { return model; }
     std::vector<llava_layer*>& get_layers() { return layers; }
     bool upload_from_host(void* device_dst, const void* host_src, size_t bytes);

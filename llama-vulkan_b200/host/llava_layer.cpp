@@ -12,7 +12,9 @@
 using namespace std;
 
 llava_layer::llava_layer(llava_context* _context, u32 _layer_id) : layer_id(_layer_id), context(_context) {
-    layer_allocation = new llava_device_memory(context);
+    // every layer's tensors go into the context's one weight arena (the reference gives each layer a
+    // device memory of its own, llava_layer.cpp:10-12); see llava_buffer.cpp for why
+    layer_allocation = context->weights_memory();
     const ggml_file* model = context->get_model();
     const string prefix = "layers." + to_string(layer_id) + ".";
     bool ok = true;
@@ -56,10 +58,9 @@ llava_layer::~llava_layer() {
     for (llava_buffer* b : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2,
                             feed_forward_w3, attention_norm, ffn_norm})
         delete b;
-    delete layer_allocation;
 }
 
-bool llava_layer::freeze_storage() { return valid && layer_allocation->freeze(); }
+bool llava_layer::freeze_storage() { return valid && layer_allocation->is_frozen(); }     // the context froze the shared arena
 
 bool llava_layer::load_to_gpu() {
     if (!valid) return false;

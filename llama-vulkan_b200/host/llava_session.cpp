@@ -5,6 +5,7 @@
 #include <unistd.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <ctime>
 #include <iostream>
@@ -13,6 +14,7 @@
 #include "llava_command_buffer.h"
 #include "llava_context.h"
 #include "llava_device_memory.h"
+#include "llava_layer.h"
 #include "llava_layer_session_data.h"
 #include "utils.h"
 
@@ -39,6 +41,7 @@ llava_session::llava_session(llava_context* _ctx)
 llava_session::~llava_session() {
     lv_stream_sync(ctx->lv(), 0);
     drop_command_buffers();
+    lv_step_plan_destroy(step_plan);
     for (auto* x : layer_data) delete x;
     reset_main_buffers();
     if (pinned) lv_host_free(ctx->lv(), pinned);
@@ -56,8 +59,49 @@ bool llava_session::ensure_buffers_created() {
         layer_data.reserve(ctx->get_layers().size());
         for (u32 i = 0; i < ctx->get_layers().size(); ++i) layer_data.push_back(new llava_layer_session_data(this));
     }
+    ensure_step_plan();
     if (main_buffer_memory == nullptr) return recreate_buffers();
     return true;
+}
+
+// Binds the context's weights and this session's caches for lv_decode_step.  Failing to create a plan is not
+// an error: the session then records one kernel per operation.
+void llava_session::ensure_step_plan() {
+    if (step_plan_tried) return;
+    step_plan_tried = true;
+    const char* env = getenv("LV_DECODE_STEP");
+    if (env != nullptr && env[0] == '0') return;
+    if (ctx->tp_size() != 1) return;
+    const ggml_header& h = model->get_header();
+    const auto& layers = ctx->get_layers();
+    std::vector<lv_step_layer> tab(layers.size());
+    for (size_t i = 0; i < layers.size(); ++i) {
+        const llava_layer* l = layers[i];
+        lv_step_layer& t = tab[i];
+        t.wq = l->wq()->device_ptr(); t.wk = l->wk()->device_ptr(); t.wv = l->wv()->device_ptr(); t.wo = l->wo()->device_ptr();
+        t.w1 = l->w1()->device_ptr(); t.w2 = l->w2()->device_ptr(); t.w3 = l->w3()->device_ptr();
+        t.attention_norm = static_cast<const float*>(l->attn_norm()->device_ptr());
+        t.ffn_norm = static_cast<const float*>(l->ff_norm()->device_ptr());
+        t.k_cache = layer_data[i]->get_k_cache()->device_ptr();
+        t.v_cache = layer_data[i]->get_v_cache()->device_ptr();
+        if (l->wq()->type != ctx->output_w->type) return;              // one matrix type per model
+    }
+    lv_step_model m{};
+    m.dim = h.dim; m.ff = model->get_ff_size(); m.heads = h.n_heads; m.n_layers = u32(layers.size()); m.vocab = h.vocab_size;
+    m.ctx_rows = max_backlog_size;
+    m.wtype = int(ctx->output_w->type);
+    m.emb_type = int(ctx->tok_embeddings->type);
+    m.weights_base = ctx->weights_memory()->device_base();
+    m.weights_bytes = ctx->weights_memory()->get_size();
+    m.tok_embeddings = ctx->tok_embeddings->device_ptr();
+    m.norm = static_cast<const float*>(ctx->norm_w->device_ptr());
+    m.output = ctx->output_w->device_ptr();
+    m.rope_table = ctx->rope_table;
+    m.layers = tab.data();
+    if (lv_step_plan_create(ctx->lv(), &m, &step_plan) != LV_OK) {
+        cerr << "[?] no one-launch step for this model (one kernel per operation instead): " << lv_last_error_string() << endl;
+        step_plan = nullptr;
+    }
 }
 
 bool llava_session::recreate_buffers() {
@@ -174,6 +218,19 @@ u32 llava_session::finish_next_token_prediction() {
 u32 llava_session::predict_next_token() {
     if (!start_next_token_prediction()) return ~0U;
     return finish_next_token_prediction();
+}
+
+bool llava_session::set_step_trace(bool on) {
+    if (!ensure_buffers_created() || step_plan == nullptr) return false;
+    lv_stream_sync(ctx->lv(), 0);
+    drop_command_buffers();                       // the trace buffer is an argument of the recorded launch
+    return lv_step_plan_set_trace(step_plan, on ? 1 : 0) == LV_OK;
+}
+
+bool llava_session::read_step_trace(vector<u64>* out, u32* n_ops, u32* n_ctas, u32* n_points) {
+    if (step_plan == nullptr) return false;
+    out->resize(size_t(4 * ctx->get_layers().size() + 1) * 1024 * 8);
+    return lv_step_plan_read_trace(step_plan, out->data(), out->size(), n_ops, n_ctas, n_points) == LV_OK;
 }
 
 u32 llava_session::step_kernel_launches() const {

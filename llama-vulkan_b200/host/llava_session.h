@@ -10,6 +10,7 @@
 #include <string>
 #include <vector>
 
+#include "../../include/lv_b200.h"
 #include "ggml_file.h"
 #include "types.h"
 
@@ -64,6 +65,9 @@ public:
     bool get_logits(std::vector<float>* out);
     u32 get_backlog_size() const { return backlog_size; }
     u32 get_tokens_in_gpu() const { return current_tokens_in_gpu; }
+    // timeline of the one-launch token step (lv_step_plan_set_trace); false when the session has no such step
+    bool set_step_trace(bool on);
+    bool read_step_trace(std::vector<u64>* out, u32* n_ops, u32* n_ctas, u32* n_points);
     u32 step_kernel_launches() const;          // kernel launches of one replay of the step evaluated last
 
     static constexpr u32 max_batch_limit = 64;
@@ -127,6 +131,12 @@ private:
     u32* pinned = nullptr;        // [max_backlog] token staging + [8] config/argmax words
     bool upload_pending_tokens(u32 first, u32 count);
     bool sync_device_position(u32 pos);
+
+    // one-launch token step (lv_decode_step): weights of the context + caches of this session; null when
+    // the session cannot use it (sharded contexts) or LV_DECODE_STEP=0 asks for one kernel per operation
+    lv_step_plan* step_plan = nullptr;
+    bool step_plan_tried = false;
+    void ensure_step_plan();
 
     u32 enqueued_greedy = 0;      // steps queued by enqueue_greedy_on_device and not yet collected
     u32 options = 0;              // non-zero: tracing
