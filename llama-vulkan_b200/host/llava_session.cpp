@@ -70,7 +70,7 @@ void llava_session::ensure_step_plan() {
     if (step_plan_tried) return;
     step_plan_tried = true;
     const char* env = getenv("LV_DECODE_STEP");
-    if (env != nullptr && env[0] == '0') return;
+    if (env == nullptr || env[0] != '1') return;          // opt-in while it is slower than one kernel per operation
     if (ctx->tp_size() != 1) return;
     const ggml_header& h = model->get_header();
     const auto& layers = ctx->get_layers();
