@@ -104,6 +104,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tensor_m
         : "memory");
 }
 
+// 3-D tiled TMA load (coordinates x = inner element index, y, z).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tensor_map, int x, int y, int z, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(smem_u32(smem_dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));

@@ -161,6 +161,9 @@ __device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity) {
         if (clock64() - t0 > 20000000ll) break;
 }
 
+// emit_block_record out of line: the step kernel calls it from a dozen places and its code size matters more than a call
+__device__ __noinline__ void emit_record(uint8_t* __restrict__ xrec, float4 v, uint32_t e, int lane) { emit_block_record(xrec, v, e, lane); }
+
 // ---- geometry of one weight operation for this CTA -------------------------------------------------
 
 struct OpGeo {
@@ -533,19 +536,19 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                 for (int j = 0; j < kStepValuePrefetch; ++j) {
                     const uint32_t i = rg + kRowGroups * j;
                     if (i < n_old) {
-                        const float e = expf(s_e[i] - m);
+                        const float e = __expf(s_e[i] - m);
                         lsum += e;
                         add_row(vpre[j], e);
                     }
                 }
                 for (uint32_t i = rg + kRowGroups * kStepValuePrefetch; i < n_old; i += kRowGroups) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * p.dim + d8);
-                    const float e = expf(s_e[i] - m);
+                    const float e = __expf(s_e[i] - m);
                     lsum += e;
                     add_row(raw, e);
                 }
                 if (has_new && rg == int((n - 1) % kRowGroups)) {                       // the row of this token, from shared memory
-                    const float e = expf(s_e[n - 1] - m);
+                    const float e = __expf(s_e[n - 1] - m);
                     lsum += e;
 #pragma unroll
                     for (int k = 0; k < 8; ++k) acc[k] = fmaf(s_v[d8 + k], e, acc[k]);
@@ -643,7 +646,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
             for (int i = 0; i < kNormIters; ++i) {
                 const uint32_t e = uint32_t(i) * (kThreads * 4) + threadIdx.x * 4;
                 if (e >= K) break;              // whole warps leave together: dim is a multiple of 128
-                emit_block_record(xrec, make_float4(v[i].x * w[i].x, v[i].y * w[i].y, v[i].z * w[i].z, v[i].w * w[i].w), e, lane);
+                emit_record(xrec, make_float4(v[i].x * w[i].x, v[i].y * w[i].y, v[i].z * w[i].z, v[i].w * w[i].w), e, lane);
             }
             if (!mine) s_flag = 0;
         } else if (g.kind == OP_WO) {
@@ -676,13 +679,14 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
 #pragma unroll
                 for (uint32_t c = 0; c < uint32_t(kStepNchMax); ++c) {
                     if (c < nch) {
-                        const float wgt = nch == 1 ? 1.0f : expf(mc[c] - M);
+                        const float wgt = nch == 1 ? 1.0f : __expf(mc[c] - M);
                         num.x = fmaf(o[c].x, wgt, num.x); num.y = fmaf(o[c].y, wgt, num.y);
                         num.z = fmaf(o[c].z, wgt, num.z); num.w = fmaf(o[c].w, wgt, num.w);
                         den = fmaf(lc[c], wgt, den);
                     }
                 }
-                emit_block_record(xrec, make_float4(num.x / den, num.y / den, num.z / den, num.w / den), e, lane);
+                const float rden = 1.0f / den;
+                emit_record(xrec, make_float4(num.x * rden, num.y * rden, num.z * rden, num.w * rden), e, lane);
             }
             if (!mine) s_flag = 0;
         } else {
@@ -716,7 +720,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                 for (int i = 0; i < kActIters; ++i) {
                     const uint32_t e = chunk + uint32_t(i) * (kThreads * 4) + threadIdx.x * 4;
                     if (e >= K) break;              // whole warps leave together: ff is a multiple of 128
-                    emit_block_record(xrec, v[i], e, lane);
+                    emit_record(xrec, v[i], e, lane);
                 }
             }
             if (!mine) s_flag = 0;
@@ -774,7 +778,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                     }
                     up *= factor;
                     gate *= factor;
-                    ll_store(p.g_ll + gg * 2 + rr, up * gate / (expf(-gate) + 1.0f), my_epoch);      // matmul_silu_ff.comp:95
+                    ll_store(p.g_ll + gg * 2 + rr, up * gate / (__expf(-gate) + 1.0f), my_epoch);      // matmul_silu_ff.comp:95
                     continue;
                 }
                 float v = 0.f;

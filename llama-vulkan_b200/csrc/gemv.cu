@@ -340,6 +340,21 @@ int make_weight_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t 
     return LV_OK;
 }
 
+// Tiled view of `rank` dimensions over 8-byte elements: dims[0] is the contiguous one, strides[i] (bytes) belongs to
+// dims[i + 1].  No swizzle, no interleave, out-of-range elements read as zero.
+int make_tiled_map(CUtensorMap* out, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], el[5];
+    for (uint32_t i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; el[i] = 1; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) st[i] = strides[i];
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, rank, const_cast<void*>(base), d, st, b, el, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return LV_OK;
+}
+
 template <int QT, int NS, bool SILU, int W>
 static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_t groups) {
     const size_t smem = gemv_smem_bytes<QT, NS, W>(p.K);
