@@ -494,6 +494,22 @@ def measure_decode(rig, ctx, name, args, repeats):
         rig.barrier()
         if toks_e2e != toks_dev:
             raise SystemExit("device-resident and host-driven decoding disagree on the greedy tokens")
+    # ---- the same loop with the reference's sampler (its CLI never decodes greedily): token drawn on the device ----
+    s.set_deterministic(False)
+    s.set_seed(1)
+    sampled_times = []
+    for r in range(min(repeats, 3)):
+        restart()
+        pkg.check(klib.lv_stream_sync(lv, 0))
+        rig.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            assert s.start_next_token_prediction()
+            tok = s.finish_next_token_prediction()
+            assert tok != pkg.NO_TOKEN
+            s.push_token(tok)
+        sampled_times.append(rig.max_over_ranks(time.perf_counter() - t0))
+        rig.barrier()
     s.close()
     sec_dev, dev_spread = median_spread(dev_times)
     sec_e2e, e2e_spread = median_spread(e2e_times)
@@ -506,6 +522,7 @@ def measure_decode(rig, ctx, name, args, repeats):
             "spread_tokens_per_s": {"min": args.steps / dev_spread["max"], "max": args.steps / dev_spread["min"], "repeats": repeats},
             "e2e_tokens_per_s": args.steps / sec_e2e,
             "e2e_spread_tokens_per_s": {"min": args.steps / e2e_spread["max"], "max": args.steps / e2e_spread["min"], "repeats": repeats},
+            "sampled_e2e_tokens_per_s": args.steps / median_spread(sampled_times)[0],
             "bytes_per_token": bytes_per_token, "launches_per_token": launches, "tokens_digest": int(sum((i + 1) * t for i, t in enumerate(toks_dev)) % (1 << 31)),
             "prompt_eval": dict(prompt_eval, tokens_per_s=prompt_eval["tokens"] / prompt_eval["seconds"])}
 
@@ -609,7 +626,9 @@ def main():
         "spread": dict(m["spread_tokens_per_s"], unit="tokens/s", value_is="median"),
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": m["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
-                "spread": m["e2e_spread_tokens_per_s"]},
+                "spread": m["e2e_spread_tokens_per_s"],
+                # same loop, token drawn by the reference's sampler (temperature 0.8, mirostat-style cut) on the device
+                "sampled_tokens_per_s": m["sampled_e2e_tokens_per_s"]},
         "gpu_launches": m["launches_per_token"] * args.steps, "clocks": clocks,
         "parity": parity, "tokens_digest": m["tokens_digest"], "config3_13b": config3,
         # not part of the metric: wall time of the prompt's evaluation, first use (records the steps) included

@@ -78,6 +78,10 @@ uint32_t llava_session_get_tokens(void* session, uint32_t* out, uint32_t cap);
 /* additions of this build (see llava_session.h) */
 void     llava_session_set_deterministic(void* session, int on);
 void     llava_session_set_seed(void* session, uint32_t seed);
+/* non-greedy tokens come from the device sampler (lv_sample_mirostat) unless on != 0 selects the host's
+ * (std::discrete_distribution over std::mt19937, as the reference draws them) */
+void     llava_session_set_host_sampler(void* session, int on);
+float    llava_session_get_mirostat_mu(void* session);
 int      llava_session_set_max_batch(void* session, uint32_t n);
 int      llava_session_generate_greedy_on_device(void* session, uint32_t n, uint32_t* out);
 int      llava_session_enqueue_greedy_on_device(void* session, uint32_t n);     /* returns once queued */

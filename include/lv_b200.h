@@ -169,6 +169,25 @@ int lv_decode_advance(lv_ctx* ctx, uint32_t* config, const uint32_t* argmax, uin
 int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32_t* config, uint32_t* token_log, uint32_t batch,
                       uint32_t log_capacity, uint32_t* argmax_out, uint32_t* host_token);
 
+/* The non-deterministic branch of llava_session::get_last_predicted_token (llava_session.cpp:154-194) on the
+ * device, for the logits of one token: the repeat penalty of llava_session.cpp:157-167 (token 13 only, counted
+ * over the last 64 of the n_tokens tokens in token_log), temperature 0.8, probabilities without subtracting the
+ * maximum, the candidates with probability >= 0.5^mu, one draw among them in proportion to their probability, and
+ * mu += 0.1 * (5 + log2(p_drawn / kept mass)).  The reference draws with std::discrete_distribution over a
+ * std::mt19937; here the cumulative distribution of the same candidates (in index order) is inverted at a uniform
+ * variate from a counter-based generator (Philox 4x32-10) keyed by state[1] and counted in state[2]; a
+ * forced_uniform in [0, 1) replaces the generator (tests).  All pointers are device memory:
+ *   logits f32 [n_vocab] (16-byte aligned, n_vocab <= 32768); token_log u32, *n_tokens tokens of history;
+ *   state u32 [4] = {mu as f32 bits, seed, draws so far, unused}, updated;
+ *   feed_token_log (may be null): the drawn token is also stored to feed_token_log[*n_tokens], where a recorded
+ *   step that follows reads its input token (index checked against log_capacity);
+ *   out_token (device, may be null), host_token (pinned host word, may be null) receive the token, 0xFFFFFFFF when
+ *   no candidate is left (NaN logits; also reported through the error word);
+ *   report (may be null) u32 [4] = {candidates kept, kept mass, p_drawn, uniform variate} (f32 bits). */
+int lv_sample_mirostat(lv_ctx* ctx, const float* logits, uint32_t n_vocab, const uint32_t* token_log, const uint32_t* n_tokens,
+                       uint32_t* state, float forced_uniform, uint32_t* feed_token_log, uint32_t log_capacity,
+                       uint32_t* out_token, uint32_t* host_token, uint32_t* report);
+
 /* ---- batched products on the tensor cores (prompt evaluation) -------------- */
 
 /* When several tokens are evaluated together the reference dispatches its
@@ -285,8 +304,14 @@ typedef struct lv_step_layer {
 } lv_step_layer;
 
 typedef struct lv_step_model {
-    uint32_t dim, ff, heads, n_layers, vocab, ctx_rows;
+    uint32_t dim, ff, heads, n_layers, vocab, ctx_rows;     /* of the whole model */
     int wtype, emb_type;
+    /* Tensor parallelism (all zero on one GPU): this context is rank tp_rank of tp_ranks and holds, per layer, row
+     * shards of wq / wk / wv (dim / tp_ranks rows: whole heads) and of w1 / w3 (ff / tp_ranks rows), and column shards
+     * of wo and w2 whose rows are padded with zero blocks to shard_cols_o / shard_cols_2 columns (multiples of 256); the
+     * caches are [ctx_rows][dim / tp_ranks].  The peer windows of the context (lv_peer_connect) must be connected:
+     * the partial rows of wo and w2 travel through them.  Every rank must launch the same steps. */
+    uint32_t tp_ranks, tp_rank, shard_cols_o, shard_cols_2;
     const void* weights_base;
     size_t weights_bytes;
     const void* tok_embeddings;

@@ -92,6 +92,7 @@ KERNEL_API = {
     "lv_gemm_tc_qkv_kvappend": (_int, [_p, _p, _p, _p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_norm_gate_up_silu": (_int, [_p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
     "lv_norm_gemv": (_int, [_p, _p, _p, _int, _p, _p, _u32, _u32, _u32]),
+    "lv_sample_mirostat": (_int, [_p, _p, _u32, _p, _p, _p, C.c_float, _p, _u32, _p, _p, _p]),
     "lv_step_plan_create": (_int, [_p, _p, C.POINTER(_p)]),
     "lv_step_plan_destroy": (_int, [_p]),
     "lv_step_plan_set_trace": (_int, [_p, _int]),
@@ -247,6 +248,8 @@ HOST_API = {
     "llava_session_get_tokens": (_u32, [_p, _p, _u32]),
     "llava_session_set_deterministic": (None, [_p, _int]),
     "llava_session_set_seed": (None, [_p, _u32]),
+    "llava_session_set_host_sampler": (None, [_p, _int]),
+    "llava_session_get_mirostat_mu": (C.c_float, [_p]),
     "llava_session_set_max_batch": (_int, [_p, _u32]),
     "llava_session_generate_greedy_on_device": (_int, [_p, _u32, _p]),
     "llava_session_enqueue_greedy_on_device": (_int, [_p, _u32]),
@@ -445,6 +448,13 @@ class Session:
 
     def set_seed(self, seed):
         self.lib.llava_session_set_seed(self.handle, seed)
+
+    def set_host_sampler(self, on=True):
+        """Non-greedy tokens from the host sampler (std::discrete_distribution, as the reference) instead of the device one."""
+        self.lib.llava_session_set_host_sampler(self.handle, int(on))
+
+    def mirostat_mu(self):
+        return self.lib.llava_session_get_mirostat_mu(self.handle)
 
     def set_max_batch(self, n):
         return bool(self.lib.llava_session_set_max_batch(self.handle, n))

@@ -197,6 +197,18 @@ extern "C" int lv_allreduce_add_f32(lv_ctx* ctx, float* residual, float* partial
 
 namespace lv {
 
+// The connected windows of a context, for kernels that run their own exchange in them (lv_decode_step uses slot
+// sets 0 and 1, like the exchanges fused into the GEMVs, which it replaces).  False without connected windows.
+bool peer_windows(lv_ctx* ctx, float** windows, int* n_ranks, int* rank, uint32_t* capacity) {
+    auto* st = static_cast<PeerState*>(ctx->peer);
+    if (st == nullptr || !ctx->peer_ready) return false;
+    for (int r = 0; r < st->params.n_ranks; ++r) windows[r] = st->params.window[r];
+    *n_ranks = st->params.n_ranks;
+    *rank = st->params.rank;
+    *capacity = st->params.capacity;
+    return true;
+}
+
 uint32_t* peer_step_counter(lv_ctx* ctx) {
     auto* st = static_cast<PeerState*>(ctx->peer);
     return (st != nullptr && ctx->peer_ready) ? st->d_epoch + 2 : nullptr;

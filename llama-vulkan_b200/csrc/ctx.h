@@ -39,7 +39,8 @@ int gemv_configure(lv_ctx* ctx);
 int attention_configure(lv_ctx* ctx);
 int gemm_tc_configure(lv_ctx* ctx);
 void gemm_tc_release(lv_ctx* ctx);
-uint32_t* peer_step_counter(lv_ctx* ctx);          // device word counting evaluation steps, or null without a peer window
+uint32_t* peer_step_counter(lv_ctx* ctx);
+bool peer_windows(lv_ctx* ctx, float** windows, int* n_ranks, int* rank, uint32_t* capacity);   // the connected peer windows, if any          // device word counting evaluation steps, or null without a peer window
 
 #define LV_CUDA(call)                                          \
     do {                                                       \

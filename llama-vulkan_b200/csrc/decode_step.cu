@@ -48,6 +48,7 @@ constexpr int kStepAttRec = 132;            // flag-in-data words of one (head, 
 constexpr int kStepChunkRowsMax = 2048;     // rows of one attention chunk, at most
 constexpr int kStepPartFloats = 2048;       // row-segment partial sums of one operation of one CTA
 constexpr uint32_t kStepRot = 128;
+constexpr int kStepMaxRanks = 8;
 constexpr int kStepKeyBatch = 8;            // cache rows per warp whose loads are in flight together
 constexpr int kStepValuePrefetch = 2;       // value rows per thread fetched before the scores
 
@@ -66,14 +67,23 @@ struct StepLayerDev {
 static_assert(sizeof(StepLayerDev) % 16 == 0, "the layer table is copied in 16-byte units");
 
 // Tensor maps, one per (row size, box height):
-//   [0] rows of K = dim columns, box of 4 rows      (wk, wq, wv, wo, output)
-//   [1] rows of K = dim columns, box of 2 rows      (w3 / w1: two rows of each per work item)
-//   [2] rows of K = ff columns, box of 4 rows       (w2)
-struct StepMaps { CUtensorMap m[3]; };
+//   [0] rows of dim columns, box of 4 rows      (wk, wq, wv, output)
+//   [1] rows of dim columns, box of 2 rows      (w3 / w1: two rows of each per work item)
+//   [2] rows of k_2 columns, box of 4 rows      (w2)
+//   [3] rows of k_o columns, box of 4 rows      (wo; the same view as [0] on one GPU)
+struct StepMaps { CUtensorMap m[4]; };
 
 struct StepParams {
-    uint32_t dim, ff, heads, n_layers, vocab, ctx_rows;
-    uint32_t row_bytes_d, row_bytes_f;
+    // dim: length of the residual stream.  The rest is this rank's share (equal to the model's on one GPU): dq rows of
+    // each of wq / wk / wv = width of its cache rows = heads * 128; ff rows of w1 / w3; k_o, k_2 columns of the wo / w2
+    // shards (dq and ff padded with zero blocks to the shard's row length)
+    uint32_t dim, dq, ff, heads, k_o, k_2, n_layers, vocab, ctx_rows;
+    uint32_t row_bytes_d, row_bytes_f, row_bytes_o;     // bytes of a row of dim / k_2 / k_o columns
+    // tensor parallelism: n_ranks > 1 -> wo and w2 produce partial rows that every rank sums.  xw[r]: the exchange
+    // vectors in rank r's peer window as seen from this GPU, [2 sets][n_ranks senders][xw_stride words]
+    int n_ranks, rank;
+    uint64_t* xw[kStepMaxRanks];
+    uint32_t xw_stride;
     const StepLayerDev* layers;
     const uint8_t* emb; int emb_type;
     const float* final_norm;
@@ -106,6 +116,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
 __device__ __forceinline__ void ll_store(uint64_t* p, float v, uint32_t epoch) {
     const uint64_t w = (uint64_t(epoch) << 32) | uint64_t(__float_as_uint(v));
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+// The same across NVLink: a peer's window is written with system-scope stores and read with system-scope loads.
+__device__ __forceinline__ void ll_store_sys(uint64_t* p, float v, uint32_t epoch) {
+    const uint64_t w = (uint64_t(epoch) << 32) | uint64_t(__float_as_uint(v));
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+__device__ __forceinline__ bool ll_try4_sys(const uint64_t* __restrict__ buf, uint32_t e, uint32_t epoch, float4& out) {
+    uint64_t a, b, c, d;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(buf + e) : "memory");
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(c), "=l"(d) : "l"(buf + e + 2) : "memory");
+    out = make_float4(__uint_as_float(uint32_t(a)), __uint_as_float(uint32_t(b)), __uint_as_float(uint32_t(c)), __uint_as_float(uint32_t(d)));
+    return (uint32_t(a >> 32) == epoch) & (uint32_t(b >> 32) == epoch) & (uint32_t(c >> 32) == epoch) & (uint32_t(d >> 32) == epoch);
 }
 
 __device__ __forceinline__ void ll_store_u32(uint64_t* p, uint32_t v, uint32_t epoch) {
@@ -199,10 +223,10 @@ __device__ __forceinline__ OpGeo op_geo(const StepParams& p, const StepLayerDev*
             g.K = p.dim; g.row_bytes = p.row_bytes_d;
             g.row0[0] = L.row_k; g.row0[1] = L.row_q; g.row0[2] = L.row_v;
             g.w[0] = L.w_k; g.w[1] = L.w_q; g.w[2] = L.w_v;
-            g.groups_per_mat = p.dim / 4;
+            g.groups_per_mat = p.dq / 4;
             groups = 3 * g.groups_per_mat;
         } else if (g.kind == OP_WO) {
-            g.K = p.dim; g.row_bytes = p.row_bytes_d;
+            g.K = p.k_o; g.row_bytes = p.row_bytes_o;
             g.row0[0] = L.row_o; g.w[0] = L.w_o;
             groups = p.dim / 4;
             g.groups_per_mat = groups;
@@ -213,7 +237,7 @@ __device__ __forceinline__ OpGeo op_geo(const StepParams& p, const StepLayerDev*
             groups = p.ff / 2;                     // two rows of each of the two matrices per group
             g.groups_per_mat = groups;
         } else {
-            g.K = p.ff; g.row_bytes = p.row_bytes_f;
+            g.K = p.k_2; g.row_bytes = p.row_bytes_f;
             g.row0[0] = L.row_2; g.w[0] = L.w_2;
             groups = p.dim / 4;
             g.groups_per_mat = groups;
@@ -272,7 +296,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
     float* part = reinterpret_cast<float*>(smem + S::kRing + S::kBars + S::kScratch);
     float* xres = reinterpret_cast<float*>(smem + S::kRing + S::kBars + S::kScratch + S::kPart);
     uint8_t* xrec = reinterpret_cast<uint8_t*>(xres + p.dim);
-    const uint32_t kmax = max(p.dim, p.ff);
+    const uint32_t kmax = max(p.dim, p.k_2);
     const StepLayerDev* tab = reinterpret_cast<const StepLayerDev*>(xrec + S::rec_bytes(kmax));
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -280,6 +304,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
     uint64_t* my_bars = bars + warp * kStages;
     ReqGeo* rq = reinterpret_cast<ReqGeo*>(smem + S::kRing + 512) + warp;
     __shared__ uint32_t s_flag;
+    __shared__ float s_x0[2];
 
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&my_bars[s], 1);
@@ -342,6 +367,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                     const uint32_t m = kind == OP_QKV ? gg / gpm : 0u;
                     const int y = int(rq->row0[m] + (gg - m * gpm) * 4);
                     if (kind == OP_W2) tma_load_2d(dst, &maps.m[2], x, y, bar, policy);
+                    else if (kind == OP_WO) tma_load_2d(dst, &maps.m[3], x, y, bar, policy);
                     else tma_load_2d(dst, &maps.m[0], x, y, bar, policy);
                 }
             }
@@ -426,6 +452,9 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
     }
     __syncthreads();
 
+    uint32_t norm_count = 0;                 // normalised inputs staged so far (selects the entry of s_x0)
+    if (threadIdx.x == 0) { s_x0[0] = xres[0]; s_x0[1] = xres[0]; }
+    __syncthreads();
     const uint32_t nch = att_chunks(P, p.heads);
     const float att_scale = rsqrtf(float(kStepRot));
 
@@ -463,13 +492,13 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
 #pragma unroll
                 for (int j = 0; j < kStepValuePrefetch; ++j) {
                     const uint32_t i = rg + kRowGroups * j;
-                    vpre[j] = i < n_old ? *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * p.dim + d8) : make_uint4(0, 0, 0, 0);
+                    vpre[j] = i < n_old ? *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * p.dq + d8) : make_uint4(0, 0, 0, 0);
                 }
                 // q, and the new k and v rows, of this head from the QKV operation (order k, q, v)
                 if (threadIdx.x < 96) {
                     const uint32_t which = threadIdx.x >> 5, e4 = (threadIdx.x & 31) * 4;
                     float4 v;
-                    if (!ll_wait4(p.qkv_ll, which * p.dim + h * kStepRot + e4, qkv_epoch, v, p.err)) s_flag = 0;
+                    if (!ll_wait4(p.qkv_ll, which * p.dq + h * kStepRot + e4, qkv_epoch, v, p.err)) s_flag = 0;
                     if (which != 1) {      // the cache holds halves (copy_to_cache.comp:35): attention sees the rounded row
                         v.x = __half2float(__float2half_rn(v.x)); v.y = __half2float(__float2half_rn(v.y));
                         v.z = __half2float(__float2half_rn(v.z)); v.w = __half2float(__float2half_rn(v.w));
@@ -488,7 +517,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                     for (int b = 0; b < kStepKeyBatch; ++b) {
                         const uint32_t i = i0 + b * W;
                         if (i < n_old) {
-                            kraw[b] = *reinterpret_cast<const uint2*>(kc + size_t(p0 + i) * p.dim + 4 * lane);
+                            kraw[b] = *reinterpret_cast<const uint2*>(kc + size_t(p0 + i) * p.dq + 4 * lane);
                             cs[b] = *reinterpret_cast<const float4*>(p.rope + size_t(P - (p0 + i)) * kStepRot + 4 * lane);
                         }
                     }
@@ -542,7 +571,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                     }
                 }
                 for (uint32_t i = rg + kRowGroups * kStepValuePrefetch; i < n_old; i += kRowGroups) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * p.dim + d8);
+                    const uint4 raw = *reinterpret_cast<const uint4*>(vc + size_t(p0 + i) * p.dq + d8);
                     const float e = __expf(s_e[i] - m);
                     lsum += e;
                     add_row(raw, e);
@@ -605,6 +634,37 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                     v[i] = e < K ? *reinterpret_cast<const float4*>(xres + e) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
                 x0 = xres[0];
+            } else if (p.n_ranks > 1) {
+                // input = residual + the partial rows of every rank, added in rank order (the same bits on every rank).
+                // The partials arrive in this rank's window: set 0 after wo, set 1 after w2.  One float4 of the vector at
+                // a time, the words of all ranks in flight together.
+                const uint64_t* base = p.xw[p.rank] + size_t(g.kind == OP_GU ? 0u : 1u) * p.n_ranks * p.xw_stride;
+                x0 = s_x0[norm_count & 1u];            // a shift near the data, the same on every thread: the residual's first element one operation ago
+#pragma unroll
+                for (int i = 0; i < kNormIters; ++i) {
+                    const uint32_t e = uint32_t(i) * (kThreads * 4) + threadIdx.x * 4;
+                    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (e >= K || !mine) continue;
+                    float4 t[kStepMaxRanks];
+                    uint32_t pending = (1u << p.n_ranks) - 1u;
+                    Poll poll(p.err);
+                    for (;;) {
+#pragma unroll
+                        for (int r = 0; r < kStepMaxRanks; ++r)
+                            if ((pending >> r) & 1u)
+                                if (ll_try4_sys(base + size_t(r) * p.xw_stride, e, src_epoch, t[r])) pending &= ~(1u << r);
+                        if (pending == 0) break;
+                        if (!poll.again()) { mine = false; break; }
+                    }
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int r = 0; r < kStepMaxRanks; ++r)
+                        if (r < p.n_ranks) { sum.x += t[r].x; sum.y += t[r].y; sum.z += t[r].z; sum.w += t[r].w; }
+                    const float4 old = *reinterpret_cast<const float4*>(xres + e);
+                    v[i] = make_float4(old.x + sum.x, old.y + sum.y, old.z + sum.z, old.w + sum.w);
+                    *reinterpret_cast<float4*>(xres + e) = v[i];
+                    if (e == 0) s_x0[(norm_count + 1u) & 1u] = v[i].x;
+                }
             } else {
                 // every word of the thread is requested before any is examined; stragglers are polled again
                 uint32_t pending = 0;
@@ -649,11 +709,16 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                 emit_record(xrec, make_float4(v[i].x * w[i].x, v[i].y * w[i].y, v[i].z * w[i].z, v[i].w * w[i].w), e, lane);
             }
             if (!mine) s_flag = 0;
+            ++norm_count;
         } else if (g.kind == OP_WO) {
             // attention output of element e: the chunks of its head combined (the last step of flash decoding)
             const uint32_t att_epoch = epoch0 + layer * 5u + 1u;
             bool mine = true;
-            for (uint32_t e = threadIdx.x * 4; e < p.dim; e += kThreads * 4) {
+            for (uint32_t e = threadIdx.x * 4; e < p.k_o; e += kThreads * 4) {
+                if (e >= p.dq) {                 // columns that pad the shard's rows: zero weights, zero records
+                    emit_record(xrec, make_float4(0.f, 0.f, 0.f, 0.f), e, lane);
+                    continue;
+                }
                 const uint32_t h = e / kStepRot, j = e - h * kStepRot;
                 const uint64_t* rec = p.att_ll + size_t(h) * kStepNchMax * kStepAttRec;
                 float4 o[kStepNchMax];
@@ -691,7 +756,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
             if (!mine) s_flag = 0;
         } else {
             // w2: the gated activations of the whole FFN width
-            const uint32_t K = p.ff;
+            const uint32_t K = p.k_2, Kin = p.ff;       // columns of the shard; those beyond the FFN rows of this rank are padding
             const uint32_t src_epoch = epoch0 + layer * 5u + 3u;
             bool mine = true;
             for (uint32_t chunk = 0; chunk < K; chunk += kThreads * 4 * kActIters) {
@@ -701,7 +766,7 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                 for (int i = 0; i < kActIters; ++i) {
                     const uint32_t e = chunk + uint32_t(i) * (kThreads * 4) + threadIdx.x * 4;
                     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (e < K && !ll_try4(p.g_ll, e, src_epoch, v[i])) pending |= 1u << i;
+                    if (e < Kin && !ll_try4(p.g_ll, e, src_epoch, v[i])) pending |= 1u << i;
                 }
                 if (pending != 0) {
                     Poll poll(p.err);
@@ -786,17 +851,26 @@ __global__ void __launch_bounds__(QTraits<QT>::kWarps * 32, 1) lv_decode_step_ke
                 v *= factor;
                 if (g.kind == OP_QKV) {
                     const uint32_t m = gg / g.groups_per_mat, row = (gg - m * g.groups_per_mat) * 4 + rr;
-                    ll_store(p.qkv_ll + m * p.dim + row, v, my_epoch);
+                    ll_store(p.qkv_ll + m * p.dq + row, v, my_epoch);
                     if (m != 1) {                                                                      // copy_to_cache.comp:35
                         __half* cache = m == 0 ? L.k_cache : L.v_cache;
-                        cache[size_t(P) * p.dim + row] = __float2half_rn(v);
+                        cache[size_t(P) * p.dq + row] = __float2half_rn(v);
                     }
                 } else if (g.kind == OP_WO) {
                     const uint32_t row = gg * 4 + rr;
-                    ll_store(p.x_ll + row, xres[row] + v, my_epoch);                                   // matmul.glsl:68-70
+                    if (p.n_ranks > 1) {
+                        for (int r = 0; r < p.n_ranks; ++r) ll_store_sys(p.xw[r] + size_t(p.rank) * p.xw_stride + row, v, my_epoch);
+                    } else {
+                        ll_store(p.x_ll + row, xres[row] + v, my_epoch);                               // matmul.glsl:68-70
+                    }
                 } else if (g.kind == OP_W2) {
                     const uint32_t row = gg * 4 + rr;
-                    ll_store(p.x_ll + p.dim + row, xres[row] + v, my_epoch);
+                    if (p.n_ranks > 1) {
+                        for (int r = 0; r < p.n_ranks; ++r)
+                            ll_store_sys(p.xw[r] + (size_t(p.n_ranks) + p.rank) * p.xw_stride + row, v, my_epoch);
+                    } else {
+                        ll_store(p.x_ll + p.dim + row, xres[row] + v, my_epoch);
+                    }
                 } else {
                     const uint32_t row = gg * 4 + rr;
                     p.logits[row] = v;
@@ -969,27 +1043,38 @@ extern "C" int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* m, lv_step_
                "need dim = heads * 128 <= 6144, dim and ff multiples of 256");
     LV_REQUIRE(m->vocab % 4 == 0 && m->vocab >= 4 && m->ctx_rows >= 1 && m->ctx_rows <= uint32_t(kStepChunkRowsMax), "vocab / context out of range");
     LV_REQUIRE(m->weights_base && m->tok_embeddings && m->norm && m->output && m->rope_table, "null model pointer");
+    // this rank's share
+    const uint32_t ranks = m->tp_ranks > 1 ? m->tp_ranks : 1u;
+    LV_REQUIRE(ranks <= uint32_t(kStepMaxRanks) && m->tp_rank < ranks, "rank out of range");
+    LV_REQUIRE(m->heads % ranks == 0 && (m->ff / ranks) % 4 == 0 && m->ff % ranks == 0, "heads and ff must divide evenly over the ranks");
+    const uint32_t dq = m->dim / ranks, heads = m->heads / ranks, ff = m->ff / ranks;
+    const uint32_t k_o = ranks > 1 ? m->shard_cols_o : m->dim, k_2 = ranks > 1 ? m->shard_cols_2 : m->ff;
+    LV_REQUIRE(k_o % 256 == 0 && k_2 % 256 == 0 && k_o >= dq && k_2 >= ff, "shard rows must be padded to multiples of 256 columns");
+    float* windows[kStepMaxRanks] = {nullptr};
+    int w_ranks = 0, w_rank = 0;
+    uint32_t w_capacity = 0;
+    if (ranks > 1) {
+        LV_REQUIRE(peer_windows(ctx, windows, &w_ranks, &w_rank, &w_capacity), "a sharded step needs connected peer windows");
+        LV_REQUIRE(uint32_t(w_ranks) == ranks && uint32_t(w_rank) == m->tp_rank, "the peer windows belong to another rank layout");
+        LV_REQUIRE(w_capacity >= 2 * m->dim, "peer window slots too small for the exchange vectors");
+    }
     const uint32_t bb = m->wtype == T_Q4_0 ? kQ4BlockBytes : kQ8BlockBytes;
-    const uint32_t rb_d = m->dim / 32 * bb, rb_f = m->ff / 32 * bb;
+    const uint32_t rb_d = m->dim / 32 * bb, rb_f = k_2 / 32 * bb, rb_o = k_o / 32 * bb;
     const int grid = ctx->sm_count;
     // shares: every operation gives each CTA whole groups of 4 rows; partial sums and row threads must fit
-    const uint32_t nseg_d = (m->dim / 32 + kSegBlocks - 1) / kSegBlocks, nseg_f = (m->ff / 32 + kSegBlocks - 1) / kSegBlocks;
+    auto nseg_of = [](uint32_t K) { return (K / 32 + kSegBlocks - 1) / kSegBlocks; };
     auto share = [&](uint32_t groups) { return (groups + grid - 1) / grid; };
-    const uint32_t worst_part = std::max(std::max(share(3 * m->dim / 4) * nseg_d, share(m->ff / 2) * nseg_d),
-                                         std::max(share(m->dim / 4) * nseg_f, share(m->vocab / 4) * nseg_d)) * 4;
+    const uint32_t worst_part = std::max(std::max(share(3 * dq / 4) * nseg_of(m->dim), share(ff / 2) * nseg_of(m->dim)),
+                                         std::max(std::max(share(m->dim / 4) * nseg_of(k_2), share(m->dim / 4) * nseg_of(k_o)),
+                                                  share(m->vocab / 4) * nseg_of(m->dim))) * 4;
     LV_REQUIRE(worst_part <= uint32_t(kStepPartFloats), "too many rows per CTA for the partial-sum buffer");
 
     auto* plan = new lv_step_plan();
     plan->ctx = ctx;
     plan->wtype = m->wtype;
     plan->grid = grid;
-    plan->smem = m->wtype == T_Q4_0 ? StepSmem<T_Q4_0>::total(m->dim, std::max(m->dim, m->ff), m->n_layers)
-                                    : StepSmem<T_Q8_0>::total(m->dim, std::max(m->dim, m->ff), m->n_layers);
-    if (plan->smem > size_t(ctx->max_smem_optin)) {
-        const size_t need = plan->smem;
-        delete plan;
-        return fail(LV_ERR_BAD_ARGUMENTS, "lv_step_plan_create: the model needs " + std::to_string(need) + " bytes of shared memory per CTA");
-    }
+    const uint32_t kmax = std::max(m->dim, k_2);
+    plan->smem = m->wtype == T_Q4_0 ? StepSmem<T_Q4_0>::total(m->dim, kmax, m->n_layers) : StepSmem<T_Q8_0>::total(m->dim, kmax, m->n_layers);
     // every matrix is a row range of the 2-D view [arena bytes / row size][row size] of the weight arena
     const uint8_t* base = static_cast<const uint8_t*>(m->weights_base);
     bool aligned = (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
@@ -1007,8 +1092,8 @@ extern "C" int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* m, lv_step_
             delete plan;
             return fail(LV_ERR_BAD_ARGUMENTS, "lv_step_plan_create: null pointer in layer " + std::to_string(l));
         }
-        row_of(a.wk, rb_d, m->dim, &d.row_k); row_of(a.wq, rb_d, m->dim, &d.row_q); row_of(a.wv, rb_d, m->dim, &d.row_v);
-        row_of(a.wo, rb_d, m->dim, &d.row_o); row_of(a.w3, rb_d, m->ff, &d.row_3); row_of(a.w1, rb_d, m->ff, &d.row_1);
+        row_of(a.wk, rb_d, dq, &d.row_k); row_of(a.wq, rb_d, dq, &d.row_q); row_of(a.wv, rb_d, dq, &d.row_v);
+        row_of(a.wo, rb_o, m->dim, &d.row_o); row_of(a.w3, rb_d, ff, &d.row_3); row_of(a.w1, rb_d, ff, &d.row_1);
         row_of(a.w2, rb_f, m->dim, &d.row_2);
         d.w_k = static_cast<const uint8_t*>(a.wk); d.w_q = static_cast<const uint8_t*>(a.wq); d.w_v = static_cast<const uint8_t*>(a.wv);
         d.w_o = static_cast<const uint8_t*>(a.wo); d.w_3 = static_cast<const uint8_t*>(a.w3); d.w_1 = static_cast<const uint8_t*>(a.w1);
@@ -1023,8 +1108,12 @@ extern "C" int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* m, lv_step_
             }
     }
     StepParams& p = plan->params;
-    p.dim = m->dim; p.ff = m->ff; p.heads = m->heads; p.n_layers = m->n_layers; p.vocab = m->vocab; p.ctx_rows = m->ctx_rows;
-    p.row_bytes_d = rb_d; p.row_bytes_f = rb_f;
+    p.dim = m->dim; p.dq = dq; p.ff = ff; p.heads = heads; p.k_o = k_o; p.k_2 = k_2;
+    p.n_layers = m->n_layers; p.vocab = m->vocab; p.ctx_rows = m->ctx_rows;
+    p.row_bytes_d = rb_d; p.row_bytes_f = rb_f; p.row_bytes_o = rb_o;
+    p.n_ranks = int(ranks); p.rank = int(m->tp_rank);
+    for (uint32_t r = 0; r < ranks && ranks > 1; ++r) p.xw[r] = reinterpret_cast<uint64_t*>(windows[r]);
+    p.xw_stride = w_capacity / 2;                  // a slot of `capacity` floats, counted in 8-byte words
     p.emb = static_cast<const uint8_t*>(m->tok_embeddings); p.emb_type = m->emb_type;
     p.final_norm = m->norm;
     p.head_w = static_cast<const uint8_t*>(m->output);
@@ -1034,21 +1123,22 @@ extern "C" int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* m, lv_step_
     // tiled loads need boxes of at most 256 eight-byte elements (q4_0: 144; q8_0: 272 -> bulk copies) and every matrix on the row grid
     constexpr uint32_t seg_q4 = kSegBlocks * kQ4BlockBytes;
     static const char* no_tmap = getenv("LV_GEMV_NO_TENSOR_MAP");
-    plan->tmap = m->wtype == T_Q4_0 && aligned && rb_d % 16 == 0 && rb_f % 16 == 0 && !(no_tmap != nullptr && no_tmap[0] == '1');
+    plan->tmap = m->wtype == T_Q4_0 && aligned && rb_d % 16 == 0 && rb_f % 16 == 0 && rb_o % 16 == 0 && !(no_tmap != nullptr && no_tmap[0] == '1');
     if (plan->tmap) {
-        const uint64_t rows_d = m->weights_bytes / rb_d, rows_f = m->weights_bytes / rb_f;
+        const uint64_t rows_d = m->weights_bytes / rb_d, rows_f = m->weights_bytes / rb_f, rows_o = m->weights_bytes / rb_o;
         int rc = LV_OK;
-        if (rows_d > 0xffffffffull || rows_f > 0xffffffffull) rc = fail(LV_ERR_BAD_ARGUMENTS, "weight arena too large for the tensor maps");
+        if (rows_d > 0xffffffffull || rows_f > 0xffffffffull || rows_o > 0xffffffffull) rc = fail(LV_ERR_BAD_ARGUMENTS, "weight arena too large for the tensor maps");
         if (rc == LV_OK) rc = make_weight_map(&plan->maps.m[0], base, uint32_t(rows_d), rb_d, 4, seg_q4);
         if (rc == LV_OK) rc = make_weight_map(&plan->maps.m[1], base, uint32_t(rows_d), rb_d, 2, seg_q4);
         if (rc == LV_OK) rc = make_weight_map(&plan->maps.m[2], base, uint32_t(rows_f), rb_f, 4, seg_q4);
+        if (rc == LV_OK) rc = make_weight_map(&plan->maps.m[3], base, uint32_t(rows_o), rb_o, 4, seg_q4);
         if (rc != LV_OK) { delete plan; return rc; }
-    } else if (rb_d % 16 != 0 || rb_f % 16 != 0) {
+    } else if (rb_d % 16 != 0 || rb_f % 16 != 0 || rb_o % 16 != 0) {
         delete plan;
         return fail(LV_ERR_BAD_ARGUMENTS, "lv_step_plan_create: row sizes must be multiples of 16 bytes");
     }
     // device copies: the layer table and the workspace of flag-in-data vectors
-    const size_t ws_words = size_t(2) * m->dim + size_t(3) * m->dim + size_t(m->heads) * kStepNchMax * kStepAttRec + m->ff + size_t(grid) * 2 + 64;
+    const size_t ws_words = size_t(2) * m->dim + size_t(3) * dq + size_t(heads) * kStepNchMax * kStepAttRec + ff + size_t(grid) * 2 + 64;
     cudaError_t e = cudaMalloc(&plan->d_layers, tab.size() * sizeof(StepLayerDev));
     if (e == cudaSuccess) e = cudaMemcpy(plan->d_layers, tab.data(), tab.size() * sizeof(StepLayerDev), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMalloc(&plan->d_ws, ws_words * 8);
@@ -1062,9 +1152,9 @@ extern "C" int lv_step_plan_create(lv_ctx* ctx, const lv_step_model* m, lv_step_
     p.layers = static_cast<const StepLayerDev*>(plan->d_layers);
     uint64_t* ws = static_cast<uint64_t*>(plan->d_ws);
     p.x_ll = ws; ws += size_t(2) * m->dim;
-    p.qkv_ll = ws; ws += size_t(3) * m->dim;
-    p.att_ll = ws; ws += size_t(m->heads) * kStepNchMax * kStepAttRec;
-    p.g_ll = ws; ws += m->ff;
+    p.qkv_ll = ws; ws += size_t(3) * dq;
+    p.att_ll = ws; ws += size_t(heads) * kStepNchMax * kStepAttRec;
+    p.g_ll = ws; ws += (ff + 3) / 4 * 4;
     p.amax_ll = ws; ws += size_t(grid) * 2;
     p.step = reinterpret_cast<uint32_t*>(ws);
     int rc = m->wtype == T_Q4_0 ? step_configure<T_Q4_0>(ctx, plan->smem) : step_configure<T_Q8_0>(ctx, plan->smem);

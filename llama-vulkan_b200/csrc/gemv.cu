@@ -45,7 +45,7 @@ struct GemvMaps {
 };
 
 template <int QT, int NS, bool SILU, int W, bool TMAP>
-__global__ void __launch_bounds__(W * 32, 1) lv_qrow_stream_kernel(const GemvParams p, const __grid_constant__ GemvMaps maps) {
+__global__ void __launch_bounds__(W * 32, W <= 8 && QT == T_Q4_0 ? 2 : 1) lv_qrow_stream_kernel(const GemvParams p, const __grid_constant__ GemvMaps maps) {
     using Q = QTraits<QT>;
     constexpr int kWarps = W;
     static_assert(size_t(W) * kStages * sizeof(uint64_t) <= kBarBytes, "mbarrier area too small for this many warps");
@@ -356,10 +356,10 @@ int make_tiled_map(CUtensorMap* out, const void* base, uint32_t rank, const uint
 }
 
 template <int QT, int NS, bool SILU, int W>
-static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_t groups) {
+static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_t groups, uint32_t ctas_per_sm = 1) {
     const size_t smem = gemv_smem_bytes<QT, NS, W>(p.K);
     LV_REQUIRE(smem <= size_t(ctx->max_smem_optin), "lv_gemv: K too large for the shared-memory activation buffer");
-    const uint32_t ctas = min(uint32_t(ctx->sm_count), groups);
+    const uint32_t ctas = min(uint32_t(ctx->sm_count) * ctas_per_sm, groups);
     dim3 grid(ctas, batch);
     constexpr uint32_t seg_bytes = kSegBlocks * QTraits<QT>::kBlockBytes;
     // the tiled form needs a box of at most 256 eight-byte elements (q4_0: 144) and rows of a multiple of 16 bytes
@@ -379,6 +379,14 @@ static int launch_gemv(lv_ctx* ctx, const GemvParams& p, uint32_t batch, uint32_
     return LV_OK;
 }
 
+static bool gemv_two_per_sm() {
+    static const bool on = []() {
+        const char* e = getenv("LV_GEMV_TWO_PER_SM");
+        return e != nullptr && e[0] == '1';
+    }();
+    return on;
+}
+
 template <int QT, bool SILU>
 static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t batch) {
     uint32_t rows = 0;
@@ -389,6 +397,17 @@ static int launch_gemv_pick_streams(lv_ctx* ctx, const GemvParams& p, uint32_t b
     // matrices with fewer row groups than SMs
     const uint32_t groups4 = SILU ? rows / 2 : rows / 4;
     constexpr int W = QTraits<QT>::kWarps;      // 20 warps instead of 16 measured no faster
+    if constexpr (QT == T_Q4_0) {
+        // Two CTAs of eight warps per SM instead of one of sixteen: the slots of an SM turn over one CTA at a time, so the
+        // first CTAs of the next launch (programmatic dependent launch) become resident and start their weight copies while
+        // the last CTAs of this one are still in their row pass.  Needs the shared memory of two CTAs: four rows per item
+        // while the activation records are small, two rows for the FFN-wide inputs.
+        if (gemv_two_per_sm() && p.tp.n_ranks == 0 && groups4 >= 2 * uint32_t(ctx->sm_count)) {
+            constexpr size_t kHalf = 113 * 1024;
+            if (gemv_smem_bytes<QT, 4, 8>(p.K) <= kHalf) return launch_gemv<QT, 4, SILU, 8>(ctx, p, batch, groups4, 2);
+            if (gemv_smem_bytes<QT, 2, 8>(p.K) <= kHalf) return launch_gemv<QT, 2, SILU, 8>(ctx, p, batch, groups4 * 2, 2);
+        }
+    }
     if (groups4 >= uint32_t(ctx->sm_count)) return launch_gemv<QT, 4, SILU, W>(ctx, p, batch, groups4);
     return launch_gemv<QT, 2, SILU, W>(ctx, p, batch, groups4 * 2);
 }
@@ -404,6 +423,7 @@ int gemv_configure(lv_ctx* ctx) {
     LV_CFG1(QT, 4, SILU, QTraits<QT>::kWarps); \
     LV_CFG1(QT, 2, SILU, QTraits<QT>::kWarps)
     LV_CFG(T_Q4_0, false); LV_CFG(T_Q4_0, true); LV_CFG(T_Q8_0, false); LV_CFG(T_Q8_0, true);
+    LV_CFG1(T_Q4_0, 4, false, 8); LV_CFG1(T_Q4_0, 2, false, 8); LV_CFG1(T_Q4_0, 4, true, 8); LV_CFG1(T_Q4_0, 2, true, 8);
 #undef LV_CFG
 #undef LV_CFG1
     return LV_OK;

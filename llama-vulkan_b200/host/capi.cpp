@@ -216,6 +216,8 @@ int llava_session_get_logits(void* s, float* out, uint32_t cap) {
 
 uint32_t llava_session_get_backlog_size(void* s) { return S(s)->get_backlog_size(); }
 uint32_t llava_session_get_tokens_in_gpu(void* s) { return S(s)->get_tokens_in_gpu(); }
+void llava_session_set_host_sampler(void* s, int on) { S(s)->set_host_sampler(on != 0); }
+float llava_session_get_mirostat_mu(void* s) { return S(s)->get_mirostat_mu(); }
 uint32_t llava_session_step_kernel_launches(void* s) { return S(s)->step_kernel_launches(); }
 int llava_session_set_step_trace(void* s, int on) { return S(s)->set_step_trace(on != 0); }
 uint64_t llava_session_read_step_trace(void* s, uint64_t* out, uint64_t cap, uint32_t* dims3) {

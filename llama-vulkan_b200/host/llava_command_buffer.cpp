@@ -10,9 +10,9 @@
 
 using namespace std;
 
-llava_command_buffer::llava_command_buffer(llava_session* _session, u32 _batch_size, bool _with_head)
+llava_command_buffer::llava_command_buffer(llava_session* _session, u32 _batch_size, bool _with_head, bool _sample)
     : session(_session), backlog_size(_session->backlog_size), workgroup_size(_session->ctx->workgroup_size),
-      batch_size(_batch_size), with_head(_with_head) {}
+      batch_size(_batch_size), with_head(_with_head), sample(_sample && _with_head) {}
 
 llava_command_buffer::~llava_command_buffer() {
     wait_idle();
@@ -54,6 +54,18 @@ bool llava_command_buffer::run() {
     return lv_graph_launch(lv(), graph) == LV_OK;
 }
 
+// The reference's sampler as the last kernel of the step (llava_session.cpp:154-194): reads the logits and the token
+// history where they are, leaves the drawn token in the pinned staging word and -- for decoding without the host in
+// the loop -- in the token log slot that the next step reads.
+void llava_command_buffer::record_sampler() {
+    llava_session* s = session;
+    u32* config = static_cast<u32*>(s->config_buffer->device_ptr());
+    u32* log = static_cast<u32*>(s->token_log->device_ptr());
+    note(lv_sample_mirostat(lv(), static_cast<float*>(s->output_probs->device_ptr()), s->model->get_header().vocab_size, log, config,
+                            static_cast<u32*>(s->sampler_state->device_ptr()), -1.0f, log, max_backlog_size + 1,
+                            static_cast<u32*>(s->argmax_result->device_ptr()) + 1, s->pinned + max_backlog_size + 5, nullptr));
+}
+
 bool llava_command_buffer::record_execution() {
     if (graph) return false;
     llava_session* s = session;
@@ -70,6 +82,7 @@ bool llava_command_buffer::record_execution() {
         // a single token: the whole list below as one persistent kernel
         note(lv_decode_step(lv(), s->step_plan, config, log, max_backlog_size + 1, static_cast<float*>(s->output_probs->device_ptr()),
                             static_cast<u32*>(s->argmax_result->device_ptr()), s->pinned + max_backlog_size + 4, with_head ? 1 : 0));
+        if (sample) record_sampler();
         lv_graph* g1 = nullptr;
         note(lv_graph_end_capture(lv(), &g1));
         if (first_error != LV_OK) {
@@ -101,6 +114,7 @@ bool llava_command_buffer::record_execution() {
         u32* am = static_cast<u32*>(s->argmax_result->device_ptr());
         note(lv_argmax_advance(lv(), logits, h.vocab_size, config, log, batch_size, max_backlog_size + 1, am,
                                s->pinned + max_backlog_size + 4));
+        if (sample) record_sampler();
     } else {
         // leading chunk of a prompt: only the position advances
         note(lv_decode_advance(lv(), config, nullptr, nullptr, batch_size, 0));

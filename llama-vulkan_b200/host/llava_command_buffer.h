@@ -13,7 +13,8 @@ class llava_command_buffer {
 public:
     // with_head: record the final norm + output matrix + argmax (not needed for
     // the leading chunks of a long prompt)
-    llava_command_buffer(llava_session* session, u32 batch_size, bool with_head);
+    // sample: after the head, draw the next token on the device (the reference's sampler) as part of the step
+    llava_command_buffer(llava_session* session, u32 batch_size, bool with_head, bool sample = false);
     ~llava_command_buffer();
     llava_command_buffer(const llava_command_buffer&) = delete;
     llava_command_buffer& operator=(const llava_command_buffer&) = delete;
@@ -22,6 +23,7 @@ public:
     bool run();
     bool wait_idle() const;
     u32 kernel_launches() const;       // kernel nodes of the recorded graph
+    void record_sampler();
 
     // the reference's op set (llava_command_buffer.h:30-38)
     void normalize_logit(llava_buffer* outbuf, llava_buffer* inbuf, llava_buffer* weights);
@@ -64,6 +66,7 @@ public:
     u32 const workgroup_size;
     u32 const batch_size;
     bool const with_head;
+    bool const sample;
 
 private:
     void note(int rc);

@@ -24,11 +24,14 @@ namespace {
 // words of the pinned staging block after the token area
 constexpr u32 kCfgWords = 0;      // 4 words: position to upload
 constexpr u32 kArgmaxWord = 4;    // argmax written by the recorded step
-constexpr u32 kPinnedExtra = 8;
+constexpr u32 kSampleWord = 5;    // token drawn by the device sampler
+constexpr u32 kStateWords = 8;    // 4 words: sampler state to upload / read back
+constexpr u32 kPinnedExtra = 16;
 }  // namespace
 
 llava_session::llava_session(llava_context* _ctx)
-    : ctx(_ctx), model(_ctx->get_model()), rng(u32(time(nullptr))), mirostat_mu(2 * mirostat_tau), backlog_size(min_backlog_size) {
+    : ctx(_ctx), model(_ctx->get_model()), rng(u32(time(nullptr))), mirostat_mu(2 * mirostat_tau), sampler_seed(u32(time(nullptr))),
+      backlog_size(min_backlog_size) {
     void* p = nullptr;
     if (lv_host_alloc(ctx->lv(), size_t(max_backlog_size + kPinnedExtra) * 4, &p) == LV_OK) {
         pinned = static_cast<u32*>(p);
@@ -68,10 +71,11 @@ bool llava_session::ensure_buffers_created() {
 // an error: the session then records one kernel per operation.
 void llava_session::ensure_step_plan() {
     if (step_plan_tried) return;
+    if (ctx->tp_size() != 1 && !ctx->fused_exchange()) return;      // ask again once the windows are connected
     step_plan_tried = true;
     const char* env = getenv("LV_DECODE_STEP");
     if (env == nullptr || env[0] != '1') return;          // opt-in while it is slower than one kernel per operation
-    if (ctx->tp_size() != 1) return;
+    if (ctx->tp_size() != 1 && !ctx->fused_exchange()) return;      // sharded: the partial rows travel through the peer windows
     const ggml_header& h = model->get_header();
     const auto& layers = ctx->get_layers();
     std::vector<lv_step_layer> tab(layers.size());
@@ -89,6 +93,12 @@ void llava_session::ensure_step_plan() {
     lv_step_model m{};
     m.dim = h.dim; m.ff = model->get_ff_size(); m.heads = h.n_heads; m.n_layers = u32(layers.size()); m.vocab = h.vocab_size;
     m.ctx_rows = max_backlog_size;
+    if (ctx->tp_size() > 1) {
+        m.tp_ranks = ctx->tp_size();
+        m.tp_rank = ctx->tp_rank();
+        m.shard_cols_o = layers[0]->wo()->shape.second;
+        m.shard_cols_2 = layers[0]->w2()->shape.second;
+    }
     m.wtype = int(ctx->output_w->type);
     m.emb_type = int(ctx->tok_embeddings->type);
     m.weights_base = ctx->weights_memory()->device_base();
@@ -132,6 +142,8 @@ bool llava_session::recreate_buffers() {
     output_probs = new llava_buffer(ctx, F, h.vocab_size, 1, m);
     token_log = new llava_buffer(ctx, F, max_backlog_size + kPinnedExtra, 1, m);
     argmax_result = new llava_buffer(ctx, F, 4, 1, m);
+    sampler_state = new llava_buffer(ctx, F, 4, 1, m);
+    sampler_state_dirty = true;
     const size_t scratch = lv_attention_scratch_bytes(h.n_heads / ranks, h.rot, max_backlog_size, B);
     if (scratch == 0) return false;
     attn_scratch = new llava_buffer(ctx, F, u32((scratch + 3) / 4), 1, m);
@@ -144,7 +156,7 @@ bool llava_session::recreate_buffers() {
 void llava_session::reset_main_buffers() {
     for (llava_buffer** b : {&current_thought, &current_thought_sublayer, &current_thought_middle_normd, &current_Q, &current_K,
                              &current_V, &current_Vout, &main_attn_result, &config_buffer, &output_probs, &main_ff_result,
-                             &token_log, &argmax_result, &attn_scratch, &tp_partial, &act_split}) {
+                             &token_log, &argmax_result, &attn_scratch, &tp_partial, &act_split, &sampler_state}) {
         delete *b;
         *b = nullptr;
     }
@@ -152,11 +164,49 @@ void llava_session::reset_main_buffers() {
     main_buffer_memory = nullptr;
 }
 
+void llava_session::set_seed(u32 seed) {
+    rng.seed(seed);
+    sampler_seed = seed;
+    sampler_state_dirty = true;
+}
+
+void llava_session::set_host_sampler(bool on) {
+    if (on == host_sampler) return;
+    get_mirostat_mu();              // bring mu over to the side that continues
+    host_sampler = on;
+    sampler_state_dirty = true;
+}
+
+// mu lives where the last token was drawn: on the device after device draws
+float llava_session::get_mirostat_mu() {
+    if (sampler_state != nullptr && !sampler_state_dirty && sampling_on_device()) {
+        lv_stream_sync(ctx->lv(), 0);
+        u32 words[4] = {0, 0, 0, 0};
+        if (sampler_state->read_raw(0, words, sizeof words)) memcpy(&mirostat_mu, &words[0], 4);
+    }
+    return mirostat_mu;
+}
+
+// {mu, seed, draws so far, -} to the device, when the host copy is newer
+bool llava_session::upload_sampler_state() {
+    if (!sampler_state_dirty) return true;
+    if (lv_stream_sync(ctx->lv(), 0) != LV_OK) return false;
+    u32* w = pinned + max_backlog_size + kStateWords;
+    memcpy(&w[0], &mirostat_mu, 4);
+    w[1] = sampler_seed;
+    w[2] = 0;
+    w[3] = 0;
+    if (lv_upload_async(ctx->lv(), sampler_state->device_ptr(), w, 16) != LV_OK) return false;
+    sampler_state_dirty = false;
+    return true;
+}
+
 llava_command_buffer* llava_session::get_command_buffer(u32 batch, bool with_head) {
-    const auto key = make_pair(batch, with_head);
+    const bool sample = with_head && sampling_on_device();
+    const u32 key = batch | (with_head ? 1u << 16 : 0u) | (sample ? 1u << 17 : 0u);
     auto it = command_buffers.find(key);
     if (it != command_buffers.end()) return it->second;
-    auto* cb = new llava_command_buffer(this, batch, with_head);
+    auto* cb = new llava_command_buffer(this, batch, with_head, sample);
     if (!cb->record_execution()) {
         delete cb;
         return nullptr;
@@ -193,6 +243,7 @@ bool llava_session::start_next_token_prediction() {
     }
     lock_guard<mutex> guard(ctx->queue_mutex);
     if (!sync_device_position(current_tokens_in_gpu)) return false;
+    if (sampling_on_device() && !upload_sampler_state()) return false;
     if (!upload_pending_tokens(current_tokens_in_gpu, to_process)) return false;
     while (to_process > 0) {
         const u32 n = min(to_process, max_batch);
@@ -249,6 +300,7 @@ u32 llava_session::get_last_predicted_token(bool want_deterministic) {
         // first index of the largest logit (llava_session.cpp:144-152), computed on the device
         return pinned[max_backlog_size + kArgmaxWord];
     }
+    if (!host_sampler) return pinned[max_backlog_size + kSampleWord];      // drawn by the recorded step (lv_sample_mirostat)
     vector<float> logits;
     if (!get_logits(&logits)) return ~0U;
     for (float x : logits) {
@@ -309,6 +361,7 @@ bool llava_session::enqueue_greedy_on_device(u32 n) {
     if (need > max_backlog_size || !set_backlog_size(need)) return false;
     lock_guard<mutex> guard(ctx->queue_mutex);
     if (!sync_device_position(current_tokens_in_gpu)) return false;
+    if (sampling_on_device() && !upload_sampler_state()) return false;
     if (!upload_pending_tokens(current_tokens_in_gpu, 1)) return false;
     llava_command_buffer* cb = get_command_buffer(1, true);
     if (cb == nullptr) return false;

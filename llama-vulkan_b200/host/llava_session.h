@@ -48,7 +48,11 @@ public:
     // logit (the argmax branch of the reference's get_last_predicted_token, which
     // its own callers never select); false: the reference's sampler.
     void set_deterministic(bool on) { deterministic = on; }
-    void set_seed(u32 seed) { rng.seed(seed); }
+    void set_seed(u32 seed);
+    // false (default): non-greedy tokens are drawn on the device (lv_sample_mirostat: 4 bytes come back instead of the
+    // 128 KB of logits); true: on the host, with std::discrete_distribution over std::mt19937 as the reference does
+    void set_host_sampler(bool on);
+    float get_mirostat_mu();
     // tokens evaluated per recorded step while a prompt is ingested (1 ..
     // max_batch_limit); the reference evaluates the whole prompt as one batch
     bool set_max_batch(u32 n);
@@ -87,6 +91,9 @@ private:
     const float mirostat_eta = 0.1f;
     float mirostat_mu;
     bool deterministic = false;
+    bool host_sampler = false;
+    u32 sampler_seed;
+    bool sampler_state_dirty = true;          // mu / seed on the host are newer than the device copy
 
     // scratch buffers, named as in the reference (llava_session.h:80-94); second dimension = max_batch
     llava_device_memory* main_buffer_memory = nullptr;
@@ -105,6 +112,7 @@ private:
     llava_buffer* token_log = nullptr;
     llava_buffer* argmax_result = nullptr;
     llava_buffer* attn_scratch = nullptr;
+    llava_buffer* sampler_state = nullptr;        // device sampler: {mu, seed, draws, -}
     llava_buffer* act_split = nullptr;            // max_batch >= 6: fp16 (hi, lo) planes of a batch of activations
     llava_buffer* tp_partial = nullptr;           // tensor-parallel only: this rank's partial wo / w2 product
     std::vector<llava_layer_session_data*> layer_data;
@@ -121,8 +129,11 @@ private:
     bool ensure_buffers_created();
     void drop_command_buffers();
     llava_command_buffer* get_command_buffer(u32 batch, bool with_head);
+    bool sampling_on_device() const { return !deterministic && !host_sampler; }
+    bool upload_sampler_state();
 
-    std::map<std::pair<u32, bool>, llava_command_buffer*> command_buffers;
+    // key: batch | with_head << 16 | device sampler << 17
+    std::map<u32, llava_command_buffer*> command_buffers;
     llava_command_buffer* last_command_buffer = nullptr;
 
     std::vector<u32> token_buffer;

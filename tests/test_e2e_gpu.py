@@ -329,10 +329,13 @@ def test_trace_frames_match_oracle_layer_outputs(run, tmp_path):
             break
 
 
-def test_sampler_draws_from_the_reference_candidate_set(run):
-    """Non-greedy mode is the reference's sampler (llava_session.cpp:154-194): the drawn token must be one of
-    the candidates the oracle's restatement keeps for the same logits, token history and mu = 2 * tau."""
+@pytest.mark.parametrize("where", ["device", "host"])
+def test_sampler_draws_from_the_reference_candidate_set(run, where):
+    """Non-greedy mode is the reference's sampler (llava_session.cpp:154-194), on the device by default or on the
+    host: the drawn token must be one of the candidates the oracle's restatement keeps for the same logits, token
+    history and mu = 2 * tau, and mu moves by the reference's rule."""
     s = run["ctx"].session()
+    s.set_host_sampler(where == "host")
     s.set_seed(7)
     for t in run["prompt"]:
         s.push_token(t)
@@ -343,6 +346,13 @@ def test_sampler_draws_from_the_reference_candidate_set(run):
     probs, ids, kept = np.empty(run["vocab"], np.float32), np.empty(run["vocab"], np.uint32), C.c_float()
     k = lib.orc_sampler_candidates(ob.ptr(logits), run["vocab"], ob.ptr(toks), toks.size, 10.0, ob.ptr(probs), ob.ptr(ids), kept)
     assert k >= 1 and tok in set(int(i) for i in ids[:k])
+    p_sel = float(probs[list(ids[:k]).index(tok)])
+    want_mu = lib.orc_sampler_mu_update(C.c_float(10.0), C.c_float(p_sel), kept)
+    assert abs(s.mirostat_mu() - want_mu) <= 1e-4
+    # a second token continues from there, without the host in the loop when drawn on the device
+    assert s.push_token(tok)
+    nxt = s.generate_greedy_on_device(2) if where == "device" else [s.predict_next_token()]
+    assert all(t < run["vocab"] for t in nxt)
     s.close()
 
 

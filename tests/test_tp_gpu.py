@@ -47,8 +47,10 @@ def ctx_is_single(ctx):
     return getattr(ctx, "n_ranks", 1) == 1
 
 
-def _worker(rank, world, path, id_q, out_q, peer_q=None):
+def _worker(rank, world, path, id_q, out_q, peer_q=None, one_launch=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if one_launch:
+        os.environ["LV_DECODE_STEP"] = "1"          # read when a session is created: every token as one persistent kernel
     pkg = load_pkg()
     klib = pkg.load_kernels()
     if rank == 0:
@@ -72,7 +74,7 @@ def _worker(rank, world, path, id_q, out_q, peer_q=None):
     out_q.put((rank, toks, [l.tobytes() for l in logits]))
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer", "peer-one-launch"])
 def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path, exchange):
     if _device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -84,8 +86,8 @@ def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path, exchange):
     ctx.close()
     mpc = mp.get_context("spawn")
     id_q, out_q = mpc.Queue(), mpc.Queue()
-    peer_q = [mpc.Queue() for _ in range(2)] if exchange == "peer" else None
-    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q, peer_q)) for r in range(2)]
+    peer_q = [mpc.Queue() for _ in range(2)] if exchange != "nccl" else None
+    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q, peer_q, exchange == "peer-one-launch")) for r in range(2)]
     for p in procs:
         p.start()
     results = {}
