@@ -21,6 +21,12 @@ extern "C" {
 /* ---- synthetic ggjt-v3 models (seeded N(0,0.02) weights; q4_0 = 2, q8_0 = 8) */
 int      llava_synth_write(const char* path, uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff_size,
                            uint32_t vocab_size, int wtype, uint64_t seed, uint32_t threads);
+/* the same with a file version (3, or 1: q4_0 blocks with f32 scales and interleaved nibbles, as old ggjt files have
+ * them) and, optionally, tok_embeddings stored as f32 */
+int      llava_synth_write_ex(const char* path, uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff_size,
+                              uint32_t vocab_size, int wtype, uint64_t seed, uint32_t threads, uint32_t file_version,
+                              int f32_embeddings);
+void     llava_synth_quantize_v1(const float* src, size_t count, uint8_t* dst);
 uint64_t llava_synth_file_size(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff_size,
                                uint32_t vocab_size, int wtype);
 float    llava_synth_normal(uint64_t seed, uint32_t tensor, uint64_t element);

@@ -40,7 +40,12 @@ enum {
     LV_ERR_COMM = 103          /* NCCL failure */
 };
 
-enum { LV_TYPE_F32 = 0, LV_TYPE_F16 = 1, LV_TYPE_Q4_0 = 2, LV_TYPE_Q8_0 = 8 };
+enum { LV_TYPE_F32 = 0, LV_TYPE_F16 = 1, LV_TYPE_Q4_0 = 2, LV_TYPE_Q8_0 = 8,
+       /* the q4_0 blocks of ggjt version 1 files (llava_buffer.cpp:66-71,350-359): 20 bytes, f32 scale, byte j holding
+        * elements 2j (low nibble) and 2j+1 (high); accepted by lv_gemv, lv_norm_gemv, lv_gemv_silu,
+        * lv_norm_gate_up_silu, lv_norm_qkv_kvappend and lv_dequant_rows (the shaders matmul_dim.comp /
+        * matmul_silu_ff.comp without the _fp16 suffix).  Not a GGML code: such files say "q4_0" too. */
+       LV_TYPE_Q4_0_V1 = 258 };
 
 typedef struct lv_ctx lv_ctx;
 typedef struct lv_graph lv_graph;

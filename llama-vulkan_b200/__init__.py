@@ -23,6 +23,7 @@ LV_ERR_TIMEOUT = 102
 LV_ERR_COMM = 103
 
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
+TYPE_Q4_0_V1 = 258
 
 _p = C.c_void_p
 _u32 = C.c_uint32
@@ -209,6 +210,8 @@ _u32p = C.POINTER(C.c_uint32)
 # name -> (restype, argtypes); mirrors include/llava_host.h
 HOST_API = {
     "llava_synth_write": (_int, [C.c_char_p, _u32, _u32, _u32, _u32, _u32, _int, _u64, _u32]),
+    "llava_synth_write_ex": (_int, [C.c_char_p, _u32, _u32, _u32, _u32, _u32, _int, _u64, _u32, _u32, _int]),
+    "llava_synth_quantize_v1": (None, [_p, _sz, _p]),
     "llava_synth_file_size": (_u64, [_u32, _u32, _u32, _u32, _u32, _int]),
     "llava_synth_normal": (C.c_float, [_u64, _u32, _u64]),
     "llava_synth_quantize": (None, [_p, _sz, _int, _p]),
@@ -293,11 +296,13 @@ def load_host():
     return _host
 
 
-def write_synthetic_model(path, geometry="7b", n_layers=None, wtype=TYPE_Q4_0, vocab=32000, seed=1234, threads=0):
-    """Writes a seeded synthetic ggjt-v3 model file and returns its size in bytes."""
+def write_synthetic_model(path, geometry="7b", n_layers=None, wtype=TYPE_Q4_0, vocab=32000, seed=1234, threads=0, file_version=3,
+                          f32_embeddings=False):
+    """Writes a seeded synthetic ggjt model file (version 3, or 1 for the old q4_0 block layout) and returns its size in bytes."""
     dim, heads, ff, depth = GEOMETRY[geometry]
     n_layers = depth if n_layers is None else n_layers
-    if not load_host().llava_synth_write(os.fsencode(path), dim, heads, n_layers, ff, vocab, wtype, seed, threads):
+    if not load_host().llava_synth_write_ex(os.fsencode(path), dim, heads, n_layers, ff, vocab, wtype, seed, threads, file_version,
+                                            int(f32_embeddings)):
         raise RuntimeError(f"cannot write synthetic model {path}")
     return os.path.getsize(path)
 

@@ -9,11 +9,14 @@
 namespace lv {
 
 // GGML tensor type codes as they appear in ggjt files.
-enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8 };
+// T_Q4_0_V1: the q4_0 blocks of ggjt version 1 files -- f32 scale, byte j holding elements 2j (low nibble) and 2j+1 (high);
+// not a GGML code: the file says "q4_0" and its version says which block layout that is.
+enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_0_V1 = 258 };
 
 constexpr int kBlockElems = 32;   // weights per quantisation block
 constexpr int kQ4BlockBytes = 18; // f16 scale + 16 nibble bytes (ggjt v3)
 constexpr int kQ8BlockBytes = 34; // f16 scale + 32 int8 (ggjt v3)
+constexpr int kQ4V1BlockBytes = 20; // f32 scale + 16 nibble bytes (ggjt v1)
 
 // Error word layout (one u32 per context, in device memory).  A kernel that
 // gives up on a wait ORs its code in and every later wait returns at once.

@@ -423,6 +423,7 @@ int gemv_configure(lv_ctx* ctx) {
     LV_CFG1(QT, 4, SILU, QTraits<QT>::kWarps); \
     LV_CFG1(QT, 2, SILU, QTraits<QT>::kWarps)
     LV_CFG(T_Q4_0, false); LV_CFG(T_Q4_0, true); LV_CFG(T_Q8_0, false); LV_CFG(T_Q8_0, true);
+    LV_CFG(T_Q4_0_V1, false); LV_CFG(T_Q4_0_V1, true);
     LV_CFG1(T_Q4_0, 4, false, 8); LV_CFG1(T_Q4_0, 2, false, 8); LV_CFG1(T_Q4_0, 4, true, 8); LV_CFG1(T_Q4_0, 2, true, 8);
 #undef LV_CFG
 #undef LV_CFG1
@@ -431,7 +432,7 @@ int gemv_configure(lv_ctx* ctx) {
 
 static int check_matrix_args(const void* const* ws, int nw, int wtype, uint32_t cols, uint32_t rows_mult,
                              const uint32_t* rows, uint32_t batch, uint32_t* row_bytes, const float* x, const float* norm_w) {
-    LV_REQUIRE(wtype == T_Q4_0 || wtype == T_Q8_0, "matrix type must be q4_0 (2) or q8_0 (8)");
+    LV_REQUIRE(wtype == T_Q4_0 || wtype == T_Q8_0 || wtype == T_Q4_0_V1, "matrix type must be q4_0 (2), q8_0 (8) or version-1 q4_0 (258)");
     LV_REQUIRE(cols != 0 && cols % 256 == 0, "cols must be a non-zero multiple of 256");
     LV_REQUIRE(batch >= 1 && batch <= 65535, "batch out of range");
     LV_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(norm_w) & 15u) == 0,
@@ -440,7 +441,7 @@ static int check_matrix_args(const void* const* ws, int nw, int wtype, uint32_t 
         LV_REQUIRE(ws[i] != nullptr && (reinterpret_cast<uintptr_t>(ws[i]) & 15u) == 0, "matrix pointer null or not 16-byte aligned");
         LV_REQUIRE(rows[i] != 0 && rows[i] % rows_mult == 0, "rows must be a non-zero multiple of 4");
     }
-    *row_bytes = cols / 32 * (wtype == T_Q4_0 ? kQ4BlockBytes : kQ8BlockBytes);
+    *row_bytes = cols / 32 * (wtype == T_Q4_0 ? kQ4BlockBytes : wtype == T_Q8_0 ? kQ8BlockBytes : kQ4V1BlockBytes);
     return LV_OK;
 }
 
@@ -467,6 +468,7 @@ static int gemv_dispatch(lv_ctx* ctx, GemvParams& p, int wtype, bool silu, uint3
         }
     }
     if (wtype == T_Q4_0) return silu ? launch_gemv_pick_streams<T_Q4_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q4_0, false>(ctx, p, batch);
+    if (wtype == T_Q4_0_V1) return silu ? launch_gemv_pick_streams<T_Q4_0_V1, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q4_0_V1, false>(ctx, p, batch);
     return silu ? launch_gemv_pick_streams<T_Q8_0, true>(ctx, p, batch) : launch_gemv_pick_streams<T_Q8_0, false>(ctx, p, batch);
 }
 

@@ -37,6 +37,11 @@ template <> struct QTraits<T_Q4_0> {
     static constexpr int kPairWords = 9;
     static constexpr int kWarps = 16;                 // consumer warps per CTA
 };
+template <> struct QTraits<T_Q4_0_V1> {
+    static constexpr int kBlockBytes = kQ4V1BlockBytes;
+    static constexpr int kPairWords = 10;                // an even stride: two lanes share a bank (the layout of old files; not tuned)
+    static constexpr int kWarps = 16;
+};
 template <> struct QTraits<T_Q8_0> {
     static constexpr int kBlockBytes = kQ8BlockBytes;
     static constexpr int kPairWords = 17;
@@ -182,7 +187,39 @@ __device__ __forceinline__ float block_sum_q8(const uint32_t (&q)[8], const uint
 // Contribution of one lane's block pair to one row stream.
 template <int QT>
 __device__ __forceinline__ float dot_pair(const uint32_t* __restrict__ sw, const PairX& px) {
-    if constexpr (QT == T_Q4_0) {
+    if constexpr (QT == T_Q4_0_V1) {
+        // ggjt v1 (llava_buffer.cpp:350-359): words 0 and 5 are the f32 scales, byte j of a block holds elements 2j and 2j+1.
+        // The records keep the elements in natural order, four per word; the low nibbles of a weight word meet the even
+        // elements of two record words, the high nibbles the odd ones.
+        uint32_t w[10];
+#pragma unroll
+        for (int i = 0; i < 10; ++i) w[i] = sw[i];
+        float out = 0.f;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t* q = &w[5 * blk + 1];
+            const uint32_t* a = &px.a[8 * blk];
+            const uint32_t* b = &px.b[8 * blk];
+            const uint32_t* c = &px.c[8 * blk];
+            int al = 0, bl = 0, cl = 0, ah = 0, bh = 0, ch = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // word k: bytes 4k..4k+3 = elements 8k..8k+7, which the natural-order records hold in words 2k and 2k+1
+                // (v3 layout of px: words 0..3 elements 0..15, words 4..7 elements 16..31)
+                const int r0 = 2 * k, r1 = 2 * k + 1;
+                const uint32_t lo = q[k] & 0x0f0f0f0fu, hi = q[k] & 0xf0f0f0f0u;
+                const uint32_t ae = __byte_perm(a[r0], a[r1], 0x6420), ao = __byte_perm(a[r0], a[r1], 0x7531);
+                const uint32_t be = __byte_perm(b[r0], b[r1], 0x6420), bo = __byte_perm(b[r0], b[r1], 0x7531);
+                const uint32_t ce = __byte_perm(c[r0], c[r1], 0x6420), co = __byte_perm(c[r0], c[r1], 0x7531);
+                al = dp4a_us(lo, ae, al); bl = dp4a_us(lo, be, bl); cl = dp4a_us(lo, ce, cl);
+                ah = dp4a_us(hi, ao, ah); bh = dp4a_us(hi, bo, bh); ch = dp4a_us(hi, co, ch);
+            }
+            const int hi_ab = (ah * 256 + bh) >> 4;
+            const int sum = ((al * 256 + bl + hi_ab) * 256 + cl + (ch >> 4)) - px.t8[blk];
+            out = fmaf(static_cast<float>(sum), __uint_as_float(w[5 * blk]) * px.scale[blk], out);
+        }
+        return out;
+    } else if constexpr (QT == T_Q4_0) {
         uint32_t w[9];
 #pragma unroll
         for (int i = 0; i < 9; ++i) w[i] = sw[i];

@@ -74,6 +74,19 @@ __global__ void dequant_rows_kernel(float* __restrict__ out, const uint8_t* __re
         return;
     }
     const uint32_t nb = cols / 32;
+    if (wtype == T_Q4_0_V1) {       // llava_buffer.cpp:350-359: f32 scale, byte j = elements 2j (low nibble) and 2j+1
+        const uint8_t* row = table + size_t(id) * nb * kQ4V1BlockBytes;
+        for (uint32_t b = threadIdx.x; b < nb; b += blockDim.x) {
+            const uint8_t* blk = row + size_t(b) * kQ4V1BlockBytes;
+            const float d = *reinterpret_cast<const float*>(blk);
+            for (int j = 0; j < 16; ++j) {
+                const int qv = blk[4 + j];
+                o[b * 32 + 2 * j] = static_cast<float>((qv & 0xf) - 8) * d;
+                o[b * 32 + 2 * j + 1] = static_cast<float>((qv >> 4) - 8) * d;
+            }
+        }
+        return;
+    }
     const uint32_t bb = wtype == T_Q4_0 ? kQ4BlockBytes : kQ8BlockBytes;
     const uint8_t* row = table + size_t(id) * nb * bb;
     for (uint32_t b = threadIdx.x; b < nb; b += blockDim.x) {
@@ -272,7 +285,7 @@ extern "C" int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int w
                                const uint32_t* first, uint32_t cols, uint32_t vocab, uint32_t n) {
     LV_ENTER(ctx);
     LV_REQUIRE(out && table && token_ids && n && vocab, "bad dequant arguments");
-    LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0, "unsupported table type");
+    LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0 || wtype == T_Q4_0_V1, "unsupported table type");
     LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
     LV_CUDA(launch_pdl(ctx, dequant_rows_kernel, dim3(n), dim3(256), 0, out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err));
     return LV_OK;

@@ -45,6 +45,19 @@ int llava_synth_write(const char* path, uint32_t dim, uint32_t n_heads, uint32_t
     return synth_write_ggjt(path, c, &err) ? 1 : 0;
 }
 
+int llava_synth_write_ex(const char* path, uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab,
+                         int wtype, uint64_t seed, uint32_t threads, uint32_t file_version, int f32_embeddings) {
+    synth_config c = make_cfg(dim, n_heads, n_layers, ff, vocab, wtype);
+    c.seed = seed;
+    c.threads = threads;
+    c.file_version = file_version;
+    c.f32_embeddings = f32_embeddings != 0;
+    std::string err;
+    return synth_write_ggjt(path, c, &err) ? 1 : 0;
+}
+
+void llava_synth_quantize_v1(const float* src, size_t count, uint8_t* dst) { synth_quantize_v1(src, count, dst); }
+
 uint64_t llava_synth_file_size(uint32_t dim, uint32_t n_heads, uint32_t n_layers, uint32_t ff, uint32_t vocab, int wtype) {
     return synth_file_size(make_cfg(dim, n_heads, n_layers, ff, vocab, wtype));
 }

@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "llava_context.h"
+#include "../../include/lv_b200.h"
 #include "llava_device_memory.h"
 #include "utils.h"
 
@@ -173,6 +174,16 @@ void llava_buffer::dump_raw(int out_fd, const string& name) {
     write_noshort(out_fd, header.data(), header.size());
     vector<u8> data(bytes);
     if (read_raw(0, data.data(), bytes)) write_noshort(out_fd, data.data(), data.size());
+}
+
+bool llava_buffer::weight_buffer_is_quantised() const {
+    return weight_buffer_is_f16() || (type == ggml_value_type::q4_0 && model_version == 1);
+}
+
+// Version-1 files store q4_0 with an f32 scale and interleaved nibbles (llava_buffer.cpp:66-71,350-359 of the
+// reference); the kernels take that layout under a code of its own.
+int llava_buffer::kernel_type() const {
+    return (type == ggml_value_type::q4_0 && model_version == 1) ? LV_TYPE_Q4_0_V1 : int(type);
 }
 
 bool llava_buffer::weight_buffer_is_f16() const {

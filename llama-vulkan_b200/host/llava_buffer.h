@@ -42,6 +42,8 @@ public:
     void dump_raw(int out_fd, const std::string& name);   // one trace-frame record (llava_buffer.cpp:497-522)
     const std::string& get_pretty_name() const { return pretty_name; }
     bool weight_buffer_is_f16() const;            // block scale stored as f16 (every ggjt v3 file)
+    bool weight_buffer_is_quantised() const;      // a block layout the kernels read: q4_0 / q8_0 of version 3, q4_0 of version 1
+    int kernel_type() const;                      // type code for the lv_* entry points: the GGML code, or LV_TYPE_Q4_0_V1
 
     llava_context* const context;
     const std::string backing_buffer_name;

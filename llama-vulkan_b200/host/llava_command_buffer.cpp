@@ -95,7 +95,7 @@ bool llava_command_buffer::record_execution() {
     // embedding rows of the tokens at positions config.token_count .. + batch (the reference
     // dequantises them on the host, llava_session.cpp:219-223)
     note(lv_dequant_rows(lv(), static_cast<float*>(s->current_thought->device_ptr()), c->tok_embeddings->device_ptr(),
-                         int(c->tok_embeddings->type), log, config, h.dim, h.vocab_size, batch_size));
+                         c->tok_embeddings->kernel_type(), log, config, h.dim, h.vocab_size, batch_size));
     llava_buffer* current = s->current_thought;
     for (u32 i = 0; i < c->get_layers().size(); ++i) current = c->get_layers()[i]->execute(this, s->get_layer_data()[i], current);
     if (with_head) {
@@ -107,7 +107,7 @@ bool llava_command_buffer::record_execution() {
         // normalisation takes residual + the ranks' sum
         if (c->tp_size() > 1 && c->fused_exchange())
             tp_arm_pull(2 * u32(c->get_layers().size()) - 1, h.dim, current == s->current_thought ? s->current_thought_sublayer : s->current_thought);
-        note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), int(c->output_w->type), last,
+        note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), c->output_w->kernel_type(), last,
                           static_cast<const float*>(c->norm_w->device_ptr()), h.vocab_size, h.dim, 1));
         // greedy choice, token log and position word in one launch; the kernel stores the token
         // into the pinned staging word itself
@@ -140,19 +140,19 @@ void llava_command_buffer::normalize_logit(llava_buffer* outbuf, llava_buffer* i
 void llava_command_buffer::matmul(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf) {
     if (!expect(inbuf->shape.first == matrix->shape.second && outbuf->shape.first == matrix->shape.first &&
                 inbuf->shape.second >= batch_size && outbuf->shape.second >= batch_size, "matmul shapes")) return;
-    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 0));
+    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), matrix->kernel_type(), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 0));
 }
 
 void llava_command_buffer::matmul_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* inbuf) {
     if (!expect(inbuf->shape.first == matrix->shape.second && outbuf->shape.first == matrix->shape.first &&
                 inbuf->shape.second >= batch_size && outbuf->shape.second >= batch_size, "matmul_add shapes")) return;
-    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 1));
+    note(lv_gemv(lv(), f32(outbuf), matrix->device_ptr(), matrix->kernel_type(), f32(inbuf), matrix->shape.first, matrix->shape.second, batch_size, 1));
 }
 
 void llava_command_buffer::matmul_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* inbuf) {
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&
                 outbuf->shape.first == w3->shape.first, "matmul_silu_ff shapes")) return;
-    note(lv_gemv_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), f32(inbuf), w3->shape.first, w3->shape.second, batch_size));
+    note(lv_gemv_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), w3->kernel_type(), f32(inbuf), w3->shape.first, w3->shape.second, batch_size));
 }
 
 void llava_command_buffer::kv_copy(llava_buffer* cache, llava_buffer* line) {
@@ -196,7 +196,7 @@ void llava_command_buffer::norm_qkv_kvappend(llava_buffer* q_out, llava_buffer* 
                 q_out->shape.first == wq->shape.first && k_cache->shape.second == wq->shape.first &&
                 v_cache->shape.second == wq->shape.first, "qkv shapes")) return;
     note(lv_norm_qkv_kvappend(lv(), f32(q_out), k_cache->device_ptr(), v_cache->device_ptr(), wq->device_ptr(), wk->device_ptr(),
-                              wv->device_ptr(), int(wq->type), f32(inbuf), f32(norm_weights),
+                              wv->device_ptr(), wq->kernel_type(), f32(inbuf), f32(norm_weights),
                               static_cast<u32*>(session->config_buffer->device_ptr()), wq->shape.first, dim, batch_size,
                               k_cache->shape.first));
 }
@@ -223,7 +223,7 @@ void llava_command_buffer::allreduce_add(llava_buffer* residual, llava_buffer* p
 bool llava_command_buffer::use_tensor_cores(const llava_buffer* matrix) const {
     // from six tokens on one pass over the matrix on the tensor cores beats one GEMV per token
     // (4096x4096 q4_0: 17 us flat against 4.3 us per token)
-    return batch_size >= kTensorCoreMinBatch && batch_size <= 64 && (matrix->type == ggml_value_type::q4_0 || matrix->type == ggml_value_type::q8_0) &&
+    return batch_size >= kTensorCoreMinBatch && batch_size <= 64 && matrix->weight_buffer_is_f16() &&        // v3 blocks only
            session->act_split != nullptr &&
            session->ctx->tp_size() == 1;
 }
@@ -240,20 +240,20 @@ void llava_command_buffer::gemm_qkv_kvappend(llava_buffer* q_out, llava_buffer* 
     if (!expect(wq->shape == wk->shape && wq->shape == wv->shape && wq->shape.second == dim && q_out->shape.first == wq->shape.first &&
                 k_cache->shape.second == wq->shape.first && v_cache->shape.second == wq->shape.first, "qkv shapes")) return;
     note(lv_gemm_tc_qkv_kvappend(lv(), f32(q_out), k_cache->device_ptr(), v_cache->device_ptr(), wq->device_ptr(), wk->device_ptr(),
-                                 wv->device_ptr(), int(wq->type), split->device_ptr(),
+                                 wv->device_ptr(), wq->kernel_type(), split->device_ptr(),
                                  static_cast<u32*>(session->config_buffer->device_ptr()), wq->shape.first, dim, batch_size,
                                  k_cache->shape.first));
 }
 
 void llava_command_buffer::gemm_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split) {
     if (!expect(outbuf->shape.first == matrix->shape.first, "gemm_add_inplace shapes")) return;
-    note(lv_gemm_tc(lv(), f32(outbuf), matrix->device_ptr(), int(matrix->type), split->device_ptr(), matrix->shape.first,
+    note(lv_gemm_tc(lv(), f32(outbuf), matrix->device_ptr(), matrix->kernel_type(), split->device_ptr(), matrix->shape.first,
                     matrix->shape.second, batch_size, 1));
 }
 
 void llava_command_buffer::gemm_silu_ff(llava_buffer* outbuf, llava_buffer* w3, llava_buffer* w1, llava_buffer* split) {
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && outbuf->shape.first >= w3->shape.first, "gemm_silu_ff shapes")) return;
-    note(lv_gemm_tc_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), split->device_ptr(), w3->shape.first,
+    note(lv_gemm_tc_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), w3->kernel_type(), split->device_ptr(), w3->shape.first,
                          w3->shape.second, batch_size));
 }
 
@@ -269,6 +269,6 @@ void llava_command_buffer::norm_matmul_silu_ff(llava_buffer* outbuf, llava_buffe
                                                llava_buffer* norm_weights) {
     if (!expect(w3->shape == w1->shape && w3->type == w1->type && inbuf->shape.first == w3->shape.second &&
                 outbuf->shape.first >= w3->shape.first, "norm_matmul_silu_ff shapes")) return;
-    note(lv_norm_gate_up_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), int(w3->type), f32(inbuf), f32(norm_weights),
+    note(lv_norm_gate_up_silu(lv(), f32(outbuf), w3->device_ptr(), w1->device_ptr(), w3->kernel_type(), f32(inbuf), f32(norm_weights),
                               w3->shape.first, w3->shape.second, batch_size));
 }

@@ -104,8 +104,8 @@ bool llava_context::open(const string& model_path, int device) {
     tok_embeddings = new llava_buffer(this, *emb, shared_memory);
     norm_w = new llava_buffer(this, *norm, shared_memory);
     output_w = new llava_buffer(this, *out, shared_memory);
-    if (norm_w->type != ggml_value_type::f32 || !output_w->weight_buffer_is_f16() || emb->shape1 != h.vocab_size ||
-        !(tok_embeddings->weight_buffer_is_f16() || tok_embeddings->type == ggml_value_type::f32)) {
+    if (norm_w->type != ggml_value_type::f32 || !output_w->weight_buffer_is_quantised() || emb->shape1 != h.vocab_size ||
+        !(tok_embeddings->weight_buffer_is_quantised() || tok_embeddings->type == ggml_value_type::f32)) {
         cerr << "[!] unsupported tensor types for tok_embeddings / norm / output" << endl;
         return false;
     }

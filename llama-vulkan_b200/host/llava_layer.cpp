@@ -45,11 +45,13 @@ llava_layer::llava_layer(llava_context* _context, u32 _layer_id) : layer_id(_lay
     attention_norm = make("attention_norm", tp_split::none);
     ffn_norm = make("ffn_norm", tp_split::none);
     if (ok) {
-        // norms must be f32 vectors, matrices quantised with an f16 block scale (ggjt v3)
+        // norms must be f32 vectors, matrices q4_0 / q8_0 blocks of ggjt v3 or q4_0 blocks of ggjt v1 (the combinations
+        // the reference loads, llava_buffer.cpp:63-99), all of one kind
         for (llava_buffer* m : {attention_wq, attention_wk, attention_wv, attention_wo, feed_forward_w1, feed_forward_w2, feed_forward_w3})
-            ok = ok && m->weight_buffer_is_f16();
+            ok = ok && m->weight_buffer_is_quantised() && m->kernel_type() == attention_wq->kernel_type();
+        if (n_ranks > 1) ok = ok && attention_wq->weight_buffer_is_f16();      // shards are packed in v3 blocks only
         ok = ok && attention_norm->type == ggml_value_type::f32 && ffn_norm->type == ggml_value_type::f32;
-        if (!ok) cerr << "[!] layer " << layer_id << ": unsupported tensor types (need q4_0/q8_0 ggjt v3 matrices, f32 norms)" << endl;
+        if (!ok) cerr << "[!] layer " << layer_id << ": unsupported tensor types (need q4_0/q8_0 ggjt v3 or q4_0 ggjt v1 matrices, f32 norms)" << endl;
     }
     valid = ok;
 }

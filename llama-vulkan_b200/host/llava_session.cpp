@@ -99,8 +99,8 @@ void llava_session::ensure_step_plan() {
         m.shard_cols_o = layers[0]->wo()->shape.second;
         m.shard_cols_2 = layers[0]->w2()->shape.second;
     }
-    m.wtype = int(ctx->output_w->type);
-    m.emb_type = int(ctx->tok_embeddings->type);
+    m.wtype = ctx->output_w->kernel_type();
+    m.emb_type = ctx->tok_embeddings->kernel_type();
     m.weights_base = ctx->weights_memory()->device_base();
     m.weights_bytes = ctx->weights_memory()->get_size();
     m.tok_embeddings = ctx->tok_embeddings->device_ptr();

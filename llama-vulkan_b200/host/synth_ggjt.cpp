@@ -42,12 +42,13 @@ struct tensor_plan {
     u64 header_at, data_at, data_bytes;
 };
 
-size_t block_bytes(ggml_value_type t) { return t == ggml_value_type::q4_0 ? 18 : 34; }
+size_t block_bytes(ggml_value_type t, u32 version = 3) { return t == ggml_value_type::q4_0 ? (version == 1 ? 20 : 18) : 34; }
 
 bool valid(const synth_config& c) {
     return c.dim && c.n_heads && c.n_layers && c.ff_size && c.vocab_size >= 259 && c.dim % c.n_heads == 0 &&
            c.dim % 32 == 0 && c.ff_size % 32 == 0 &&
-           (c.wtype == ggml_value_type::q4_0 || c.wtype == ggml_value_type::q8_0);
+           (c.wtype == ggml_value_type::q4_0 || c.wtype == ggml_value_type::q8_0) &&
+           (c.file_version == 3 || (c.file_version == 1 && c.wtype == ggml_value_type::q4_0));
 }
 
 // Token strings: ids 0-2 specials, 3-258 the 256 single bytes (the tokenizer's byte fallback
@@ -82,13 +83,13 @@ vector<tensor_plan> make_plan(const synth_config& c, const vector<ggml_token>& v
         at += 4 * (cols == 1 ? 4 : 5) + name.size();
         at = (at + 31) & ~u64(31);
         p.data_at = at;
-        p.data_bytes = type == ggml_value_type::f32 ? u64(rows) * cols * 4 : u64(rows) * cols / 32 * block_bytes(type);
+        p.data_bytes = type == ggml_value_type::f32 ? u64(rows) * cols * 4 : u64(rows) * cols / 32 * block_bytes(type, c.file_version);
         at += p.data_bytes;
         plan.push_back(p);
     };
     const auto W = c.wtype;
     const auto F = ggml_value_type::f32;
-    add("tok_embeddings.weight", c.vocab_size, c.dim, W);
+    add("tok_embeddings.weight", c.vocab_size, c.dim, c.f32_embeddings ? F : W);
     add("norm.weight", c.dim, 1, F);
     add("output.weight", c.vocab_size, c.dim, W);
     for (u32 l = 0; l < c.n_layers; ++l) {
@@ -113,6 +114,21 @@ float synth_normal(u64 seed, u32 tensor, u64 element) {
     float z0, z1;
     normal_pair(seed, tensor, element >> 1, &z0, &z1);
     return (element & 1) ? z1 : z0;
+}
+
+void synth_quantize_v1(const float* src, size_t count, u8* dst) {
+    for (size_t b = 0; b < count / 32; ++b) {
+        const float* w = src + b * 32;
+        float amax = 0.f;
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(w[j]));
+        const float d = amax / 8.0f;
+        const float inv = d > 0.f ? 1.0f / d : 0.f;
+        u8* out = dst + b * 20;
+        memcpy(out, &d, 4);
+        u8 q[32];
+        for (int j = 0; j < 32; ++j) q[j] = u8(fminf(15.f, fmaxf(0.f, rintf(w[j] * inv) + 8.f)));
+        for (int j = 0; j < 16; ++j) out[4 + j] = u8(q[2 * j] | (q[2 * j + 1] << 4));
+    }
 }
 
 void synth_quantize(const float* src, size_t count, ggml_value_type wtype, u8* dst) {
@@ -168,7 +184,7 @@ bool synth_write_ggjt(const string& path, const synth_config& cfg, string* error
     if (map == MAP_FAILED) return fail("cannot map " + path + ": " + strerror(errno));
 
     // header, vocabulary and tensor records (ggjt layout: ggml_file.cpp:46-122 of the reference)
-    ggml_header h{0x67676a74u, 3, cfg.vocab_size, cfg.dim, 256, cfg.n_heads, cfg.n_layers, cfg.dim / cfg.n_heads, u32(cfg.wtype)};
+    ggml_header h{0x67676a74u, cfg.file_version, cfg.vocab_size, cfg.dim, 256, cfg.n_heads, cfg.n_layers, cfg.dim / cfg.n_heads, u32(cfg.wtype)};
     memcpy(map, &h, sizeof h);
     u64 at = sizeof h;
     for (const auto& t : vocab) {
@@ -210,13 +226,26 @@ bool synth_write_ggjt(const string& path, const synth_config& cfg, string* error
             const size_t i = next.fetch_add(1);
             if (i >= items.size()) return;
             const tensor_plan& p = plan[items[i].tensor];
+            if (p.type == ggml_value_type::f32 && p.cols != 1) {   // f32 embedding rows: the N(0, 0.02) values themselves
+                float* out = reinterpret_cast<float*>(map + p.data_at);
+                for (u32 r = items[i].row0; r < items[i].row1; ++r) {
+                    const u64 e0 = u64(r) * p.cols;
+                    for (u32 k = 0; k < p.cols; k += 2) {
+                        float z0, z1;
+                        normal_pair(cfg.seed, items[i].tensor, (e0 + k) >> 1, &z0, &z1);
+                        out[e0 + k] = 0.02f * z0;
+                        out[e0 + k + 1] = 0.02f * z1;
+                    }
+                }
+                continue;
+            }
             if (p.type == ggml_value_type::f32) {         // norm vectors: N(1, 0.01)
                 float* out = reinterpret_cast<float*>(map + p.data_at);
                 for (u32 e = items[i].row0; e < items[i].row1; ++e) out[e] = 1.0f + 0.01f * synth_normal(cfg.seed, items[i].tensor, e);
                 continue;
             }
             row.resize(p.cols);
-            const size_t rb = size_t(p.cols) / 32 * block_bytes(p.type);
+            const size_t rb = size_t(p.cols) / 32 * block_bytes(p.type, cfg.file_version);
             for (u32 r = items[i].row0; r < items[i].row1; ++r) {
                 const u64 e0 = u64(r) * p.cols;            // cols is even: pairs never straddle rows
                 for (u32 k = 0; k < p.cols; k += 2) {
@@ -225,7 +254,8 @@ bool synth_write_ggjt(const string& path, const synth_config& cfg, string* error
                     row[k] = 0.02f * z0;
                     row[k + 1] = 0.02f * z1;
                 }
-                synth_quantize(row.data(), p.cols, p.type, map + p.data_at + size_t(r) * rb);
+                if (cfg.file_version == 1) synth_quantize_v1(row.data(), p.cols, map + p.data_at + size_t(r) * rb);
+                else synth_quantize(row.data(), p.cols, p.type, map + p.data_at + size_t(r) * rb);
             }
         }
     };

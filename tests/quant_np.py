@@ -4,6 +4,7 @@ matrices with the block formulas the synthetic model writer uses
 import numpy as np
 
 Q4_0, Q8_0 = 2, 8
+Q4_0_V1 = 258          # kernel type code of version-1 q4_0 blocks (the oracle calls them type 2, version 1)
 
 
 def quantize_q4_0(w):
@@ -29,6 +30,18 @@ def quantize_q8_0(w):
     out = np.empty((w.shape[0], 34), np.uint8)
     out[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
     out[:, 2:] = q.view(np.uint8)
+    return out.reshape(-1)
+
+
+def quantize_q4_0_v1(w):
+    """ggjt version 1: f32 scale = absmax / 8, byte j = elements 2j (low nibble) and 2j + 1 (high nibble)."""
+    w = np.asarray(w, np.float32).reshape(-1, 32)
+    d = (np.abs(w).max(axis=1) / np.float32(8)).astype(np.float32)
+    inv = np.where(d > 0, 1.0 / np.where(d > 0, d, 1), 0).astype(np.float32)
+    q = np.clip(np.rint(w * inv[:, None]) + 8, 0, 15).astype(np.uint8)
+    out = np.empty((w.shape[0], 20), np.uint8)
+    out[:, 0:4] = d.view(np.uint8).reshape(-1, 4)
+    out[:, 4:] = q[:, 0::2] | (q[:, 1::2] << 4)
     return out.reshape(-1)
 
 

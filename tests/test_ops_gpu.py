@@ -100,6 +100,49 @@ def test_gemv_and_residual_add(gpu, pkg, wtype, rows, cols):
         gpu.free(d)
 
 
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (4096, 11008), (5120, 13824), (8, 512)])
+def test_gemv_on_version_1_blocks(gpu, pkg, rows, cols):
+    """q4_0 as ggjt version 1 files store it (f32 scale, byte j = elements 2j and 2j+1; matmul_dim.comp / matmul_ff.comp
+    without the _fp16 suffix, llava_buffer.cpp:193-224): plain, add-in-place, with a norm in front, and the SiLU pair."""
+    rng = np.random.default_rng(rows * 3 + cols)
+    W = qn.quantize_q4_0_v1((rng.standard_normal((rows, cols)) * 0.02).astype(np.float32))
+    x = rng.standard_normal(cols).astype(np.float32)
+    base = rng.standard_normal(rows).astype(np.float32)
+    dW, dx, d_out = gpu.upload(W), gpu.upload(x), gpu.upload(base)
+    want = ob.gemv(W, qn.Q4_0, x, rows, cols, workers_for(cols), version=1)
+    pkg.check(gpu.lib.lv_gemv(gpu.handle, d_out, dW, qn.Q4_0_V1, dx, rows, cols, 1, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, rows), base + want)
+    nw = (1 + 0.01 * rng.standard_normal(cols)).astype(np.float32)
+    pkg.check(gpu.lib.lv_norm_gemv(gpu.handle, d_out, dW, qn.Q4_0_V1, dx, gpu.upload(nw), rows, cols, 1))
+    gpu.sync()
+    close(gpu.download(d_out, np.float32, rows), ob.gemv(W, qn.Q4_0, ob.norm(x, nw), rows, cols, workers_for(cols), version=1))
+    if rows % 2 == 0 and rows >= 4096:
+        half = rows // 2
+        d_g = gpu.alloc(half * 4)
+        rb = cols // 32 * 20
+        pkg.check(gpu.lib.lv_gemv_silu(gpu.handle, d_g, dW, pkg.offset(dW, half * rb), qn.Q4_0_V1, dx, half, cols, 1))
+        gpu.sync()
+        close(gpu.download(d_g, np.float32, half), ob.gemv_silu(W[:half * rb], W[half * rb:], qn.Q4_0, x, half, cols, workers_for(cols), version=1))
+        gpu.free(d_g)
+    for d in (dW, dx, d_out):
+        gpu.free(d)
+
+
+def test_dequant_rows_of_version_1_blocks_bit_exact(gpu, pkg):
+    rng = np.random.default_rng(41)
+    vocab, cols = 64, 4096
+    table = qn.quantize_q4_0_v1((rng.standard_normal((vocab, cols)) * 0.02).astype(np.float32))
+    ids = np.array([5, 0, 63, 17], np.uint32)
+    d_out = gpu.alloc(ids.size * cols * 4)
+    pkg.check(gpu.lib.lv_dequant_rows(gpu.handle, d_out, gpu.upload(table), qn.Q4_0_V1, gpu.upload(ids), None, cols, vocab, ids.size))
+    gpu.sync()
+    got = gpu.download(d_out, np.float32, ids.size * cols).reshape(ids.size, cols)
+    rb = cols // 32 * 20
+    for z, t in enumerate(ids):
+        assert np.array_equal(got[z].view(np.uint32), ob.dequant(table[t * rb:(t + 1) * rb], qn.Q4_0, cols, version=1).view(np.uint32))
+
+
 def _outlier_activations(rng, cols):
     """Activations as a trained LLaMA's residual stream has them: a few channels two to three orders of
     magnitude above the rest -- alone in a 32-block, several in one block, in many blocks -- plus an
