@@ -48,6 +48,8 @@ int      llava_dequantize(const void* in, int type, uint32_t model_version, floa
 
 /* ---- llava_context (llava_context.h:21-42) */
 void*    llava_context_open(const char* model_path, int device);   /* NULL on failure */
+/* the model file only (vocabulary, tensor table), no device: serves the front end's session-independent requests */
+void*    llava_context_open_model_only(const char* model_path);
 /* tensor-parallel: this process is rank `rank` of `n_ranks`, one GPU each; nccl_id = the 128 bytes
  * of lv_comm_unique_id made by rank 0 (ignored when n_ranks == 1) */
 void*    llava_context_open_sharded(const char* model_path, int device, uint32_t rank, uint32_t n_ranks,
@@ -121,6 +123,16 @@ void     llava_wrapper_push_order(void* wrapper, uint32_t client_id, uint32_t re
                                   const char* s, size_t len);
 void     llava_wrapper_join(void* wrapper);
 void     llava_wrapper_destroy(void* wrapper);
+
+/* ---- lsrv::tlv_server: the TCP front end of the session protocol (reference server/server.cpp:44-331,
+ * server/client.cpp:43-313).  create binds and listens (port 0 = any free port; NULL address = 127.0.0.1) and
+ * returns NULL on failure; start runs the event loop on a thread of its own; stop kills the sessions, waits
+ * for them and joins the loop.  deterministic != 0: sessions decode greedily (the reference always samples). */
+void*    llava_server_create(void* ctx, uint32_t port, const char* bind_address, int deterministic);
+uint32_t llava_server_port(void* server);
+void     llava_server_start(void* server);
+void     llava_server_stop(void* server);
+void     llava_server_destroy(void* server);
 
 #ifdef __cplusplus
 }

@@ -9,6 +9,7 @@ libraries are missing, ``load_kernels()`` / ``load_host()`` raise.
 """
 import ctypes as C
 import os
+import struct
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 KERNEL_LIB = os.path.join(HERE, "liblv_b200.so")
@@ -226,6 +227,7 @@ HOST_API = {
     "ggml_file_token": (_u32, [_p, _u32, C.c_char_p, _u32, _f32p]),
     "llava_dequantize": (_int, [_p, _int, _u32, _p, _u32]),
     "llava_context_open": (_p, [C.c_char_p, _int]),
+    "llava_context_open_model_only": (_p, [C.c_char_p]),
     "llava_context_open_sharded": (_p, [C.c_char_p, _int, _u32, _u32, _p]),
     "llava_context_peer_window_create": (_int, [_p, _p]),
     "llava_context_peer_connect": (_int, [_p, _p]),
@@ -274,6 +276,11 @@ HOST_API = {
     "llava_wrapper_push_order": (None, [_p, _u32, _u32, _u32, _u32, C.c_char_p, _sz]),
     "llava_wrapper_join": (None, [_p]),
     "llava_wrapper_destroy": (None, [_p]),
+    "llava_server_create": (_p, [_p, _u32, C.c_char_p, _int]),
+    "llava_server_port": (_u32, [_p]),
+    "llava_server_start": (None, [_p]),
+    "llava_server_stop": (None, [_p]),
+    "llava_server_destroy": (None, [_p]),
 }
 
 NO_TOKEN = 0xFFFFFFFF
@@ -362,7 +369,9 @@ class HostContext:
 
     def __init__(self, model_path, device=0, rank=0, n_ranks=1, nccl_id=None):
         self.lib = load_host()
-        if n_ranks == 1:
+        if device is None:            # the model file only: no device context, no sessions
+            self.handle = self.lib.llava_context_open_model_only(os.fsencode(model_path))
+        elif n_ranks == 1:
             self.handle = self.lib.llava_context_open(os.fsencode(model_path), device)
         else:
             buf = (C.c_uint8 * 128).from_buffer_copy(bytes(nccl_id))
@@ -516,3 +525,82 @@ class Session:
         if not self.lib.llava_session_read_kv(self.handle, layer, which, row0, nrows, out.ctypes.data_as(_p)):
             raise RuntimeError("read_kv failed")
         return out
+
+
+class Server:
+    """lsrv::tlv_server on a thread of its own: the TCP front end of the session protocol
+    (reference server/server.cpp:44-331).  `port` 0 binds any free port; read it back from `.port`."""
+
+    def __init__(self, ctx, port=0, address="127.0.0.1", deterministic=False):
+        self.lib = ctx.lib
+        self.handle = self.lib.llava_server_create(ctx.handle, port, address.encode(), int(deterministic))
+        if not self.handle:
+            raise RuntimeError(f"cannot listen on {address}:{port}")
+        self.port = self.lib.llava_server_port(self.handle)
+        self.lib.llava_server_start(self.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.llava_server_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class Client:
+    """A blocking client of the session protocol: frames of {u32 command, u32 request id, u32 length, payload}
+    out, {u32 reply opcode, u32 request id (0 = broadcast), u32 size, payload} back
+    (reference server/client.cpp:116-144 and 302-313)."""
+
+    # requests (server/types.h:50-71) and replies (server/types.h:73-84)
+    GET_TOKEN_MAP, NEW_SESSION, LIST_SESSIONS = 0, 1, 2
+    GET_SESSION_TOKENS, SUBSCRIBE, UNSUBSCRIBE, KILL_SESSION, START, STOP, TICK, GET_STATUS = 16, 17, 18, 19, 20, 21, 22, 23
+    REWIND, ADD_TOKEN, ADD_TEXT, SET_OPTIONS, SAVE_FRAME, SNAPSHOT, RESTORE = 32, 33, 34, 35, 36, 37, 38
+    NEW_TOKEN, BUFFER, TOKEN_MAP, SESSION_CREATED, SESSION_LIST, DROPPED_SESSION, ACK, STATUS = range(8)
+
+    def __init__(self, port, address="127.0.0.1", timeout=30.0):
+        import socket
+        self.sock = socket.create_connection((address, port), timeout=timeout)
+        self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+        self._request = 0
+
+    def close(self):
+        self.sock.close()
+
+    def send(self, command, payload=b"", request_id=None):
+        """Sends one request; returns its request id."""
+        if request_id is None:
+            self._request += 1
+            request_id = self._request
+        self.sock.sendall(struct.pack("<III", command, request_id, len(payload)) + payload)
+        return request_id
+
+    def _exactly(self, n):
+        parts = []
+        while n:
+            b = self.sock.recv(n)
+            if not b:
+                raise ConnectionError("server closed the connection")
+            parts.append(b)
+            n -= len(b)
+        return b"".join(parts)
+
+    def recv(self):
+        """-> (reply opcode, request id, payload) of the next packet."""
+        op, request_id, size = struct.unpack("<III", self._exactly(12))
+        return op, request_id, self._exactly(size)
+
+    def call(self, command, payload=b""):
+        """Sends a request and returns (opcode, payload) of the reply that carries its id; packets that arrive
+        in between (broadcasts, other replies) are collected in `.others`."""
+        rid = self.send(command, payload)
+        self.others = []
+        while True:
+            op, got, data = self.recv()
+            if got == rid:
+                return op, data
+            self.others.append((op, got, data))

@@ -14,8 +14,10 @@
 #include <condition_variable>
 #include <deque>
 #include <mutex>
+#include <thread>
 
 #include "server/session_wrapper.h"
+#include "server/tlv_server.h"
 #include "synth_ggjt.h"
 #include "tp_shard.h"
 
@@ -135,6 +137,15 @@ int llava_dequantize(const void* in, int type, uint32_t model_version, float* ou
 void* llava_context_open(const char* model_path, int device) {
     auto* c = new llava_context();
     if (!c->open(model_path, device)) {
+        delete c;
+        return nullptr;
+    }
+    return c;
+}
+
+void* llava_context_open_model_only(const char* model_path) {
+    auto* c = new llava_context();
+    if (!c->open_model_only(model_path)) {
         delete c;
         return nullptr;
     }
@@ -309,6 +320,39 @@ void llava_wrapper_join(void* w) { static_cast<lsrv::session_wrapper*>(w)->join(
 void llava_wrapper_destroy(void* w) { delete static_cast<lsrv::session_wrapper*>(w); }
 void llava_wrapper_push_order(void* w, uint32_t client_id, uint32_t request_id, uint32_t opcode, uint32_t arg1, const char* s, size_t len) {
     static_cast<lsrv::session_wrapper*>(w)->push_order(client_id, request_id, opcode, arg1, s ? std::string(s, len) : std::string());
+}
+
+// ---- lsrv::tlv_server on a thread of its own ----
+namespace {
+struct served {
+    lsrv::tlv_server server;
+    std::thread loop;
+    served(llava_context* c, uint16_t port, const char* addr) : server(c, port, addr, false) {}
+};
+}  // namespace
+
+void* llava_server_create(void* ctx, uint32_t port, const char* bind_address, int deterministic) {
+    lsrv::session_wrapper::set_deterministic_sessions(deterministic != 0);
+    auto* s = new served(static_cast<llava_context*>(ctx), uint16_t(port), bind_address ? bind_address : "127.0.0.1");
+    if (!s->server.open()) {
+        delete s;
+        return nullptr;
+    }
+    return s;
+}
+uint32_t llava_server_port(void* server) { return static_cast<served*>(server)->server.port(); }
+void llava_server_start(void* server) {
+    auto* s = static_cast<served*>(server);
+    if (!s->loop.joinable()) s->loop = std::thread([s]() { s->server.serve_forever(); });
+}
+void llava_server_stop(void* server) {
+    auto* s = static_cast<served*>(server);
+    s->server.stop();
+    if (s->loop.joinable()) s->loop.join();
+}
+void llava_server_destroy(void* server) {
+    llava_server_stop(server);
+    delete static_cast<served*>(server);
 }
 
 }  // extern "C"

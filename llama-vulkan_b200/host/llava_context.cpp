@@ -15,6 +15,7 @@
 #include "llava_device_memory.h"
 #include "llava_layer.h"
 #include "llava_session.h"
+#include "server/tlv_server.h"
 #include "synth_ggjt.h"
 
 using namespace std;
@@ -68,6 +69,12 @@ bool llava_context::peer_window_create(u8* handle64) {
 bool llava_context::peer_connect(const u8* handles) {
     peers_connected = lv_context != nullptr && lv_peer_connect(lv_context, int(rank_), handles) == LV_OK;
     return peers_connected;
+}
+
+bool llava_context::open_model_only(const string& model_path) {
+    close_all();
+    model = new ggml_file(model_path.c_str());
+    return model->is_open();
 }
 
 bool llava_context::open(const string& model_path, int device) {
@@ -168,11 +175,12 @@ bool read_token_file(const string& path, vector<u32>* out) {
 
 // Flags of the reference (llava_context.cpp:163-200) that still mean something, plus the
 // ones its CLI lacks: --greedy, --tokens, --n-predict, --ignore-eos, --seed, --device,
-// --on-device and --write-synthetic.
+// --on-device, --write-synthetic, and --port / --bind for --server.
 int llava_context::run(int argc, char** argv) {
     bool server_mode = false, only_print_header = false, greedy = false, ignore_eos = false, on_device = false;
     bool model_path_provided = false, have_seed = false;
-    string model_path, tokens_path, synth_spec;
+    string model_path, tokens_path, synth_spec, bind_address = "0.0.0.0";
+    u32 server_port = 1337;
     string prompt = "The ten best monuments to see in Paris are";
     u32 n_predict = 0, seed = 0;
     int device = 0;
@@ -196,7 +204,7 @@ int llava_context::run(int argc, char** argv) {
             model_path = need_value(i);
         } else if (streq(a, "--help") || streq(a, "-h")) {
             cout << (argc ? argv[0] : "./vulkan_llama")
-                 << " [-h] [-m model.bin] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
+                 << " [-h] [-m model.bin] [--server [--port P] [--bind ADDR]] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
                     " [--device D] [--on-device] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
                  << endl;
             exit(0);
@@ -207,6 +215,10 @@ int llava_context::run(int argc, char** argv) {
             exit(1);
         } else if (streq(a, "--server") || streq(a, "-s")) {
             server_mode = true;
+        } else if (streq(a, "--port")) {
+            server_port = u32(strtoul(need_value(i), nullptr, 10));
+        } else if (streq(a, "--bind")) {
+            bind_address = need_value(i);
         } else if (streq(a, "--sigdebug")) {
             signal_debug = true;
         } else if (streq(a, "--greedy")) {
@@ -276,16 +288,20 @@ int llava_context::run(int argc, char** argv) {
         f.print_info();
         return 0;
     }
-    if (server_mode) {
-        cerr << "[!] the TCP server front end is not part of this build; sessions can be driven through lsrv::session_wrapper" << endl;
-        return 1;
-    }
     if (!setup_signal_handling()) {
         cerr << "[!] Cannot setup signal handling" << endl;
         return 1;
     }
     if (!open(model_path, device)) return 1;
     if (verbosity) cout << "Selected device: cuda:" << device << " (" << lv_ctx_sm_count(lv_context) << " SMs)" << endl;
+    if (server_mode) {
+        // llava_context.cpp:246-249: sessions are created and driven by the clients; standard input or a signal ends it
+        lsrv::session_wrapper::set_deterministic_sessions(greedy);
+        lsrv::tlv_server server(this, u16(server_port), bind_address.c_str(), true);
+        if (!server.open()) return 1;
+        server.serve_forever();
+        return 0;
+    }
 
     // generation loop, llava_context.cpp:336-373
     const u32 eos_id = 2;

@@ -24,6 +24,10 @@ public:
     int run(int argc, char** argv);
     // Opens the model, creates the device context and uploads all layers.
     bool open(const std::string& model_path, int device = 0);
+    // Reads the model file only (header, vocabulary, tensor table) and creates no device context: enough for the
+    // front end's session-independent requests; sessions cannot be created on such a context.
+    bool open_model_only(const std::string& model_path);
+    bool has_device() const { return lv_context != nullptr; }
     // Tensor-parallel open: this process is rank `rank` of `n_ranks` (one GPU each) and uploads
     // only its shard of every layer.  nccl_id: the 128 bytes of lv_comm_unique_id made by rank 0.
     bool open_sharded(const std::string& model_path, int device, u32 rank, u32 n_ranks, const u8* nccl_id);

@@ -2,7 +2,7 @@
 // run/tick loop that overlaps order processing with token evaluation, and outbound packets
 // handed back to the owner.  Counterpart of the reference's lsrv::session_wrapper
 // (server/session_wrapper.h:17-23, server/session_wrapper.cpp:19-229); the owner is an
-// interface here because the reference's llava_server (TCP front end) is not part of this build.
+// interface here so that the TCP front end (lsrv::tlv_server) and an in-process collector can both drive it.
 #ifndef LLAVA_B200_SESSION_WRAPPER_H
 #define LLAVA_B200_SESSION_WRAPPER_H
 

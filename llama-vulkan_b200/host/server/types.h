@@ -1,5 +1,5 @@
-// Opcodes and reply codes of the reference's session protocol (server/types.h:50-84) as far
-// as lsrv::session_wrapper needs them; the TCP front end itself is not part of this build.
+// Opcodes and reply codes of the reference's session protocol (server/types.h:50-84), shared by
+// lsrv::session_wrapper (one thread per session) and lsrv::tlv_server (the TCP front end).
 #ifndef LLAVA_B200_SERVER_TYPES_H
 #define LLAVA_B200_SERVER_TYPES_H
 

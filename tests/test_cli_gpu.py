@@ -54,3 +54,34 @@ def test_cli_print_header_and_missing_model(cli):
     assert b"4096" in out and b"32000" in out
     assert subprocess.run([cli["exe"], "-m", cli["model"] + ".missing", "--greedy", "--n-predict", "1"], timeout=120,
                           stdout=subprocess.PIPE, stderr=subprocess.PIPE).returncode != 0
+
+
+def test_cli_server_mode_generates_over_tcp(cli, pkg):
+    """`--server`: the process listens, a client makes a session, feeds the prompt and ticks; a line on standard
+    input ends the server (reference llava_context.cpp:246-249, server/server.cpp:178-184)."""
+    import struct
+    p = subprocess.Popen([cli["exe"], "-m", cli["model"], "--server", "--port", "0", "--bind", "127.0.0.1", "--greedy"],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE)
+    try:
+        port = None
+        for _ in range(50):
+            line = p.stdout.readline()
+            assert line, "the server ended before it listened"
+            if b"Started server on" in line:
+                port = int(line.rsplit(b":", 1)[1])
+                break
+        assert port
+        c = pkg.Client(port, timeout=120.0)
+        op, sid = c.call(c.NEW_SESSION)
+        assert op == c.SESSION_CREATED
+        for t in prompt_tokens(12):
+            assert c.call(c.ADD_TOKEN, sid + struct.pack("<I", t)) == (c.ACK, struct.pack("<I", 0))
+        for i in range(3):
+            assert c.call(c.TICK, sid) == (c.NEW_TOKEN, sid + struct.pack("<II", cli["greedy"][i], 12 + i))
+        c.close()
+        p.stdin.write(b"\n")
+        p.stdin.flush()
+        assert p.wait(timeout=120) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()

@@ -1,0 +1,158 @@
+"""The TCP front end (lsrv::tlv_server) over loopback.
+
+Without a GPU: the framing and every reply that needs no session (token map, session list, the error
+acknowledgements of reference server/client.cpp:146-300).  With one: every opcode against a live session,
+the generated tokens compared with the CPU oracle's greedy trajectory.
+"""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import quant_np as qn
+
+OK, NOK, NO_SUCH_SESSION, TICK_ALREADY_REQUESTED, ALREADY_RUNNING, NOT_TRACING, BATCHED_TICK, BAD_ARGUMENTS, UNKNOWN_COMMAND = range(9)
+
+
+def ack(code):
+    return struct.pack("<I", code)
+
+
+@pytest.fixture(scope="module")
+def tiny_model(pkg, tmp_path_factory):
+    path = str(tmp_path_factory.mktemp("srv") / "tiny.bin")
+    pkg.write_synthetic_model(path, "7b", n_layers=2, wtype=qn.Q4_0)
+    return path
+
+
+def test_session_independent_requests_and_framing(pkg, tiny_model):
+    ctx = pkg.HostContext(tiny_model, None)
+    model = pkg.ModelFile(tiny_model)
+    with pkg.Server(ctx) as server:
+        assert server.port != 0
+        a, b = pkg.Client(server.port), pkg.Client(server.port)
+        # token map: {u32 length, bytes} per token, in id order
+        op, data = a.call(a.GET_TOKEN_MAP)
+        assert op == a.TOKEN_MAP
+        at, texts = 0, []
+        while at < len(data):
+            n, = struct.unpack_from("<I", data, at)
+            texts.append(data[at + 4:at + 4 + n])
+            at += 4 + n
+        assert at == len(data) and len(texts) == model.vocab_size
+        assert texts[:300] == [model.token(i)[0] for i in range(300)]
+        assert a.call(a.LIST_SESSIONS) == (a.SESSION_LIST, b"")
+        # no device behind this context: a session cannot be made
+        assert a.call(a.NEW_SESSION) == (a.ACK, ack(NOK))
+        # error replies
+        assert a.call(5) == (a.ACK, ack(UNKNOWN_COMMAND))                                   # below 16, not a command
+        assert a.call(a.TICK, b"\x01\x00") == (a.ACK, ack(BAD_ARGUMENTS))                   # shorter than a session id
+        assert a.call(a.TICK, struct.pack("<II", 1, 2)) == (a.ACK, ack(BAD_ARGUMENTS))      # longer than one
+        assert a.call(a.ADD_TOKEN, struct.pack("<I", 1)) == (a.ACK, ack(BAD_ARGUMENTS))     # token id missing
+        assert a.call(a.ADD_TEXT, struct.pack("<I", 1)) == (a.ACK, ack(BAD_ARGUMENTS))      # empty text
+        assert a.call(40, struct.pack("<II", 1, 2)) == (a.ACK, ack(UNKNOWN_COMMAND))
+        for cmd in (a.GET_SESSION_TOKENS, a.SUBSCRIBE, a.UNSUBSCRIBE, a.KILL_SESSION, a.START, a.STOP, a.TICK, a.GET_STATUS):
+            assert a.call(cmd, struct.pack("<I", 77)) == (a.ACK, ack(NO_SUCH_SESSION))
+        for cmd in (a.REWIND, a.ADD_TOKEN, a.SET_OPTIONS):
+            assert a.call(cmd, struct.pack("<II", 77, 0)) == (a.ACK, ack(NO_SUCH_SESSION))
+        for cmd in (a.ADD_TEXT, a.SAVE_FRAME, a.SNAPSHOT, a.RESTORE):
+            assert a.call(cmd, struct.pack("<I", 77) + b"x") == (a.ACK, ack(NO_SUCH_SESSION))
+        # three requests in one segment, then one request in three segments
+        a.sock.sendall(b"".join(struct.pack("<III", a.LIST_SESSIONS, 900 + i, 0) for i in range(3)))
+        assert [a.recv() for _ in range(3)] == [(a.SESSION_LIST, 900 + i, b"") for i in range(3)]
+        frame = struct.pack("<IIII", a.TICK, 950, 4, 77)
+        for part in (frame[:5], frame[5:13], frame[13:]):
+            a.sock.sendall(part)
+        assert a.recv() == (a.ACK, 950, ack(NO_SUCH_SESSION))
+        # the second client is served independently
+        assert b.call(b.LIST_SESSIONS) == (b.SESSION_LIST, b"")
+        # a frame above 64 KiB closes that connection only (server/client.cpp:128-131)
+        b.sock.sendall(struct.pack("<III", b.ADD_TEXT, 1, 0x10001))
+        with pytest.raises(ConnectionError):
+            b.recv()
+        assert a.call(a.LIST_SESSIONS) == (a.SESSION_LIST, b"")
+        a.close()
+        b.close()
+    model.close()
+    ctx.close()
+
+
+@pytest.mark.gpu
+def test_every_opcode_against_a_live_session(pkg, tiny_model, tmp_path):
+    from test_e2e_gpu import N_PROMPT, OracleSession, prompt_tokens
+    orc = OracleSession(tiny_model)
+    prompt = prompt_tokens()
+    for t in prompt:
+        orc.push(t)
+    greedy = []
+    for _ in range(8):
+        orc.eval()
+        greedy.append(orc.argmax())
+        orc.push(greedy[-1])
+    orc.close()
+
+    ctx = pkg.HostContext(tiny_model, 0)
+    with pkg.Server(ctx, deterministic=True) as server:
+        a, b = pkg.Client(server.port), pkg.Client(server.port)
+        # newSession: the caller gets its request id back, the other client a broadcast
+        op, data = a.call(a.NEW_SESSION)
+        assert op == a.SESSION_CREATED and len(data) == 4
+        sid = data
+        session, = struct.unpack("<I", sid)
+        assert b.recv() == (b.SESSION_CREATED, 0, sid)
+        assert b.call(b.LIST_SESSIONS) == (b.SESSION_LIST, sid)
+        assert b.call(b.SUBSCRIBE, sid) == (b.ACK, ack(OK))
+        assert a.call(a.GET_STATUS, sid) == (a.ACK, ack(OK))
+        assert a.call(a.SET_OPTIONS, sid + struct.pack("<I", 0)) == (a.ACK, ack(OK))
+        for t in prompt:
+            assert a.call(a.ADD_TOKEN, sid + struct.pack("<I", t)) == (a.ACK, ack(OK))
+        assert a.call(a.ADD_TOKEN, sid + struct.pack("<I", 32000)) == (a.ACK, ack(NOK))
+        # tick: the ticker gets the token under its request id, the subscriber as a broadcast
+        token0 = sid + struct.pack("<II", greedy[0], N_PROMPT)
+        assert a.call(a.TICK, sid) == (a.NEW_TOKEN, token0)
+        assert a.others == []                                                  # not subscribed: no broadcast for a
+        assert b.recv() == (b.NEW_TOKEN, 0, token0)
+        op, data = a.call(a.GET_SESSION_TOKENS, sid)
+        assert op == a.BUFFER and list(np.frombuffer(data, np.uint32)) == prompt + greedy[:1]
+        # snapshot, run on, rewind, restore
+        snap = os.fsencode(str(tmp_path / "snap.bin"))
+        assert a.call(a.SNAPSHOT, sid + snap) == (a.ACK, ack(OK))
+        assert a.call(a.SNAPSHOT, sid + b"/nonexistent-dir/x") [0] == a.ACK
+        assert a.call(a.SAVE_FRAME, sid + os.fsencode(str(tmp_path / "frame.bin")))[0] == a.ACK
+        assert a.call(a.START, sid) == (a.ACK, ack(OK))
+        assert a.call(a.TICK, sid) == (a.ACK, ack(ALREADY_RUNNING))
+        assert a.call(a.RESTORE, sid + snap) == (a.ACK, ack(ALREADY_RUNNING))
+        got = []
+        while len(got) < 5:
+            op, rid, data = b.recv()
+            assert (op, rid) == (b.NEW_TOKEN, 0) and data[:4] == sid
+            got.append(struct.unpack("<II", data[4:]))
+        assert [t for t, _ in got] == greedy[1:6] and [p for _, p in got] == list(range(N_PROMPT + 1, N_PROMPT + 6))
+        assert a.call(a.STOP, sid) == (a.ACK, ack(OK))
+        assert b.call(b.UNSUBSCRIBE, sid) == (b.ACK, ack(OK))
+        assert a.call(a.REWIND, sid + struct.pack("<I", N_PROMPT)) == (a.ACK, ack(OK))
+        op, data = a.call(a.GET_SESSION_TOKENS, sid)
+        assert list(np.frombuffer(data, np.uint32)) == prompt
+        assert a.call(a.TICK, sid) == (a.NEW_TOKEN, token0)                    # the same token again after the rewind
+        assert a.call(a.RESTORE, sid + snap) == (a.ACK, ack(OK))
+        op, data = a.call(a.GET_SESSION_TOKENS, sid)
+        assert list(np.frombuffer(data, np.uint32)) == prompt + greedy[:1]
+        assert a.call(a.TICK, sid) == (a.NEW_TOKEN, sid + struct.pack("<II", greedy[1], N_PROMPT + 1))
+        # text goes through the tokenizer of the model file
+        op, data = a.call(a.NEW_SESSION)
+        sid2 = data
+        assert a.call(a.ADD_TEXT, sid2 + b"hello") [0] == a.ACK
+        op, data = a.call(a.LIST_SESSIONS)
+        assert sorted(np.frombuffer(data, np.uint32)) == sorted([session, struct.unpack("<I", sid2)[0]])
+        # kill: acknowledged, and the session leaves the list
+        assert a.call(a.KILL_SESSION, sid) == (a.ACK, ack(OK))
+        for _ in range(200):
+            op, data = a.call(a.LIST_SESSIONS)
+            if data == sid2:
+                break
+        assert data == sid2
+        assert a.call(a.TICK, sid) == (a.ACK, ack(NO_SUCH_SESSION))
+        a.close()
+        b.close()
+    ctx.close()      # the server's stop() has killed and joined the second session
