@@ -134,10 +134,15 @@ def test_every_opcode_against_a_live_session(pkg, tiny_model, tmp_path):
         assert a.call(a.REWIND, sid + struct.pack("<I", N_PROMPT)) == (a.ACK, ack(OK))
         op, data = a.call(a.GET_SESSION_TOKENS, sid)
         assert list(np.frombuffer(data, np.uint32)) == prompt
+        assert a.call(a.TICK, sid) == (a.ACK, ack(NOK))                        # every token is on the device: nothing to evaluate
+        assert a.call(a.REWIND, sid + struct.pack("<I", N_PROMPT - 1)) == (a.ACK, ack(OK))
+        assert a.call(a.ADD_TOKEN, sid + struct.pack("<I", prompt[-1])) == (a.ACK, ack(OK))
         assert a.call(a.TICK, sid) == (a.NEW_TOKEN, token0)                    # the same token again after the rewind
+        # a snapshot holds the tokens that were on the device when it was taken: the prompt, not yet the first reply
         assert a.call(a.RESTORE, sid + snap) == (a.ACK, ack(OK))
         op, data = a.call(a.GET_SESSION_TOKENS, sid)
-        assert list(np.frombuffer(data, np.uint32)) == prompt + greedy[:1]
+        assert list(np.frombuffer(data, np.uint32)) == prompt
+        assert a.call(a.ADD_TOKEN, sid + struct.pack("<I", greedy[0])) == (a.ACK, ack(OK))
         assert a.call(a.TICK, sid) == (a.NEW_TOKEN, sid + struct.pack("<II", greedy[1], N_PROMPT + 1))
         # text goes through the tokenizer of the model file
         op, data = a.call(a.NEW_SESSION)
