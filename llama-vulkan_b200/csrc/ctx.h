@@ -22,6 +22,7 @@ struct lv_ctx {
     bool peer_ready = false;
     void* tc_scratch = nullptr;       // partial accumulators of the K-split tensor-core products
     void* tc_counters = nullptr;
+    bool tc_exact = false;            // batched q4_0 products with the exact hi/lo weight planes instead of one fp16 plane
     // exchange roles that lv_tp_arm_push / lv_tp_arm_pull set for the next GEMV-family launch
     struct {
         int push = -1, pull = -1;

@@ -26,6 +26,16 @@
 // in a scratch buffer; the last to arrive adds them in split order (deterministic) and applies
 // the epilogue.
 //
+// Two forms of the A operand (template flag FAST, q4_0 only):
+//   exact (FAST = false)  the hi/lo pair described above, one 64-column tile per producer step;
+//   fast  (FAST = true)   hi = fp16((q - 8) * d) alone: a weight is rounded to 11 significant bits (relative error
+//                         <= 2^-12, none for q - 8 in {0, +-1, +-2, +-4, -8}); the activations keep both planes.
+//                         One producer step covers four tiles of K (a whole raw stage): a warp handles 8 rows x 4 tiles,
+//                         so that its 32-bit loads of the 144-byte raw rows and its 16-byte tile stores are free of bank
+//                         conflicts, a thread dequantises the two blocks of one tile of one row, and one MMA per K step
+//                         (W_hi x [x_hi; x_lo]) replaces two.  Any matrix is split along K so that the CTAs fill the SMs
+//                         in whole waves.
+//
 // Every wait is bounded (common.cuh); a lost wait sets the context's error word, the CTA
 // drains and frees its tensor memory.
 #include <cuda.h>
@@ -65,8 +75,14 @@ template <> struct TcTraits<T_Q8_0> {
 };
 template <int QT> __host__ __device__ constexpr int tc_raw_row_bytes() { return kTcRawBlocks * TcTraits<QT>::kBlockBytes; }       // 144 / 272
 template <int QT> __host__ __device__ constexpr int tc_raw_stage() { return kTcRows * tc_raw_row_bytes<QT>(); }                   // 18432 / 34816
-template <int QT> __host__ __device__ constexpr size_t tc_smem_bytes() {
-    return 1024 /* alignment slack */ + size_t(kTcSlots) * kTcSlotBytes + TcTraits<QT>::kBRingBytes + size_t(kTcRawStages) * tc_raw_stage<QT>() + 512;
+constexpr int kTcFastGroup = 4;                // fast form: tiles of K per producer step (= one raw stage)
+constexpr int kTcFastBufs = 2;
+constexpr int kTcFastBufBytes = kTcFastGroup * kTcTileBytes;          // 65536
+constexpr int kTcFastBRingBytes = 49152;
+template <int QT, bool FAST> __host__ __device__ constexpr int tc_a_bytes() { return FAST ? kTcFastBufs * kTcFastBufBytes : kTcSlots * kTcSlotBytes; }
+template <int QT, bool FAST> __host__ __device__ constexpr int tc_b_ring_bytes() { return FAST ? kTcFastBRingBytes : TcTraits<QT>::kBRingBytes; }
+template <int QT, bool FAST = false> __host__ __device__ constexpr size_t tc_smem_bytes() {
+    return 1024 /* alignment slack */ + size_t(tc_a_bytes<QT, FAST>()) + tc_b_ring_bytes<QT, FAST>() + size_t(kTcRawStages) * tc_raw_stage<QT>() + 512;
 }
 
 struct GemmTcParams {
@@ -140,6 +156,19 @@ __device__ __forceinline__ void dequant_word(uint32_t w, __half2 d2, __half2 (&h
     }
 }
 
+// Eight nibbles of one word -> fp16((q - 8) * d), same output order as dequant_word.
+__device__ __forceinline__ void dequant_word_hi(uint32_t w, __half2 d2, uint32_t (&hi)[4]) {
+    const uint32_t v01 = __byte_perm(w, 0u, 0x4140), v23 = __byte_perm(w, 0u, 0x4342);
+    const uint32_t raw[4] = {(v01 & 0x000f000fu) | 0x64006400u, (v23 & 0x000f000fu) | 0x64006400u,
+                             ((v01 >> 4) & 0x000f000fu) | 0x64006400u, ((v23 >> 4) & 0x000f000fu) | 0x64006400u};
+    const __half2 off = __floats2half2_rn(1032.0f, 1032.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&raw[i]), off), d2);
+        hi[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
 // Four int8 of one word -> exact (hi, lo) fp16 pairs of q * d: e[0] = elements (4k, 4k+1), e[1] = (4k+2, 4k+3).
 __device__ __forceinline__ void dequant_word_q8(uint32_t w, __half2 d2, __half2 (&hi)[2], __half2 (&lo)[2]) {
     const uint32_t u = w ^ 0x80808080u;                                       // q + 128 as unsigned bytes
@@ -153,16 +182,17 @@ __device__ __forceinline__ void dequant_word_q8(uint32_t w, __half2 d2, __half2 
     }
 }
 
-template <int QT>
+template <int QT, bool FAST>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcParams p, const __grid_constant__ GemmTcMaps maps) {
+    static_assert(!FAST || QT == T_Q4_0, "the fast form exists for q4_0 only");
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     uint8_t* slots = smem;
-    constexpr int kRawRowBytes = tc_raw_row_bytes<QT>(), kRawStage = tc_raw_stage<QT>(), kBRingBytes = TcTraits<QT>::kBRingBytes;
+    constexpr int kRawRowBytes = tc_raw_row_bytes<QT>(), kRawStage = tc_raw_stage<QT>(), kBRingBytes = tc_b_ring_bytes<QT, FAST>();
     constexpr int kTileWords = kRawRowBytes / 16;                    // 32-bit words of one 64-column tile of a row: 9 / 17
-    uint8_t* bring = smem + kTcSlots * kTcSlotBytes;
+    uint8_t* bring = smem + tc_a_bytes<QT, FAST>();
     uint8_t* rawring = bring + kBRingBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(rawring + kTcRawStages * kRawStage);
     uint64_t* raw_full = bars;                       // [2]
@@ -197,12 +227,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kBRingBytes) / b_bytes);         // B stages: 3-4 (zpad 64) .. 16
     // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
     // the allocation is a power of two >= 32
-    const uint32_t bank_cols = 3u * p.zpad;
-    const uint32_t tmem_cols = p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u);
+    const uint32_t bank_cols = (FAST ? 2u : 3u) * p.zpad;
+    const uint32_t tmem_cols = FAST ? (p.zpad <= 16 ? 64u : (p.zpad <= 32 ? 128u : 256u)) : (p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u));
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kTcRawStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kTcProducerWarps); }
-        for (int i = 0; i < kTcSlots; ++i) { mbar_init(&slot_full[i], kTcGroupWarps); mbar_init(&slot_empty[i], 1); }
+        for (int i = 0; i < kTcSlots; ++i) { mbar_init(&slot_full[i], FAST ? kTcProducerWarps : kTcGroupWarps); mbar_init(&slot_empty[i], 1); }
         for (int i = 0; i < kTcMaxBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
         mbar_init(acc_full, 1);
         fence_mbar_init();
@@ -264,6 +294,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             const uint32_t idesc_common = (1u << 4) | ((uint32_t(kTcRows) >> 4) << 24);
             const uint32_t idesc_wide = idesc_common | (((2u * p.zpad) >> 3) << 17);
             const uint32_t idesc_narrow = idesc_common | ((p.zpad >> 3) << 17);
+            if constexpr (FAST) {
+                for (uint32_t g = 0; g < n_groups && ok; ++g) {
+                    const uint32_t ab = g % kTcFastBufs;
+                    ok = mbar_wait(&slot_full[ab], (g / kTcFastBufs) & 1u, p.err);
+                    for (uint32_t t = 0; t < uint32_t(kTcFastGroup) && ok; ++t) {
+                        const uint32_t c = g * kTcFastGroup + t, bs = c % nb;
+                        ok = mbar_wait(&b_full[bs], (c / nb) & 1u, p.err);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        const uint32_t a_hi = smem_u32(slots + ab * kTcFastBufBytes + t * kTcTileBytes);
+                        const uint32_t b_all = smem_u32(bring + bs * b_bytes);
+                        const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
+#pragma unroll
+                        for (int k = 0; k < kTcChunkK / 16; ++k) {
+                            const uint32_t off = uint32_t(k) * 32u;
+                            tc_mma_f16(bank, tc_smem_desc(a_hi + off), tc_smem_desc(b_all + off), idesc_wide, (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u);
+                        }
+                        tc_commit(&b_empty[bs]);
+                    }
+                    if (ok) tc_commit(&slot_empty[ab]);
+                }
+            } else
             for (uint32_t c = 0; c < n_chunks && ok; ++c) {
                 const int s = int(c % kTcSlots);
                 const uint32_t bs = c % nb;
@@ -287,6 +339,51 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         }
     } else {
         // ---------------- producer warps: q4_0 blocks -> swizzled fp16 hi/lo tiles ---------------
+        if constexpr (FAST) {
+            // a warp: 8 rows x the 4 tiles of a raw stage; the word offsets 36 r + 9 t of its lanes fall into 32 different banks
+            const uint32_t fr = uint32_t(warp) * 8u + (uint32_t(lane) & 7u), ft = uint32_t(lane) >> 3;
+            for (uint32_t g = 0; g < n_groups && ok; ++g) {
+                const int rs = int(g % kTcRawStages);
+                ok = mbar_wait(&raw_full[rs], (g / kTcRawStages) & 1u, p.err);
+                if (!ok) break;
+                uint32_t w[9];
+                {
+                    const uint32_t* src = reinterpret_cast<const uint32_t*>(rawring + rs * kRawStage + fr * kRawRowBytes) + 9u * ft;
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) w[i] = src[i];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[rs]);
+                const uint32_t ab = g % kTcFastBufs;
+                if (g >= uint32_t(kTcFastBufs)) {
+                    ok = mbar_wait(&slot_empty[ab], ((g / kTcFastBufs) - 1) & 1u, p.err);
+                    if (!ok) break;
+                }
+                uint8_t* a_tile = slots + ab * kTcFastBufBytes + ft * kTcTileBytes;
+                // block 0: bytes 0-1 scale, 2-17 nibbles; block 1: bytes 18-19 scale, 20-35 nibbles
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t q[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k] = b == 0 ? __funnelshift_r(w[k], w[k + 1], 16) : w[5 + k];
+                    const uint32_t dbits = b == 0 ? (w[0] & 0xffffu) : (w[4] >> 16);
+                    const __half2 d2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(dbits)));
+                    uint32_t hi[4][4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) dequant_word_hi(q[k], d2, hi[k]);
+                    // 16-byte chunks of the block in element order: 0-7 (low nibbles of words 0, 1), 8-15, 16-23 (high nibbles), 24-31
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int k0 = (cc & 1) * 2, part = (cc >> 1) * 2;
+                        *reinterpret_cast<uint4*>(a_tile + tc_swizzled(fr, uint32_t(b * 4 + cc))) =
+                            make_uint4(hi[k0][part], hi[k0][part + 1], hi[k0 + 1][part], hi[k0 + 1][part + 1]);
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&slot_full[ab]);
+            }
+        } else {
         const uint32_t r = threadIdx.x & (kTcRows - 1);       // tile row of this thread
         const uint32_t khalf = (threadIdx.x >> 7) & 1u;       // which block of a 64-column tile
         const uint32_t jpar = threadIdx.x >> 8;               // producer group: even or odd tiles of K
@@ -378,6 +475,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 if (lane == 0) mbar_arrive(&slot_full[s]);
             }
         }
+        }
         // ---------------- epilogue: warps 0-3 own accumulator rows 32w .. 32w+31 -----------------
         if (warp < 4) {
             pdl_wait();
@@ -427,9 +525,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;
                     const uint32_t banks_used = min(uint32_t(kTcBanks), n_chunks);
                     for (uint32_t b = 0; b < banks_used; ++b) {
+                        constexpr int kAcc = FAST ? 2 : 3;
                         uint32_t u[3][16];
 #pragma unroll
-                        for (int a = 0; a < 3; ++a) {
+                        for (int a = 0; a < kAcc; ++a) {
                             asm volatile(
                                 "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                                 : "=r"(u[a][0]), "=r"(u[a][1]), "=r"(u[a][2]), "=r"(u[a][3]), "=r"(u[a][4]), "=r"(u[a][5]), "=r"(u[a][6]),
@@ -439,8 +538,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                         }
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)      // the two small cross terms first, then the main one
-                            v[i] += (__uint_as_float(u[1][i]) + __uint_as_float(u[2][i])) + __uint_as_float(u[0][i]);
+                        for (int i = 0; i < 16; ++i) {    // the small cross terms first, then the main one
+                            if constexpr (FAST) v[i] += __uint_as_float(u[1][i]) + __uint_as_float(u[0][i]);
+                            else v[i] += (__uint_as_float(u[1][i]) + __uint_as_float(u[2][i])) + __uint_as_float(u[0][i]);
+                        }
                     }
                 } else {
 #pragma unroll
@@ -575,7 +676,7 @@ __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh,
     }
 }
 
-constexpr size_t kTcScratchBytes = size_t(8) << 20;
+constexpr size_t kTcScratchBytes = size_t(32) << 20;
 constexpr uint32_t kTcMaxTiles = 1024;
 
 void gemm_tc_release(lv_ctx* ctx) {
@@ -591,8 +692,13 @@ int gemm_tc_configure(lv_ctx* ctx) {
     LV_CUDA(cudaMemset(ctx->tc_counters, 0, kTcMaxTiles * sizeof(uint32_t)));
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q4_0>() && size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q8_0>(),
                "device has too little shared memory for the batched product");
-    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>())));
-    LV_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>())));
+    constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, true>();
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kFastSmem, "device has too little shared memory for the batched product");
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>()))));
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFastSmem))));
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>()))));
+    const char* exact = getenv("LV_GEMM_TC_EXACT");
+    ctx->tc_exact = exact != nullptr && exact[0] == '1';
     return LV_OK;
 }
 
@@ -618,19 +724,39 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
         if (int rc = make_weight_map(&maps.gate, p.m[0].w_gate, p.m[0].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
     }
     p.xh = xh;
-    // few row tiles: up to four CTAs per tile, each with at least two raw stages of K, as far as SMs and scratch allow
-    uint32_t splits = 1;
     const uint32_t groups_all = p.K / (4 * kTcChunkK);
-    while (splits < 4 && tiles * (splits + 1) <= uint32_t(ctx->sm_count) && groups_all / (splits + 1) >= 2 &&
-           size_t(tiles) * (splits + 1) * p.zpad * kTcRows * sizeof(float) <= kTcScratchBytes && tiles <= kTcMaxTiles)
-        ++splits;
+    const bool fast = QT == T_Q4_0 && !ctx->tc_exact;
+    uint32_t splits = 1;
+    auto fits = [&](uint32_t s) {
+        return groups_all / s >= 2 && tiles <= kTcMaxTiles && size_t(tiles) * s * p.zpad * kTcRows * sizeof(float) <= kTcScratchBytes;
+    };
+    if (fast) {
+        // every CTA holds an SM to itself, so the launch runs in waves of sm_count CTAs: take the split whose last wave is
+        // the fullest (time ~ waves / splits), charging each further split 3 % for its pass through the scratch buffer
+        float best = 1e30f;
+        for (uint32_t s = 1; s <= 8 && fits(s); ++s) {
+            const uint32_t waves = (tiles * s + uint32_t(ctx->sm_count) - 1) / uint32_t(ctx->sm_count);
+            const float cost = float(waves) / float(s) * (1.0f + 0.03f * float(s - 1));
+            if (cost < best) { best = cost; splits = s; }
+        }
+    } else {
+        // few row tiles: up to four CTAs per tile, each with at least two raw stages of K, as far as SMs and scratch allow
+        while (splits < 4 && tiles * (splits + 1) <= uint32_t(ctx->sm_count) && fits(splits + 1)) ++splits;
+    }
     static const char* no_split = getenv("LV_GEMM_TC_NO_SPLIT");
     if (no_split != nullptr && no_split[0] == '1') splits = 1;
     p.splits = splits;
     p.scratch = static_cast<float*>(ctx->tc_scratch);
     p.counters = static_cast<uint32_t*>(ctx->tc_counters);
     tiles *= splits;
-    LV_CUDA(launch_pdl(ctx, gemm_tc_kernel<QT>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps));
+    if constexpr (QT == T_Q4_0) {
+        if (fast) {
+            constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, true>();
+            LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, true>, dim3(tiles), dim3(kTcThreads), kFastSmem, p, maps)));
+            return LV_OK;
+        }
+    }
+    LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<QT, false>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps)));
     return LV_OK;
 }
 
@@ -645,6 +771,12 @@ using namespace lv;
 
 extern "C" size_t lv_act_split_bytes(uint32_t cols, uint32_t batch) {
     return size_t(2) * ((batch + 15u) & ~15u) * cols * sizeof(__half);
+}
+
+extern "C" int lv_gemm_tc_set_exact(lv_ctx* ctx, int exact) {
+    LV_ENTER(ctx);
+    ctx->tc_exact = exact != 0;
+    return LV_OK;
 }
 
 extern "C" int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch) {

@@ -4,6 +4,12 @@ The oracle (matmul.glsl restated) is evaluated token by token.  The products tha
 cores are exact; their fp32 accumulator truncates instead of rounding, which over K = 4096..11008
 leaves a relative error of about 1e-5, so the tolerances here are rel-L2 <= 3e-5 and max-abs <=
 1e-4 of the largest output (the GEMV tests hold 1e-5), the f16 cache rows up to a neighbouring half.
+
+Every test runs in both forms of the q4_0 weight tiles.  "exact" (hi/lo fp16 pair) is held to the tolerances above.
+"fast" (one fp16 plane: each weight rounded to 11 significant bits, the default of the library) is held to the same
+tight tolerances against the product with fp16-rounded weights -- the kernel does what it says -- and to rel-L2 <=
+5e-4 / max-abs <= 2e-3 of the largest output against the oracle (observed: 1.5e-4 for one product, 3.1e-4 for the gated pair): what the rounding of the weights costs.  q8_0
+matrices always take the exact form.
 """
 import ctypes as C
 
@@ -14,6 +20,28 @@ import oracle_bind as ob
 import quant_np as qn
 
 pytestmark = pytest.mark.gpu
+
+FAST_REL_L2, FAST_MAX_ABS_FRAC = 5e-4, 2e-3
+
+
+@pytest.fixture(autouse=True, params=["exact", "fast"])
+def form(request, gpu, pkg):
+    pkg.check(gpu.lib.lv_gemm_tc_set_exact(gpu.handle, int(request.param == "exact")))
+    yield request.param
+    pkg.check(gpu.lib.lv_gemm_tc_set_exact(gpu.handle, 0))
+
+
+def loose(form, wtype, rel_l2=3e-5, max_abs_frac=1e-4):
+    """Tolerances against the oracle for this form and weight type."""
+    if form == "fast" and wtype == qn.Q4_0:
+        return dict(rel_l2=max(rel_l2, FAST_REL_L2), max_abs_frac=max(max_abs_frac, FAST_MAX_ABS_FRAC))
+    return dict(rel_l2=rel_l2, max_abs_frac=max_abs_frac)
+
+
+def rounded_weights_product(W, x, rows, cols):
+    """x @ fp16(w)^T in float64: what the fast form computes, up to the accumulation order."""
+    w16 = qn.dequantize_np(W, qn.Q4_0).reshape(rows, cols).astype(np.float16).astype(np.float64)
+    return x.astype(np.float64) @ w16.T
 
 
 def close(got, want, rel_l2=3e-5, max_abs_frac=1e-4):
@@ -76,7 +104,7 @@ def test_act_split_planes_add_up_to_the_input(gpu, pkg):
 
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
 @pytest.mark.parametrize("rows,cols,batch", [(128, 256, 16), (256, 4096, 5), (4096, 4096, 64), (384, 11008, 33), (640, 5120, 17)])
-def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch, wtype):
+def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch, wtype, form):
     rng = np.random.default_rng(51)
     W = matrix(rng, rows, cols, wtype=wtype)
     x = rng.standard_normal((batch, cols)).astype(np.float32)
@@ -87,17 +115,20 @@ def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch, wtype):
     pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, wtype, xh, rows, cols, batch, 0))
     gpu.sync()
     got = gpu.download(out, np.float32, (batch + 1) * rows).reshape(batch + 1, rows)
-    close(got[:batch], want)
+    close(got[:batch], want, **loose(form, wtype))
+    if form == "fast" and wtype == qn.Q4_0:
+        close(got[:batch], rounded_weights_product(W, x, rows, cols))
     assert (got[batch] == 7.0).all()                                     # nothing written past the batch
     base = rng.standard_normal((batch, rows)).astype(np.float32)
     out = gpu.upload(base)
     pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, dW, wtype, xh, rows, cols, batch, 1))
     gpu.sync()
-    close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), base + want)
+    close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), base + want, **loose(form, wtype))
 
 
-def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg):
-    """Blocks whose scale is tiny, huge or negative: hi + lo reproduces (q - 8) * d exactly."""
+def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg, form):
+    """Blocks whose scale is tiny, huge or negative: hi + lo reproduces (q - 8) * d exactly; the single plane of the
+    fast form reproduces fp16((q - 8) * d), subnormal products included."""
     rng = np.random.default_rng(52)
     rows, cols, batch = 128, 256, 16
     W = matrix(rng, rows, cols).reshape(rows, cols // 32, 18).copy()
@@ -110,12 +141,14 @@ def test_gemm_tc_extreme_scales_are_exact_products(gpu, pkg):
     pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, gpu.upload(W), qn.Q4_0, xh, rows, cols, batch, 0))
     gpu.sync()
     want = x.astype(np.float64) @ qn.dequantize_np(W, qn.Q4_0).reshape(rows, cols).astype(np.float64).T
+    if form == "fast":
+        want = rounded_weights_product(W, x, rows, cols)
     close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows), want, rel_l2=2e-6, max_abs_frac=2e-6)
 
 
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
 @pytest.mark.parametrize("ff,dim,batch", [(192, 512, 16), (256, 4096, 24), (11008, 4096, 20)])     # the middle one is split along K
-def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype):
+def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype, form):
     rng = np.random.default_rng(53)
     w3, w1 = matrix(rng, ff, dim, wtype=wtype), matrix(rng, ff, dim, wtype=wtype)
     x = rng.standard_normal((batch, dim)).astype(np.float32)
@@ -126,11 +159,11 @@ def test_gemm_tc_silu_pair(gpu, pkg, ff, dim, batch, wtype):
     gpu.sync()
     got = gpu.download(out, np.float32, batch * ff).reshape(batch, ff)
     for z in range(0, batch, 7):
-        close(got[z], ob.gemv_silu(w3, w1, wtype, ob.norm(x[z], nw), ff, dim, workers_for(dim)), rel_l2=3e-5, max_abs_frac=1e-4)
+        close(got[z], ob.gemv_silu(w3, w1, wtype, ob.norm(x[z], nw), ff, dim, workers_for(dim)), **loose(form, wtype))
 
 
 @pytest.mark.parametrize("dim", [512, 1024])             # 1024: two CTAs per row tile, each with half of K
-def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg, dim):
+def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg, dim, form):
     rng = np.random.default_rng(54)
     batch, ctx_rows, pos = 18, 64, 9
     wq, wk, wv = (matrix(rng, dim, dim, 0.05) for _ in range(3))
@@ -146,7 +179,7 @@ def test_gemm_tc_qkv_writes_cache_rows_at_the_position(gpu, pkg, dim):
     gk = gpu.download(kc, np.float16, ctx_rows * dim).reshape(ctx_rows, dim)
     gv = gpu.download(vc, np.float16, ctx_rows * dim).reshape(ctx_rows, dim)
     for z in range(batch):
-        close(gq[z], ob.gemv(wq, qn.Q4_0, x[z], dim, dim, 128), rel_l2=1e-5)
+        close(gq[z], ob.gemv(wq, qn.Q4_0, x[z], dim, dim, 128), **loose(form, qn.Q4_0, rel_l2=1e-5))
         close(gk[pos + z], ob.gemv(wk, qn.Q4_0, x[z], dim, dim, 128), rel_l2=6e-4, max_abs_frac=1e-3)
         close(gv[pos + z], ob.gemv(wv, qn.Q4_0, x[z], dim, dim, 128), rel_l2=6e-4, max_abs_frac=1e-3)
     assert not gk[:pos].any() and not gk[pos + batch:].any()
@@ -162,7 +195,7 @@ def test_gemm_tc_refuses_what_it_cannot_do(gpu, pkg):
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, None, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS
 
 
-def test_gemm_tc_split_along_k_is_reproducible(gpu, pkg):
+def test_gemm_tc_split_along_k_is_reproducible(gpu, pkg, form):
     """Tiles shared by several CTAs are summed in a fixed order: two launches give the same bits, and a launch right
     after another one (the arrival counters must be back at zero) is as good as the first."""
     rng = np.random.default_rng(55)
@@ -179,4 +212,4 @@ def test_gemm_tc_split_along_k_is_reproducible(gpu, pkg):
     got = [gpu.download(o, np.float32, batch * rows) for o in outs]
     assert np.array_equal(got[0], got[1]) and np.array_equal(got[0], got[2])
     want = np.stack([ob.gemv(W, qn.Q4_0, x[z], rows, cols, 128) for z in range(batch)])
-    close(got[0].reshape(batch, rows), want)
+    close(got[0].reshape(batch, rows), want, **loose(form, qn.Q4_0))
