@@ -62,6 +62,20 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking form: try_wait may suspend the thread for a while when the phase is not complete, test_wait returns at once.
+// For loops that poll several barriers.
+__device__ __forceinline__ bool mbar_poll(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Waits for the phase with the given parity.  Gives up after kWaitCycleLimit cycles
 // (or at once if another wait already failed), records the failure in *err and
 // returns false; the caller must then stop touching the guarded data.

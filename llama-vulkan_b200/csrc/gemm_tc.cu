@@ -269,22 +269,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             issue_raw(0);
             if (n_groups > 1) issue_raw(1);
             pdl_wait();                                    // the activations come from the previous kernel
-            for (uint32_t c = 0; c < n_chunks && ok; ++c) {
-                if ((c & 3u) == 0) {
-                    const uint32_t g = c >> 2;
-                    if (g >= kTcRawStages) {
-                        ok = mbar_wait(&raw_empty[g % kTcRawStages], ((g / kTcRawStages) - 1) & 1u, p.err);
-                        if (!ok) break;
-                        issue_raw(g);
+            // the two rings advance independently: a raw stage is refilled as soon as the producers have taken it into
+            // registers, a B stage as soon as its MMAs have completed, whichever comes first
+            uint32_t g_next = min(uint32_t(kTcRawStages), n_groups), c_next = 0, idle = 0, bs = 0, b_wait_phase = 0;
+            long long t_idle = 0;
+            while (ok && (g_next < n_groups || c_next < n_chunks)) {
+                bool progressed = false;
+                if (g_next < n_groups && mbar_poll(&raw_empty[g_next % kTcRawStages], ((g_next / kTcRawStages) - 1) & 1u)) {
+                    issue_raw(g_next++);
+                    progressed = true;
+                }
+                if (c_next < n_chunks) {
+                    // stage bs was last freed in the round before this one: its phase parity is b_wait_phase
+                    if (c_next < nb || mbar_poll(&b_empty[bs], b_wait_phase)) {
+                        mbar_expect_tx(&b_full[bs], b_bytes);
+                        bulk_g2s(bring + bs * b_bytes, reinterpret_cast<const uint8_t*>(p.xh) + size_t(4 * g_begin + c_next) * b_bytes, b_bytes, &b_full[bs]);
+                        ++c_next;
+                        if (++bs == nb) { bs = 0; if (c_next > nb) b_wait_phase ^= 1u; }
+                        progressed = true;
                     }
                 }
-                const uint32_t bs = c % nb;
-                if (c >= nb) {
-                    ok = mbar_wait(&b_empty[bs], ((c / nb) - 1) & 1u, p.err);
-                    if (!ok) break;
+                if (progressed) {
+                    idle = 0;
+                } else if ((++idle & 0xffu) == 0) {                 // bounded like mbar_wait
+                    if (idle == 0x100u) t_idle = clock64();
+                    if (*reinterpret_cast<volatile uint32_t*>(p.err) != 0) ok = false;
+                    else if (clock64() - t_idle > kWaitCycleLimit) { atomicOr(p.err, ERR_MBAR_TIMEOUT); ok = false; }
                 }
-                mbar_expect_tx(&b_full[bs], b_bytes);
-                bulk_g2s(bring + bs * b_bytes, reinterpret_cast<const uint8_t*>(p.xh) + size_t(4 * g_begin + c) * b_bytes, b_bytes, &b_full[bs]);
             }
         }
     } else if (warp == kTcProducerWarps + 1) {
@@ -294,24 +305,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             const uint32_t idesc_common = (1u << 4) | ((uint32_t(kTcRows) >> 4) << 24);
             const uint32_t idesc_wide = idesc_common | (((2u * p.zpad) >> 3) << 17);
             const uint32_t idesc_narrow = idesc_common | ((p.zpad >> 3) << 17);
+            const uint64_t a_desc0 = tc_smem_desc(smem_u32(slots)), b_desc0 = tc_smem_desc(smem_u32(bring));
             if constexpr (FAST) {
+                uint32_t bs = 0, b_phase = 0;                  // B stage and its phase, advanced without divisions
                 for (uint32_t g = 0; g < n_groups && ok; ++g) {
                     const uint32_t ab = g % kTcFastBufs;
                     ok = mbar_wait(&slot_full[ab], (g / kTcFastBufs) & 1u, p.err);
+                    // descriptors differ from the first tile's only in the address field (units of 16 bytes; the whole
+                    // shared memory stays below the field's 256 KB)
+                    uint64_t a_desc = a_desc0 + ((ab * uint32_t(kTcFastBufBytes)) >> 4);
                     for (uint32_t t = 0; t < uint32_t(kTcFastGroup) && ok; ++t) {
-                        const uint32_t c = g * kTcFastGroup + t, bs = c % nb;
-                        ok = mbar_wait(&b_full[bs], (c / nb) & 1u, p.err);
+                        const uint32_t c = g * kTcFastGroup + t;
+                        ok = mbar_wait(&b_full[bs], b_phase, p.err);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        const uint32_t a_hi = smem_u32(slots + ab * kTcFastBufBytes + t * kTcTileBytes);
-                        const uint32_t b_all = smem_u32(bring + bs * b_bytes);
+                        const uint64_t b_desc = b_desc0 + ((bs * b_bytes) >> 4);
                         const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
 #pragma unroll
-                        for (int k = 0; k < kTcChunkK / 16; ++k) {
-                            const uint32_t off = uint32_t(k) * 32u;
-                            tc_mma_f16(bank, tc_smem_desc(a_hi + off), tc_smem_desc(b_all + off), idesc_wide, (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u);
-                        }
+                        for (int k = 0; k < kTcChunkK / 16; ++k)          // 16 fp16 along K = 32 bytes = 2 address units
+                            tc_mma_f16(bank, a_desc + 2u * k, b_desc + 2u * k, idesc_wide, (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u);
                         tc_commit(&b_empty[bs]);
+                        a_desc += uint32_t(kTcTileBytes) >> 4;
+                        if (++bs == nb) { bs = 0; b_phase ^= 1u; }
                     }
                     if (ok) tc_commit(&slot_empty[ab]);
                 }
@@ -322,15 +337,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 ok = mbar_wait(&b_full[bs], (c / nb) & 1u, p.err) && mbar_wait(&slot_full[s], (c / kTcSlots) & 1u, p.err);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t a_hi = smem_u32(slots + s * kTcSlotBytes), a_lo = a_hi + kTcTileBytes;
-                const uint32_t b_all = smem_u32(bring + bs * b_bytes);        // rows 0..zpad-1: x_hi, zpad..2 zpad-1: x_lo
+                const uint64_t a_hi = a_desc0 + ((uint32_t(s) * uint32_t(kTcSlotBytes)) >> 4), a_lo = a_hi + (kTcTileBytes >> 4);
+                const uint64_t b_all = b_desc0 + ((bs * b_bytes) >> 4);       // rows 0..zpad-1: x_hi, zpad..2 zpad-1: x_lo
                 const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
 #pragma unroll
-                for (int k = 0; k < kTcChunkK / 16; ++k) {
-                    const uint32_t off = uint32_t(k) * 32u;                  // 16 fp16 along K inside the swizzled row
+                for (int k = 0; k < kTcChunkK / 16; ++k) {                    // 16 fp16 along K inside the swizzled row = 2 address units
                     const uint32_t acc = (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u;
-                    tc_mma_f16(bank, tc_smem_desc(a_hi + off), tc_smem_desc(b_all + off), idesc_wide, acc);
-                    tc_mma_f16(bank + 2u * p.zpad, tc_smem_desc(a_lo + off), tc_smem_desc(b_all + off), idesc_narrow, acc);
+                    tc_mma_f16(bank, a_hi + 2u * k, b_all + 2u * k, idesc_wide, acc);
+                    tc_mma_f16(bank + 2u * p.zpad, a_lo + 2u * k, b_all + 2u * k, idesc_narrow, acc);
                 }
                 tc_commit(&slot_empty[s]);                                   // arrive when these MMAs have read the tiles
                 tc_commit(&b_empty[bs]);
@@ -477,14 +491,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         }
         }
         // ---------------- epilogue: warps 0-3 own accumulator rows 32w .. 32w+31 -----------------
-        if (warp < 4) {
-            pdl_wait();
-            if (ok) ok = mbar_wait(acc_full, 0u, p.err);
-            tc_fence_after_sync();
-            float* gate_s = reinterpret_cast<float*>(slots);      // [64][17] floats, free once the accumulator is complete
-            const uint32_t tr = uint32_t(warp * 32 + lane);       // tile row
-            // 16 tokens z0 .. z0+15 of one output row
-            auto store_plain = [&](uint32_t z0, const float (&r32)[16]) {
+        // 16 tokens z0 .. z0+15 of one output row (tile row tr)
+        auto store_plain = [&](uint32_t tr, uint32_t z0, const float (&r32)[16]) {
                 const uint32_t row = row0 + tr;
                 if (M.epilogue == EPI_STORE_F16_AT_POS) {
                     __half* cache = static_cast<__half*>(M.out);
@@ -508,7 +516,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     }
                 }
             };
-            auto store_pair = [&](uint32_t z0, const float (&up)[16], const float (&gate)[16]) {
+        auto store_pair = [&](uint32_t tr, uint32_t z0, const float (&up)[16], const float (&gate)[16]) {
                 const uint32_t row = row0 + tr;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -516,6 +524,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     if (z < p.Z) static_cast<float*>(M.out)[size_t(z) * M.rows + row] = up[i] * gate[i] / (expf(-gate[i]) + 1.0f);   // matmul_silu_ff.comp:95
                 }
             };
+        uint32_t* s_last = tmem_slot + 1;
+        if (warp < 4) {
+            pdl_wait();
+            if (ok) ok = mbar_wait(acc_full, 0u, p.err);
+            tc_fence_after_sync();
+            float* gate_s = reinterpret_cast<float*>(slots);      // [64][17] floats, free once the accumulator is complete
+            const uint32_t tr = uint32_t(warp * 32 + lane);       // tile row
             float* my_partial = p.scratch + (size_t(tile_all) * p.splits + split) * p.zpad * kTcRows;
             for (uint32_t z0 = 0; z0 < p.zpad; z0 += 16) {
                 float v[16];
@@ -562,16 +577,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                         float gate[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) gate[i] = gate_s[tr * 17 + i];
-                        store_pair(z0, v, gate);
+                        store_pair(tr, z0, v, gate);
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 } else if (ok) {
-                    store_plain(z0, v);
+                    store_plain(tr, z0, v);
                 }
             }
             if (p.splits > 1) {
                 // the last of the tile's CTAs to get here adds the partial sums in split order and finishes the rows
-                uint32_t* s_last = tmem_slot + 1;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (tr == 0) {
                     __threadfence();
@@ -579,34 +593,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     *s_last = (prev + 1 == p.splits) ? 1u : 0u;
                     if (prev + 1 == p.splits) p.counters[tile_all] = 0;         // ready for the next launch
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*reinterpret_cast<volatile uint32_t*>(s_last) != 0 && ok) {
-                    __threadfence();
-                    const float* base = p.scratch + size_t(tile_all) * p.splits * p.zpad * kTcRows;
-                    for (uint32_t z0 = 0; z0 < p.zpad; z0 += 16) {
-                        if (pair) {
-                            if (tr < 64) {
-                                float up[16], gate[16];
+            }
+        }
+        if (p.splits > 1) {
+            // all sixteen producer warps share the pass over the partial sums: a quarter of the tokens each
+            asm volatile("bar.sync 2, 512;" ::: "memory");
+            if (*reinterpret_cast<volatile uint32_t*>(s_last) != 0 && ok) {
+                pdl_wait();                                   // warps 4-15 have not waited for the previous kernel yet
+                __threadfence();
+                const uint32_t tr = threadIdx.x & (kTcRows - 1), zq = threadIdx.x >> 7;
+                const float* base = p.scratch + size_t(tile_all) * p.splits * p.zpad * kTcRows;
+                for (uint32_t z0 = 16u * zq; z0 < p.zpad; z0 += 64u) {
+                    if (pair) {
+                        if (tr < 64) {
+                            float up[16], gate[16];
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) { up[i] = 0.f; gate[i] = 0.f; }
-                                for (uint32_t sp = 0; sp < p.splits; ++sp) {
-                                    const float* q = base + (size_t(sp) * p.zpad + z0) * kTcRows;
-#pragma unroll
-                                    for (int i = 0; i < 16; ++i) { up[i] += __ldcg(q + size_t(i) * kTcRows + tr); gate[i] += __ldcg(q + size_t(i) * kTcRows + tr + 64); }
-                                }
-                                store_pair(z0, up, gate);
-                            }
-                        } else {
-                            float v[16];
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                            for (int i = 0; i < 16; ++i) { up[i] = 0.f; gate[i] = 0.f; }
                             for (uint32_t sp = 0; sp < p.splits; ++sp) {
                                 const float* q = base + (size_t(sp) * p.zpad + z0) * kTcRows;
+                                float a[16], b[16];
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) v[i] += __ldcg(q + size_t(i) * kTcRows + tr);
+                                for (int i = 0; i < 16; ++i) { a[i] = __ldcg(q + size_t(i) * kTcRows + tr); b[i] = __ldcg(q + size_t(i) * kTcRows + tr + 64); }
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) { up[i] += a[i]; gate[i] += b[i]; }
                             }
-                            store_plain(z0, v);
+                            store_pair(tr, z0, up, gate);
                         }
+                    } else {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                        for (uint32_t sp = 0; sp < p.splits; ++sp) {
+                            const float* q = base + (size_t(sp) * p.zpad + z0) * kTcRows;
+                            float a[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) a[i] = __ldcg(q + size_t(i) * kTcRows + tr);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] += a[i];
+                        }
+                        store_plain(tr, z0, v);
                     }
                 }
             }
@@ -731,12 +756,12 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
         return groups_all / s >= 2 && tiles <= kTcMaxTiles && size_t(tiles) * s * p.zpad * kTcRows * sizeof(float) <= kTcScratchBytes;
     };
     if (fast) {
-        // every CTA holds an SM to itself, so the launch runs in waves of sm_count CTAs: take the split whose last wave is
-        // the fullest (time ~ waves / splits), charging each further split 3 % for its pass through the scratch buffer
+        // every CTA holds an SM to itself, so the launch runs in waves of sm_count CTAs; a CTA costs a fixed part (set-up,
+        // filling its rings, the epilogue or the pass over the partial sums: about three group steps) plus its share of K
         float best = 1e30f;
         for (uint32_t s = 1; s <= 8 && fits(s); ++s) {
             const uint32_t waves = (tiles * s + uint32_t(ctx->sm_count) - 1) / uint32_t(ctx->sm_count);
-            const float cost = float(waves) / float(s) * (1.0f + 0.03f * float(s - 1));
+            const float cost = float(waves) * (3.0f + (s > 1 ? 0.5f : 0.0f) + float(groups_all) / float(s));
             if (cost < best) { best = cost; splits = s; }
         }
     } else {
