@@ -403,6 +403,11 @@ class HostContext:
     def session(self):
         return Session(self)
 
+    def set_exact_batched_products(self, on):
+        """Batched (prompt) q4_0 products with the exact hi/lo weight planes instead of one fp16 plane (lv_gemm_tc_set_exact).
+        Takes effect for steps recorded afterwards: set it before the session evaluates its first batch."""
+        check(load_kernels().lv_gemm_tc_set_exact(_p(self.lib.llava_context_lv(self.handle)), int(bool(on))))
+
 
 class Session:
     """llava_session."""

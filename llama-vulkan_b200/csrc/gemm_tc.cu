@@ -230,11 +230,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     const uint32_t bank_cols = (FAST ? 2u : 3u) * p.zpad;
     const uint32_t tmem_cols = FAST ? (p.zpad <= 16 ? 64u : (p.zpad <= 32 ? 128u : 256u)) : (p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u));
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kTcRawStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kTcProducerWarps); }
-        for (int i = 0; i < kTcSlots; ++i) { mbar_init(&slot_full[i], FAST ? kTcProducerWarps : kTcGroupWarps); mbar_init(&slot_empty[i], 1); }
-        for (int i = 0; i < kTcMaxBStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-        mbar_init(acc_full, 1);
+    // one barrier per thread (a single thread takes about a microsecond for all of them)
+    if (threadIdx.x < 44) {
+        const int i = int(threadIdx.x);
+        uint32_t count = 1;                                             // raw_full, slot_empty, acc_full, b_full, b_empty
+        if (i >= 2 && i < 4) count = kTcProducerWarps;                  // raw_empty
+        else if (i >= 4 && i < 7) count = FAST ? kTcProducerWarps : kTcGroupWarps;      // slot_full
+        mbar_init(&bars[i], count);
         fence_mbar_init();
     }
     if (warp == kTcProducerWarps + 1) {
@@ -330,11 +332,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     }
                     if (ok) tc_commit(&slot_empty[ab]);
                 }
-            } else
+            } else {
+            uint32_t bs = 0, b_phase = 0;
             for (uint32_t c = 0; c < n_chunks && ok; ++c) {
                 const int s = int(c % kTcSlots);
-                const uint32_t bs = c % nb;
-                ok = mbar_wait(&b_full[bs], (c / nb) & 1u, p.err) && mbar_wait(&slot_full[s], (c / kTcSlots) & 1u, p.err);
+                ok = mbar_wait(&b_full[bs], b_phase, p.err) && mbar_wait(&slot_full[s], (c / kTcSlots) & 1u, p.err);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint64_t a_hi = a_desc0 + ((uint32_t(s) * uint32_t(kTcSlotBytes)) >> 4), a_lo = a_hi + (kTcTileBytes >> 4);
@@ -348,6 +350,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 }
                 tc_commit(&slot_empty[s]);                                   // arrive when these MMAs have read the tiles
                 tc_commit(&b_empty[bs]);
+                if (++bs == nb) { bs = 0; b_phase ^= 1u; }
+            }
             }
             if (ok) tc_commit(acc_full);
         }

@@ -175,10 +175,10 @@ bool read_token_file(const string& path, vector<u32>* out) {
 
 // Flags of the reference (llava_context.cpp:163-200) that still mean something, plus the
 // ones its CLI lacks: --greedy, --tokens, --n-predict, --ignore-eos, --seed, --device,
-// --on-device, --write-synthetic, and --port / --bind for --server.
+// --on-device, --exact-prompt (batched prompt products with exact weight tiles), --write-synthetic, and --port / --bind for --server.
 int llava_context::run(int argc, char** argv) {
     bool server_mode = false, only_print_header = false, greedy = false, ignore_eos = false, on_device = false;
-    bool model_path_provided = false, have_seed = false;
+    bool model_path_provided = false, have_seed = false, exact_prompt = false;
     string model_path, tokens_path, synth_spec, bind_address = "0.0.0.0";
     u32 server_port = 1337;
     string prompt = "The ten best monuments to see in Paris are";
@@ -205,7 +205,7 @@ int llava_context::run(int argc, char** argv) {
         } else if (streq(a, "--help") || streq(a, "-h")) {
             cout << (argc ? argv[0] : "./vulkan_llama")
                  << " [-h] [-m model.bin] [--server [--port P] [--bind ADDR]] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
-                    " [--device D] [--on-device] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
+                    " [--device D] [--on-device] [--exact-prompt] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
                  << endl;
             exit(0);
         } else if (streq(a, "--verbose") || streq(a, "-v")) {
@@ -227,6 +227,8 @@ int llava_context::run(int argc, char** argv) {
             ignore_eos = true;
         } else if (streq(a, "--on-device")) {
             on_device = true;
+        } else if (streq(a, "--exact-prompt")) {
+            exact_prompt = true;
         } else if (streq(a, "--tokens")) {
             tokens_path = need_value(i);
         } else if (streq(a, "--n-predict")) {
@@ -294,6 +296,7 @@ int llava_context::run(int argc, char** argv) {
     }
     if (!open(model_path, device)) return 1;
     if (verbosity) cout << "Selected device: cuda:" << device << " (" << lv_ctx_sm_count(lv_context) << " SMs)" << endl;
+    if (exact_prompt) lv_gemm_tc_set_exact(lv_context, 1);
     if (server_mode) {
         // llava_context.cpp:246-249: sessions are created and driven by the clients; standard input or a signal ends it
         lsrv::session_wrapper::set_deterministic_sessions(greedy);

@@ -8,7 +8,8 @@ import numpy as np
 import pytest
 
 import quant_np as qn
-from test_e2e_gpu import CACHE_DIFFERING_HALVES, N_DECODE, N_PROMPT, OracleSession, assert_logits_close, note_parity, prompt_tokens
+from test_e2e_gpu import (CACHE_DIFFERING_HALVES, FAST_PROMPT_REL_L2, LOGIT_REL_L2, N_DECODE, N_PROMPT, OracleSession, assert_logits_close,
+                          note_parity, prompt_tokens, same_choice)
 
 pytestmark = pytest.mark.gpu
 
@@ -59,18 +60,28 @@ def test_13b_geometry_greedy_tokens_identical_and_logits_within_tolerance(run13)
     s.close()
 
 
-def test_13b_geometry_device_resident_loop_and_tensor_core_prompt(run13):
+@pytest.mark.parametrize("tc_form", ["exact", "fast"])
+def test_13b_geometry_device_resident_loop_and_tensor_core_prompt(run13, tc_form):
     # the prompt as one batch of 16 on the tensor cores, then decoding without the host in the loop
+    run13["ctx"].set_exact_batched_products(tc_form == "exact")
     s = run13["ctx"].session()
     s.set_deterministic(True)
     assert s.set_max_batch(16)
     for t in run13["prompt"]:
         assert s.push_token(t)
     first = s.predict_next_token()
-    m, r = assert_logits_close(s.logits(run13["vocab"]), run13["logits"][0])
-    assert first == run13["greedy"][0]
-    assert s.push_token(first)
-    rest = s.generate_greedy_on_device(N_DECODE - 1)
-    assert [first] + rest == run13["greedy"]
-    note_parity(f"13b geometry prompt as one tensor-core batch of 16: logits max-abs {m:.3e} rel-L2 {r:.3e}")
+    run13["ctx"].set_exact_batched_products(False)
+    m, r = assert_logits_close(s.logits(run13["vocab"]), run13["logits"][0], LOGIT_REL_L2 if tc_form == "exact" else FAST_PROMPT_REL_L2)
+    assert same_choice(first, s.logits(run13["vocab"]), run13["logits"][0])
+    if first == run13["greedy"][0]:
+        assert s.push_token(first)
+        rest = s.generate_greedy_on_device(N_DECODE - 1)
+        if tc_form == "exact":
+            assert [first] + rest == run13["greedy"]
+        else:       # the cache rows of the prompt differ in their last bits: a near-tie may go the other way later on
+            agree = next((i for i, (a, b) in enumerate(zip([first] + rest, run13["greedy"])) if a != b), N_DECODE)
+            assert agree >= 8, f"trajectories part after {agree} tokens"
+    else:
+        assert tc_form == "fast"
+    note_parity(f"13b geometry prompt as one tensor-core batch of 16 ({tc_form} tiles): logits max-abs {m:.3e} rel-L2 {r:.3e}")
     s.close()

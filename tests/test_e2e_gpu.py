@@ -17,6 +17,10 @@ pytestmark = pytest.mark.gpu
 
 N_PROMPT, N_DECODE = 16, 32
 LOGIT_MAX_ABS, LOGIT_REL_L2 = 1e-2, 1e-3
+# A prompt evaluated in batches on the tensor cores in the default ("fast") form of the q4_0 weight tiles -- one fp16
+# plane, each weight rounded to 11 significant bits -- leaves the logits about 1.1e-3 (rel-L2) from the oracle's after
+# two layers; the exact form (hi/lo planes) stays inside the decode tolerance.
+FAST_PROMPT_REL_L2 = 3e-3
 # A cache value whose fp32 source differs from the oracle's in its last bits may round to the neighbouring half.
 # Observed on B200: 0.3 % of the halves of a layer-0 cache and 9-11 % of a layer-1 cache (a layer-0 half that
 # rounds the other way moves the attention scores of every later row by ~3e-4, which reaches layer 1 as a
@@ -71,12 +75,29 @@ def note_parity(line):
             f.write(line + "\n")
 
 
-def assert_logits_close(got, want):
+def assert_logits_close(got, want, rel_l2=LOGIT_REL_L2):
     diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
     rel = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
     assert diff.max() <= LOGIT_MAX_ABS, f"max-abs {diff.max():.3e}"
-    assert rel <= LOGIT_REL_L2, f"rel-L2 {rel:.3e}"
+    assert rel <= rel_l2, f"rel-L2 {rel:.3e}"
     return diff.max(), rel
+
+
+def same_choice(tok, got_logits, want_logits):
+    """The greedy token equals the oracle's, or the oracle's two best logits are closer than the logits differ."""
+    want_tok = int(np.argmax(want_logits))
+    if tok == want_tok:
+        return True
+    top2 = np.sort(want_logits.astype(np.float64))[-2:]
+    return (top2[1] - top2[0]) <= 2 * np.abs(got_logits.astype(np.float64) - want_logits).max()
+
+
+@pytest.fixture(params=["exact", "fast"])
+def tc_form(request, run):
+    """Form of the batched q4_0 products for the sessions a test creates (q8_0 models always use the exact form)."""
+    run["ctx"].set_exact_batched_products(request.param == "exact")
+    yield request.param
+    run["ctx"].set_exact_batched_products(False)
 
 
 @pytest.fixture(scope="module", params=[qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
@@ -166,7 +187,7 @@ def test_prompt_in_batches_matches_token_by_token(run):
     s.close()
 
 
-def test_prompt_as_one_batch_on_the_tensor_cores(run):
+def test_prompt_as_one_batch_on_the_tensor_cores(run, tc_form):
     """16 prompt tokens in one recorded step: q4_0 models take the tcgen05 path (lv_gemm_tc*), q8_0
     models the per-token GEMV; either way the logits, the greedy token and the cache rows agree
     with the oracle's token-by-token evaluation."""
@@ -175,9 +196,10 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run):
     assert s.set_max_batch(16)
     for t in run["prompt"]:
         assert s.push_token(t)
+    rel_l2 = FAST_PROMPT_REL_L2 if (tc_form == "fast" and run["wtype"] == qn.Q4_0) else LOGIT_REL_L2
     tok = s.predict_next_token()
-    m, r = assert_logits_close(s.logits(run["vocab"]), run["logits"][0])
-    assert tok == run["greedy"][0]
+    m, r = assert_logits_close(s.logits(run["vocab"]), run["logits"][0], rel_l2)
+    assert same_choice(tok, s.logits(run["vocab"]), run["logits"][0])
     for layer in range(2):
         for which in (0, 1):
             got = s.read_kv(layer, which, 0, N_PROMPT, run["dim"]).view(np.float16).astype(np.float32)
@@ -185,16 +207,20 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run):
             assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
     # decoding continues from the batched prompt with the per-token kernels
     for step in range(1, 6):
+        if tok != run["greedy"][step - 1]:
+            break                                    # a near-tie went the other way: the trajectories part here
         assert s.push_token(tok)
         tok = s.predict_next_token()
-        assert_logits_close(s.logits(run["vocab"]), run["logits"][step])
-        assert tok == run["greedy"][step]
-    note_parity(f"config0 wtype={run['wtype']} prompt as one batch of 16: logits after the prompt max-abs {m:.3e} rel-L2 {r:.3e}")
+        assert_logits_close(s.logits(run["vocab"]), run["logits"][step], rel_l2)
+        assert same_choice(tok, s.logits(run["vocab"]), run["logits"][step])
+    if tc_form == "exact":
+        assert tok == run["greedy"][5]
+    note_parity(f"config0 wtype={run['wtype']} prompt as one batch of 16 ({tc_form} tiles): logits after the prompt max-abs {m:.3e} rel-L2 {r:.3e}")
     s.close()
 
 
 @pytest.mark.parametrize("n_tokens,max_batch", [(40, 16), (150, 64)])
-def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run, n_tokens, max_batch):
+def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run, n_tokens, max_batch, tc_form):
     """A prompt evaluated in several recorded steps (16 + 16 + 8, or 64 + 64 + 22 tokens), each later step
     attending over the rows of the earlier ones: logits and cache rows against the oracle's
     token-by-token evaluation."""
@@ -209,8 +235,11 @@ def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run, n_tokens, m
     for t in toks:
         assert s.push_token(t)
     tok = s.predict_next_token()
-    assert_logits_close(s.logits(run["vocab"]), want)
-    assert tok == orc.argmax()
+    m, r = assert_logits_close(s.logits(run["vocab"]), want, FAST_PROMPT_REL_L2 if (tc_form == "fast" and run["wtype"] == qn.Q4_0) else LOGIT_REL_L2)
+    assert same_choice(tok, s.logits(run["vocab"]), want)
+    if tc_form == "exact":
+        assert tok == orc.argmax()
+    note_parity(f"config0 wtype={run['wtype']} prompt of {n_tokens} in batches of {max_batch} ({tc_form} tiles): logits max-abs {m:.3e} rel-L2 {r:.3e}")
     for layer in range(2):
         for which in (0, 1):
             got = s.read_kv(layer, which, 0, n_tokens, run["dim"]).view(np.float16).astype(np.float32)
