@@ -1,11 +1,17 @@
 #include "llava_context.h"
 
 #include <signal.h>
+#include <sys/mman.h>
+#include <sys/wait.h>
 #include <sys/poll.h>
 #include <sys/signalfd.h>
 #include <unistd.h>
 
+#include <atomic>
+#include <chrono>
 #include <cstdlib>
+#include <new>
+#include <thread>
 #include <cstring>
 #include <fstream>
 #include <iostream>
@@ -171,18 +177,37 @@ bool read_token_file(const string& path, vector<u32>* out) {
     while (in >> v) out->push_back(u32(v));
     return !out->empty();
 }
+
+// What the ranks of `--gpus N` (one forked process per GPU) share: rank 0's communicator id and every rank's
+// peer-window handle, in an anonymous shared mapping made before the fork.
+struct tp_rendezvous {
+    std::atomic<u32> id_ready, handles_ready, connected, failed, done;
+    u8 nccl_id[128];
+    u8 handles[8][64];
+};
+
+// Waits until `counter` reaches `target`; false after two minutes or when a rank reported a failure.
+bool rendezvous_wait(const tp_rendezvous* rv, const std::atomic<u32>& counter, u32 target) {
+    const auto t0 = std::chrono::steady_clock::now();
+    while (counter.load(std::memory_order_acquire) < target) {
+        if (rv->failed.load(std::memory_order_acquire)) return false;
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) return false;
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+    return true;
+}
 }  // namespace
 
 // Flags of the reference (llava_context.cpp:163-200) that still mean something, plus the
 // ones its CLI lacks: --greedy, --tokens, --n-predict, --ignore-eos, --seed, --device,
-// --on-device, --exact-prompt (batched prompt products with exact weight tiles), --write-synthetic, and --port / --bind for --server.
+// --gpus N (tensor-parallel over devices D..D+N-1, one forked process each), --on-device, --exact-prompt (batched prompt products with exact weight tiles), --write-synthetic, and --port / --bind for --server.
 int llava_context::run(int argc, char** argv) {
     bool server_mode = false, only_print_header = false, greedy = false, ignore_eos = false, on_device = false;
     bool model_path_provided = false, have_seed = false, exact_prompt = false;
     string model_path, tokens_path, synth_spec, bind_address = "0.0.0.0";
     u32 server_port = 1337;
     string prompt = "The ten best monuments to see in Paris are";
-    u32 n_predict = 0, seed = 0;
+    u32 n_predict = 0, seed = 0, gpus = 1;
     int device = 0;
 
     auto need_value = [&](int& i) -> const char* {
@@ -205,7 +230,7 @@ int llava_context::run(int argc, char** argv) {
         } else if (streq(a, "--help") || streq(a, "-h")) {
             cout << (argc ? argv[0] : "./vulkan_llama")
                  << " [-h] [-m model.bin] [--server [--port P] [--bind ADDR]] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
-                    " [--device D] [--on-device] [--exact-prompt] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
+                    " [--device D] [--gpus N] [--on-device] [--exact-prompt] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
                  << endl;
             exit(0);
         } else if (streq(a, "--verbose") || streq(a, "-v")) {
@@ -238,6 +263,8 @@ int llava_context::run(int argc, char** argv) {
             have_seed = true;
         } else if (streq(a, "--device")) {
             device = atoi(need_value(i));
+        } else if (streq(a, "--gpus")) {
+            gpus = u32(strtoul(need_value(i), nullptr, 10));
         } else if (streq(a, "--write-synthetic")) {
             synth_spec = need_value(i);
         } else if (i + 1 != argc) {
@@ -290,11 +317,91 @@ int llava_context::run(int argc, char** argv) {
         f.print_info();
         return 0;
     }
-    if (!setup_signal_handling()) {
-        cerr << "[!] Cannot setup signal handling" << endl;
+    // --gpus N: the process forks N-1 times before anything touches CUDA; rank r drives device D + r, rank 0 (the
+    // parent) speaks, the others run the same loop silently (same tokens: the ranks' logits are bit-identical)
+    tp_rendezvous* rv = nullptr;
+    u32 my_rank = 0;
+    vector<pid_t> children;
+    if (gpus == 0 || gpus > 8) {
+        cerr << "[!] --gpus takes 1..8" << endl;
         return 1;
     }
-    if (!open(model_path, device)) return 1;
+    if (gpus > 1) {
+        if (server_mode) {
+            cerr << "[!] --server drives one GPU; --gpus is for the generation loop" << endl;
+            return 1;
+        }
+        void* mem = ::mmap(nullptr, sizeof(tp_rendezvous), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0);
+        if (mem == MAP_FAILED) {
+            perror("mmap");
+            return 1;
+        }
+        rv = new (mem) tp_rendezvous{};
+        cout.flush();
+        for (u32 r = 1; r < gpus; ++r) {
+            const pid_t pid = ::fork();
+            if (pid < 0) {
+                perror("fork");
+                rv->failed = 1;
+                break;
+            }
+            if (pid == 0) {
+                my_rank = r;
+                children.clear();
+                cout.setstate(ios::failbit);            // only rank 0 prints
+                break;
+            }
+            children.push_back(pid);
+        }
+    }
+    auto finish = [&](int code) -> int {
+        if (rv == nullptr) return code;
+        if (code != 0) rv->failed = 1;
+        // no rank releases its peer window while another may still launch kernels that store into it: everyone
+        // reports here once its own loop has ended (a rank that stopped early makes the others' bounded device waits
+        // run out, which ends their loops too)
+        rv->done.fetch_add(1, std::memory_order_acq_rel);
+        const auto t0 = std::chrono::steady_clock::now();
+        while (rv->done.load(std::memory_order_acquire) < gpus && std::chrono::steady_clock::now() - t0 < std::chrono::seconds(120))
+            std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        if (my_rank != 0) ::_exit(code);
+        for (pid_t pid : children) {
+            int status = 0;
+            if (::waitpid(pid, &status, 0) < 0 || !WIFEXITED(status) || WEXITSTATUS(status) != 0) code = code ? code : 1;
+        }
+        return code;
+    };
+    if (!setup_signal_handling()) {
+        cerr << "[!] Cannot setup signal handling" << endl;
+        return finish(1);
+    }
+    if (rv == nullptr) {
+        if (!open(model_path, device)) return 1;
+    } else {
+        if (my_rank == 0) {
+            if (lv_comm_unique_id(rv->nccl_id) != LV_OK) {
+                cerr << "[!] cannot make a communicator id: " << lv_last_error_string() << endl;
+                return finish(1);
+            }
+            rv->id_ready.store(1, std::memory_order_release);
+        } else if (!rendezvous_wait(rv, rv->id_ready, 1)) {
+            return finish(1);
+        }
+        if (!open_sharded(model_path, device + int(my_rank), my_rank, gpus, rv->nccl_id)) return finish(1);
+        // peer windows for the exchange fused into the GEMVs: every rank publishes its handle, then maps the others'
+        if (!peer_window_create(rv->handles[my_rank])) {
+            cerr << "[!] rank " << my_rank << ": cannot create the peer window: " << lv_last_error_string() << endl;
+            return finish(1);
+        }
+        rv->handles_ready.fetch_add(1, std::memory_order_acq_rel);
+        if (!rendezvous_wait(rv, rv->handles_ready, gpus)) return finish(1);
+        if (!peer_connect(&rv->handles[0][0])) {
+            cerr << "[!] rank " << my_rank << ": cannot map the peers' windows: " << lv_last_error_string() << endl;
+            return finish(1);
+        }
+        rv->connected.fetch_add(1, std::memory_order_acq_rel);
+        if (!rendezvous_wait(rv, rv->connected, gpus)) return finish(1);
+    }
     if (verbosity) cout << "Selected device: cuda:" << device << " (" << lv_ctx_sm_count(lv_context) << " SMs)" << endl;
     if (exact_prompt) lv_gemm_tc_set_exact(lv_context, 1);
     if (server_mode) {
@@ -315,18 +422,18 @@ int llava_context::run(int argc, char** argv) {
         vector<u32> ids;
         if (!read_token_file(tokens_path, &ids)) {
             cerr << "[!] cannot read token ids from " << tokens_path << endl;
-            return 1;
+            return finish(1);
         }
         for (u32 t : ids) {
             if (!session.push_token(t)) {
                 cerr << "[!] System prompt overflows backlog buffer !" << endl;
-                exit(1);
+                return finish(1);
             }
         }
     } else {
         if (!session.set_text(prompt)) {
             cerr << "[!] System prompt overflows backlog buffer !" << endl;
-            exit(1);
+            return finish(1);
         }
         cout << prompt << flush;
     }
@@ -335,21 +442,23 @@ int llava_context::run(int argc, char** argv) {
     if (on_device && greedy && n_predict > 1) {
         // evaluate the prompt, then let the device feed itself
         u32 tok = session.predict_next_token();
-        if (~tok == 0 || !session.push_token(tok)) return 1;
+        if (~tok == 0 || !session.push_token(tok)) return finish(1);
         vector<u32> rest;
         if (!session.generate_greedy_on_device(n_predict - 1, &rest)) {
             cerr << "Unknown error" << endl;
-            return 1;
+            return finish(1);
         }
         cout << model->get_tokens()[tok].text;
         for (u32 t : rest) cout << model->get_tokens()[t].text;
         cout << endl;
-        return 0;
+        return finish(0);
     }
+    int status = 0;
     u32 next_token = session.predict_next_token();
     while (true) {
         if (~next_token == 0) {
             cerr << "Unknown error" << endl;
+            status = 1;
             break;
         }
         ++produced;
@@ -358,6 +467,7 @@ int llava_context::run(int argc, char** argv) {
         if (!session.push_token(next_token)) break;      // too many tokens
         if (!session.start_next_token_prediction()) {
             cerr << "Cannot start processing, unknown error" << endl;
+            status = 1;
             break;
         }
         cout << model->get_tokens()[next_token].text << flush;     // printed while the device works
@@ -365,5 +475,5 @@ int llava_context::run(int argc, char** argv) {
     }
     if (~next_token != 0 && (next_token != eos_id || ignore_eos)) cout << model->get_tokens()[next_token].text;
     cout << endl;
-    return 0;
+    return finish(status);
 }

@@ -85,3 +85,24 @@ def test_cli_server_mode_generates_over_tcp(cli, pkg):
     finally:
         if p.poll() is None:
             p.kill()
+
+
+def _device_count(pkg):
+    import ctypes as C
+    n = C.c_int(0)
+    pkg.load_kernels().lv_device_count(C.byref(n))
+    return n.value
+
+
+@pytest.mark.parametrize("extra", [[], ["--on-device"]], ids=["host-in-the-loop", "device-resident"])
+def test_cli_tensor_parallel_over_two_gpus(cli, pkg, extra):
+    """`--gpus 2`: the tool forks one process per GPU (row / column shards, exchange fused into the GEMVs); rank 0 prints
+    the same greedy tokens as the oracle."""
+    if _device_count(pkg) < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.pop("NCCL_DEBUG", None)
+    out = subprocess.run([cli["exe"], "-m", cli["model"], "--gpus", "2", "--greedy", "--tokens", cli["tokens"], "--n-predict", str(N_PREDICT),
+                          "--ignore-eos"] + extra, check=True, timeout=600, stdout=subprocess.PIPE, env=env).stdout
+    lines = [l for l in out.split(b"\n") if not l.startswith(b"NCCL version")]      # the library's own banner, if it prints one
+    assert b"\n".join(lines) == cli["text"] + b"\n", (out, cli["text"])
