@@ -106,6 +106,11 @@ uint64_t llava_session_read_step_trace(void* session, uint64_t* out, uint64_t ca
 /* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
 int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
 
+/* where a rank's column slice of a cache row lives in a snapshot file (host/tp_shard.h), and the size of the file */
+uint64_t llava_tp_snapshot_slice_offset(uint32_t n_tokens, uint32_t dim, uint32_t layer, uint32_t which, uint32_t row,
+                                        uint32_t rank, uint32_t n_ranks);
+uint64_t llava_tp_snapshot_file_size(uint32_t n_tokens, uint32_t dim, uint32_t n_layers);
+
 /* ---- lsrv::session_wrapper (server/session_wrapper.h:17-23): one thread and one session per
  *      served session, driven by orders (opcodes of server/types.h:50-73).  The owner created
  *      here plays the reference's llava_server: it collects the outbound packets. */

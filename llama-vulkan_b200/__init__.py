@@ -267,6 +267,8 @@ HOST_API = {
     "llava_session_set_step_trace": (_int, [_p, _int]),
     "llava_session_read_step_trace": (_u64, [_p, _p, _u64, _p]),
     "llava_session_read_kv": (_int, [_p, _u32, _int, _u32, _u32, _p]),
+    "llava_tp_snapshot_slice_offset": (_u64, [_u32, _u32, _u32, _u32, _u32, _u32, _u32]),
+    "llava_tp_snapshot_file_size": (_u64, [_u32, _u32, _u32]),
     "llava_wrapper_owner_create": (_p, [_p]),
     "llava_wrapper_owner_destroy": (None, [_p]),
     "llava_wrapper_owner_dead_sessions": (_u32, [_p]),

@@ -322,6 +322,12 @@ void llava_wrapper_push_order(void* w, uint32_t client_id, uint32_t request_id, 
     static_cast<lsrv::session_wrapper*>(w)->push_order(client_id, request_id, opcode, arg1, s ? std::string(s, len) : std::string());
 }
 
+uint64_t llava_tp_snapshot_slice_offset(uint32_t n_tokens, uint32_t dim, uint32_t layer, uint32_t which, uint32_t row, uint32_t rank,
+                                        uint32_t n_ranks) {
+    return tp_snapshot_slice_offset(n_tokens, dim, layer, which, row, rank, n_ranks);
+}
+uint64_t llava_tp_snapshot_file_size(uint32_t n_tokens, uint32_t dim, uint32_t n_layers) { return tp_snapshot_file_size(n_tokens, dim, n_layers); }
+
 // ---- lsrv::tlv_server on a thread of its own ----
 namespace {
 struct served {

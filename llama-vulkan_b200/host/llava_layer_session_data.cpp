@@ -62,12 +62,13 @@ void llava_layer_session_data::dump_tracing_layers(int out_fd, const string& nam
     if (trace_allocation) trace_allocation->dump_buffers(out_fd, name);
 }
 
+// The rows this rank holds: [token_count][dim / ranks] halves of K, then of V (the whole rows on one GPU).
 bool llava_layer_session_data::dump_kv_cache(u8* dst, u32 token_count) {
-    const size_t n = size_t(2) * session->model->get_header().dim * token_count;     // llava_layer_session_data.cpp:165-172
+    const size_t n = size_t(2) * (session->model->get_header().dim / session->ctx->tp_size()) * token_count;     // llava_layer_session_data.cpp:165-172
     return k_cache->read_raw(0, dst, n) && v_cache->read_raw(0, dst + n, n);
 }
 
 bool llava_layer_session_data::restore_kv_cache(const u8* src, u32 token_count) {
-    const size_t n = size_t(2) * session->model->get_header().dim * token_count;     // llava_layer_session_data.cpp:174-181
+    const size_t n = size_t(2) * (session->model->get_header().dim / session->ctx->tp_size()) * token_count;     // llava_layer_session_data.cpp:174-181
     return k_cache->write_raw(0, src, n) && v_cache->write_raw(0, src + n, n);
 }

@@ -15,6 +15,7 @@
 #include "llava_context.h"
 #include "llava_device_memory.h"
 #include "llava_layer.h"
+#include "tp_shard.h"
 #include "llava_layer_session_data.h"
 #include "utils.h"
 
@@ -484,28 +485,42 @@ ReturnCode llava_session::save_frame(const string& path) {
 
 // File layout (llava_session.cpp:447-495): u32 n; u32 tokens[n]; then per layer the first n
 // rows of the K cache followed by the first n rows of the V cache, f16 [n][dim] each.
+// File layout of the reference (llava_session.cpp:447-500): {u32 n; u32 tokens[n]; per layer: K rows [n][dim] f16, V rows
+// [n][dim] f16}.  A tensor-parallel rank holds the columns [rank * dim / ranks, (rank + 1) * dim / ranks) of every row (its
+// heads): each rank writes its column slices at their place in the same file, so that the file equals the one a single
+// GPU writes.  Every rank sizes the file and writes the header; the caller waits for all ranks before reading it.
 ReturnCode llava_session::snapshot(const string& path) {
-    if (ctx->tp_size() > 1) return ReturnCode::nok;        // each rank holds a head slice of the caches
     if (!ensure_buffers_created()) return ReturnCode::nok;
     if (last_command_buffer) last_command_buffer->wait_idle();
-    const u32 n = current_tokens_in_gpu, dim = model->get_header().dim;
-    const size_t per_layer = size_t(2) * n * dim * 2;
-    const int fd = ::open(path.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
+    const u32 n = current_tokens_in_gpu, dim = model->get_header().dim, ranks = ctx->tp_size(), width = dim / ranks;
+    const size_t per_layer = size_t(2) * n * dim * 2, local = size_t(2) * n * width * 2;
+    const int fd = ::open(path.c_str(), ranks > 1 ? (O_WRONLY | O_CREAT) : (O_WRONLY | O_CREAT | O_TRUNC), 0644);
     if (fd < 0) {
         perror("open");
         return ReturnCode::nok;
     }
-    bool ok = write_noshort(fd, &n, 4) == 4 && write_noshort(fd, token_buffer.data(), size_t(n) * 4) == size_t(n) * 4;
-    vector<u8> rows(per_layer);
+    bool ok = ::ftruncate(fd, off_t(tp_snapshot_file_size(n, dim, u32(layer_data.size())))) == 0;
+    ok = ok && pwrite_noshort(fd, &n, 4, 0) == 4 && pwrite_noshort(fd, token_buffer.data(), size_t(n) * 4, 4) == size_t(n) * 4;
+    vector<u8> rows(local);
+    const size_t row_bytes = size_t(width) * 2;
+    u32 layer = 0;
     for (llava_layer_session_data* l : layer_data) {
-        ok = ok && l->dump_kv_cache(rows.data(), n) && write_noshort(fd, rows.data(), per_layer) == per_layer;
+        ok = ok && l->dump_kv_cache(rows.data(), n);
+        if (ranks == 1) {
+            ok = ok && pwrite_noshort(fd, rows.data(), per_layer, (long long)tp_snapshot_slice_offset(n, dim, layer, 0, 0, 0, 1)) == per_layer;
+        } else {
+            for (u32 which = 0; which < 2 && ok; ++which)           // K rows, then V rows
+                for (u32 i = 0; i < n && ok; ++i)
+                    ok = pwrite_noshort(fd, rows.data() + (size_t(which) * n + i) * row_bytes, row_bytes,
+                                        (long long)tp_snapshot_slice_offset(n, dim, layer, which, i, ctx->tp_rank(), ranks)) == row_bytes;
+        }
+        ++layer;
     }
     if (::close(fd) < 0) ok = false;
     return ok ? ReturnCode::ok : ReturnCode::nok;
 }
 
 ReturnCode llava_session::restore(const string& path) {
-    if (ctx->tp_size() > 1) return ReturnCode::nok;
     if (!ensure_buffers_created()) return ReturnCode::nok;
     const int fd = ::open(path.c_str(), O_RDONLY);
     if (fd < 0) {
@@ -534,9 +549,23 @@ ReturnCode llava_session::restore(const string& path) {
     lv_stream_sync(ctx->lv(), 0);
     rewind(0);
     if (!set_backlog_size(needed)) return bail("Cannot set backlog size");
-    vector<u8> rows(per_layer);
+    // a tensor-parallel rank takes its column slice of every row (see snapshot)
+    const u32 ranks = ctx->tp_size(), width = dim / ranks;
+    const size_t row_bytes = size_t(width) * 2;
+    vector<u8> rows(size_t(2) * n * row_bytes);
+    u32 layer = 0;
     for (llava_layer_session_data* l : layer_data) {
-        if (read_noshort(fd, rows.data(), per_layer) != per_layer || !l->restore_kv_cache(rows.data(), n)) return bail("Short read");
+        if (ranks == 1) {
+            if (pread_noshort(fd, rows.data(), per_layer, (long long)tp_snapshot_slice_offset(n, dim, layer, 0, 0, 0, 1)) != per_layer) return bail("Short read");
+        } else {
+            for (u32 which = 0; which < 2; ++which)
+                for (u32 i = 0; i < n; ++i)
+                    if (pread_noshort(fd, rows.data() + (size_t(which) * n + i) * row_bytes, row_bytes,
+                                      (long long)tp_snapshot_slice_offset(n, dim, layer, which, i, ctx->tp_rank(), ranks)) != row_bytes)
+                        return bail("Short read");
+        }
+        if (!l->restore_kv_cache(rows.data(), n)) return bail("Cannot upload the cache rows");
+        ++layer;
     }
     ::close(fd);
     token_buffer = toks;

@@ -57,3 +57,12 @@ bool tp_pack(const u8* src, ggml_value_type type, u32 rows, u32 cols, tp_split h
     }
     return true;
 }
+
+u64 tp_snapshot_slice_offset(u32 n_tokens, u32 dim, u32 layer, u32 which, u32 row, u32 rank, u32 n_ranks) {
+    const u64 header = 4 + u64(n_tokens) * 4, per_cache = u64(n_tokens) * dim * 2;
+    return header + (u64(layer) * 2 + which) * per_cache + u64(row) * dim * 2 + u64(rank) * (dim / n_ranks) * 2;
+}
+
+u64 tp_snapshot_file_size(u32 n_tokens, u32 dim, u32 n_layers) {
+    return 4 + u64(n_tokens) * 4 + u64(n_layers) * 2 * n_tokens * dim * 2;
+}

@@ -29,4 +29,11 @@ tp_shard_shape tp_shape(ggml_value_type type, u32 rows, u32 cols, tp_split how, 
 // writes the local matrix of `rank` to dst (tp_shape(...).bytes bytes) from the whole tensor at src
 bool tp_pack(const u8* src, ggml_value_type type, u32 rows, u32 cols, tp_split how, u32 rank, u32 n_ranks, u8* dst);
 
+// Snapshot files keep the reference's layout (llava_session.cpp:447-500): {u32 n; u32 tokens[n]; per layer: K rows
+// [n][dim] f16, V rows [n][dim] f16}.  A rank holds the columns [rank * dim / n_ranks, (rank + 1) * dim / n_ranks) of
+// every cache row.  Byte offset of that slice of row `row` of cache `which` (0 = K, 1 = V) of layer `layer`, and the
+// size of the whole file.
+u64 tp_snapshot_slice_offset(u32 n_tokens, u32 dim, u32 layer, u32 which, u32 row, u32 rank, u32 n_ranks);
+u64 tp_snapshot_file_size(u32 n_tokens, u32 dim, u32 n_layers);
+
 #endif

@@ -61,6 +61,34 @@ size_t write_noshort(int fd, const void* src, size_t sz) {
     return done;
 }
 
+size_t pread_noshort(int fd, void* dst, size_t sz, long long offset) {
+    size_t done = 0;
+    while (done < sz) {
+        const ssize_t r = ::pread(fd, static_cast<u8*>(dst) + done, sz - done, static_cast<off_t>(offset) + static_cast<off_t>(done));
+        if (r < 0 && errno == EINTR) continue;
+        if (r <= 0) {
+            if (r < 0) perror("pread_noshort");
+            break;
+        }
+        done += static_cast<size_t>(r);
+    }
+    return done;
+}
+
+size_t pwrite_noshort(int fd, const void* src, size_t sz, long long offset) {
+    size_t done = 0;
+    while (done < sz) {
+        const ssize_t r = ::pwrite(fd, static_cast<const u8*>(src) + done, sz - done, static_cast<off_t>(offset) + static_cast<off_t>(done));
+        if (r < 0 && errno == EINTR) continue;
+        if (r <= 0) {
+            perror("pwrite_noshort");
+            break;
+        }
+        done += static_cast<size_t>(r);
+    }
+    return done;
+}
+
 float half_to_float(u16 h) {
     const u32 sign = (h & 0x8000u) << 16;
     u32 exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, bits;

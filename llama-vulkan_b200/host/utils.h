@@ -17,6 +17,9 @@ bool starts_with(const std::string& a, const std::string& b);
 // read/write all of `sz` bytes unless the descriptor fails; return bytes moved (utils.cpp:63-90)
 size_t read_noshort(int fd, void* dst, size_t sz);
 size_t write_noshort(int fd, const void* src, size_t sz);
+// the same at a file offset (the descriptor's position is left alone)
+size_t pread_noshort(int fd, void* dst, size_t sz, long long offset);
+size_t pwrite_noshort(int fd, const void* src, size_t sz, long long offset);
 // IEEE binary16 <-> binary32 on the host
 float half_to_float(u16 h);
 u16 float_to_half(float f);        // round to nearest even

@@ -124,3 +124,54 @@ def test_two_rank_gloo_ffn_block_matches_the_unsharded_block():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert err < 2e-5
+
+
+def _snapshot_worker(rank, world, port, path, q):
+    """Every rank writes its column slices of seeded cache rows where llava_session::snapshot would put them; after a
+    barrier rank 0 compares the file with the single-GPU layout {n, tokens, per layer K [n][dim], V [n][dim]}."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lib = load_pkg().load_host()
+    n, dim, layers = 7, 256, 3
+    rng = np.random.default_rng(99)                       # the same "caches" on every rank; each keeps its columns
+    tokens = rng.integers(0, 32000, n).astype(np.uint32)
+    caches = rng.integers(0, 65536, (layers, 2, n, dim)).astype(np.uint16)
+    width = dim // world
+    fd = os.open(path, os.O_WRONLY | os.O_CREAT, 0o644)
+    os.ftruncate(fd, lib.llava_tp_snapshot_file_size(n, dim, layers))
+    os.pwrite(fd, np.uint32(n).tobytes() + tokens.tobytes(), 0)
+    for layer in range(layers):
+        for which in range(2):
+            for row in range(n):
+                mine = caches[layer, which, row, rank * width:(rank + 1) * width]
+                os.pwrite(fd, mine.tobytes(), lib.llava_tp_snapshot_slice_offset(n, dim, layer, which, row, rank, world))
+    os.close(fd)
+    dist.barrier()
+    if rank == 0:
+        want = np.uint32(n).tobytes() + tokens.tobytes() + caches.tobytes()
+        q.put(open(path, "rb").read() == want)
+        # and back: the slices a rank would read on restore
+        raw = np.frombuffer(want, np.uint8)
+        ok = True
+        for r in range(world):
+            at = lib.llava_tp_snapshot_slice_offset(n, dim, 2, 1, 5, r, world)
+            ok = ok and raw[at:at + 2 * width].tobytes() == caches[2, 1, 5, r * width:(r + 1) * width].tobytes()
+        q.put(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_snapshot_slices_assemble_the_single_gpu_file(tmp_path):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    path = str(tmp_path / "snap.bin")
+    procs = [ctx.Process(target=_snapshot_worker, args=(r, 2, port, path, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    assert q.get(timeout=120) and q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0

@@ -109,3 +109,122 @@ def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path, exchange):
             assert np.abs(got - want).max() <= 1e-2
             assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
         assert np.array_equal(results[0][1][step], results[1][1][step])      # every rank holds the same logits
+
+
+def _snapshot_worker(rank, world, path, id_q, out_q, peer_q, snap_in, snap_out, n_first, n_more):
+    """Restores snap_in (if given), or feeds the prompt and decodes n_first tokens; decodes n_more tokens; writes snap_out."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    pkg = load_pkg()
+    klib = pkg.load_kernels()
+    if rank == 0:
+        buf = (C.c_uint8 * 128)()
+        pkg.check(klib.lv_comm_unique_id(buf))
+        for _ in range(world - 1):
+            id_q.put(bytes(buf))
+        ident = bytes(buf)
+    else:
+        ident = id_q.get(timeout=120)
+    ctx = pkg.HostContext(path, rank, rank, world, ident)
+    mine = ctx.peer_window_handle()
+    for r in range(world):
+        peer_q[r].put((rank, mine))
+    got = dict(peer_q[rank].get(timeout=120) for _ in range(world))
+    ctx.peer_connect([got[r] for r in range(world)])
+    s = ctx.session()
+    s.set_deterministic(True)
+    toks = []
+    if snap_in:
+        assert s.restore(snap_in) == 0
+        before = s.tokens()
+    else:
+        for t in _prompt():
+            assert s.push_token(t)
+        for _ in range(n_first):
+            toks.append(s.predict_next_token())
+            s.push_token(toks[-1])
+        before = None
+    if snap_out:
+        s.predict_next_token()                 # evaluate the last pushed token too, so that it is part of the snapshot
+        assert s.snapshot(snap_out) == 0
+    more = []
+    if snap_in and n_more:
+        # the snapshot holds evaluated tokens only; the token that followed them is the next greedy choice of the
+        # uninterrupted run, which the test passes in n_first
+        s.push_token(n_first)
+        for _ in range(n_more):
+            more.append(s.predict_next_token())
+            s.push_token(more[-1])
+    out_q.put((rank, toks, before, more))
+    s.close()
+    ctx.close()
+
+
+def _run_ranks(target, args_of_rank, world=2):
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    id_q, out_q = mpc.Queue(), mpc.Queue()
+    peer_q = [mpc.Queue() for _ in range(world)]
+    procs = [mpc.Process(target=target, args=(r, world) + args_of_rank(r, id_q, out_q, peer_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        try:
+            res = out_q.get(timeout=300)
+        except queue.Empty:
+            for p in procs:
+                p.kill()
+            raise AssertionError("a rank did not finish")
+        results[res[0]] = res[1:]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return results
+
+
+def test_snapshot_written_by_two_ranks_restores_on_one_gpu_and_back(pkg, tmp_path):
+    """llava_session::snapshot on a sharded session gathers every rank's head slice into the reference's file layout:
+    the file written by 2 ranks is byte-identical in size to a 1-GPU one and a 1-GPU session restored from it continues
+    with the tokens of an uninterrupted run; a 1-GPU snapshot restores on 2 ranks likewise."""
+    if _device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    path = str(tmp_path / "tiny.bin")
+    pkg.write_synthetic_model(path, "7b", n_layers=2)
+    ctx = pkg.HostContext(path, 0)
+    want_toks, _ = _decode(ctx)                                   # uninterrupted: prompt + N_DECODE greedy tokens
+    n_first = 5
+    # --- 2 ranks write, 1 GPU restores ---
+    snap2 = str(tmp_path / "snap_2ranks.bin")
+    res = _run_ranks(_snapshot_worker, lambda r, id_q, out_q, peer_q: (path, id_q, out_q, peer_q, None, snap2, n_first, 0))
+    assert res[0][0] == res[1][0] == want_toks[:n_first]
+    n_eval = N_PROMPT + n_first
+    assert os.path.getsize(snap2) == 4 + 4 * n_eval + 2 * 2 * n_eval * 4096 * 2
+    s = ctx.session()
+    s.set_deterministic(True)
+    assert s.restore(snap2) == 0
+    assert s.tokens() == _prompt() + want_toks[:n_first]
+    # the next greedy token is known from the uninterrupted run; push it and go on
+    cont = []
+    s.push_token(want_toks[n_first])
+    for _ in range(n_first + 1, N_DECODE):
+        cont.append(s.predict_next_token())
+        s.push_token(cont[-1])
+    assert cont == want_toks[n_first + 1:]
+    # --- 1 GPU writes, 2 ranks restore ---
+    snap1 = str(tmp_path / "snap_1gpu.bin")
+    s.rewind(0)
+    for t in _prompt() + want_toks[:n_first]:
+        s.push_token(t)
+    s.predict_next_token()
+    assert s.snapshot(snap1) == 0
+    s.close()
+    ctx.close()
+    a, b = np.fromfile(snap1, np.uint8), np.fromfile(snap2, np.uint8)
+    assert a.size == b.size and np.array_equal(a[:4 + 4 * n_eval], b[:4 + 4 * n_eval])
+    # cache rows: the same numbers up to neighbouring halves (the sharded exchange sums in another order)
+    ha, hb = a[4 + 4 * n_eval:].view(np.float16).astype(np.float32), b[4 + 4 * n_eval:].view(np.float16).astype(np.float32)
+    assert np.abs(ha - hb).max() <= 2e-3 * np.abs(ha).max()
+    n_more = N_DECODE - n_first - 1
+    res = _run_ranks(_snapshot_worker, lambda r, id_q, out_q, peer_q: (path, id_q, out_q, peer_q, snap1, None, want_toks[n_first], n_more))
+    assert res[0][1] == res[1][1] == _prompt() + want_toks[:n_first]
+    assert res[0][2] == res[1][2] == want_toks[n_first + 1:]                  # the sharded session continues the same trajectory
