@@ -440,13 +440,15 @@ def measure_decode(rig, ctx, name, args, repeats):
 
     s = ctx.session()
     s.set_deterministic(True)
-    if world == 1:
-        assert s.set_max_batch(64)          # prompt in steps of up to 64 tokens (tensor-core path)
+    # prompt in steps of up to 64 tokens (tensor-core path); a sharded session whose shard shapes do not fit the tiles
+    # (7B at 8 ranks: 1376 rows of w3 / w1 per rank) refuses and goes token by token
+    batched = bool(s.set_max_batch(64))
+    assert batched or world > 1
     for t in prompt_tokens(n_prompt):
         assert s.push_token(t)
     t0 = time.perf_counter()
     first = s.predict_next_token()          # ingests the prompt (records its steps on first use)
-    prompt_eval.update(tokens=n_prompt, seconds=time.perf_counter() - t0, max_batch=64 if world == 1 else 1)
+    prompt_eval.update(tokens=n_prompt, seconds=time.perf_counter() - t0, max_batch=64 if batched else 1)
     assert first != pkg.NO_TOKEN
     assert s.push_token(first)
     warm = s.generate_greedy_on_device(args.warmup)
@@ -512,7 +514,7 @@ def measure_decode(rig, ctx, name, args, repeats):
         rig.barrier()
     s.close()
     # ---- a long prompt through the batched (tensor-core) steps, second pass so that the steps are already recorded ----
-    if world == 1:
+    if batched:
         long_n = 1024
         sp = ctx.session()
         sp.set_deterministic(True)
@@ -523,9 +525,10 @@ def measure_decode(rig, ctx, name, args, repeats):
             for t in prompt_tokens(long_n):
                 assert sp.push_token(t)
             pkg.check(klib.lv_stream_sync(lv, 0))
+            rig.barrier()
             t0 = time.perf_counter()
             assert sp.predict_next_token() != pkg.NO_TOKEN
-            long_secs.append(time.perf_counter() - t0)
+            long_secs.append(rig.max_over_ranks(time.perf_counter() - t0))
         sp.close()
         prompt_eval["long_prompt"] = {"tokens": long_n, "max_batch": 64, "first_pass_seconds": long_secs[0],
                                       "seconds": min(long_secs[1:]), "tokens_per_s": long_n / min(long_secs[1:])}

@@ -223,6 +223,11 @@ size_t lv_act_split_bytes(uint32_t cols, uint32_t batch);
  * (zpad = batch rounded up to 16; rows < zpad: hi of a token, then lo; a
  * row's 16-byte units at unit ^ (row & 7)); tokens >= batch are zero. */
 int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch);
+/* The same for an input of cols_used values per token (dense rows) that meets a matrix of cols >= cols_used columns:
+ * columns from cols_used on are zero.  This is the input of a tensor-parallel column shard whose rows are padded with
+ * zero blocks (host/tp_shard.h).  No normalisation with padding. */
+int lv_act_split_f16_padded(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols_used, uint32_t cols,
+                            uint32_t batch);
 
 /* out[z][r] (+)= sum_k W[r][k] x[z][k]: matmul / matmul_add_inplace for a batch. */
 int lv_gemm_tc(lv_ctx* ctx, float* out, const void* W, int wtype, const void* xh, uint32_t rows, uint32_t cols,

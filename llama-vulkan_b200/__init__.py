@@ -89,6 +89,7 @@ KERNEL_API = {
     "lv_attention_fused_static": (_int, [_p, _p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
     "lv_act_split_bytes": (_sz, [_u32, _u32]),
     "lv_act_split_f16": (_int, [_p, _p, _p, _p, _u32, _u32]),
+    "lv_act_split_f16_padded": (_int, [_p, _p, _p, _p, _u32, _u32, _u32]),
     "lv_gemm_tc_set_exact": (_int, [_p, _int]),
     "lv_gemm_tc": (_int, [_p, _p, _p, _int, _p, _u32, _u32, _u32, _int]),
     "lv_gemm_tc_silu": (_int, [_p, _p, _p, _p, _int, _p, _u32, _u32, _u32]),

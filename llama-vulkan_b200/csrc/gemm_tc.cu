@@ -655,13 +655,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
 // 16-byte units stored at unit ^ (row & 7) -- the 128-byte swizzle the tensor core's descriptors expect.
 // Grid: zpad CTAs; tokens z >= Z are zero so that the padded columns
 // of the product are defined.  A thread converts one unit of eight values.
+// K_used <= K: the rows of x hold K_used values (row stride K_used); columns from K_used on are zero (the padding of a
+// tensor-parallel column shard).
 __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh, const float* __restrict__ x,
-                                                        const float* __restrict__ norm_w, uint32_t K, uint32_t Z, uint32_t zpad) {
+                                                        const float* __restrict__ norm_w, uint32_t K, uint32_t K_used, uint32_t Z, uint32_t zpad) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[64];
     const uint32_t z = blockIdx.x;
-    const float* xr = x + size_t(z) * K;
+    const float* xr = x + size_t(z) * K_used;
     float factor = 1.0f;
     if (z < Z && norm_w != nullptr) {
         float part = 0.f;
@@ -676,7 +678,7 @@ __global__ void __launch_bounds__(512) act_split_kernel(__half* __restrict__ xh,
     }
     for (uint32_t unit = threadIdx.x; unit < K / 8; unit += blockDim.x) {
         float v[8];
-        if (z < Z) {
+        if (z < Z && 8 * unit < K_used) {
             const float4 a = *reinterpret_cast<const float4*>(xr + 8 * unit), b = *reinterpret_cast<const float4*>(xr + 8 * unit + 4);
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
             if (norm_w != nullptr) {
@@ -808,12 +810,19 @@ extern "C" int lv_gemm_tc_set_exact(lv_ctx* ctx, int exact) {
     return LV_OK;
 }
 
-extern "C" int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch) {
+extern "C" int lv_act_split_f16_padded(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols_used, uint32_t cols,
+                                       uint32_t batch) {
     LV_ENTER(ctx);
     LV_REQUIRE(xh && x && cols && batch >= 1 && batch <= uint32_t(kTcMaxZ), "bad act_split arguments");
+    LV_REQUIRE(cols_used != 0 && cols_used <= cols && cols_used % 8 == 0 && cols % 64 == 0, "act_split: cols a multiple of 64, cols_used of 8 and at most cols");
+    LV_REQUIRE(norm_w == nullptr || cols_used == cols, "act_split: a normalised input has no padding");
     const uint32_t zpad = (batch + 15u) & ~15u;
-    LV_CUDA(launch_pdl(ctx, act_split_kernel, dim3(zpad), dim3(512), 0, static_cast<__half*>(xh), x, norm_w, cols, batch, zpad));
+    LV_CUDA(launch_pdl(ctx, act_split_kernel, dim3(zpad), dim3(512), 0, static_cast<__half*>(xh), x, norm_w, cols, cols_used, batch, zpad));
     return LV_OK;
+}
+
+extern "C" int lv_act_split_f16(lv_ctx* ctx, void* xh, const float* x, const float* norm_w, uint32_t cols, uint32_t batch) {
+    return lv_act_split_f16_padded(ctx, xh, x, norm_w, cols, cols, batch);
 }
 
 extern "C" int lv_gemm_tc(lv_ctx* ctx, float* out, const void* W, int wtype, const void* xh, uint32_t rows, uint32_t cols,

@@ -105,7 +105,7 @@ bool llava_command_buffer::record_execution() {
         float* logits = static_cast<float*>(s->output_probs->device_ptr());
         // sharded with fused exchanges: the last layer's w2 pushed its partial rows; the head's
         // normalisation takes residual + the ranks' sum
-        if (c->tp_size() > 1 && c->fused_exchange())
+        if (c->tp_size() > 1 && c->fused_exchange() && !use_tensor_cores(c->get_layers()[0]->wq()))
             tp_arm_pull(2 * u32(c->get_layers().size()) - 1, h.dim, current == s->current_thought ? s->current_thought_sublayer : s->current_thought);
         note(lv_norm_gemv(lv(), logits, c->output_w->device_ptr(), c->output_w->kernel_type(), last,
                           static_cast<const float*>(c->norm_w->device_ptr()), h.vocab_size, h.dim, 1));
@@ -223,15 +223,21 @@ void llava_command_buffer::allreduce_add(llava_buffer* residual, llava_buffer* p
 bool llava_command_buffer::use_tensor_cores(const llava_buffer* matrix) const {
     // from six tokens on one pass over the matrix on the tensor cores beats one GEMV per token
     // (4096x4096 q4_0: 17 us flat against 4.3 us per token)
+    // sharded: the rank's rows of wq / wk / wv must fill 128-row tiles and its rows of w3 / w1 64-row halves
     return batch_size >= kTensorCoreMinBatch && batch_size <= 64 && matrix->weight_buffer_is_f16() &&        // v3 blocks only
-           session->act_split != nullptr &&
-           session->ctx->tp_size() == 1;
+           session->act_split != nullptr && session->tensor_core_shapes_ok();
 }
 
-void llava_command_buffer::act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights) {
-    const u32 cols = inbuf->shape.first;
-    if (!expect(size_t(split->shape.first) * 4 >= lv_act_split_bytes(cols, batch_size), "act_split shapes")) return;
-    note(lv_act_split_f16(lv(), split->device_ptr(), f32(inbuf), norm_weights ? f32(norm_weights) : nullptr, cols, batch_size));
+void llava_command_buffer::act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights, u32 cols_used, u32 cols) {
+    if (cols_used == 0) cols_used = cols = inbuf->shape.first;
+    if (!expect(size_t(split->shape.first) * 4 >= lv_act_split_bytes(cols, batch_size) && cols_used <= inbuf->shape.first, "act_split shapes")) return;
+    note(lv_act_split_f16_padded(lv(), split->device_ptr(), f32(inbuf), norm_weights ? f32(norm_weights) : nullptr, cols_used, cols, batch_size));
+}
+
+void llava_command_buffer::gemm(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split) {
+    if (!expect(outbuf->shape.first == matrix->shape.first, "gemm shapes")) return;
+    note(lv_gemm_tc(lv(), f32(outbuf), matrix->device_ptr(), matrix->kernel_type(), split->device_ptr(), matrix->shape.first,
+                    matrix->shape.second, batch_size, 0));
 }
 
 void llava_command_buffer::gemm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq,

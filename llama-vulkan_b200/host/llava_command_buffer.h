@@ -53,7 +53,9 @@ public:
     // batched forms on the tensor cores (6..64 tokens per step): the activations are first
     // split into two fp16 planes (optionally normalised), then every matrix is read once
     bool use_tensor_cores(const llava_buffer* matrix) const;
-    void act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights);
+    // cols_used != 0: the rows of inbuf are dense with cols_used values and meet a matrix of `cols` (padded) columns
+    void act_split(llava_buffer* split, llava_buffer* inbuf, llava_buffer* norm_weights, u32 cols_used = 0, u32 cols = 0);
+    void gemm(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split);          // store, no residual
     void gemm_qkv_kvappend(llava_buffer* q_out, llava_buffer* k_cache, llava_buffer* v_cache, llava_buffer* wq, llava_buffer* wk,
                            llava_buffer* wv, llava_buffer* split);
     void gemm_add_inplace(llava_buffer* outbuf, llava_buffer* matrix, llava_buffer* split);

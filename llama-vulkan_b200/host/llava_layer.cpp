@@ -88,6 +88,20 @@ llava_buffer* llava_layer::execute(llava_command_buffer* cmd_buf, llava_layer_se
             cmd_buf->gemm_qkv_kvappend(session->current_Q, layer_data->k_cache, layer_data->v_cache, attention_wq, attention_wk,
                                        attention_wv, split);
             cmd_buf->attention_fused(session->current_Vout, session->current_Q, layer_data->k_cache, layer_data->v_cache);
+            if (context->tp_size() > 1) {
+                // this rank's heads and FFN rows; the column shards of wo and w2 have rows padded with zero blocks, so
+                // their (dense) inputs are padded while they are split; the partial products of all tokens are summed
+                // over the ranks by one exchange per sub-block
+                cmd_buf->act_split(split, session->current_Vout, nullptr, attention_wq->shape.first, attention_wo->shape.second);
+                cmd_buf->gemm(session->tp_partial, attention_wo, split);
+                cmd_buf->allreduce_add(x, session->tp_partial);
+                cmd_buf->act_split(split, x, ffn_norm);
+                cmd_buf->gemm_silu_ff(session->main_ff_result, feed_forward_w3, feed_forward_w1, split);
+                cmd_buf->act_split(split, session->main_ff_result, nullptr, feed_forward_w3->shape.first, feed_forward_w2->shape.second);
+                cmd_buf->gemm(session->tp_partial, feed_forward_w2, split);
+                cmd_buf->allreduce_add(x, session->tp_partial);
+                return x;
+            }
             cmd_buf->act_split(split, session->current_Vout, nullptr);
             cmd_buf->gemm_add_inplace(x, attention_wo, split);
             cmd_buf->act_split(split, x, ffn_norm);

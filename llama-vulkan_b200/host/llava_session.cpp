@@ -148,7 +148,8 @@ bool llava_session::recreate_buffers() {
     const size_t scratch = lv_attention_scratch_bytes(h.n_heads / ranks, h.rot, max_backlog_size, B);
     if (scratch == 0) return false;
     attn_scratch = new llava_buffer(ctx, F, u32((scratch + 3) / 4), 1, m);
-    if (B >= llava_command_buffer::kTensorCoreMinBatch && ranks == 1) act_split = new llava_buffer(ctx, F, u32(lv_act_split_bytes(max(dim, ff), B) / 4), 1, m);
+    if (B >= llava_command_buffer::kTensorCoreMinBatch)
+        act_split = new llava_buffer(ctx, F, u32(lv_act_split_bytes(max(max(dim, ff_len), vout_len), B) / 4), 1, m);
     if (!m->freeze() || !m->zero(0, m->get_size())) return false;
     device_pos = ~0U;
     return true;
@@ -247,7 +248,10 @@ bool llava_session::start_next_token_prediction() {
     if (sampling_on_device() && !upload_sampler_state()) return false;
     if (!upload_pending_tokens(current_tokens_in_gpu, to_process)) return false;
     while (to_process > 0) {
-        const u32 n = min(to_process, max_batch);
+        u32 n = min(to_process, max_batch);
+        // sharded: a batch goes through the tensor-core step with its stand-alone exchanges; what is too short for that
+        // goes token by token through the step with the exchange fused into the GEMVs
+        if (ctx->tp_size() > 1 && n < llava_command_buffer::kTensorCoreMinBatch) n = 1;
         llava_command_buffer* cb = get_command_buffer(n, n == to_process);
         if (cb == nullptr || !cb->run()) return false;
         batch_size = n;
@@ -435,9 +439,17 @@ bool llava_session::set_backlog_size(u32 new_size) {
     return flush_layers_data_buffers();
 }
 
+bool llava_session::tensor_core_shapes_ok() const {
+    const u32 ranks = ctx->tp_size();
+    if (ranks == 1) return true;
+    return (model->get_header().dim / ranks) % 128 == 0 && (model->get_ff_size() / ranks) % 64 == 0;
+}
+
 bool llava_session::set_max_batch(u32 n) {
     if (n < 1 || n > max_batch_limit) return false;
-    if (n > 1 && ctx->tp_size() > 1) return false;        // sharded sessions evaluate token by token
+    // sharded sessions evaluate prompt batches on the tensor cores (one exchange per sub-block for the whole batch) or,
+    // where the shard shapes do not fit the tiles, token by token
+    if (n > 1 && ctx->tp_size() > 1 && (n < llava_command_buffer::kTensorCoreMinBatch || !tensor_core_shapes_ok())) return false;
     if (n == max_batch) return true;
     lv_stream_sync(ctx->lv(), 0);
     drop_command_buffers();

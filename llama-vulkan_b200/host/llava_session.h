@@ -56,6 +56,9 @@ public:
     // tokens evaluated per recorded step while a prompt is ingested (1 ..
     // max_batch_limit); the reference evaluates the whole prompt as one batch
     bool set_max_batch(u32 n);
+    // whether the batched (tensor-core) products can take this context's matrices: always on one GPU; sharded, the
+    // rank's rows of wq / wk / wv must fill 128-row tiles and its rows of w3 / w1 64-row halves
+    bool tensor_core_shapes_ok() const;
     // Greedy decoding of n tokens with no host round trip between tokens: the
     // recorded step feeds its own argmax back in.  Requires every token pushed
     // so far to be evaluated except the last one.  Appends to the token buffer.

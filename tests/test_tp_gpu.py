@@ -43,11 +43,29 @@ def _decode(ctx):
     return toks, logits
 
 
+def _decode_batched(ctx, n_prompt=40, max_batch=16, n_decode=4):
+    """A prompt in tensor-core batches (16 + 16 + 8), then a few single tokens."""
+    s = ctx.session()
+    s.set_deterministic(True)
+    assert s.set_max_batch(max_batch)
+    for t in [int(t) for t in np.random.default_rng(99).integers(3, 32000, n_prompt)]:
+        assert s.push_token(t)
+    toks, logits = [], []
+    for _ in range(n_decode):
+        tok = s.predict_next_token()
+        assert tok != 0xFFFFFFFF
+        toks.append(tok)
+        logits.append(s.logits(32000))
+        s.push_token(tok)
+    s.close()
+    return toks, logits
+
+
 def ctx_is_single(ctx):
     return getattr(ctx, "n_ranks", 1) == 1
 
 
-def _worker(rank, world, path, id_q, out_q, peer_q=None, one_launch=False):
+def _worker(rank, world, path, id_q, out_q, peer_q=None, one_launch=False, batched=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     if one_launch:
         os.environ["LV_DECODE_STEP"] = "1"          # read when a session is created: every token as one persistent kernel
@@ -69,7 +87,7 @@ def _worker(rank, world, path, id_q, out_q, peer_q=None, one_launch=False):
             peer_q[r].put((rank, mine))
         got = dict(peer_q[rank].get(timeout=120) for _ in range(world))
         ctx.peer_connect([got[r] for r in range(world)])
-    toks, logits = _decode(ctx)
+    toks, logits = _decode_batched(ctx) if batched else _decode(ctx)
     ctx.close()
     out_q.put((rank, toks, [l.tobytes() for l in logits]))
 
@@ -109,6 +127,45 @@ def test_two_gpu_tensor_parallel_matches_one_gpu(pkg, tmp_path, exchange):
             assert np.abs(got - want).max() <= 1e-2
             assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
         assert np.array_equal(results[0][1][step], results[1][1][step])      # every rank holds the same logits
+
+
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_two_gpu_prompt_batches_on_the_tensor_cores(pkg, tmp_path, exchange):
+    """A sharded session evaluates a prompt in batches: row shards of wq / wk / wv / w3 / w1 and padded column shards of
+    wo / w2 on the tcgen05 path, one exchange per sub-block for the whole batch.  Against the same batches on one GPU."""
+    if _device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    path = str(tmp_path / "tiny.bin")
+    pkg.write_synthetic_model(path, "7b", n_layers=2)
+    ctx = pkg.HostContext(path, 0)
+    want_toks, want_logits = _decode_batched(ctx)
+    ctx.close()
+    mpc = mp.get_context("spawn")
+    id_q, out_q = mpc.Queue(), mpc.Queue()
+    peer_q = [mpc.Queue() for _ in range(2)] if exchange != "nccl" else None
+    procs = [mpc.Process(target=_worker, args=(r, 2, path, id_q, out_q, peer_q, False, True)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(2):
+        try:
+            r, toks, logits = out_q.get(timeout=300)
+        except queue.Empty:
+            for p in procs:
+                p.kill()
+            raise AssertionError("a rank did not finish")
+        results[r] = (toks, [np.frombuffer(b, np.float32) for b in logits])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results[0][0] == results[1][0] == want_toks
+    for step in range(len(want_toks)):
+        for r in (0, 1):
+            got, want = results[r][1][step].astype(np.float64), want_logits[step].astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-2
+            assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+        assert np.array_equal(results[0][1][step], results[1][1][step])
 
 
 def _snapshot_worker(rank, world, path, id_q, out_q, peer_q, snap_in, snap_out, n_first, n_more):
