@@ -106,6 +106,17 @@ uint64_t llava_session_read_step_trace(void* session, uint64_t* out, uint64_t ca
 /* rows [row0, row0 + nrows) of one layer's K (which = 0) or V (1) cache, f16 bits */
 int      llava_session_read_kv(void* session, uint32_t layer, int which, uint32_t row0, uint32_t nrows, uint16_t* out);
 
+/* ---- llava_session_group: one decoding step for several sessions with one pass over the weights (greedy).
+ * create: 2..64 sessions of one single-GPU context, NULL when that cannot work.  step: every member holds exactly one
+ * token that is not evaluated yet; next_tokens[i] = member i's greedy next token (not pushed).  generate: n steps with
+ * the tokens fed back on the device; out[i * n + j] = token j of member i (appended to the members' buffers). */
+void*    llava_session_group_create(void* ctx, void* const* sessions, uint32_t n);
+void     llava_session_group_destroy(void* group);
+int      llava_session_group_step(void* group, uint32_t* next_tokens);
+int      llava_session_group_generate_greedy_on_device(void* group, uint32_t n, uint32_t* out);
+int      llava_session_group_get_logits(void* group, uint32_t member, float* out, uint32_t n);   /* of the last step */
+uint32_t llava_session_group_kernel_launches(void* group);
+
 /* where a rank's column slice of a cache row lives in a snapshot file (host/tp_shard.h), and the size of the file */
 uint64_t llava_tp_snapshot_slice_offset(uint32_t n_tokens, uint32_t dim, uint32_t layer, uint32_t which, uint32_t row,
                                         uint32_t rank, uint32_t n_ranks);

@@ -193,6 +193,36 @@ int lv_sample_mirostat(lv_ctx* ctx, const float* logits, uint32_t n_vocab, const
                        uint32_t* state, float forced_uniform, uint32_t* feed_token_log, uint32_t log_capacity,
                        uint32_t* out_token, uint32_t* host_token, uint32_t* report);
 
+/* ---- one step for several sessions (shared weight pass) ---------------------- */
+
+/* The reference's server runs every session's steps on their own, streaming the weights once per
+ * session and token (server/session_wrapper.cpp:55-105).  A group step evaluates one token of each
+ * of up to 64 sessions with one pass over the weights: the batched products below take the rows of
+ * all members; the entry points here are the operations that differ per member, because every
+ * member has its own caches, position and token log.  `members` is a device array of `n` entries
+ * (one array per layer: the caches differ, pos and token_log repeat). */
+typedef struct lv_group_member {
+    void* k_cache;          /* f16 [ctx_rows][dim] of the layer */
+    void* v_cache;
+    uint32_t* pos;          /* device words [4]: tokens of this member already in its caches */
+    uint32_t* token_log;    /* device: the member's token ids by position */
+} lv_group_member;
+
+/* out[z] = embedding row of members[z].token_log[*members[z].pos] (lv_dequant_rows per member). */
+int lv_dequant_rows_group(lv_ctx* ctx, float* out, const void* table, int wtype, const lv_group_member* members,
+                          uint32_t cols, uint32_t vocab, uint32_t n);
+/* lv_gemm_tc_qkv_kvappend with row z of K and V stored at row *members[z].pos of members[z]'s caches. */
+int lv_gemm_tc_qkv_kvappend_group(lv_ctx* ctx, float* q_out, const void* wq, const void* wk, const void* wv, int wtype,
+                                  const void* xh, const lv_group_member* members, uint32_t rows_each, uint32_t dim,
+                                  uint32_t n, uint32_t ctx_rows);
+/* lv_attention_fused with query row z attending over members[z]'s caches up to *members[z].pos. */
+int lv_attention_fused_group(lv_ctx* ctx, float* out, const float* q, const lv_group_member* members, const float* rope_table,
+                             void* scratch, uint32_t heads, uint32_t rot, uint32_t backlog, uint32_t n);
+/* lv_argmax_advance per member: the first index of the largest of logits[z][0..vocab) goes to
+ * members[z].token_log[*pos + 1], to out_tokens[z] and (when given) host_tokens[z] (pinned memory); pos advances by one. */
+int lv_argmax_advance_group(lv_ctx* ctx, const float* logits, uint32_t vocab, const lv_group_member* members, uint32_t n,
+                            uint32_t log_capacity, uint32_t* out_tokens, uint32_t* host_tokens);
+
 /* ---- batched products on the tensor cores (prompt evaluation) -------------- */
 
 /* When several tokens are evaluated together the reference dispatches its

@@ -280,6 +280,12 @@ HOST_API = {
     "llava_wrapper_push_order": (None, [_p, _u32, _u32, _u32, _u32, C.c_char_p, _sz]),
     "llava_wrapper_join": (None, [_p]),
     "llava_wrapper_destroy": (None, [_p]),
+    "llava_session_group_create": (_p, [_p, C.POINTER(_p), _u32]),
+    "llava_session_group_destroy": (None, [_p]),
+    "llava_session_group_step": (_int, [_p, _u32p]),
+    "llava_session_group_generate_greedy_on_device": (_int, [_p, _u32, _u32p]),
+    "llava_session_group_get_logits": (_int, [_p, _u32, _p, _u32]),
+    "llava_session_group_kernel_launches": (_u32, [_p]),
     "llava_server_create": (_p, [_p, _u32, C.c_char_p, _int]),
     "llava_server_port": (_u32, [_p]),
     "llava_server_start": (None, [_p]),
@@ -534,6 +540,46 @@ class Session:
         if not self.lib.llava_session_read_kv(self.handle, layer, which, row0, nrows, out.ctypes.data_as(_p)):
             raise RuntimeError("read_kv failed")
         return out
+
+
+class SessionGroup:
+    """llava_session_group: one greedy decoding step for several sessions with one pass over the weights."""
+
+    def __init__(self, ctx, sessions):
+        self.lib = ctx.lib
+        self.sessions = list(sessions)
+        arr = (_p * len(self.sessions))(*[s.handle for s in self.sessions])
+        self.handle = self.lib.llava_session_group_create(ctx.handle, arr, len(self.sessions))
+        if not self.handle:
+            raise RuntimeError("these sessions cannot form a group")
+
+    def close(self):
+        if self.handle:
+            self.lib.llava_session_group_destroy(self.handle)
+            self.handle = None
+
+    def step(self):
+        """-> the greedy next token of every member (not pushed), or None on failure."""
+        out = (_u32 * len(self.sessions))()
+        return list(out) if self.lib.llava_session_group_step(self.handle, out) else None
+
+    def generate_greedy_on_device(self, n):
+        """n steps with the tokens fed back on the device -> per member its n tokens (appended to the members' buffers)."""
+        k = len(self.sessions)
+        out = (_u32 * (k * n))()
+        if not self.lib.llava_session_group_generate_greedy_on_device(self.handle, n, out):
+            return None
+        return [list(out[i * n:(i + 1) * n]) for i in range(k)]
+
+    def logits(self, member, vocab):
+        import numpy as np
+        v = np.empty(vocab, np.float32)
+        if not self.lib.llava_session_group_get_logits(self.handle, member, v.ctypes.data_as(_p), vocab):
+            raise RuntimeError("no logits")
+        return v
+
+    def kernel_launches(self):
+        return self.lib.llava_session_group_kernel_launches(self.handle)
 
 
 class Server:

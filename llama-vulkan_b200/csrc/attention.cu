@@ -154,11 +154,11 @@ constexpr size_t kCompactSmemBytes = kCompactTableBytes + size_t(kAttnChunk) * k
 
 template <int MIN_CTAS_PER_SM, int STAGED>
 __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fused_kernel(float* __restrict__ out, const float* __restrict__ q,
-                                                                       const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                                                       const __half* kc, const __half* vc,
                                                                        const uint32_t* __restrict__ pos, const float* __restrict__ table,
                                                                        float* __restrict__ partial, uint32_t* __restrict__ counters,
                                                                        uint32_t heads, uint32_t nchunks, uint32_t max_ctx, float scale,
-                                                                       uint32_t* err) {
+                                                                       uint32_t* err, const lv_group_member* __restrict__ group) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_e[kAttnChunk];
@@ -170,7 +170,12 @@ __global__ void __launch_bounds__(kFusedThreads, MIN_CTAS_PER_SM) attention_fuse
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t h = blockIdx.x, c = blockIdx.y, z = blockIdx.z;
-    const uint32_t P = *pos + z;
+    // a group step: query row z belongs to member z, with its own caches and position
+    if (group != nullptr) {
+        kc = static_cast<const __half*>(group[z].k_cache);
+        vc = static_cast<const __half*>(group[z].v_cache);
+    }
+    const uint32_t P = group != nullptr ? *group[z].pos : *pos + z;
     if (P >= max_ctx) {
         // the position lies outside the caches and the rotation table: report it and touch nothing
         // (neither `out` nor the arrival counters), like the cache append does
@@ -402,7 +407,7 @@ int attention_configure(lv_ctx* ctx) {
 // ones (context beyond ~1280 rows, batches) stage key rows and the compact table, two CTAs per SM.
 static int launch_attention_fused(lv_ctx* ctx, dim3 grid, float* out, const float* q, const void* k_cache, const void* v_cache,
                                   const uint32_t* pos, const float* rope_table, float* partial, uint32_t* counters, uint32_t heads,
-                                  uint32_t nchunks, uint32_t max_ctx, uint32_t rot) {
+                                  uint32_t nchunks, uint32_t max_ctx, uint32_t rot, const lv_group_member* group = nullptr) {
     const float scale = 1.0f / sqrtf(static_cast<float>(rot));
     static const char* no_stage = getenv("LV_ATTENTION_NO_STAGING");
     // the compact table variant always copies the table rows of distances 0..31
@@ -411,19 +416,19 @@ static int launch_attention_fused(lv_ctx* ctx, dim3 grid, float* out, const floa
     if (!staged) {
         if (big) {
             LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err));
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err, group));
         } else {
             LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 0>, grid, dim3(kFusedThreads), 0, out, q, static_cast<const __half*>(k_cache),
-                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err));
+                               static_cast<const __half*>(v_cache), pos, rope_table, partial, counters, heads, nchunks, max_ctx, scale, ctx->d_err, group));
         }
     } else if (big) {
         LV_CUDA(launch_pdl(ctx, attention_fused_kernel<2, 1>, grid, dim3(kFusedThreads), kCompactSmemBytes, out, q,
                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
-                           heads, nchunks, max_ctx, scale, ctx->d_err));
+                           heads, nchunks, max_ctx, scale, ctx->d_err, group));
     } else {
         LV_CUDA(launch_pdl(ctx, attention_fused_kernel<1, 2>, grid, dim3(kFusedThreads), kStagedSmemBytes, out, q,
                            static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), pos, rope_table, partial, counters,
-                           heads, nchunks, max_ctx, scale, ctx->d_err));
+                           heads, nchunks, max_ctx, scale, ctx->d_err, group));
     }
     return LV_OK;
 }
@@ -529,6 +534,18 @@ extern "C" int lv_attention_fused(lv_ctx* ctx, float* out, const float* q, const
     dim3 grid(heads, nchunks, batch);
     if (int rc = launch_attention_fused(ctx, grid, out, q, k_cache, v_cache, pos, rope_table, partial, counters, heads, nchunks, max_ctx, rot)) return rc;
     return LV_OK;
+}
+
+extern "C" int lv_attention_fused_group(lv_ctx* ctx, float* out, const float* q, const lv_group_member* members, const float* rope_table,
+                                        void* scratch, uint32_t heads, uint32_t rot, uint32_t max_ctx, uint32_t n) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && q && members && rope_table && scratch, "null argument");
+    if (int rc = check_attn_shape(max_ctx, heads, rot, n)) return rc;
+    const uint32_t nchunks = (max_ctx + kAttnChunk - 1) / kAttnChunk;
+    float* partial = static_cast<float*>(scratch);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(partial + attn_partial_floats(heads, nchunks, n));
+    dim3 grid(heads, nchunks, n);
+    return launch_attention_fused(ctx, grid, out, q, nullptr, nullptr, nullptr, rope_table, partial, counters, heads, nchunks, max_ctx, rot, members);
 }
 
 extern "C" size_t lv_attention_static_scratch_limit(void) { return kStaticScratchBytes; }

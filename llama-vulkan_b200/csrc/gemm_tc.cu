@@ -98,6 +98,7 @@ struct GemmTcParams {
     float* scratch;          // splits > 1: partial accumulators [tile][split][zpad][128]
     uint32_t* counters;      // splits > 1: arrivals per tile (zero between launches)
     uint32_t* err;
+    const lv_group_member* group;   // non-null: token z is member z of a group step; cache rows go to its own caches at its own position
 };
 
 struct GemmTcMaps {
@@ -498,7 +499,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         // 16 tokens z0 .. z0+15 of one output row (tile row tr)
         auto store_plain = [&](uint32_t tr, uint32_t z0, const float (&r32)[16]) {
                 const uint32_t row = row0 + tr;
-                if (M.epilogue == EPI_STORE_F16_AT_POS) {
+                if (M.epilogue == EPI_STORE_F16_AT_POS && p.group != nullptr) {
+                    // matrix 0 is wk, matrix 2 is wv (lv_gemm_tc_qkv_kvappend_group)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t z = z0 + i;
+                        if (z < p.Z) {
+                            const lv_group_member& m = p.group[z];
+                            __half* cache = static_cast<__half*>(mi == 0 ? m.k_cache : m.v_cache);
+                            const uint32_t at = *m.pos;
+                            if (at < p.ctx_rows) cache[size_t(at) * M.rows + row] = __float2half_rn(r32[i]);
+                            else atomicOr(p.err, ERR_BAD_INDEX);
+                        }
+                    }
+                } else if (M.epilogue == EPI_STORE_F16_AT_POS) {
                     __half* cache = static_cast<__half*>(M.out);
                     const uint32_t first = *p.pos;
 #pragma unroll
@@ -866,6 +880,25 @@ extern "C" int lv_gemm_tc_qkv_kvappend(lv_ctx* ctx, float* q_out, void* k_cache,
     p.ctx_rows = ctx_rows;
     p.K = dim;
     p.Z = batch;
+    p.err = ctx->d_err;
+    return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh), wtype);
+}
+
+extern "C" int lv_gemm_tc_qkv_kvappend_group(lv_ctx* ctx, float* q_out, const void* wq, const void* wk, const void* wv, int wtype,
+                                             const void* xh, const lv_group_member* members, uint32_t rows_each, uint32_t dim,
+                                             uint32_t n, uint32_t ctx_rows) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(q_out && wq && wk && wv && members, "null argument");
+    GemmTcParams p{};
+    // the cache pointers come from the members; `out` of the two cache matrices only has to be non-null
+    p.m[0] = {static_cast<const uint8_t*>(wk), nullptr, q_out, rows_each, EPI_STORE_F16_AT_POS};
+    p.m[1] = {static_cast<const uint8_t*>(wq), nullptr, q_out, rows_each, EPI_STORE};
+    p.m[2] = {static_cast<const uint8_t*>(wv), nullptr, q_out, rows_each, EPI_STORE_F16_AT_POS};
+    p.n_mat = 3;
+    p.group = members;
+    p.ctx_rows = ctx_rows;
+    p.K = dim;
+    p.Z = n;
     p.err = ctx->d_err;
     return launch_gemm_tc(ctx, p, static_cast<const __half*>(xh), wtype);
 }

@@ -56,13 +56,14 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 
 // llava_buffer.cpp:360-370 (q4_0 v3), :387-394 (q8_0 v3), :377-381 (f32).
 // One CTA per row; one thread per block of 32 weights.
+// group != null: row z belongs to member z (its own token log and position).
 __global__ void dequant_rows_kernel(float* __restrict__ out, const uint8_t* __restrict__ table, int wtype,
                                     const uint32_t* __restrict__ ids, const uint32_t* __restrict__ first, uint32_t cols,
-                                    uint32_t vocab, uint32_t* err) {
+                                    uint32_t vocab, uint32_t* err, const lv_group_member* __restrict__ group) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t z = blockIdx.x;
-    uint32_t id = ids[(first ? *first : 0u) + z];
+    uint32_t id = group != nullptr ? group[z].token_log[*group[z].pos] : ids[(first ? *first : 0u) + z];
     if (id >= vocab) {
         if (threadIdx.x == 0) atomicOr(err, ERR_BAD_INDEX);
         id = 0;
@@ -212,6 +213,31 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
     }
 }
 
+// The same for the members of a group step: CTA z works on logits row z and member z.
+__global__ void __launch_bounds__(1024) argmax_advance_group_kernel(const float* __restrict__ logits, uint32_t n,
+                                                                    const lv_group_member* __restrict__ group, uint32_t log_capacity,
+                                                                    uint32_t* out_tokens, volatile uint32_t* host_tokens, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_val[32];
+    __shared__ uint32_t s_idx[32];
+    const uint32_t z = blockIdx.x;
+    const float* v = logits + size_t(z) * n;
+    const uint32_t count = threadIdx.x == 0 ? group[z].pos[0] : 0u;
+    const uint32_t bi = block_argmax(v, n, s_val, s_idx);
+    if (threadIdx.x == 0) {
+        const uint32_t token = argmax_result(bi, v);
+        if (count + 1 < log_capacity) group[z].token_log[count + 1] = token;
+        else atomicOr(err, ERR_BAD_INDEX);
+        for (int i = 0; i < 4; ++i) group[z].pos[i] = count + 1;
+        if (out_tokens != nullptr) out_tokens[z] = token;
+        if (host_tokens != nullptr) {
+            host_tokens[z] = token;
+            __threadfence_system();
+        }
+    }
+}
+
 __global__ void decode_advance_kernel(uint32_t* config, const uint32_t* argmax, uint32_t* token_log, uint32_t batch,
                                       uint32_t log_capacity, uint32_t* tp_step, uint32_t* err) {
     pdl_launch_dependents();
@@ -244,6 +270,15 @@ extern "C" int lv_argmax_advance(lv_ctx* ctx, const float* v, uint32_t n, uint32
     LV_REQUIRE(v && n && config && token_log && batch, "bad argmax_advance arguments");
     LV_CUDA(launch_pdl(ctx, argmax_advance_kernel, dim3(1), dim3(1024), 0, v, n, config, token_log, batch, log_capacity,
                        argmax_out, static_cast<volatile uint32_t*>(host_token), peer_step_counter(ctx), ctx->d_err));
+    return LV_OK;
+}
+
+extern "C" int lv_argmax_advance_group(lv_ctx* ctx, const float* logits, uint32_t vocab, const lv_group_member* members, uint32_t n,
+                                       uint32_t log_capacity, uint32_t* out_tokens, uint32_t* host_tokens) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(logits && vocab && members && n, "bad argmax_advance arguments");
+    LV_CUDA(launch_pdl(ctx, argmax_advance_group_kernel, dim3(n), dim3(1024), 0, logits, vocab, members, log_capacity, out_tokens,
+                       static_cast<volatile uint32_t*>(host_tokens), ctx->d_err));
     return LV_OK;
 }
 
@@ -287,7 +322,19 @@ extern "C" int lv_dequant_rows(lv_ctx* ctx, float* out, const void* table, int w
     LV_REQUIRE(out && table && token_ids && n && vocab, "bad dequant arguments");
     LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0 || wtype == T_Q4_0_V1, "unsupported table type");
     LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
-    LV_CUDA(launch_pdl(ctx, dequant_rows_kernel, dim3(n), dim3(256), 0, out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err));
+    LV_CUDA(launch_pdl(ctx, dequant_rows_kernel, dim3(n), dim3(256), 0, out, static_cast<const uint8_t*>(table), wtype, token_ids, first, cols, vocab, ctx->d_err,
+                       static_cast<const lv_group_member*>(nullptr)));
+    return LV_OK;
+}
+
+extern "C" int lv_dequant_rows_group(lv_ctx* ctx, float* out, const void* table, int wtype, const lv_group_member* members,
+                                     uint32_t cols, uint32_t vocab, uint32_t n) {
+    LV_ENTER(ctx);
+    LV_REQUIRE(out && table && members && n && vocab, "bad dequant arguments");
+    LV_REQUIRE(wtype == T_F32 || wtype == T_Q4_0 || wtype == T_Q8_0 || wtype == T_Q4_0_V1, "unsupported table type");
+    LV_REQUIRE(cols && cols % 32 == 0, "cols must be a multiple of 32");
+    LV_CUDA(launch_pdl(ctx, dequant_rows_kernel, dim3(n), dim3(256), 0, out, static_cast<const uint8_t*>(table), wtype,
+                       static_cast<const uint32_t*>(nullptr), static_cast<const uint32_t*>(nullptr), cols, vocab, ctx->d_err, members));
     return LV_OK;
 }
 

@@ -16,6 +16,7 @@
 #include <mutex>
 #include <thread>
 
+#include "llava_session_group.h"
 #include "server/session_wrapper.h"
 #include "server/tlv_server.h"
 #include "synth_ggjt.h"
@@ -327,6 +328,41 @@ uint64_t llava_tp_snapshot_slice_offset(uint32_t n_tokens, uint32_t dim, uint32_
     return tp_snapshot_slice_offset(n_tokens, dim, layer, which, row, rank, n_ranks);
 }
 uint64_t llava_tp_snapshot_file_size(uint32_t n_tokens, uint32_t dim, uint32_t n_layers) { return tp_snapshot_file_size(n_tokens, dim, n_layers); }
+
+// ---- llava_session_group ----
+void* llava_session_group_create(void* ctx, void* const* sessions, uint32_t n) {
+    std::vector<llava_session*> members;
+    for (uint32_t i = 0; i < n; ++i) members.push_back(static_cast<llava_session*>(sessions[i]));
+    auto* g = new llava_session_group(static_cast<llava_context*>(ctx), members);
+    if (!g->is_valid()) {
+        delete g;
+        return nullptr;
+    }
+    return g;
+}
+void llava_session_group_destroy(void* group) { delete static_cast<llava_session_group*>(group); }
+int llava_session_group_step(void* group, uint32_t* next_tokens) {
+    auto* g = static_cast<llava_session_group*>(group);
+    std::vector<uint32_t> toks;
+    if (!g->step(&toks)) return 0;
+    if (next_tokens) std::memcpy(next_tokens, toks.data(), toks.size() * 4);
+    return 1;
+}
+int llava_session_group_generate_greedy_on_device(void* group, uint32_t n, uint32_t* out) {
+    auto* g = static_cast<llava_session_group*>(group);
+    std::vector<std::vector<uint32_t>> toks;
+    if (!g->generate_greedy_on_device(n, &toks)) return 0;
+    if (out)
+        for (size_t i = 0; i < toks.size(); ++i) std::memcpy(out + i * n, toks[i].data(), size_t(n) * 4);
+    return 1;
+}
+int llava_session_group_get_logits(void* group, uint32_t member, float* out, uint32_t n) {
+    std::vector<float> v;
+    if (!static_cast<llava_session_group*>(group)->get_logits(member, &v) || v.size() != n) return 0;
+    std::memcpy(out, v.data(), size_t(n) * sizeof(float));
+    return 1;
+}
+uint32_t llava_session_group_kernel_launches(void* group) { return static_cast<llava_session_group*>(group)->kernel_launches(); }
 
 // ---- lsrv::tlv_server on a thread of its own ----
 namespace {

@@ -21,6 +21,7 @@ class llava_session {
     friend class llava_layer;
     friend class llava_layer_session_data;
     friend class llava_command_buffer;
+    friend class llava_session_group;
 public:
     explicit llava_session(llava_context* ctx);
     ~llava_session();

@@ -28,6 +28,7 @@ class llava_buffer;
 class llava_device_memory;
 class llava_command_buffer;
 class llava_session;
+class llava_session_group;
 class llava_layer_session_data;
 class ggml_file;
 
