@@ -93,9 +93,9 @@ def ensure_model(pkg, name, w, rank, world):
     return path
 
 
-def prompt_tokens(n):
+def prompt_tokens(n, seed=PROMPT_SEED):
     import numpy as np
-    return [int(t) for t in np.random.default_rng(PROMPT_SEED).integers(3, 32000, n)]
+    return [int(t) for t in np.random.default_rng(seed).integers(3, 32000, n)]
 
 
 class ClockSampler:
@@ -548,6 +548,39 @@ def measure_decode(rig, ctx, name, args, repeats):
             "prompt_eval": dict(prompt_eval, tokens_per_s=prompt_eval["tokens"] / prompt_eval["seconds"])}
 
 
+def measure_concurrent_sessions(rig, ctx, name, args, counts=(4, 16, 64)):
+    """Aggregate greedy decode tokens/s of k sessions stepped together by llava_session_group (one pass over the weights
+    per step for all of them): every session has its own seeded 32-token prompt; args.steps steps with the tokens fed
+    back on the device, timed on the host around the queued steps and their completion (second run, steps recorded)."""
+    pkg = rig.pkg
+    out = {}
+    for k in counts:
+        sessions = []
+        for i in range(k):
+            s = ctx.session()
+            s.set_deterministic(True)
+            assert s.set_max_batch(64)
+            for t in prompt_tokens(32, seed=PROMPT_SEED + 1 + i):
+                assert s.push_token(t)
+            tok = s.predict_next_token()
+            assert tok != pkg.NO_TOKEN and s.push_token(tok)
+            sessions.append(s)
+        group = pkg.SessionGroup(ctx, sessions)
+        assert group.generate_greedy_on_device(args.warmup) is not None          # records the step
+        secs = []
+        for r in range(3):
+            t0 = time.perf_counter()
+            toks = group.generate_greedy_on_device(args.steps)
+            secs.append(time.perf_counter() - t0)
+            assert toks is not None
+        sec = sorted(secs)[1]
+        out[str(k)] = {"tokens_per_s": k * args.steps / sec, "ms_per_step": sec * 1e3 / args.steps, "launches_per_step": group.kernel_launches()}
+        group.close()
+        for s in sessions:
+            s.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -559,6 +592,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison that precedes the timed runs")
     ap.add_argument("--no-13b", action="store_true", help="skip the second measurement on LLaMA-13B q4_0 (BASELINE config 3)")
+    ap.add_argument("--no-sessions", action="store_true", help="skip the aggregate throughput of 4 / 16 / 64 sessions stepped together")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="N > 1: exchanges over NVLink peer memory (default) or NCCL + add")
     args = ap.parse_args()
@@ -610,6 +644,9 @@ def main():
                 "algorithmic_bytes_per_launch": k_bytes,
                 "whole_step": {"bytes_per_token": m["bytes_per_token"], "achieved": m["bytes_per_token"] * tps / 1e9,
                                "aggregate_peak": peak_all, "frac": m["bytes_per_token"] * tps / 1e9 / peak_all}}
+    sessions = None
+    if world == 1 and not args.no_sessions and w["wtype"] == 2:
+        sessions = measure_concurrent_sessions(rig, ctx, args.workload, args)
     ctx.close()
     rig.barrier()
 
@@ -652,6 +689,7 @@ def main():
                 "sampled_tokens_per_s": m["sampled_e2e_tokens_per_s"]},
         "gpu_launches": m["launches_per_token"] * args.steps, "clocks": clocks,
         "parity": parity, "tokens_digest": m["tokens_digest"], "config3_13b": config3,
+        "concurrent_sessions": sessions,
         # not part of the metric: wall time of the prompt's evaluation, first use (records the steps) included
         "prompt_eval": m["prompt_eval"],
     }
