@@ -90,6 +90,10 @@ KERNEL_API = {
     "lv_act_split_bytes": (_sz, [_u32, _u32]),
     "lv_act_split_f16": (_int, [_p, _p, _p, _p, _u32, _u32]),
     "lv_act_split_f16_padded": (_int, [_p, _p, _p, _p, _u32, _u32, _u32]),
+    "lv_dequant_rows_group": (_int, [_p, _p, _p, _int, _p, _u32, _u32, _u32]),
+    "lv_gemm_tc_qkv_kvappend_group": (_int, [_p, _p, _p, _p, _p, _int, _p, _p, _u32, _u32, _u32, _u32]),
+    "lv_attention_fused_group": (_int, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32]),
+    "lv_argmax_advance_group": (_int, [_p, _p, _u32, _p, _u32, _u32, _p, _p]),
     "lv_gemm_tc_set_exact": (_int, [_p, _int]),
     "lv_gemm_tc": (_int, [_p, _p, _p, _int, _p, _u32, _u32, _u32, _int]),
     "lv_gemm_tc_silu": (_int, [_p, _p, _p, _p, _int, _p, _u32, _u32, _u32]),
