@@ -146,6 +146,10 @@ void     llava_wrapper_destroy(void* wrapper);
  * for them and joins the loop.  deterministic != 0: sessions decode greedily (the reference always samples). */
 void*    llava_server_create(void* ctx, uint32_t port, const char* bind_address, int deterministic);
 uint32_t llava_server_port(void* server);
+/* sessions in the running state are stepped together (one pass over the weights per round): rounds that served two or
+ * more sessions, and the tokens they produced */
+uint64_t llava_server_grouped_steps(void* server);
+uint64_t llava_server_grouped_tokens(void* server);
 void     llava_server_start(void* server);
 void     llava_server_stop(void* server);
 void     llava_server_destroy(void* server);

@@ -292,6 +292,8 @@ HOST_API = {
     "llava_session_group_kernel_launches": (_u32, [_p]),
     "llava_server_create": (_p, [_p, _u32, C.c_char_p, _int]),
     "llava_server_port": (_u32, [_p]),
+    "llava_server_grouped_steps": (_u64, [_p]),
+    "llava_server_grouped_tokens": (_u64, [_p]),
     "llava_server_start": (None, [_p]),
     "llava_server_stop": (None, [_p]),
     "llava_server_destroy": (None, [_p]),
@@ -597,6 +599,10 @@ class Server:
             raise RuntimeError(f"cannot listen on {address}:{port}")
         self.port = self.lib.llava_server_port(self.handle)
         self.lib.llava_server_start(self.handle)
+
+    def grouped(self):
+        """-> (rounds that stepped two or more sessions together, tokens those rounds produced)."""
+        return self.lib.llava_server_grouped_steps(self.handle), self.lib.llava_server_grouped_tokens(self.handle)
 
     def close(self):
         if self.handle:

@@ -175,6 +175,7 @@ extern "C" int lv_graph_begin_capture(lv_ctx* ctx) {
     LV_REQUIRE(!ctx->capturing, "a capture is already open on this context");
     LV_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
+    ctx->api_mutex.lock();            // kept until lv_graph_end_capture (on this thread)
     return LV_OK;
 }
 
@@ -185,7 +186,9 @@ extern "C" int lv_graph_end_capture(lv_ctx* ctx, lv_graph** out) {
     *out = nullptr;
     ctx->capturing = false;
     cudaGraph_t graph = nullptr;
-    LV_CUDA(cudaStreamEndCapture(ctx->stream, &graph));
+    const cudaError_t ended = cudaStreamEndCapture(ctx->stream, &graph);
+    ctx->api_mutex.unlock();          // taken by lv_graph_begin_capture
+    if (ended != cudaSuccess) return cuda_fail(ended, "cudaStreamEndCapture");
     auto* g = new lv_graph();
     g->graph = graph;
     size_t n_nodes = 0;
@@ -230,7 +233,8 @@ extern "C" int lv_graph_destroy(lv_graph* g) {
 }
 
 extern "C" int lv_stream_sync(lv_ctx* ctx, int timeout_ms) {
-    LV_ENTER(ctx);
+    LV_ENTER(ctx);                     // a capture that another thread has open ends first
+    LV_REQUIRE(!ctx->capturing, "cannot wait for the stream while it is being captured");
     if (timeout_ms <= 0) {
         LV_CUDA(cudaStreamSynchronize(ctx->stream));
     } else {

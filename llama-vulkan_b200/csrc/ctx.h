@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <mutex>
 #include <string>
 
 #include "../../include/lv_b200.h"
@@ -16,6 +17,7 @@ struct lv_ctx {
     uint32_t* h_err = nullptr;        // pinned mirror used by lv_ctx_check
     cudaGraph_t capture_graph = nullptr;
     bool capturing = false;
+    std::recursive_mutex api_mutex;   // see LV_ENTER
     void* comm = nullptr;             // ncclComm_t when a communicator is attached
     int comm_rank = 0, comm_size = 1;
     void* peer = nullptr;             // lv::PeerState of the peer-memory all-reduce
@@ -50,11 +52,13 @@ bool peer_windows(lv_ctx* ctx, float** windows, int* n_ranks, int* rank, uint32_
     } while (0)
 
 // First statement of every entry point that takes a context.
+// Entry points of one context are serialised: a stream capture keeps the context's lock from
+// lv_graph_begin_capture to lv_graph_end_capture, so that no other thread can put work on (or
+// synchronise) the capturing stream in between, which would invalidate the capture.
 #define LV_ENTER(ctx)                                                        \
-    do {                                                                     \
-        if ((ctx) == nullptr) return lv::fail(LV_ERR_BAD_ARGUMENTS, "null context"); \
-        LV_CUDA(cudaSetDevice((ctx)->device));                               \
-    } while (0)
+    if ((ctx) == nullptr) return lv::fail(LV_ERR_BAD_ARGUMENTS, "null context"); \
+    std::lock_guard<std::recursive_mutex> lv_api_guard__((ctx)->api_mutex);  \
+    LV_CUDA(cudaSetDevice((ctx)->device))
 
 #define LV_REQUIRE(cond, msg)                                              \
     do {                                                                   \

@@ -383,6 +383,8 @@ void* llava_server_create(void* ctx, uint32_t port, const char* bind_address, in
     return s;
 }
 uint32_t llava_server_port(void* server) { return static_cast<served*>(server)->server.port(); }
+uint64_t llava_server_grouped_steps(void* server) { return static_cast<served*>(server)->server.grouped_steps(); }
+uint64_t llava_server_grouped_tokens(void* server) { return static_cast<served*>(server)->server.grouped_tokens(); }
 void llava_server_start(void* server) {
     auto* s = static_cast<served*>(server);
     if (!s->loop.joinable()) s->loop = std::thread([s]() { s->server.serve_forever(); });

@@ -134,6 +134,9 @@ private:
     void drop_command_buffers();
     llava_command_buffer* get_command_buffer(u32 batch, bool with_head);
     bool sampling_on_device() const { return !deterministic && !host_sampler; }
+public:
+    bool samples_on_host() const { return !deterministic && host_sampler; }
+private:
     bool upload_sampler_state();
 
     // key: batch | with_head << 16 | device sampler << 17

@@ -98,9 +98,20 @@ bool llava_session_group::prepare_members(u32* backlog) {
         if (!tables->write_raw(0, table.data(), table_bytes)) return false;
         uploaded_table.assign(reinterpret_cast<const u8*>(table.data()), reinterpret_cast<const u8*>(table.data()) + table_bytes);
     }
+    vector<bool> sampled_now;
     for (llava_session* s : members) {
         if (!s->sync_device_position(s->current_tokens_in_gpu)) return false;
+        if (s->sampling_on_device() && !s->upload_sampler_state()) return false;
         if (!s->upload_pending_tokens(s->current_tokens_in_gpu, 1)) return false;
+        if (!s->deterministic && s->host_sampler) {
+            cerr << "[!] group step: a member samples on the host; only greedy members and the device sampler are supported" << endl;
+            return false;
+        }
+        sampled_now.push_back(s->sampling_on_device());
+    }
+    if (sampled_now != sampled) {            // the sampler launches are part of the recorded step
+        drop_graph();
+        sampled = sampled_now;
     }
     *backlog = need;
     return true;
@@ -137,6 +148,16 @@ bool llava_session_group::record(u32 backlog) {
     note(lv_gemm_tc(lv, f32(logits), ctx->output_w->device_ptr(), ctx->output_w->kernel_type(), split->device_ptr(), h.vocab_size, dim, k, 0));
     note(lv_argmax_advance_group(lv, f32(logits), h.vocab_size, table, k, max_backlog_size + 1, static_cast<u32*>(tokens_dev->device_ptr()),
                                  pinned_tokens));
+    // members that sample (the reference's default): the sampler of their own step, on their row of the logits;
+    // it overwrites the greedy token in the member's token log and in the pinned word
+    for (u32 i = 0; i < k; ++i) {
+        if (!sampled[i]) continue;
+        llava_session* s = members[i];
+        u32* log = static_cast<u32*>(s->token_log->device_ptr());
+        note(lv_sample_mirostat(lv, f32(logits) + size_t(i) * h.vocab_size, h.vocab_size, log, static_cast<u32*>(s->config_buffer->device_ptr()),
+                                static_cast<u32*>(s->sampler_state->device_ptr()), -1.0f, log, max_backlog_size + 1,
+                                static_cast<u32*>(tokens_dev->device_ptr()) + i, pinned_tokens + i, nullptr));
+    }
     lv_graph* g = nullptr;
     const int end = lv_graph_end_capture(lv, &g);
     note(end);

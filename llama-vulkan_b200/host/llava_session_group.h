@@ -9,7 +9,8 @@
 // llava_session objects: their caches, token buffers and positions are the ones a group step
 // reads and advances, so a session can leave a group and go on by itself (and the other way round).
 //
-// Greedy decoding only (the sampler of a session runs in the session's own step).
+// A member decodes greedily or draws its token with the device sampler, whichever its session is set to
+// (set_deterministic); members that sample on the host are refused.
 #ifndef LLAVA_B200_SESSION_GROUP_H
 #define LLAVA_B200_SESSION_GROUP_H
 
@@ -50,6 +51,7 @@ private:
     llava_device_memory* memory = nullptr;
     llava_buffer *x = nullptr, *q = nullptr, *vout = nullptr, *ff = nullptr, *split = nullptr, *logits = nullptr, *scratch = nullptr,
                  *tables = nullptr, *tokens_dev = nullptr;
+    std::vector<bool> sampled;               // per member: the recorded step ends with its sampler launch
     std::vector<u8> uploaded_table;          // the member tables as the device holds them
     u32* pinned_tokens = nullptr;
     lv_graph* graph = nullptr;

@@ -1,0 +1,117 @@
+#include "group_scheduler.h"
+
+#include <algorithm>
+
+#include "../llava_context.h"
+#include "../llava_session.h"
+#include "../llava_session_group.h"
+
+using namespace std;
+using namespace lsrv;
+
+namespace {
+constexpr auto kWindow = chrono::microseconds(500);      // how long the first caller of a round waits for the other runners
+constexpr size_t kCachedGroups = 8;
+}  // namespace
+
+group_scheduler::group_scheduler(llava_context* _ctx) : ctx(_ctx) {}
+
+group_scheduler::~group_scheduler() {
+    for (auto& [key, g] : groups) delete g;
+}
+
+void group_scheduler::runner_enters() {
+    lock_guard<mutex> lock(m);
+    ++runners;
+}
+
+void group_scheduler::runner_leaves() {
+    {
+        lock_guard<mutex> lock(m);
+        if (runners) --runners;
+    }
+    cv.notify_all();            // a leader may be waiting for a runner that will not come
+}
+
+void group_scheduler::forget(llava_session* session) {
+    lock_guard<mutex> lock(m);
+    for (auto it = groups.begin(); it != groups.end();) {
+        if (find(it->first.begin(), it->first.end(), session) != it->first.end()) {
+            delete it->second;
+            it = groups.erase(it);
+        } else {
+            ++it;
+        }
+    }
+}
+
+u32 group_scheduler::evaluate(llava_session* session) {
+    // what a group step cannot serve goes through the session's own step
+    const bool groupable = session->get_token_count() - session->get_tokens_in_gpu() == 1 && !session->samples_on_host() &&
+                           !session->is_tracing_enabled() && ctx->tp_size() == 1;
+    if (!groupable) return session->predict_next_token();
+    unique_lock<mutex> lock(m);
+    waiting.push_back(session);
+    cv.notify_all();                          // a leader that collects a round counts the callers
+    while (results.count(session) == 0) {
+        if (!leader_present) {
+            // whoever finds no leader leads the next round (it is one of the waiting callers itself)
+            leader_present = true;
+            lead(lock);                       // collects the round, runs it, publishes the results
+            leader_present = false;
+            cv.notify_all();
+        } else {
+            cv.wait(lock);
+        }
+    }
+    const u32 token = results[session];
+    results.erase(session);
+    return token;
+}
+
+// Called with the lock held by the first caller of a round.
+void group_scheduler::lead(unique_lock<mutex>& lock) {
+    const auto deadline = chrono::steady_clock::now() + kWindow;
+    cv.wait_until(lock, deadline, [&]() { return waiting.size() >= max<u32>(runners, 1u) || waiting.size() >= llava_session::max_batch_limit; });
+    vector<llava_session*> round;
+    round.swap(waiting);
+    if (round.size() > llava_session::max_batch_limit) {          // the rest forms the next round
+        waiting.assign(round.begin() + llava_session::max_batch_limit, round.end());
+        round.resize(llava_session::max_batch_limit);
+    }
+    vector<u32> tokens(round.size(), ~0U);
+    if (round.size() == 1) {
+        lock.unlock();
+        tokens[0] = round[0]->predict_next_token();
+        lock.lock();
+    } else {
+        vector<llava_session*> key = round;
+        sort(key.begin(), key.end());
+        llava_session_group* g = nullptr;
+        const auto it = groups.find(key);
+        if (it != groups.end()) {
+            g = it->second;
+        } else {
+            if (groups.size() >= kCachedGroups) {             // membership changes rarely; keep the table small
+                delete groups.begin()->second;
+                groups.erase(groups.begin());
+            }
+            g = new llava_session_group(ctx, key);
+            groups.emplace(key, g);
+        }
+        lock.unlock();
+        vector<u32> by_key;
+        const bool ok = g->is_valid() && g->step(&by_key);
+        if (ok) {
+            for (size_t i = 0; i < round.size(); ++i)
+                tokens[i] = by_key[size_t(lower_bound(key.begin(), key.end(), round[i]) - key.begin())];
+            n_grouped_steps += 1;
+            n_grouped_tokens += round.size();
+        } else {
+            // e.g. a model the batched products do not take: every caller falls back to its own step
+            for (size_t i = 0; i < round.size(); ++i) tokens[i] = round[i]->predict_next_token();
+        }
+        lock.lock();
+    }
+    for (size_t i = 0; i < round.size(); ++i) results[round[i]] = tokens[i];
+}

@@ -6,6 +6,7 @@
 
 #include "../llava_context.h"
 #include "../llava_session.h"
+#include "group_scheduler.h"
 
 using namespace std;
 using namespace lsrv;
@@ -48,9 +49,42 @@ void session_wrapper::run() {
     llava_session session(owner->context());
     session.set_deterministic(deterministic);
 
+    group_scheduler* sched = owner->scheduler();
+    bool registered = false;                 // counted by the scheduler among the sessions that ask for token after token
+    auto sync_registration = [&]() {
+        if (sched == nullptr || registered == should_run) return;
+        if (should_run) sched->runner_enters();
+        else sched->runner_leaves();
+        registered = should_run;
+    };
+
     while (!should_die) {
         process_orders(session, !(should_run || should_tick));
+        sync_registration();
         if (!(should_run || should_tick)) continue;
+        if (sched != nullptr && should_run) {
+            // running: the scheduler evaluates this session's token together with the other running sessions'
+            const u32 token = sched->evaluate(&session);
+            process_orders(session, false);
+            if (token == ~0U) {
+                cerr << "Error starting token generation" << endl;
+                should_run = false;
+                sync_registration();
+                continue;
+            }
+            vector<u8> payload(12);
+            const u32 pos = session.get_token_count();
+            memcpy(payload.data(), &session_id, 4);
+            memcpy(payload.data() + 4, &token, 4);
+            memcpy(payload.data() + 8, &pos, 4);
+            if (!session.push_token(token)) {
+                cerr << "Out of buffer ?" << endl;
+                should_run = false;
+            }
+            outbound_broadcasts.emplace_back(session_id, outCmdNewToken, payload);
+            flush_outbound_packets();
+            continue;
+        }
         if (!session.start_next_token_prediction()) {
             should_run = false;
             cerr << "Error starting token generation" << endl;
@@ -81,6 +115,9 @@ void session_wrapper::run() {
         tick_client = 0;
     }
     process_orders(session, false);
+    should_run = false;
+    sync_registration();
+    if (sched != nullptr) sched->forget(&session);
     owner->notify_session_death(session_id);
 }
 

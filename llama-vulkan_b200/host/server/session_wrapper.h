@@ -18,6 +18,8 @@
 
 namespace lsrv {
 
+class group_scheduler;
+
 // (client id, reply opcode, request id, payload) and (session id, opcode, payload)
 using outbound_packet = std::tuple<u32, OutCommands, u32, std::vector<u8>>;
 using outbound_broadcast = std::tuple<u32, OutCommands, std::vector<u8>>;
@@ -29,6 +31,8 @@ public:
     virtual llava_context* context() = 0;
     virtual void receive_session_outbound_packets(std::list<outbound_packet>& packets, std::list<outbound_broadcast>& broadcasts) = 0;
     virtual void notify_session_death(u32 session_id) = 0;
+    // non-null: sessions in the running state ask it for their tokens, so that it can step them together
+    virtual group_scheduler* scheduler() { return nullptr; }
 };
 
 class session_wrapper {

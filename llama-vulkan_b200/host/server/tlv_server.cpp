@@ -15,6 +15,7 @@
 
 #include "../ggml_file.h"
 #include "../llava_context.h"
+#include "group_scheduler.h"
 
 using namespace std;
 using namespace lsrv;
@@ -40,6 +41,7 @@ bool watch(int epoll_fd, int fd, u32 events, bool modify = false) {
 
 tlv_server::tlv_server(llava_context* _ctx, u16 port, const char* bind_address, bool watch_stdin)
     : ctx(_ctx), requested_port(port), address(bind_address ? bind_address : "0.0.0.0"), stdin_watched(watch_stdin) {
+    if (ctx->has_device()) sched = new group_scheduler(ctx);
     // tokenMap reply: for every token {u32 length; bytes} (server/server.cpp:28-42)
     for (const ggml_token& t : ctx->get_model()->get_tokens()) {
         const u32 n = u32(t.text.size());
@@ -59,7 +61,11 @@ tlv_server::~tlv_server() {
     for (auto& [id, c] : clients) ::close(c.fd);
     for (int fd : {listen_fd, epoll_fd, wake_fd})
         if (fd >= 0) ::close(fd);
+    delete sched;
 }
+
+u64 tlv_server::grouped_steps() const { return sched ? sched->grouped_steps() : 0; }
+u64 tlv_server::grouped_tokens() const { return sched ? sched->grouped_tokens() : 0; }
 
 bool tlv_server::open() {
     listen_fd = ::socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);

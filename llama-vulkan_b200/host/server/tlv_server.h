@@ -40,6 +40,10 @@ public:
 
     // session_owner
     llava_context* context() override { return ctx; }
+    group_scheduler* scheduler() override { return sched; }
+    // steps that served two or more sessions at once, and the tokens they produced
+    u64 grouped_steps() const;
+    u64 grouped_tokens() const;
     void receive_session_outbound_packets(std::list<outbound_packet>& packets, std::list<outbound_broadcast>& broadcasts) override;
     void notify_session_death(u32 session_id) override;
 
@@ -69,6 +73,7 @@ private:
     session_wrapper* find_session(u32 id) const;
 
     llava_context* const ctx;
+    group_scheduler* sched = nullptr;        // null on a context without a device
     const u16 requested_port;
     const std::string address;
     const bool stdin_watched;

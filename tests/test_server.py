@@ -161,3 +161,60 @@ def test_every_opcode_against_a_live_session(pkg, tiny_model, tmp_path):
         a.close()
         b.close()
     ctx.close()      # the server's stop() has killed and joined the second session
+
+
+@pytest.mark.gpu
+def test_running_sessions_are_stepped_together(pkg, tiny_model):
+    """Three sessions in the running state: the server's scheduler evaluates their tokens in shared steps (one pass over
+    the weights per round), and every session still receives its own greedy trajectory."""
+    from test_e2e_gpu import OracleSession
+    n_tokens = 8
+    prompts = [[int(t) for t in np.random.default_rng(500 + i).integers(3, 32000, n)] for i, n in enumerate((6, 11, 4))]
+    want = []
+    for p in prompts:
+        orc = OracleSession(tiny_model)
+        for t in p:
+            orc.push(t)
+        toks = []
+        for _ in range(n_tokens):
+            orc.eval()
+            toks.append(int(orc.argmax()))
+            orc.push(toks[-1])
+        orc.close()
+        want.append(toks)
+    ctx = pkg.HostContext(tiny_model, 0)
+    ctx.set_exact_batched_products(True)           # exact weight tiles: the tokens must be the oracle's
+    with pkg.Server(ctx, deterministic=True) as server:
+        c = pkg.Client(server.port)
+        sids = []
+        for p in prompts:
+            op, sid = c.call(c.NEW_SESSION)
+            assert op == c.SESSION_CREATED
+            for t in p:
+                assert c.call(c.ADD_TOKEN, sid + struct.pack("<I", t)) == (c.ACK, ack(OK))
+            assert c.call(c.SUBSCRIBE, sid) == (c.ACK, ack(OK))
+            sids.append(sid)
+        got = {sid: [] for sid in sids}
+        pending = set()
+        for sid in sids:
+            pending.add(c.send(c.START, sid))
+        # broadcasts (request id 0) carry {session, token, position}; the three acknowledgements arrive in between
+        while any(len(v) < n_tokens for v in got.values()):
+            op, rid, data = c.recv()
+            if rid in pending:
+                assert (op, data) == (c.ACK, ack(OK))
+                pending.discard(rid)
+                continue
+            assert op == c.NEW_TOKEN and rid == 0
+            token, pos = struct.unpack("<II", data[4:])
+            got[data[:4]].append((token, pos))
+        for sid in sids:
+            c.send(c.STOP, sid)
+        for i, sid in enumerate(sids):
+            assert [t for t, _ in got[sid][:n_tokens]] == want[i]
+            assert [p for _, p in got[sid][:n_tokens]] == list(range(len(prompts[i]), len(prompts[i]) + n_tokens))
+        steps, tokens = server.grouped()
+        assert steps > 0 and tokens >= 2 * steps, (steps, tokens)
+        c.close()
+    ctx.set_exact_batched_products(False)
+    ctx.close()
