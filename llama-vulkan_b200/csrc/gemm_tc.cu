@@ -62,7 +62,7 @@ constexpr int kTcMaxBStages = 16;
 constexpr int kTcBanks = 2;                    // accumulator sets used in turn, to halve the length of each fp32 chain
 constexpr int kTcProducerWarps = 16;           // two groups of 8: even and odd tiles of K
 constexpr int kTcGroupWarps = 8;
-constexpr int kTcThreads = (kTcProducerWarps + 3) * 32;               // + TMA warp + two MMA warps (the second issues in the fast form only)
+constexpr int kTcThreads = (kTcProducerWarps + 2) * 32;               // + TMA warp + MMA warp
 
 template <int QT> struct TcTraits;
 template <> struct TcTraits<T_Q4_0> {
@@ -234,10 +234,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     // one barrier per thread (a single thread takes about a microsecond for all of them)
     if (threadIdx.x < 44) {
         const int i = int(threadIdx.x);
-        uint32_t count = 1;                                             // raw_full, b_full, b_empty; slot_empty and acc_full of the exact form
+        uint32_t count = 1;                                             // raw_full, slot_empty, acc_full, b_full, b_empty
         if (i >= 2 && i < 4) count = kTcProducerWarps;                  // raw_empty
         else if (i >= 4 && i < 7) count = FAST ? kTcProducerWarps : kTcGroupWarps;      // slot_full
-        else if (FAST && ((i >= 7 && i < 10) || i == 10)) count = 2;    // slot_empty, acc_full: both MMA-issuing lanes commit
         mbar_init(&bars[i], count);
         fence_mbar_init();
     }
@@ -302,42 +301,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 }
             }
         }
-    } else if (warp == kTcProducerWarps + 1 || warp == kTcProducerWarps + 2) {
-        // ---------------- MMA warps: one lane each issues tensor-core work ------------------------
-        // Exact form: the first warp issues everything.  Fast form: the issue loop of a single in-order thread (barrier
-        // wait, four MMAs, commit: ~0.3 us per tile) was as long as the producers' step, so two lanes share it: lane 0 of
-        // the first warp takes the even tiles of K into accumulator bank 0, lane 0 of the second the odd ones into bank 1.
-        const uint32_t issuer = uint32_t(warp) - (kTcProducerWarps + 1);
-        if (lane == 0 && (FAST || issuer == 0)) {
+    } else if (warp == kTcProducerWarps + 1) {
+        // ---------------- MMA warp: one lane issues the tensor-core work ------------------------
+        if (lane == 0) {
             // instruction descriptors: fp32 accumulator, fp16 A and B, both K-major, M = 128, N = 2 zpad / zpad
             const uint32_t idesc_common = (1u << 4) | ((uint32_t(kTcRows) >> 4) << 24);
             const uint32_t idesc_wide = idesc_common | (((2u * p.zpad) >> 3) << 17);
             const uint32_t idesc_narrow = idesc_common | ((p.zpad >> 3) << 17);
             const uint64_t a_desc0 = tc_smem_desc(smem_u32(slots)), b_desc0 = tc_smem_desc(smem_u32(bring));
             if constexpr (FAST) {
-                static_assert(kTcBanks == 2 && kTcFastGroup % 2 == 0, "two issuing lanes, one accumulator bank each");
-                uint32_t bs = issuer % nb, b_phase = (issuer / nb) & 1u;      // B stage and phase of this lane's next tile
-                const uint32_t bank = tmem_base + issuer * bank_cols;
-                bool first = true;
+                uint32_t bs = 0, b_phase = 0;                  // B stage and its phase, advanced without divisions
                 for (uint32_t g = 0; g < n_groups && ok; ++g) {
                     const uint32_t ab = g % kTcFastBufs;
                     ok = mbar_wait(&slot_full[ab], (g / kTcFastBufs) & 1u, p.err);
                     // descriptors differ from the first tile's only in the address field (units of 16 bytes; the whole
                     // shared memory stays below the field's 256 KB)
-                    uint64_t a_desc = a_desc0 + ((ab * uint32_t(kTcFastBufBytes) + issuer * uint32_t(kTcTileBytes)) >> 4);
-                    for (uint32_t t = issuer; t < uint32_t(kTcFastGroup) && ok; t += 2) {
+                    uint64_t a_desc = a_desc0 + ((ab * uint32_t(kTcFastBufBytes)) >> 4);
+                    for (uint32_t t = 0; t < uint32_t(kTcFastGroup) && ok; ++t) {
+                        const uint32_t c = g * kTcFastGroup + t;
                         ok = mbar_wait(&b_full[bs], b_phase, p.err);
                         if (!ok) break;
                         tc_fence_after_sync();
                         const uint64_t b_desc = b_desc0 + ((bs * b_bytes) >> 4);
+                        const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
 #pragma unroll
                         for (int k = 0; k < kTcChunkK / 16; ++k)          // 16 fp16 along K = 32 bytes = 2 address units
-                            tc_mma_f16(bank, a_desc + 2u * k, b_desc + 2u * k, idesc_wide, (!first || k != 0) ? 1u : 0u);
-                        first = false;
+                            tc_mma_f16(bank, a_desc + 2u * k, b_desc + 2u * k, idesc_wide, (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u);
                         tc_commit(&b_empty[bs]);
-                        a_desc += 2u * (uint32_t(kTcTileBytes) >> 4);
-                        bs += 2;
-                        while (bs >= nb) { bs -= nb; b_phase ^= 1u; }
+                        a_desc += uint32_t(kTcTileBytes) >> 4;
+                        if (++bs == nb) { bs = 0; b_phase ^= 1u; }
                     }
                     if (ok) tc_commit(&slot_empty[ab]);
                 }
