@@ -23,13 +23,13 @@
 namespace lv {
 
 constexpr int kPeerMaxRanks = 8;
-constexpr int kPeerCtas = 4;
+constexpr int kPeerCtas = 32;              // a batch of 64 rows is a megabyte per rank: four CTAs moved it at ~40 GB/s
 constexpr int kPeerThreads = 256;
 
 struct PeerWindowLayout {
     uint32_t capacity;        // floats per slot
     __host__ __device__ size_t slot_floats(int n_ranks) const { return size_t(kTpSlotSets) * n_ranks * capacity; }
-    // slots, the flags of the stand-alone kernel (2 x 8 x 4 words), the flags of the exchanges fused into the GEMV
+    // slots, the flags of the stand-alone kernel (2 x 8 x 32 words), the flags of the exchanges fused into the GEMV
     __host__ __device__ size_t bytes(int n_ranks) const {
         return slot_floats(n_ranks) * sizeof(float) + size_t(kTpLegacyFlagWords) * sizeof(uint32_t) +
                size_t(2) * kTpMaxRanks * kTpFlagCtas * sizeof(uint32_t) + size_t(kTpFlagCtas) * sizeof(uint32_t) /* local flags */ + 256;

@@ -72,7 +72,7 @@ constexpr int kTpMaxRanks = 8;
 constexpr int kTpSlotSets = 4;         // slot sets of a window: 0 and 1 alternate for the exchanges fused into the GEMVs,
                                        // 2 and 3 for the stand-alone all-reduce kernel, so the two never share a slot
 constexpr int kTpFlagCtas = 256;       // flags per (exchange parity, source rank)
-constexpr int kTpLegacyFlagWords = 64; // flag words of the stand-alone all-reduce kernel that precede these
+constexpr int kTpLegacyFlagWords = 512; // flag words of the stand-alone all-reduce kernel that precede these
 constexpr int kTpTwoPhaseRanks = 64;   // ranks from which a consumer launch would sum the slots once per GPU instead of once per CTA:
                                        // never by default -- on 2 GPUs the extra intra-GPU flag round costs 5 us per exchange
 
