@@ -132,3 +132,53 @@ def test_group_refuses_what_it_cannot_do(pkg, world):
     g.close()
     for x in s:
         x.close()
+
+
+def test_group_members_that_sample_draw_with_their_own_sampler(pkg, world):
+    """Members set to the reference's sampler (its default) get their token from the device sampler at the end of the
+    group step: with the same seed a member draws the same tokens in a group as alone (exact weight tiles; the draw
+    depends on the logits through the kept set and the cumulative mass, so the comparison allows a member to part from
+    its lone trajectory where a probability sits within the logits' tolerance of the cut), greedy members beside them
+    stay greedy, and mu moves."""
+    world["ctx"].set_exact_batched_products(True)
+
+    def members(sampled):
+        out = []
+        for i in range(3):
+            n, seed = PROMPTS[i]
+            s = world["ctx"].session()
+            s.set_deterministic(i == 2 or not sampled)          # member 2 stays greedy
+            s.set_seed(1000 + i)
+            for t in prompt_of(n, seed):
+                assert s.push_token(t)
+            tok = s.predict_next_token()
+            assert tok != pkg.NO_TOKEN and s.push_token(tok)
+            out.append(s)
+        return out
+
+    alone = members(True)
+    lone_tokens = [[s.tokens()[-1]] for s in alone]
+    for _ in range(5):
+        for i, s in enumerate(alone):
+            tok = s.predict_next_token()
+            assert s.push_token(tok)
+            lone_tokens[i].append(tok)
+    grouped = members(True)
+    g = pkg.SessionGroup(world["ctx"], grouped)
+    group_tokens = [[s.tokens()[-1]] for s in grouped]
+    for _ in range(5):
+        toks = g.step()
+        assert toks is not None and all(t < world["vocab"] for t in toks)
+        for i, s in enumerate(grouped):
+            assert s.push_token(toks[i])
+            group_tokens[i].append(toks[i])
+    world["ctx"].set_exact_batched_products(False)
+    assert g.kernel_launches() == 1 + 2 * 9 + 2 + 1 + 2                  # two sampler launches
+    assert group_tokens[2] == lone_tokens[2] == world["want"][2][0][:6]   # the greedy member
+    agree = [next((j for j, (a, b) in enumerate(zip(group_tokens[i], lone_tokens[i])) if a != b), 6) for i in range(2)]
+    assert min(agree) >= 3 and max(agree) == 6, (group_tokens, lone_tokens)
+    for i in range(2):
+        assert grouped[i].mirostat_mu() != pytest.approx(10.0)           # moved from its start value (2 tau)
+    g.close()
+    for s in alone + grouped:
+        s.close()
