@@ -79,10 +79,19 @@ constexpr int kTcFastGroup = 4;                // fast form: tiles of K per prod
 constexpr int kTcFastBufs = 2;
 constexpr int kTcFastBufBytes = kTcFastGroup * kTcTileBytes;          // 65536
 constexpr int kTcFastBRingBytes = 49152;
-template <int QT, bool FAST> __host__ __device__ constexpr int tc_a_bytes() { return FAST ? kTcFastBufs * kTcFastBufBytes : kTcSlots * kTcSlotBytes; }
-template <int QT, bool FAST> __host__ __device__ constexpr int tc_b_ring_bytes() { return FAST ? kTcFastBRingBytes : TcTraits<QT>::kBRingBytes; }
-template <int QT, bool FAST = false> __host__ __device__ constexpr size_t tc_smem_bytes() {
-    return 1024 /* alignment slack */ + size_t(tc_a_bytes<QT, FAST>()) + tc_b_ring_bytes<QT, FAST>() + size_t(kTcRawStages) * tc_raw_stage<QT>() + 512;
+// FORM: 0 exact (hi/lo tiles in shared memory), 1 fast (one fp16 plane in shared memory), 2 fast with the weight tile in
+// tensor memory (written by the producers with tcgen05.st and read by the MMA as its TMEM operand: the tile never passes
+// through shared memory, which is what bounds forms 0 and 1; the freed 128 KB hold eight activation stages)
+constexpr int kTcTmemBRingBytes = 131072;
+constexpr int kTcTmemScratchBytes = 8192;      // the epilogue's gate exchange
+template <int QT, int FORM> __host__ __device__ constexpr int tc_a_bytes() {
+    return FORM == 2 ? kTcTmemScratchBytes : (FORM == 1 ? kTcFastBufs * kTcFastBufBytes : kTcSlots * kTcSlotBytes);
+}
+template <int QT, int FORM> __host__ __device__ constexpr int tc_b_ring_bytes() {
+    return FORM == 2 ? kTcTmemBRingBytes : (FORM == 1 ? kTcFastBRingBytes : TcTraits<QT>::kBRingBytes);
+}
+template <int QT, int FORM = 0> __host__ __device__ constexpr size_t tc_smem_bytes() {
+    return 1024 /* alignment slack */ + size_t(tc_a_bytes<QT, FORM>()) + tc_b_ring_bytes<QT, FORM>() + size_t(kTcRawStages) * tc_raw_stage<QT>() + 512;
 }
 
 struct GemmTcParams {
@@ -127,6 +136,16 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t a_desc, uin
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same with the A operand in tensor memory (lane = row, one 32-bit column per two fp16 along K).
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -183,17 +202,18 @@ __device__ __forceinline__ void dequant_word_q8(uint32_t w, __half2 d2, __half2 
     }
 }
 
-template <int QT, bool FAST>
+template <int QT, int FORM>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcParams p, const __grid_constant__ GemmTcMaps maps) {
-    static_assert(!FAST || QT == T_Q4_0, "the fast form exists for q4_0 only");
+    constexpr bool FAST = FORM != 0, TMEMA = FORM == 2;
+    static_assert(!FAST || QT == T_Q4_0, "the fast forms exist for q4_0 only");
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     uint8_t* slots = smem;
-    constexpr int kRawRowBytes = tc_raw_row_bytes<QT>(), kRawStage = tc_raw_stage<QT>(), kBRingBytes = tc_b_ring_bytes<QT, FAST>();
+    constexpr int kRawRowBytes = tc_raw_row_bytes<QT>(), kRawStage = tc_raw_stage<QT>(), kBRingBytes = tc_b_ring_bytes<QT, FORM>();
     constexpr int kTileWords = kRawRowBytes / 16;                    // 32-bit words of one 64-column tile of a row: 9 / 17
-    uint8_t* bring = smem + tc_a_bytes<QT, FAST>();
+    uint8_t* bring = smem + tc_a_bytes<QT, FORM>();
     uint8_t* rawring = bring + kBRingBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(rawring + kTcRawStages * kRawStage);
     uint64_t* raw_full = bars;                       // [2]
@@ -229,7 +249,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
     // the allocation is a power of two >= 32
     const uint32_t bank_cols = (FAST ? 2u : 3u) * p.zpad;
-    const uint32_t tmem_cols = FAST ? (p.zpad <= 16 ? 64u : (p.zpad <= 32 ? 128u : 256u)) : (p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u));
+    // form 2: accumulators in columns [0, 256), the two weight buffers (4 tiles x 32 columns each) in [256, 512)
+    constexpr uint32_t kTmemABase = 256, kTmemTileCols = kTcChunkK / 2;
+    const uint32_t tmem_cols = TMEMA ? 512u
+                               : (FAST ? (p.zpad <= 16 ? 64u : (p.zpad <= 32 ? 128u : 256u)) : (p.zpad <= 16 ? 128u : (p.zpad <= 32 ? 256u : 512u)));
 
     // one barrier per thread (a single thread takes about a microsecond for all of them)
     if (threadIdx.x < 44) {
@@ -317,6 +340,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                     // descriptors differ from the first tile's only in the address field (units of 16 bytes; the whole
                     // shared memory stays below the field's 256 KB)
                     uint64_t a_desc = a_desc0 + ((ab * uint32_t(kTcFastBufBytes)) >> 4);
+                    uint32_t a_tmem = tmem_base + kTmemABase + ab * (kTcFastGroup * kTmemTileCols);
                     for (uint32_t t = 0; t < uint32_t(kTcFastGroup) && ok; ++t) {
                         const uint32_t c = g * kTcFastGroup + t;
                         ok = mbar_wait(&b_full[bs], b_phase, p.err);
@@ -325,10 +349,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                         const uint64_t b_desc = b_desc0 + ((bs * b_bytes) >> 4);
                         const uint32_t bank = tmem_base + (c % kTcBanks) * bank_cols;
 #pragma unroll
-                        for (int k = 0; k < kTcChunkK / 16; ++k)          // 16 fp16 along K = 32 bytes = 2 address units
-                            tc_mma_f16(bank, a_desc + 2u * k, b_desc + 2u * k, idesc_wide, (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u);
+                        for (int k = 0; k < kTcChunkK / 16; ++k) {        // 16 fp16 along K = 32 bytes = 2 address units = 8 TMEM columns
+                            const uint32_t acc = (c >= uint32_t(kTcBanks) || k != 0) ? 1u : 0u;
+                            if constexpr (TMEMA) tc_mma_f16_ta(bank, a_tmem + 8u * k, b_desc + 2u * k, idesc_wide, acc);
+                            else tc_mma_f16(bank, a_desc + 2u * k, b_desc + 2u * k, idesc_wide, acc);
+                        }
                         tc_commit(&b_empty[bs]);
                         a_desc += uint32_t(kTcTileBytes) >> 4;
+                        a_tmem += kTmemTileCols;
                         if (++bs == nb) { bs = 0; b_phase ^= 1u; }
                     }
                     if (ok) tc_commit(&slot_empty[ab]);
@@ -358,7 +386,87 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         }
     } else {
         // ---------------- producer warps: q4_0 blocks -> swizzled fp16 hi/lo tiles ---------------
-        if constexpr (FAST) {
+        if constexpr (TMEMA) {
+            // A warp can reach only its own quarter of the tensor memory's lanes (32 (warp % 4) ..): lane = tile row.  Warp w
+            // handles rows 32 (w % 4) .. + 31 of tile w / 4 of every raw stage; a thread dequantises the two blocks of its row
+            // into 32 registers (two fp16 each, in element order) and stores them as 32 columns of its lane.
+            const uint32_t tr_row = (uint32_t(warp) & 3u) * 32u + uint32_t(lane), tt = uint32_t(warp) >> 2;
+            for (uint32_t g = 0; g < n_groups && ok; ++g) {
+                const int rs = int(g % kTcRawStages);
+                ok = mbar_wait(&raw_full[rs], (g / kTcRawStages) & 1u, p.err);
+                if (!ok) break;
+                // the 36 bytes of the tile start at byte 36 t of the 144-byte raw row: three 16-byte loads from the chunk
+                // that holds the first byte (rows are 9 chunks apart, so a quarter warp's loads fall into different banks)
+                uint32_t L[12];
+                {
+                    const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kRawStage + tr_row * kRawRowBytes) + 2u * tt;
+#pragma unroll
+                    for (int i = 0; i < 3; ++i) {
+                        const uint4 v = src[i];
+                        L[4 * i] = v.x; L[4 * i + 1] = v.y; L[4 * i + 2] = v.z; L[4 * i + 3] = v.w;
+                    }
+                }
+                uint32_t w[9];
+                switch (tt) {                      // 36 t mod 16 = 4 t bytes into the first chunk (t is the same for the whole warp)
+                    case 0:
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) w[i] = L[i];
+                        break;
+                    case 1:
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) w[i] = L[i + 1];
+                        break;
+                    case 2:
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) w[i] = L[i + 2];
+                        break;
+                    default:
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) w[i] = L[i + 3];
+                        break;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_empty[rs]);
+                // registers of the row: column j of the tile = elements 2j, 2j + 1 (block 0: columns 0..15, block 1: 16..31)
+                uint32_t cols[32];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t q[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k] = b == 0 ? __funnelshift_r(w[k], w[k + 1], 16) : w[5 + k];
+                    const uint32_t dbits = b == 0 ? (w[0] & 0xffffu) : (w[4] >> 16);
+                    const __half2 d2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(dbits)));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t hi[4];
+                        dequant_word_hi(q[k], d2, hi);          // (4k, 4k+1), (4k+2, 4k+3), (16+4k, 17+4k), (18+4k, 19+4k)
+                        cols[16 * b + 2 * k] = hi[0];
+                        cols[16 * b + 2 * k + 1] = hi[1];
+                        cols[16 * b + 8 + 2 * k] = hi[2];
+                        cols[16 * b + 8 + 2 * k + 1] = hi[3];
+                    }
+                }
+                const uint32_t ab = g % kTcFastBufs;
+                if (g >= uint32_t(kTcFastBufs)) {
+                    ok = mbar_wait(&slot_empty[ab], ((g / kTcFastBufs) - 1) & 1u, p.err);
+                    if (!ok) break;
+                }
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + ((uint32_t(warp) & 3u) * 32u << 16) + kTmemABase + (ab * kTcFastGroup + tt) * kTmemTileCols;
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                    "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                    ::"r"(taddr), "r"(cols[0]), "r"(cols[1]), "r"(cols[2]), "r"(cols[3]), "r"(cols[4]), "r"(cols[5]), "r"(cols[6]), "r"(cols[7]),
+                      "r"(cols[8]), "r"(cols[9]), "r"(cols[10]), "r"(cols[11]), "r"(cols[12]), "r"(cols[13]), "r"(cols[14]), "r"(cols[15]),
+                      "r"(cols[16]), "r"(cols[17]), "r"(cols[18]), "r"(cols[19]), "r"(cols[20]), "r"(cols[21]), "r"(cols[22]), "r"(cols[23]),
+                      "r"(cols[24]), "r"(cols[25]), "r"(cols[26]), "r"(cols[27]), "r"(cols[28]), "r"(cols[29]), "r"(cols[30]), "r"(cols[31])
+                    : "memory");
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&slot_full[ab]);
+            }
+        } else if constexpr (FAST) {
             // a warp: 8 rows x the 4 tiles of a raw stage; the word offsets 36 r + 9 t of its lanes fall into 32 different banks
             const uint32_t fr = uint32_t(warp) * 8u + (uint32_t(lane) & 7u), ft = uint32_t(lane) >> 3;
             for (uint32_t g = 0; g < n_groups && ok; ++g) {
@@ -737,11 +845,14 @@ int gemm_tc_configure(lv_ctx* ctx) {
     LV_CUDA(cudaMemset(ctx->tc_counters, 0, kTcMaxTiles * sizeof(uint32_t)));
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q4_0>() && size_t(ctx->max_smem_optin) >= tc_smem_bytes<T_Q8_0>(),
                "device has too little shared memory for the batched product");
-    constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, true>();
+    constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, 1>();
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= kFastSmem, "device has too little shared memory for the batched product");
-    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>()))));
-    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFastSmem))));
-    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>()))));
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q4_0>()))));
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kFastSmem))));
+    constexpr size_t kTmemSmem = tc_smem_bytes<T_Q4_0, 2>();
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kTmemSmem, "device has too little shared memory for the batched product");
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTmemSmem))));
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>()))));
     const char* exact = getenv("LV_GEMM_TC_EXACT");
     ctx->tc_exact = exact != nullptr && exact[0] == '1';
     return LV_OK;
@@ -796,12 +907,18 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
     tiles *= splits;
     if constexpr (QT == T_Q4_0) {
         if (fast) {
-            constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, true>();
-            LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, true>, dim3(tiles), dim3(kTcThreads), kFastSmem, p, maps)));
+            static const char* smem_tiles = getenv("LV_GEMM_TC_SMEM_TILES");
+            if (smem_tiles != nullptr && smem_tiles[0] == '1') {
+                constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, 1>();
+                LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, 1>, dim3(tiles), dim3(kTcThreads), kFastSmem, p, maps)));
+            } else {
+                constexpr size_t kTmemSmem = tc_smem_bytes<T_Q4_0, 2>();
+                LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, 2>, dim3(tiles), dim3(kTcThreads), kTmemSmem, p, maps)));
+            }
             return LV_OK;
         }
     }
-    LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<QT, false>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps)));
+    LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<QT, 0>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps)));
     return LV_OK;
 }
 
