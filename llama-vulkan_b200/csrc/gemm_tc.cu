@@ -62,7 +62,7 @@ constexpr int kTcMaxBStages = 16;
 constexpr int kTcBanks = 2;                    // accumulator sets used in turn, to halve the length of each fp32 chain
 constexpr int kTcProducerWarps = 16;           // two groups of 8: even and odd tiles of K
 constexpr int kTcGroupWarps = 8;
-constexpr int kTcThreads = (kTcProducerWarps + 2) * 32;               // + TMA warp + MMA warp
+constexpr int kTcThreads = (kTcProducerWarps + 3) * 32;               // + TMA warp + two MMA warps (the second issues in form 2 only)
 
 template <int QT> struct TcTraits;
 template <> struct TcTraits<T_Q4_0> {
@@ -245,7 +245,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     const uint32_t g_begin = groups_all * split / p.splits, n_groups = groups_all * (split + 1) / p.splits - g_begin;
     const uint32_t n_chunks = 4 * n_groups;
     const uint32_t b_bytes = 2u * p.zpad * kTcChunkK * 2u;
-    const uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kBRingBytes) / b_bytes);         // B stages: 3-4 (zpad 64) .. 16
+    uint32_t nb = min(uint32_t(kTcMaxBStages), uint32_t(kBRingBytes) / b_bytes);               // B stages: 3-4 (zpad 64) .. 16
+    if constexpr (FORM == 2) nb &= ~1u;                   // 8 (zpad 64) .. 16, even: see the MMA warps
     // accumulator columns of a bank: [0, zpad) hi*hi, [zpad, 2 zpad) hi*lo, [2 zpad, 3 zpad) lo*hi; two banks;
     // the allocation is a power of two >= 32
     const uint32_t bank_cols = (FAST ? 2u : 3u) * p.zpad;
@@ -260,6 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         uint32_t count = 1;                                             // raw_full, slot_empty, acc_full, b_full, b_empty
         if (i >= 2 && i < 4) count = kTcProducerWarps;                  // raw_empty
         else if (i >= 4 && i < 7) count = FAST ? kTcProducerWarps : kTcGroupWarps;      // slot_full
+        else if (TMEMA && i >= 7 && i <= 10) count = 2;                 // slot_empty, acc_full: both MMA-issuing lanes commit
         mbar_init(&bars[i], count);
         fence_mbar_init();
     }
@@ -324,14 +326,47 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 }
             }
         }
-    } else if (warp == kTcProducerWarps + 1) {
-        // ---------------- MMA warp: one lane issues the tensor-core work ------------------------
-        if (lane == 0) {
+    } else if (warp == kTcProducerWarps + 1 || warp == kTcProducerWarps + 2) {
+        // ---------------- MMA warps: one lane each issues tensor-core work ------------------------
+        // Forms 0 and 1: the first warp issues everything.  Form 2: the issue loop of a single in-order thread (barrier
+        // wait, four MMAs, commit: ~0.25 us per tile) is longer than the producers' step, so two lanes share it: lane 0 of
+        // the first warp takes the even tiles of K into accumulator bank 0, lane 0 of the second the odd ones into bank 1.
+        // That needs an EVEN number of activation stages, so that a stage is always consumed by the same lane: with an odd
+        // number the two lanes would use a stage in turn, and a lane that runs ahead would find its barrier showing the
+        // completed phase of the same parity two uses earlier and take stale data for its tile.
+        const uint32_t issuer = uint32_t(warp) - (kTcProducerWarps + 1);
+        if (lane == 0 && (TMEMA || issuer == 0)) {
             // instruction descriptors: fp32 accumulator, fp16 A and B, both K-major, M = 128, N = 2 zpad / zpad
             const uint32_t idesc_common = (1u << 4) | ((uint32_t(kTcRows) >> 4) << 24);
             const uint32_t idesc_wide = idesc_common | (((2u * p.zpad) >> 3) << 17);
             const uint32_t idesc_narrow = idesc_common | ((p.zpad >> 3) << 17);
             const uint64_t a_desc0 = tc_smem_desc(smem_u32(slots)), b_desc0 = tc_smem_desc(smem_u32(bring));
+            if constexpr (TMEMA) {
+                static_assert(kTcBanks == 2 && kTcFastGroup % 2 == 0, "two issuing lanes, one accumulator bank each");
+                uint32_t bs = issuer, b_phase = 0;             // stage and phase of this lane's next tile (nb is even and >= 2)
+                const uint32_t bank = tmem_base + issuer * bank_cols;
+                bool first = true;
+                for (uint32_t g = 0; g < n_groups && ok; ++g) {
+                    const uint32_t ab = g % kTcFastBufs;
+                    ok = mbar_wait(&slot_full[ab], (g / kTcFastBufs) & 1u, p.err);
+                    uint32_t a_tmem = tmem_base + kTmemABase + (ab * kTcFastGroup + issuer) * kTmemTileCols;
+                    for (uint32_t t = issuer; t < uint32_t(kTcFastGroup) && ok; t += 2) {
+                        ok = mbar_wait(&b_full[bs], b_phase, p.err);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        const uint64_t b_desc = b_desc0 + ((bs * b_bytes) >> 4);
+#pragma unroll
+                        for (int k = 0; k < kTcChunkK / 16; ++k)          // 16 fp16 along K = 2 address units of B = 8 TMEM columns of A
+                            tc_mma_f16_ta(bank, a_tmem + 8u * k, b_desc + 2u * k, idesc_wide, (!first || k != 0) ? 1u : 0u);
+                        first = false;
+                        tc_commit(&b_empty[bs]);
+                        a_tmem += 2u * kTmemTileCols;
+                        bs += 2;
+                        if (bs >= nb) { bs -= nb; b_phase ^= 1u; }
+                    }
+                    if (ok) tc_commit(&slot_empty[ab]);
+                }
+            } else
             if constexpr (FAST) {
                 uint32_t bs = 0, b_phase = 0;                  // B stage and its phase, advanced without divisions
                 for (uint32_t g = 0; g < n_groups && ok; ++g) {
