@@ -213,3 +213,18 @@ def test_gemm_tc_split_along_k_is_reproducible(gpu, pkg, form):
     assert np.array_equal(got[0], got[1]) and np.array_equal(got[0], got[2])
     want = np.stack([ob.gemv(W, qn.Q4_0, x[z], rows, cols, 128) for z in range(batch)])
     close(got[0].reshape(batch, rows), want, **loose(form, qn.Q4_0))
+
+
+def test_shared_memory_form_of_the_fast_tiles_in_a_child_process():
+    """LV_GEMM_TC_SMEM_TILES=1 (read once per process) keeps the fast weight tile in shared memory instead of tensor memory:
+    the product and pair tests of this file must hold for that kernel too."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("LV_GEMM_TC_SMEM_TILES") == "1":
+        pytest.skip("already the child")
+    env = dict(os.environ, LV_GEMM_TC_SMEM_TILES="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-m", "gpu", "-k", "fast and (store_and_add or silu_pair or reproducible)"],
+                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, timeout=900)
+    tail = r.stdout.decode(errors="replace")[-600:]
+    assert r.returncode == 0 and " passed" in tail, tail
