@@ -581,6 +581,51 @@ def measure_concurrent_sessions(rig, ctx, name, args, counts=(4, 16, 64)):
     return out
 
 
+def measure_server_sessions(rig, ctx, args, counts=(1, 4, 16), seconds=1.5):
+    """Tokens/s that clients of the TCP front end receive when k sessions generate at once (greedy, 32-token seeded prompts):
+    the server's scheduler steps the running sessions together.  Counted from the newToken broadcasts that arrive on one
+    subscribed client connection over `seconds`, after half a second of warm-up."""
+    import struct
+    pkg = rig.pkg
+    out = {}
+    with pkg.Server(ctx, deterministic=True) as server:
+        for k in counts:
+            c = pkg.Client(server.port, timeout=120.0)
+            sids = []
+            for i in range(k):
+                op, sid = c.call(c.NEW_SESSION)
+                assert op == c.SESSION_CREATED
+                for t in prompt_tokens(32, seed=PROMPT_SEED + 100 + i):
+                    assert c.call(c.ADD_TOKEN, sid + struct.pack("<I", t))[0] == c.ACK
+                assert c.call(c.SUBSCRIBE, sid)[0] == c.ACK
+                sids.append(sid)
+            g0 = server.grouped()
+            for sid in sids:
+                c.send(c.START, sid)
+            t_start = time.perf_counter()
+            t0, n = None, 0
+            while True:
+                op, rid, data = c.recv()
+                now = time.perf_counter()
+                if op != c.NEW_TOKEN or rid != 0:
+                    continue
+                if t0 is None:
+                    if now - t_start >= 0.5:
+                        t0 = now
+                    continue
+                n += 1
+                if now - t0 >= seconds:
+                    break
+            elapsed = time.perf_counter() - t0
+            g1 = server.grouped()
+            for sid in sids:
+                c.call(c.KILL_SESSION, sid)
+            c.close()
+            steps, toks = g1[0] - g0[0], g1[1] - g0[1]
+            out[str(k)] = {"tokens_per_s": n / elapsed, "sessions_per_shared_step": (toks / steps) if steps else 1.0}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -647,6 +692,7 @@ def main():
     sessions = None
     if world == 1 and not args.no_sessions and w["wtype"] == 2:
         sessions = measure_concurrent_sessions(rig, ctx, args.workload, args)
+        sessions["through_the_server"] = measure_server_sessions(rig, ctx, args)
     ctx.close()
     rig.barrier()
 

@@ -376,6 +376,7 @@ struct served {
 void* llava_server_create(void* ctx, uint32_t port, const char* bind_address, int deterministic) {
     lsrv::session_wrapper::set_deterministic_sessions(deterministic != 0);
     auto* s = new served(static_cast<llava_context*>(ctx), uint16_t(port), bind_address ? bind_address : "127.0.0.1");
+    s->server.set_announce(false);           // a library caller reads the port from llava_server_port
     if (!s->server.open()) {
         delete s;
         return nullptr;

@@ -340,7 +340,7 @@ void tlv_server::begin_shutdown() {
 
 void tlv_server::serve_forever() {
     if (listen_fd < 0 && !open()) return;
-    cout << "[*] Started server on " << address << ":" << bound_port << endl;
+    if (announce) cout << "[*] Started server on " << address << ":" << bound_port << endl;
     const int sigfd = ctx->get_signal_fd();
     epoll_event events[32];
     while (!shutting_down || !sessions.empty()) {

@@ -33,6 +33,7 @@ public:
     tlv_server(const tlv_server&) = delete;
     tlv_server& operator=(const tlv_server&) = delete;
 
+    void set_announce(bool on) { announce = on; }     // print "[*] Started server on ..." on standard output (default: yes)
     bool open();                     // socket, bind, listen; false (with a message on stderr) on failure
     u16 port() const { return bound_port; }      // the port actually bound (useful with port 0)
     void serve_forever();            // returns after stop(), a signal on the context's signal fd, or input on stdin
@@ -81,6 +82,7 @@ private:
     int listen_fd = -1, epoll_fd = -1, wake_fd = -1;
     u32 next_client_id = 1;
     bool shutting_down = false;
+    bool announce = true;
     std::atomic<bool> stop_requested{false};
     std::vector<u8> token_map;                        // payload of the tokenMap reply
     std::map<u32, connection> clients;                // by client id
