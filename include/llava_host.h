@@ -150,6 +150,7 @@ uint32_t llava_server_port(void* server);
  * more sessions, and the tokens they produced */
 uint64_t llava_server_grouped_steps(void* server);
 uint64_t llava_server_grouped_tokens(void* server);
+uint64_t llava_server_steps_ahead(void* server);      /* grouped steps that were already queued when their sessions asked */
 void     llava_server_start(void* server);
 void     llava_server_stop(void* server);
 void     llava_server_destroy(void* server);

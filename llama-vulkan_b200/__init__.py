@@ -294,6 +294,7 @@ HOST_API = {
     "llava_server_port": (_u32, [_p]),
     "llava_server_grouped_steps": (_u64, [_p]),
     "llava_server_grouped_tokens": (_u64, [_p]),
+    "llava_server_steps_ahead": (_u64, [_p]),
     "llava_server_start": (None, [_p]),
     "llava_server_stop": (None, [_p]),
     "llava_server_destroy": (None, [_p]),
@@ -603,6 +604,10 @@ class Server:
     def grouped(self):
         """-> (rounds that stepped two or more sessions together, tokens those rounds produced)."""
         return self.lib.llava_server_grouped_steps(self.handle), self.lib.llava_server_grouped_tokens(self.handle)
+
+    def steps_ahead(self):
+        """Grouped steps that were already queued on the device when their sessions asked for them."""
+        return self.lib.llava_server_steps_ahead(self.handle)
 
     def close(self):
         if self.handle:

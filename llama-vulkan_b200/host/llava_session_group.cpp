@@ -53,6 +53,7 @@ llava_session_group::llava_session_group(llava_context* _ctx, vector<llava_sessi
 }
 
 llava_session_group::~llava_session_group() {
+    discard_ahead();
     drop_graph();
     if (pinned_tokens) lv_host_free(ctx->lv(), pinned_tokens);
     for (llava_buffer* b : {x, q, vout, ff, split, logits, scratch, tables, tokens_dev}) delete b;
@@ -175,6 +176,7 @@ bool llava_session_group::record(u32 backlog) {
 
 bool llava_session_group::step(vector<u32>* next_tokens) {
     if (!valid) return false;
+    discard_ahead();
     lock_guard<mutex> guard(ctx->queue_mutex);
     u32 backlog = 0;
     if (!prepare_members(&backlog) || !record(backlog)) return false;
@@ -190,8 +192,51 @@ bool llava_session_group::step(vector<u32>* next_tokens) {
     return true;
 }
 
+bool llava_session_group::can_step_ahead() const {
+    if (!valid || graph == nullptr || ahead) return false;
+    for (bool smp : sampled)
+        if (smp) return false;
+    for (llava_session* s : members)
+        if (s->token_buffer.size() + 2 > s->backlog_size) return false;       // the backlog is about to grow: re-record first
+    return true;
+}
+
+bool llava_session_group::launch_ahead() {
+    if (!can_step_ahead()) return false;
+    lock_guard<mutex> guard(ctx->queue_mutex);
+    if (lv_graph_launch(ctx->lv(), graph) != LV_OK) return false;
+    ahead = true;
+    return true;
+}
+
+bool llava_session_group::finish_ahead(vector<u32>* next_tokens) {
+    if (!ahead) return false;
+    lock_guard<mutex> guard(ctx->queue_mutex);
+    ahead = false;
+    if (lv_stream_sync(ctx->lv(), 0) != LV_OK) {
+        cerr << "[!] group step failed: " << lv_last_error_string() << endl;
+        for (llava_session* s : members) s->device_pos = ~0U;
+        return false;
+    }
+    for (llava_session* s : members) {
+        s->current_tokens_in_gpu += 1;
+        s->device_pos += 1;
+    }
+    if (next_tokens) next_tokens->assign(pinned_tokens, pinned_tokens + size());
+    return true;
+}
+
+void llava_session_group::discard_ahead() {
+    if (!ahead) return;
+    lock_guard<mutex> guard(ctx->queue_mutex);
+    ahead = false;
+    lv_stream_sync(ctx->lv(), 0);
+    for (llava_session* s : members) s->device_pos = ~0U;          // the device is one position further than the host's books
+}
+
 bool llava_session_group::generate_greedy_on_device(u32 n, vector<vector<u32>>* out) {
     if (!valid || n == 0) return false;
+    discard_ahead();
     for (llava_session* s : members) {
         // room for the n tokens in every member (llava_session::enqueue_greedy_on_device)
         u32 need = s->backlog_size;

@@ -36,6 +36,19 @@ public:
     // n steps in a row with no host round trip: every member's greedy token is fed back on the device
     // (out[i] receives member i's n tokens; they are appended to the members' token buffers).
     bool generate_greedy_on_device(u32 n, std::vector<std::vector<u32>>* out);
+    // Stepping ahead: the step after a successful step() needs nothing from the host when every member is going to push
+    // exactly the token it was given (the device fed it into the member's token log already).  launch_ahead() queues
+    // that step at once; finish_ahead() waits for it and books it to the members (call it once every member HAS pushed
+    // its token and holds it as the one pending token: the caller checks); discard_ahead() drops it when a member did
+    // something else: the members' device positions are marked unknown, so that their next evaluation uploads them again
+    // (the cache rows and log entries the dropped step wrote lie beyond the evaluated tokens and are overwritten later).
+    // Greedy members only (a sampler launch would advance the member's sampler state).
+    bool can_step_ahead() const;
+    bool launch_ahead();
+    bool finish_ahead(std::vector<u32>* next_tokens);
+    void discard_ahead();
+    bool ahead_in_flight() const { return ahead; }
+    const std::vector<llava_session*>& get_members() const { return members; }
     // logits of member i from the last step (vocab floats)
     bool get_logits(u32 member, std::vector<float>* out);
     u32 kernel_launches() const { return launches; }
@@ -57,6 +70,7 @@ private:
     lv_graph* graph = nullptr;
     u32 graph_backlog = 0;
     u32 launches = 0;
+    bool ahead = false;                      // a step queued by launch_ahead() has not been booked or dropped yet
 };
 
 #endif

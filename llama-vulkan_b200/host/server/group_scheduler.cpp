@@ -33,8 +33,23 @@ void group_scheduler::runner_leaves() {
     cv.notify_all();            // a leader may be waiting for a runner that will not come
 }
 
+void group_scheduler::settle_locked(llava_session* session) {
+    if (ahead_group == nullptr) return;
+    const auto& mem = ahead_group->get_members();
+    if (find(mem.begin(), mem.end(), session) == mem.end()) return;
+    ahead_group->discard_ahead();
+    ahead_group = nullptr;
+    given.clear();
+}
+
+void group_scheduler::settle(llava_session* session) {
+    lock_guard<mutex> lock(m);
+    settle_locked(session);
+}
+
 void group_scheduler::forget(llava_session* session) {
     lock_guard<mutex> lock(m);
+    settle_locked(session);
     for (auto it = groups.begin(); it != groups.end();) {
         if (find(it->first.begin(), it->first.end(), session) != it->first.end()) {
             delete it->second;
@@ -49,7 +64,10 @@ u32 group_scheduler::evaluate(llava_session* session) {
     // what a group step cannot serve goes through the session's own step
     const bool groupable = session->get_token_count() - session->get_tokens_in_gpu() == 1 && !session->samples_on_host() &&
                            !session->is_tracing_enabled() && ctx->tp_size() == 1;
-    if (!groupable) return session->predict_next_token();
+    if (!groupable) {
+        settle(session);
+        return session->predict_next_token();
+    }
     unique_lock<mutex> lock(m);
     waiting.push_back(session);
     cv.notify_all();                          // a leader that collects a round counts the callers
@@ -80,13 +98,54 @@ void group_scheduler::lead(unique_lock<mutex>& lock) {
         round.resize(llava_session::max_batch_limit);
     }
     vector<u32> tokens(round.size(), ~0U);
+    vector<llava_session*> key = round;
+    sort(key.begin(), key.end());
+    // a step queued ahead: booked if exactly its members came back, each having pushed the token it was handed
+    if (ahead_group != nullptr) {
+        bool same = key == ahead_group->get_members();
+        for (size_t i = 0; same && i < key.size(); ++i) {
+            const auto it = given.find(key[i]);
+            same = it != given.end() && key[i]->get_token_buffer().back() == it->second;
+        }
+        llava_session_group* g = ahead_group;
+        if (same) {
+            ahead_group = nullptr;                          // ours while the lock is released
+            lock.unlock();
+            vector<u32> by_key;
+            const bool ok = g->finish_ahead(&by_key);
+            if (ok) {
+                for (size_t i = 0; i < round.size(); ++i)
+                    tokens[i] = by_key[size_t(lower_bound(key.begin(), key.end(), round[i]) - key.begin())];
+                n_grouped_steps += 1;
+                n_grouped_tokens += round.size();
+                n_steps_ahead += 1;
+            }
+            const bool again = ok && g->launch_ahead();
+            lock.lock();
+            given.clear();
+            if (again) {
+                ahead_group = g;
+                for (size_t i = 0; i < key.size(); ++i) given[key[i]] = by_key[i];
+            }
+            if (ok) {
+                for (size_t i = 0; i < round.size(); ++i) results[round[i]] = tokens[i];
+                return;
+            }
+            // the queued step failed: the callers go through their own steps below
+        } else {
+            for (llava_session* s : round) settle_locked(s);
+            if (ahead_group != nullptr) {                  // another group's step: it would be stale by the time its callers return
+                ahead_group->discard_ahead();
+                ahead_group = nullptr;
+                given.clear();
+            }
+        }
+    }
     if (round.size() == 1) {
         lock.unlock();
         tokens[0] = round[0]->predict_next_token();
         lock.lock();
     } else {
-        vector<llava_session*> key = round;
-        sort(key.begin(), key.end());
         llava_session_group* g = nullptr;
         const auto it = groups.find(key);
         if (it != groups.end()) {
@@ -102,16 +161,23 @@ void group_scheduler::lead(unique_lock<mutex>& lock) {
         lock.unlock();
         vector<u32> by_key;
         const bool ok = g->is_valid() && g->step(&by_key);
+        bool queued = false;
         if (ok) {
             for (size_t i = 0; i < round.size(); ++i)
                 tokens[i] = by_key[size_t(lower_bound(key.begin(), key.end(), round[i]) - key.begin())];
             n_grouped_steps += 1;
             n_grouped_tokens += round.size();
+            queued = g->launch_ahead();                       // greedy members: the next step needs nothing from the host
         } else {
             // e.g. a model the batched products do not take: every caller falls back to its own step
             for (size_t i = 0; i < round.size(); ++i) tokens[i] = round[i]->predict_next_token();
         }
         lock.lock();
+        if (queued) {
+            ahead_group = g;
+            given.clear();
+            for (size_t i = 0; i < key.size(); ++i) given[key[i]] = by_key[i];
+        }
     }
     for (size_t i = 0; i < round.size(); ++i) results[round[i]] = tokens[i];
 }

@@ -34,14 +34,19 @@ public:
     void runner_leaves();
     // Evaluates the session's pending token(s) and returns its next token (~0U on failure).  Blocks.
     u32 evaluate(llava_session* session);
+    // The session is about to be used directly (a tick, an order that evaluates, the end of its running state): a step
+    // that the scheduler queued ahead for its group is dropped first, so that the device is where the session thinks it is.
+    void settle(llava_session* session);
     // The session is about to be destroyed: groups that contain it are dropped.
     void forget(llava_session* session);
 
     u64 grouped_steps() const { return n_grouped_steps; }        // steps that served two or more sessions
     u64 grouped_tokens() const { return n_grouped_tokens; }      // tokens those steps produced
+    u64 steps_ahead() const { return n_steps_ahead; }            // grouped steps that were already queued when their callers arrived
 
 private:
     void lead(std::unique_lock<std::mutex>& lock);
+    void settle_locked(llava_session* session);
 
     llava_context* const ctx;
     std::mutex m;
@@ -51,7 +56,11 @@ private:
     bool leader_present = false;
     u32 runners = 0;
     std::map<std::vector<llava_session*>, llava_session_group*> groups;     // by member list (sorted)
-    std::atomic<u64> n_grouped_steps{0}, n_grouped_tokens{0};
+    // After a grouped step of greedy members the next step of the same group is queued at once (the device fed every
+    // member its token); it is booked when the same callers come back having pushed exactly those tokens, else dropped.
+    llava_session_group* ahead_group = nullptr;
+    std::map<llava_session*, u32> given;                  // the token each member of ahead_group was handed last
+    std::atomic<u64> n_grouped_steps{0}, n_grouped_tokens{0}, n_steps_ahead{0};
 };
 
 }  // namespace lsrv

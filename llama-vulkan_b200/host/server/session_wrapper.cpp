@@ -53,8 +53,12 @@ void session_wrapper::run() {
     bool registered = false;                 // counted by the scheduler among the sessions that ask for token after token
     auto sync_registration = [&]() {
         if (sched == nullptr || registered == should_run) return;
-        if (should_run) sched->runner_enters();
-        else sched->runner_leaves();
+        if (should_run) {
+            sched->runner_enters();
+        } else {
+            sched->runner_leaves();
+            sched->settle(&session);         // a step queued ahead for this session's group is dropped
+        }
         registered = should_run;
     };
 
@@ -130,6 +134,16 @@ void session_wrapper::process_orders(llava_session& session, bool blocking) {
         orders.pop_front();
         ReturnCode rc = ReturnCode::ok;
         bool acknowledge = true;
+        // orders that change or read the session's device state: no step queued ahead for its group may be in flight
+        if (group_scheduler* sched = owner->scheduler()) {
+            switch (order.opcode) {
+                case cmdRewind: case cmdSetSessionOptions: case cmdAddToken: case cmdAddText: case cmdSaveFrame: case cmdSnapshot:
+                case cmdRestore: case cmdTick:
+                    sched->settle(&session);
+                    break;
+                default: break;
+            }
+        }
         switch (order.opcode) {
             case cmdStartSessionGeneration:
                 if (should_tick) rc = ReturnCode::tick_already_requested;

@@ -66,6 +66,7 @@ tlv_server::~tlv_server() {
 
 u64 tlv_server::grouped_steps() const { return sched ? sched->grouped_steps() : 0; }
 u64 tlv_server::grouped_tokens() const { return sched ? sched->grouped_tokens() : 0; }
+u64 tlv_server::steps_ahead() const { return sched ? sched->steps_ahead() : 0; }
 
 bool tlv_server::open() {
     listen_fd = ::socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);

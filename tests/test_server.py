@@ -176,7 +176,7 @@ def test_running_sessions_are_stepped_together(pkg, tiny_model):
         for t in p:
             orc.push(t)
         toks = []
-        for _ in range(n_tokens):
+        for _ in range(120):                    # the sessions run on while the test talks to the server
             orc.eval()
             toks.append(int(orc.argmax()))
             orc.push(toks[-1])
@@ -208,13 +208,44 @@ def test_running_sessions_are_stepped_together(pkg, tiny_model):
             assert op == c.NEW_TOKEN and rid == 0
             token, pos = struct.unpack("<II", data[4:])
             got[data[:4]].append((token, pos))
-        for sid in sids:
+        # one session stops; the other two go on (their group changes, a step queued ahead for the three is dropped)
+        stop_id = c.send(c.STOP, sids[0])
+        stopped_at = None
+        while stopped_at is None or any(len(got[sid]) < stopped_at + 6 for sid in sids[1:]):
+            op, rid, data = c.recv()
+            if rid == stop_id:
+                assert (op, data) == (c.ACK, ack(OK))
+                stopped_at = max(len(got[sid]) for sid in sids[1:])
+                continue
+            assert op == c.NEW_TOKEN and rid == 0
+            token, pos = struct.unpack("<II", data[4:])
+            got[data[:4]].append((token, pos))
+        n0 = len(got[sids[0]])
+        # the stopped session has not moved since, and a tick gives it its own next token at its own position
+        rid = c.send(c.TICK, sids[0])
+        while True:
+            op, r, data = c.recv()
+            if r == rid:
+                break
+            assert op == c.NEW_TOKEN and r == 0
+            if data[:4] != sids[0]:               # (the subscriber also gets the tick's token as a broadcast)
+                token, pos = struct.unpack("<II", data[4:])
+                got[data[:4]].append((token, pos))
+        assert op == c.NEW_TOKEN and data[:4] == sids[0]
+        token, pos = struct.unpack("<II", data[4:])
+        assert pos == len(prompts[0]) + n0
+        if n0 < len(want[0]):                     # (the oracle's trajectory is 120 tokens long)
+            assert token == want[0][n0]
+        for sid in sids[1:]:
             c.send(c.STOP, sid)
         for i, sid in enumerate(sids):
-            assert [t for t, _ in got[sid][:n_tokens]] == want[i]
-            assert [p for _, p in got[sid][:n_tokens]] == list(range(len(prompts[i]), len(prompts[i]) + n_tokens))
+            m = min(len(got[sid]), len(want[i]))
+            assert m >= n_tokens
+            assert [t for t, _ in got[sid][:m]] == want[i][:m]
+            assert [p for _, p in got[sid][:m]] == list(range(len(prompts[i]), len(prompts[i]) + m))
         steps, tokens = server.grouped()
         assert steps > 0 and tokens >= 2 * steps, (steps, tokens)
+        assert server.steps_ahead() > 0                       # greedy sessions: most shared steps were queued ahead
         c.close()
     ctx.set_exact_batched_products(False)
     ctx.close()
