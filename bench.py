@@ -584,7 +584,7 @@ def measure_concurrent_sessions(rig, ctx, name, args, counts=(4, 16, 64)):
 def measure_server_sessions(rig, ctx, args, counts=(1, 4, 16), seconds=1.5):
     """Tokens/s that clients of the TCP front end receive when k sessions generate at once (greedy, 32-token seeded prompts):
     the server's scheduler steps the running sessions together.  Counted from the newToken broadcasts that arrive on one
-    subscribed client connection over `seconds`, after half a second of warm-up."""
+    subscribed client connection over `seconds`, from the moment every session has delivered four tokens."""
     import struct
     pkg = rig.pkg
     out = {}
@@ -599,30 +599,34 @@ def measure_server_sessions(rig, ctx, args, counts=(1, 4, 16), seconds=1.5):
                     assert c.call(c.ADD_TOKEN, sid + struct.pack("<I", t))[0] == c.ACK
                 assert c.call(c.SUBSCRIBE, sid)[0] == c.ACK
                 sids.append(sid)
-            g0 = server.grouped()
             for sid in sids:
                 c.send(c.START, sid)
-            t_start = time.perf_counter()
+            # the window opens once every session has produced a few tokens (its prompt is ingested, the group has formed)
+            seen = {sid: 0 for sid in sids}
             t0, n = None, 0
             while True:
                 op, rid, data = c.recv()
-                now = time.perf_counter()
                 if op != c.NEW_TOKEN or rid != 0:
                     continue
                 if t0 is None:
-                    if now - t_start >= 0.5:
-                        t0 = now
+                    seen[data[:4]] += 1
+                    if min(seen.values()) >= 4:
+                        t0 = time.perf_counter()
+                        g0, a0, t0s = server.grouped(), server.steps_ahead(), server.scheduler_times()
                     continue
                 n += 1
-                if now - t0 >= seconds:
+                if time.perf_counter() - t0 >= seconds:
                     break
             elapsed = time.perf_counter() - t0
-            g1 = server.grouped()
+            g1, a1, t1s = server.grouped(), server.steps_ahead(), server.scheduler_times()
             for sid in sids:
                 c.call(c.KILL_SESSION, sid)
             c.close()
             steps, toks = g1[0] - g0[0], g1[1] - g0[1]
-            out[str(k)] = {"tokens_per_s": n / elapsed, "sessions_per_shared_step": (toks / steps) if steps else 1.0}
+            out[str(k)] = {"tokens_per_s": n / elapsed, "sessions_per_shared_step": (toks / steps) if steps else 1.0,
+                           "shared_steps_queued_ahead": ((a1 - a0) / steps) if steps else 0.0,
+                           "ms_per_round_waiting_for_sessions": ((t1s[0] - t0s[0]) / 1e3 / steps) if steps else None,
+                           "ms_per_round_waiting_for_device": ((t1s[1] - t0s[1]) / 1e3 / steps) if steps else None}
     return out
 
 

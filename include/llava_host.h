@@ -150,7 +150,10 @@ uint32_t llava_server_port(void* server);
  * more sessions, and the tokens they produced */
 uint64_t llava_server_grouped_steps(void* server);
 uint64_t llava_server_grouped_tokens(void* server);
-uint64_t llava_server_steps_ahead(void* server);      /* grouped steps that were already queued when their sessions asked */
+uint64_t llava_server_steps_ahead(void* server);
+/* microseconds the scheduler's rounds spent waiting for their callers to arrive / for the device */
+uint64_t llava_server_scheduler_collect_us(void* server);
+uint64_t llava_server_scheduler_device_us(void* server);      /* grouped steps that were already queued when their sessions asked */
 void     llava_server_start(void* server);
 void     llava_server_stop(void* server);
 void     llava_server_destroy(void* server);

@@ -295,6 +295,8 @@ HOST_API = {
     "llava_server_grouped_steps": (_u64, [_p]),
     "llava_server_grouped_tokens": (_u64, [_p]),
     "llava_server_steps_ahead": (_u64, [_p]),
+    "llava_server_scheduler_collect_us": (_u64, [_p]),
+    "llava_server_scheduler_device_us": (_u64, [_p]),
     "llava_server_start": (None, [_p]),
     "llava_server_stop": (None, [_p]),
     "llava_server_destroy": (None, [_p]),
@@ -604,6 +606,10 @@ class Server:
     def grouped(self):
         """-> (rounds that stepped two or more sessions together, tokens those rounds produced)."""
         return self.lib.llava_server_grouped_steps(self.handle), self.lib.llava_server_grouped_tokens(self.handle)
+
+    def scheduler_times(self):
+        """-> (microseconds the scheduler's rounds waited for their callers, microseconds they waited for the device)."""
+        return self.lib.llava_server_scheduler_collect_us(self.handle), self.lib.llava_server_scheduler_device_us(self.handle)
 
     def steps_ahead(self):
         """Grouped steps that were already queued on the device when their sessions asked for them."""

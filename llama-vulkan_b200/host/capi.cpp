@@ -385,6 +385,8 @@ void* llava_server_create(void* ctx, uint32_t port, const char* bind_address, in
 }
 uint32_t llava_server_port(void* server) { return static_cast<served*>(server)->server.port(); }
 uint64_t llava_server_grouped_steps(void* server) { return static_cast<served*>(server)->server.grouped_steps(); }
+uint64_t llava_server_scheduler_collect_us(void* server) { return static_cast<served*>(server)->server.scheduler_collect_us(); }
+uint64_t llava_server_scheduler_device_us(void* server) { return static_cast<served*>(server)->server.scheduler_device_us(); }
 uint64_t llava_server_steps_ahead(void* server) { return static_cast<served*>(server)->server.steps_ahead(); }
 uint64_t llava_server_grouped_tokens(void* server) { return static_cast<served*>(server)->server.grouped_tokens(); }
 void llava_server_start(void* server) {

@@ -30,7 +30,7 @@ void group_scheduler::runner_leaves() {
         lock_guard<mutex> lock(m);
         if (runners) --runners;
     }
-    cv.notify_all();            // a leader may be waiting for a runner that will not come
+    cv_leader.notify_one();     // a leader may be waiting for a runner that will not come
 }
 
 void group_scheduler::settle_locked(llava_session* session) {
@@ -70,16 +70,16 @@ u32 group_scheduler::evaluate(llava_session* session) {
     }
     unique_lock<mutex> lock(m);
     waiting.push_back(session);
-    cv.notify_all();                          // a leader that collects a round counts the callers
+    cv_leader.notify_one();                   // a leader that collects a round counts the callers
     while (results.count(session) == 0) {
         if (!leader_present) {
             // whoever finds no leader leads the next round (it is one of the waiting callers itself)
             leader_present = true;
             lead(lock);                       // collects the round, runs it, publishes the results
             leader_present = false;
-            cv.notify_all();
+            cv_results.notify_all();          // once per round: the callers pick up their tokens, one of the others may lead
         } else {
-            cv.wait(lock);
+            cv_results.wait(lock);
         }
     }
     const u32 token = results[session];
@@ -89,8 +89,16 @@ u32 group_scheduler::evaluate(llava_session* session) {
 
 // Called with the lock held by the first caller of a round.
 void group_scheduler::lead(unique_lock<mutex>& lock) {
-    const auto deadline = chrono::steady_clock::now() + kWindow;
-    cv.wait_until(lock, deadline, [&]() { return waiting.size() >= max<u32>(runners, 1u) || waiting.size() >= llava_session::max_batch_limit; });
+    const auto t_begin = chrono::steady_clock::now();
+    const auto deadline = t_begin + kWindow;
+    cv_leader.wait_until(lock, deadline, [&]() { return waiting.size() >= max<u32>(runners, 1u) || waiting.size() >= llava_session::max_batch_limit; });
+    const auto t_collected = chrono::steady_clock::now();
+    us_collect += u64(chrono::duration_cast<chrono::microseconds>(t_collected - t_begin).count());
+    struct device_timer {
+        std::atomic<u64>& sum;
+        chrono::steady_clock::time_point t0;
+        ~device_timer() { sum += u64(chrono::duration_cast<chrono::microseconds>(chrono::steady_clock::now() - t0).count()); }
+    } timer{us_device, t_collected};
     vector<llava_session*> round;
     round.swap(waiting);
     if (round.size() > llava_session::max_batch_limit) {          // the rest forms the next round

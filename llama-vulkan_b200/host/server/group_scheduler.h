@@ -42,7 +42,11 @@ public:
 
     u64 grouped_steps() const { return n_grouped_steps; }        // steps that served two or more sessions
     u64 grouped_tokens() const { return n_grouped_tokens; }      // tokens those steps produced
-    u64 steps_ahead() const { return n_steps_ahead; }            // grouped steps that were already queued when their callers arrived
+    u64 steps_ahead() const { return n_steps_ahead; }
+    // where the rounds' time went, in microseconds since the scheduler was made: waiting for the callers of a round to
+    // arrive, and waiting for the device (the step itself, or the rest of a step that was queued ahead)
+    u64 collect_us() const { return us_collect; }
+    u64 device_us() const { return us_device; }            // grouped steps that were already queued when their callers arrived
 
 private:
     void lead(std::unique_lock<std::mutex>& lock);
@@ -50,7 +54,8 @@ private:
 
     llava_context* const ctx;
     std::mutex m;
-    std::condition_variable cv;
+    std::condition_variable cv_leader;                    // an arrival, or a runner that left: only the collecting leader waits here
+    std::condition_variable cv_results;                   // a round's results are out (or the leadership is free)
     std::vector<llava_session*> waiting;                  // callers of the round being collected
     std::map<llava_session*, u32> results;                // tokens of finished rounds, picked up by their callers
     bool leader_present = false;
@@ -60,7 +65,7 @@ private:
     // member its token); it is booked when the same callers come back having pushed exactly those tokens, else dropped.
     llava_session_group* ahead_group = nullptr;
     std::map<llava_session*, u32> given;                  // the token each member of ahead_group was handed last
-    std::atomic<u64> n_grouped_steps{0}, n_grouped_tokens{0}, n_steps_ahead{0};
+    std::atomic<u64> n_grouped_steps{0}, n_grouped_tokens{0}, n_steps_ahead{0}, us_collect{0}, us_device{0};
 };
 
 }  // namespace lsrv

@@ -66,6 +66,8 @@ tlv_server::~tlv_server() {
 
 u64 tlv_server::grouped_steps() const { return sched ? sched->grouped_steps() : 0; }
 u64 tlv_server::grouped_tokens() const { return sched ? sched->grouped_tokens() : 0; }
+u64 tlv_server::scheduler_collect_us() const { return sched ? sched->collect_us() : 0; }
+u64 tlv_server::scheduler_device_us() const { return sched ? sched->device_us() : 0; }
 u64 tlv_server::steps_ahead() const { return sched ? sched->steps_ahead() : 0; }
 
 bool tlv_server::open() {

@@ -45,7 +45,9 @@ public:
     // steps that served two or more sessions at once, and the tokens they produced
     u64 grouped_steps() const;
     u64 grouped_tokens() const;
-    u64 steps_ahead() const;         // of those steps, the ones that were already queued when their sessions asked
+    u64 steps_ahead() const;
+    u64 scheduler_collect_us() const;   // time the scheduler's rounds waited for their callers / for the device
+    u64 scheduler_device_us() const;         // of those steps, the ones that were already queued when their sessions asked
     void receive_session_outbound_packets(std::list<outbound_packet>& packets, std::list<outbound_broadcast>& broadcasts) override;
     void notify_session_death(u32 session_id) override;
 
