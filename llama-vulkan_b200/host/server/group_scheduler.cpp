@@ -160,6 +160,10 @@ void group_scheduler::lead(unique_lock<mutex>& lock) {
             g = it->second;
         } else {
             if (groups.size() >= kCachedGroups) {             // membership changes rarely; keep the table small
+                if (groups.begin()->second == ahead_group) {  // (its destructor drops the step it has queued)
+                    ahead_group = nullptr;
+                    given.clear();
+                }
                 delete groups.begin()->second;
                 groups.erase(groups.begin());
             }
