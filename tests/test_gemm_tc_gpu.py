@@ -228,3 +228,57 @@ def test_shared_memory_form_of_the_fast_tiles_in_a_child_process():
                        env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, timeout=900)
     tail = r.stdout.decode(errors="replace")[-600:]
     assert r.returncode == 0 and " passed" in tail, tail
+
+
+def test_act_split_padded_pads_the_shard_columns_with_zeros(gpu, pkg):
+    """lv_act_split_f16_padded: dense rows of cols_used values against a matrix of cols >= cols_used columns (the padded
+    column shard of wo / w2 on a tensor-parallel rank)."""
+    rng = np.random.default_rng(60)
+    batch, used, cols = 7, 640, 768                        # a 13B head slice at 8 ranks: 20 blocks padded to 24
+    x = rng.standard_normal((batch, used)).astype(np.float32)
+    xh = gpu.alloc(gpu.lib.lv_act_split_bytes(cols, batch))
+    pkg.check(gpu.lib.lv_act_split_f16_padded(gpu.handle, xh, gpu.upload(x), None, used, cols, batch))
+    gpu.sync()
+    hi, lo = planes_of(gpu.download(xh, np.float16, 2 * 16 * cols), 16, cols)
+    assert np.array_equal(hi[:batch, :used].astype(np.float16), x.astype(np.float16))
+    assert np.abs(hi[:batch, :used] + lo[:batch, :used] - x).max() <= 2.0 ** -21 * np.abs(x).max()
+    assert not hi[:, used:].any() and not lo[:, used:].any() and not hi[batch:].any()
+    assert gpu.lib.lv_act_split_f16_padded(gpu.handle, xh, gpu.upload(x), None, 644, cols, batch) == pkg.LV_ERR_BAD_ARGUMENTS
+    assert gpu.lib.lv_act_split_f16_padded(gpu.handle, xh, gpu.upload(x), None, 800, cols, batch) == pkg.LV_ERR_BAD_ARGUMENTS
+
+
+@pytest.mark.parametrize("rows,cols,used,batch", [(5120, 768, 640, 64), (5120, 1792, 1728, 40), (4096, 1536, 1376, 16), (640, 5120, 5120, 64)],
+                         ids=["13b-wo-shard-of-8", "13b-w2-shard-of-8", "7b-w2-shard-of-8", "13b-wq-shard-of-8"])
+def test_gemm_tc_on_the_shard_shapes_of_eight_ranks(gpu, pkg, rows, cols, used, batch, form):
+    """The matrices a rank of 8 holds (few groups of K, padded columns): the product with the padded activation split
+    against the oracle on the unpadded data."""
+    rng = np.random.default_rng(61)
+    W_used = (rng.standard_normal((rows, used)) * 0.02).astype(np.float32)
+    W = np.zeros((rows, cols), np.float32)
+    W[:, :used] = W_used
+    Wq = qn.quantize(W, qn.Q4_0)
+    x = rng.standard_normal((batch, used)).astype(np.float32)
+    xh = gpu.alloc(gpu.lib.lv_act_split_bytes(cols, batch))
+    pkg.check(gpu.lib.lv_act_split_f16_padded(gpu.handle, xh, gpu.upload(x), None, used, cols, batch))
+    out = gpu.zeros(batch * rows * 4)
+    pkg.check(gpu.lib.lv_gemm_tc(gpu.handle, out, gpu.upload(Wq), qn.Q4_0, xh, rows, cols, batch, 0))
+    gpu.sync()
+    xp = np.zeros((batch, cols), np.float32)
+    xp[:, :used] = x
+    want = np.stack([ob.gemv(Wq, qn.Q4_0, xp[z], rows, cols, 128) for z in range(0, batch, 5)])
+    close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows)[::5], want, **loose(form, qn.Q4_0))
+
+
+def test_gemm_tc_silu_pair_on_the_13b_shard_of_eight_ranks(gpu, pkg, form):
+    rng = np.random.default_rng(62)
+    ff, dim, batch = 1728, 5120, 64
+    w3, w1 = matrix(rng, ff, dim), matrix(rng, ff, dim)
+    x = rng.standard_normal((batch, dim)).astype(np.float32)
+    nw = (1 + 0.05 * rng.standard_normal(dim)).astype(np.float32)
+    xh = split(gpu, pkg, x, nw)
+    out = gpu.zeros(batch * ff * 4)
+    pkg.check(gpu.lib.lv_gemm_tc_silu(gpu.handle, out, gpu.upload(w3), gpu.upload(w1), qn.Q4_0, xh, ff, dim, batch))
+    gpu.sync()
+    got = gpu.download(out, np.float32, batch * ff).reshape(batch, ff)
+    for z in range(0, batch, 13):
+        close(got[z], ob.gemv_silu(w3, w1, qn.Q4_0, ob.norm(x[z], nw), ff, dim, workers_for(dim)), **loose(form, qn.Q4_0))
