@@ -204,10 +204,22 @@ __device__ __forceinline__ void dequant_word_q8(uint32_t w, __half2 d2, __half2 
     }
 }
 
+// Four int8 of one word -> fp16(q * d): out[0] = elements (4k, 4k+1), out[1] = (4k+2, 4k+3).
+__device__ __forceinline__ void dequant_word_q8_hi(uint32_t w, __half2 d2, uint32_t (&out)[2]) {
+    const uint32_t u = w ^ 0x80808080u;                                       // q + 128 as unsigned bytes
+    const uint32_t raw[2] = {__byte_perm(u, 0x64646464u, 0x4140), __byte_perm(u, 0x64646464u, 0x4342)};   // 1024 + 128 + q
+    const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&raw[i]), off), d2);
+        out[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
 template <int QT, int FORM>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcParams p, const __grid_constant__ GemmTcMaps maps) {
     constexpr bool FAST = FORM != 0, TMEMA = FORM == 2;
-    static_assert(!FAST || QT == T_Q4_0, "the fast forms exist for q4_0 only");
+    static_assert(FORM != 1 || QT == T_Q4_0, "the shared-memory fast form exists for q4_0 only");
     pdl_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte alignment
@@ -432,55 +444,72 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
                 const int rs = int(g % kTcRawStages);
                 ok = mbar_wait(&raw_full[rs], (g / kTcRawStages) & 1u, p.err);
                 if (!ok) break;
-                // the 36 bytes of the tile start at byte 36 t of the 144-byte raw row: three 16-byte loads from the chunk
-                // that holds the first byte (rows are 9 chunks apart, so a quarter warp's loads fall into different banks)
-                uint32_t L[12];
+                // the tile's two blocks (36 / 68 bytes) start at byte 36 t / 68 t of the raw row: 16-byte loads from the chunk
+                // that holds the first byte (rows are 9 / 17 chunks apart, so a quarter warp's loads fall into different
+                // banks); the tile then starts t words into the loaded words
+                constexpr int kTileWordsQ = kRawRowBytes / 16;                 // words of a tile: 9 / 17
+                constexpr int kLoadChunks = (kTileWordsQ + 3 + 3) / 4;          // 3 / 5
+                uint32_t L[4 * kLoadChunks];
                 {
-                    const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kRawStage + tr_row * kRawRowBytes) + 2u * tt;
+                    const uint4* src = reinterpret_cast<const uint4*>(rawring + rs * kRawStage + tr_row * kRawRowBytes) +
+                                       (QT == T_Q4_0 ? 2u : 4u) * tt;
 #pragma unroll
-                    for (int i = 0; i < 3; ++i) {
+                    for (int i = 0; i < kLoadChunks; ++i) {
                         const uint4 v = src[i];
                         L[4 * i] = v.x; L[4 * i + 1] = v.y; L[4 * i + 2] = v.z; L[4 * i + 3] = v.w;
                     }
                 }
-                uint32_t w[9];
-                switch (tt) {                      // 36 t mod 16 = 4 t bytes into the first chunk (t is the same for the whole warp)
+                uint32_t w[kTileWordsQ];
+                switch (tt) {                      // (t is the same for the whole warp)
                     case 0:
 #pragma unroll
-                        for (int i = 0; i < 9; ++i) w[i] = L[i];
+                        for (int i = 0; i < kTileWordsQ; ++i) w[i] = L[i];
                         break;
                     case 1:
 #pragma unroll
-                        for (int i = 0; i < 9; ++i) w[i] = L[i + 1];
+                        for (int i = 0; i < kTileWordsQ; ++i) w[i] = L[i + 1];
                         break;
                     case 2:
 #pragma unroll
-                        for (int i = 0; i < 9; ++i) w[i] = L[i + 2];
+                        for (int i = 0; i < kTileWordsQ; ++i) w[i] = L[i + 2];
                         break;
                     default:
 #pragma unroll
-                        for (int i = 0; i < 9; ++i) w[i] = L[i + 3];
+                        for (int i = 0; i < kTileWordsQ; ++i) w[i] = L[i + 3];
                         break;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&raw_empty[rs]);
                 // registers of the row: column j of the tile = elements 2j, 2j + 1 (block 0: columns 0..15, block 1: 16..31)
                 uint32_t cols[32];
+                constexpr int kQW = (kTileWordsQ - 1) / 2;                      // payload words of a block: 4 / 8
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
-                    uint32_t q[4];
+                    // block 0: scale in the low half of word 0, payload shifted by two bytes; block 1: scale in the high half
+                    // of the middle word, payload word-aligned
+                    uint32_t q[kQW];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) q[k] = b == 0 ? __funnelshift_r(w[k], w[k + 1], 16) : w[5 + k];
-                    const uint32_t dbits = b == 0 ? (w[0] & 0xffffu) : (w[4] >> 16);
+                    for (int k = 0; k < kQW; ++k) q[k] = b == 0 ? __funnelshift_r(w[k], w[k + 1], 16) : w[kQW + 1 + k];
+                    const uint32_t dbits = b == 0 ? (w[0] & 0xffffu) : (w[kQW] >> 16);
                     const __half2 d2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(dbits)));
+                    if constexpr (QT == T_Q4_0) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint32_t hi[4];
-                        dequant_word_hi(q[k], d2, hi);          // (4k, 4k+1), (4k+2, 4k+3), (16+4k, 17+4k), (18+4k, 19+4k)
-                        cols[16 * b + 2 * k] = hi[0];
-                        cols[16 * b + 2 * k + 1] = hi[1];
-                        cols[16 * b + 8 + 2 * k] = hi[2];
-                        cols[16 * b + 8 + 2 * k + 1] = hi[3];
+                        for (int k = 0; k < 4; ++k) {
+                            uint32_t hi[4];
+                            dequant_word_hi(q[k], d2, hi);          // (4k, 4k+1), (4k+2, 4k+3), (16+4k, 17+4k), (18+4k, 19+4k)
+                            cols[16 * b + 2 * k] = hi[0];
+                            cols[16 * b + 2 * k + 1] = hi[1];
+                            cols[16 * b + 8 + 2 * k] = hi[2];
+                            cols[16 * b + 8 + 2 * k + 1] = hi[3];
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            uint32_t hi[2];
+                            dequant_word_q8_hi(q[k], d2, hi);       // int8 payload in element order: (4k, 4k+1), (4k+2, 4k+3)
+                            cols[16 * b + 2 * k] = hi[0];
+                            cols[16 * b + 2 * k + 1] = hi[1];
+                        }
                     }
                 }
                 const uint32_t ab = g % kTcFastBufs;
@@ -889,6 +918,9 @@ int gemm_tc_configure(lv_ctx* ctx) {
     constexpr size_t kTmemSmem = tc_smem_bytes<T_Q4_0, 2>();
     LV_REQUIRE(size_t(ctx->max_smem_optin) >= kTmemSmem, "device has too little shared memory for the batched product");
     LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q4_0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTmemSmem))));
+    constexpr size_t kTmemSmem8 = tc_smem_bytes<T_Q8_0, 2>();
+    LV_REQUIRE(size_t(ctx->max_smem_optin) >= kTmemSmem8, "device has too little shared memory for the batched product");
+    LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kTmemSmem8))));
     LV_CUDA((cudaFuncSetAttribute(gemm_tc_kernel<T_Q8_0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc_smem_bytes<T_Q8_0>()))));
     const char* exact = getenv("LV_GEMM_TC_EXACT");
     ctx->tc_exact = exact != nullptr && exact[0] == '1';
@@ -918,7 +950,7 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
     }
     p.xh = xh;
     const uint32_t groups_all = p.K / (4 * kTcChunkK);
-    const bool fast = QT == T_Q4_0 && !ctx->tc_exact;
+    const bool fast = !ctx->tc_exact;
     uint32_t splits = 1;
     auto fits = [&](uint32_t s) {
         return groups_all / s >= 2 && tiles <= kTcMaxTiles && size_t(tiles) * s * p.zpad * kTcRows * sizeof(float) <= kTcScratchBytes;
@@ -942,18 +974,18 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
     p.scratch = static_cast<float*>(ctx->tc_scratch);
     p.counters = static_cast<uint32_t*>(ctx->tc_counters);
     tiles *= splits;
-    if constexpr (QT == T_Q4_0) {
-        if (fast) {
-            static const char* smem_tiles = getenv("LV_GEMM_TC_SMEM_TILES");
+    if (fast) {
+        static const char* smem_tiles = getenv("LV_GEMM_TC_SMEM_TILES");
+        if constexpr (QT == T_Q4_0) {
             if (smem_tiles != nullptr && smem_tiles[0] == '1') {
                 constexpr size_t kFastSmem = tc_smem_bytes<T_Q4_0, 1>();
                 LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, 1>, dim3(tiles), dim3(kTcThreads), kFastSmem, p, maps)));
-            } else {
-                constexpr size_t kTmemSmem = tc_smem_bytes<T_Q4_0, 2>();
-                LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<T_Q4_0, 2>, dim3(tiles), dim3(kTcThreads), kTmemSmem, p, maps)));
+                return LV_OK;
             }
-            return LV_OK;
         }
+        constexpr size_t kTmemSmem = tc_smem_bytes<QT, 2>();
+        LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<QT, 2>, dim3(tiles), dim3(kTcThreads), kTmemSmem, p, maps)));
+        return LV_OK;
     }
     LV_CUDA((launch_pdl(ctx, gemm_tc_kernel<QT, 0>, dim3(tiles), dim3(kTcThreads), tc_smem_bytes<QT>(), p, maps)));
     return LV_OK;

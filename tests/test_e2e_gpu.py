@@ -94,7 +94,7 @@ def same_choice(tok, got_logits, want_logits):
 
 @pytest.fixture(params=["exact", "fast"])
 def tc_form(request, run):
-    """Form of the batched q4_0 products for the sessions a test creates (q8_0 models always use the exact form)."""
+    """Form of the batched products for the sessions a test creates."""
     run["ctx"].set_exact_batched_products(request.param == "exact")
     yield request.param
     run["ctx"].set_exact_batched_products(False)
@@ -196,7 +196,7 @@ def test_prompt_as_one_batch_on_the_tensor_cores(run, tc_form):
     assert s.set_max_batch(16)
     for t in run["prompt"]:
         assert s.push_token(t)
-    rel_l2 = FAST_PROMPT_REL_L2 if (tc_form == "fast" and run["wtype"] == qn.Q4_0) else LOGIT_REL_L2
+    rel_l2 = FAST_PROMPT_REL_L2 if tc_form == "fast" else LOGIT_REL_L2
     tok = s.predict_next_token()
     m, r = assert_logits_close(s.logits(run["vocab"]), run["logits"][0], rel_l2)
     assert same_choice(tok, s.logits(run["vocab"]), run["logits"][0])
@@ -235,7 +235,7 @@ def test_long_prompt_in_tensor_core_batches_over_a_filled_cache(run, n_tokens, m
     for t in toks:
         assert s.push_token(t)
     tok = s.predict_next_token()
-    m, r = assert_logits_close(s.logits(run["vocab"]), want, FAST_PROMPT_REL_L2 if (tc_form == "fast" and run["wtype"] == qn.Q4_0) else LOGIT_REL_L2)
+    m, r = assert_logits_close(s.logits(run["vocab"]), want, FAST_PROMPT_REL_L2 if tc_form == "fast" else LOGIT_REL_L2)
     assert same_choice(tok, s.logits(run["vocab"]), want)
     if tc_form == "exact":
         assert tok == orc.argmax()
