@@ -234,13 +234,13 @@ int lv_argmax_advance_group(lv_ctx* ctx, const float* logits, uint32_t vocab, co
  * lv_act_split_f16 writes.  rows: multiple of 128 (64 for the SiLU pair);
  * cols: multiple of 256; batch 1..64; wtype q4_0 (2) or q8_0 (8).
  *
- * q4_0 matrices have two forms of the weight tiles.  The default writes one
- * fp16 plane, fp16((q - 8) * d): the weight is rounded to 11 significant bits
+ * There are two forms of the weight tiles.  The default writes one fp16 plane,
+ * fp16((q - 8) * d) or fp16(q * d): the weight is rounded to 11 significant bits
  * (relative error <= 2^-12 per weight; the activations keep 22 bits), which is
  * what the stated logits tolerance allows and a third of the tensor-core and
  * shared-memory work.  lv_gemm_tc_set_exact(ctx, 1) (or LV_GEMM_TC_EXACT=1 in
  * the environment when the context is made) selects the exact (hi, lo) pair for
- * parity-checked runs; q8_0 always uses the exact pair. */
+ * parity-checked runs. */
 int lv_gemm_tc_set_exact(lv_ctx* ctx, int exact);
 
 /* Bytes of the split-activation buffer for [batch][cols] inputs. */

@@ -26,10 +26,10 @@
 // in a scratch buffer; the last to arrive adds them in split order (deterministic) and applies
 // the epilogue.
 //
-// Three forms of the A operand (template parameter FORM; 1 and 2 for q4_0 only):
+// Three forms of the A operand (template parameter FORM; 1 for q4_0 only):
 //   exact (FORM = 0)      the hi/lo pair described above, one 64-column tile per producer step;
-//   fast  (FORM = 1, 2)   hi = fp16((q - 8) * d) alone: a weight is rounded to 11 significant bits (relative error
-//                         <= 2^-12, none for q - 8 in {0, +-1, +-2, +-4, -8}); the activations keep both planes.
+//   fast  (FORM = 1, 2)   hi = fp16(w) alone: a weight is rounded to 11 significant bits (relative error <= 2^-12, none
+//                         for q4_0 weights with q - 8 in {0, +-1, +-2, +-4, -8}); the activations keep both planes.
 //                         One producer step covers four tiles of K (a whole raw stage): a warp handles 8 rows x 4 tiles,
 //                         so that its 32-bit loads of the 144-byte raw rows and its 16-byte tile stores are free of bank
 //                         conflicts, a thread dequantises the two blocks of one tile of one row, and one MMA per K step
