@@ -188,9 +188,8 @@ def test_prompt_in_batches_matches_token_by_token(run):
 
 
 def test_prompt_as_one_batch_on_the_tensor_cores(run, tc_form):
-    """16 prompt tokens in one recorded step: q4_0 models take the tcgen05 path (lv_gemm_tc*), q8_0
-    models the per-token GEMV; either way the logits, the greedy token and the cache rows agree
-    with the oracle's token-by-token evaluation."""
+    """16 prompt tokens in one recorded step on the tcgen05 path (lv_gemm_tc*), q4_0 and q8_0 models, both forms of
+    the weight tiles: the logits, the greedy token and the cache rows agree with the oracle's token-by-token evaluation."""
     s = run["ctx"].session()
     s.set_deterministic(True)
     assert s.set_max_batch(16)
