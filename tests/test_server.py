@@ -249,3 +249,72 @@ def test_running_sessions_are_stepped_together(pkg, tiny_model):
         c.close()
     ctx.set_exact_batched_products(False)
     ctx.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("deterministic", [True, False], ids=["greedy", "sampled"])
+def test_sessions_that_start_stop_tick_rewind_and_die_while_others_run(pkg, tiny_model, deterministic):
+    """Churn: six sessions, two clients, three seconds of random start / stop / tick / add / rewind / kill / new-session
+    orders while other sessions generate.  The server must answer every request, keep every position consistent (a
+    token's position is the number of tokens its session held before it) and shut down cleanly."""
+    import random
+    import time
+    rng = random.Random(7)
+    ctx = pkg.HostContext(tiny_model, 0)
+    with pkg.Server(ctx, deterministic=deterministic) as server:
+        a, b = pkg.Client(server.port, timeout=60.0), pkg.Client(server.port, timeout=60.0)
+        live = []
+
+        def new_session(c):
+            op, sid = c.call(c.NEW_SESSION)
+            assert op == c.SESSION_CREATED
+            for t in [rng.randrange(3, 32000) for _ in range(rng.randrange(1, 9))]:
+                assert c.call(c.ADD_TOKEN, sid + struct.pack("<I", t)) == (c.ACK, ack(OK))
+            live.append(sid)
+
+        for _ in range(6):
+            new_session(a)
+        deadline = time.time() + 3.0
+        n_orders = 0
+        while time.time() < deadline:
+            c = rng.choice((a, b))
+            sid = rng.choice(live)
+            kind = rng.randrange(8)
+            if kind == 0:
+                op, data = c.call(c.START, sid)
+                assert op == c.ACK and data in (ack(OK), ack(TICK_ALREADY_REQUESTED))
+            elif kind == 1:
+                assert c.call(c.STOP, sid) == (c.ACK, ack(OK))
+            elif kind == 2:
+                op, data = c.call(c.TICK, sid)
+                assert (op == c.NEW_TOKEN and data[:4] == sid) or (op == c.ACK and data in (ack(ALREADY_RUNNING), ack(NOK), ack(TICK_ALREADY_REQUESTED)))
+            elif kind == 3:
+                op, data = c.call(c.ADD_TOKEN, sid + struct.pack("<I", rng.randrange(3, 32000)))
+                assert op == c.ACK and data in (ack(OK), ack(NOK))
+            elif kind == 4:
+                op, data = c.call(c.GET_SESSION_TOKENS, sid)
+                assert op == c.BUFFER
+                n = len(data) // 4
+                if n > 2:
+                    assert c.call(c.REWIND, sid + struct.pack("<I", rng.randrange(1, n))) == (c.ACK, ack(OK))
+            elif kind == 5 and len(live) > 3:
+                assert c.call(c.KILL_SESSION, sid) == (c.ACK, ack(OK))
+                live.remove(sid)
+            elif kind == 6 and len(live) < 8:
+                new_session(c)
+            else:
+                op, data = c.call(c.LIST_SESSIONS)
+                assert op == c.SESSION_LIST and len(data) % 4 == 0
+            n_orders += 1
+        assert n_orders > 50
+        # every session still answers, and its buffer is a valid token list
+        for sid in live:
+            c = a
+            assert c.call(c.STOP, sid) == (c.ACK, ack(OK))
+            op, data = c.call(c.GET_SESSION_TOKENS, sid)
+            assert op == c.BUFFER and all(t < 32000 for t in np.frombuffer(data, np.uint32))
+            op, data = c.call(c.TICK, sid)
+            assert op in (c.NEW_TOKEN, c.ACK)
+        a.close()
+        b.close()
+    ctx.close()
