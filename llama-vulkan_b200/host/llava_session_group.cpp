@@ -45,6 +45,7 @@ llava_session_group::llava_session_group(llava_context* _ctx, vector<llava_sessi
     scratch = new llava_buffer(ctx, F, u32((scratch_bytes + 3) / 4), 1, memory, "group_attention_scratch");
     tables = new llava_buffer(ctx, F, u32(size_t(n_layers) * k * sizeof(lv_group_member) / 4), 1, memory, "group_members");
     tokens_dev = new llava_buffer(ctx, F, k, 1, memory, "group_tokens");
+    sampler_backup = new llava_buffer(ctx, F, 4 * k, 1, memory, "group_sampler_backup");
     if (!memory->freeze() || !memory->zero(0, memory->get_size())) return;
     void* p = nullptr;
     if (lv_host_alloc(ctx->lv(), size_t(k) * 4, &p) != LV_OK) return;
@@ -56,7 +57,7 @@ llava_session_group::~llava_session_group() {
     discard_ahead();
     drop_graph();
     if (pinned_tokens) lv_host_free(ctx->lv(), pinned_tokens);
-    for (llava_buffer* b : {x, q, vout, ff, split, logits, scratch, tables, tokens_dev}) delete b;
+    for (llava_buffer* b : {x, q, vout, ff, split, logits, scratch, tables, tokens_dev, sampler_backup}) delete b;
     delete memory;
 }
 
@@ -194,8 +195,6 @@ bool llava_session_group::step(vector<u32>* next_tokens) {
 
 bool llava_session_group::can_step_ahead() const {
     if (!valid || graph == nullptr || ahead) return false;
-    for (bool smp : sampled)
-        if (smp) return false;
     for (llava_session* s : members)
         if (s->token_buffer.size() + 2 > s->backlog_size) return false;       // the backlog is about to grow: re-record first
     return true;
@@ -204,6 +203,11 @@ bool llava_session_group::can_step_ahead() const {
 bool llava_session_group::launch_ahead() {
     if (!can_step_ahead()) return false;
     lock_guard<mutex> guard(ctx->queue_mutex);
+    // a member that samples: its sampler state {mu, seed, draws} is kept, so that a dropped step leaves no trace in it
+    for (u32 i = 0; i < size(); ++i)
+        if (sampled[i] && lv_copy_d2d(ctx->lv(), static_cast<u8*>(sampler_backup->device_ptr()) + 16 * size_t(i),
+                                      members[i]->sampler_state->device_ptr(), 16) != LV_OK)
+            return false;
     if (lv_graph_launch(ctx->lv(), graph) != LV_OK) return false;
     ahead = true;
     return true;
@@ -230,6 +234,9 @@ void llava_session_group::discard_ahead() {
     if (!ahead) return;
     lock_guard<mutex> guard(ctx->queue_mutex);
     ahead = false;
+    for (u32 i = 0; i < size(); ++i)
+        if (sampled[i]) lv_copy_d2d(ctx->lv(), members[i]->sampler_state->device_ptr(),
+                                    static_cast<const u8*>(sampler_backup->device_ptr()) + 16 * size_t(i), 16);
     lv_stream_sync(ctx->lv(), 0);
     for (llava_session* s : members) s->device_pos = ~0U;          // the device is one position further than the host's books
 }

@@ -42,7 +42,7 @@ public:
     // its token and holds it as the one pending token: the caller checks); discard_ahead() drops it when a member did
     // something else: the members' device positions are marked unknown, so that their next evaluation uploads them again
     // (the cache rows and log entries the dropped step wrote lie beyond the evaluated tokens and are overwritten later).
-    // Greedy members only (a sampler launch would advance the member's sampler state).
+    // The sampler state of members that sample is saved before the step and put back when it is dropped.
     bool can_step_ahead() const;
     bool launch_ahead();
     bool finish_ahead(std::vector<u32>* next_tokens);
@@ -63,7 +63,7 @@ private:
     bool valid = false;
     llava_device_memory* memory = nullptr;
     llava_buffer *x = nullptr, *q = nullptr, *vout = nullptr, *ff = nullptr, *split = nullptr, *logits = nullptr, *scratch = nullptr,
-                 *tables = nullptr, *tokens_dev = nullptr;
+                 *tables = nullptr, *tokens_dev = nullptr, *sampler_backup = nullptr;
     std::vector<bool> sampled;               // per member: the recorded step ends with its sampler launch
     std::vector<u8> uploaded_table;          // the member tables as the device holds them
     u32* pinned_tokens = nullptr;

@@ -179,7 +179,7 @@ void group_scheduler::lead(unique_lock<mutex>& lock) {
                 tokens[i] = by_key[size_t(lower_bound(key.begin(), key.end(), round[i]) - key.begin())];
             n_grouped_steps += 1;
             n_grouped_tokens += round.size();
-            queued = g->launch_ahead();                       // greedy members: the next step needs nothing from the host
+            queued = g->launch_ahead();                       // the next step needs nothing from the host
         } else {
             // e.g. a model the batched products do not take: every caller falls back to its own step
             for (size_t i = 0; i < round.size(); ++i) tokens[i] = round[i]->predict_next_token();

@@ -61,8 +61,8 @@ private:
     bool leader_present = false;
     u32 runners = 0;
     std::map<std::vector<llava_session*>, llava_session_group*> groups;     // by member list (sorted)
-    // After a grouped step of greedy members the next step of the same group is queued at once (the device fed every
-    // member its token); it is booked when the same callers come back having pushed exactly those tokens, else dropped.
+    // After a grouped step the next step of the same group is queued at once (the device fed every member its token,
+    // greedy or drawn); it is booked when the same callers come back having pushed exactly those tokens, else dropped.
     llava_session_group* ahead_group = nullptr;
     std::map<llava_session*, u32> given;                  // the token each member of ahead_group was handed last
     std::atomic<u64> n_grouped_steps{0}, n_grouped_tokens{0}, n_steps_ahead{0}, us_collect{0}, us_device{0};

@@ -307,6 +307,7 @@ def test_sessions_that_start_stop_tick_rewind_and_die_while_others_run(pkg, tiny
                 assert op == c.SESSION_LIST and len(data) % 4 == 0
             n_orders += 1
         assert n_orders > 50
+        assert server.grouped()[0] > 0                       # sessions did run together in between
         # every session still answers, and its buffer is a valid token list
         for sid in live:
             c = a
