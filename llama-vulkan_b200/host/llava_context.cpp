@@ -200,14 +200,15 @@ bool rendezvous_wait(const tp_rendezvous* rv, const std::atomic<u32>& counter, u
 
 // Flags of the reference (llava_context.cpp:163-200) that still mean something, plus the
 // ones its CLI lacks: --greedy, --tokens, --n-predict, --ignore-eos, --seed, --device,
-// --gpus N (tensor-parallel over devices D..D+N-1, one forked process each), --on-device, --exact-prompt (batched prompt products with exact weight tiles), --write-synthetic, and --port / --bind for --server.
+// --gpus N (tensor-parallel over devices D..D+N-1, one forked process each), --on-device, --prompt-batch N (prompt tokens
+// per recorded step, 6..64 run on the tensor cores; default 1), --exact-prompt (batched prompt products with exact weight tiles), --write-synthetic, and --port / --bind for --server.
 int llava_context::run(int argc, char** argv) {
     bool server_mode = false, only_print_header = false, greedy = false, ignore_eos = false, on_device = false;
     bool model_path_provided = false, have_seed = false, exact_prompt = false;
     string model_path, tokens_path, synth_spec, bind_address = "0.0.0.0";
     u32 server_port = 1337;
     string prompt = "The ten best monuments to see in Paris are";
-    u32 n_predict = 0, seed = 0, gpus = 1;
+    u32 n_predict = 0, seed = 0, gpus = 1, prompt_batch = 1;
     int device = 0;
 
     auto need_value = [&](int& i) -> const char* {
@@ -230,7 +231,7 @@ int llava_context::run(int argc, char** argv) {
         } else if (streq(a, "--help") || streq(a, "-h")) {
             cout << (argc ? argv[0] : "./vulkan_llama")
                  << " [-h] [-m model.bin] [--server [--port P] [--bind ADDR]] [--greedy] [--n-predict N] [--ignore-eos] [--tokens ids.txt] [--seed S]"
-                    " [--device D] [--gpus N] [--on-device] [--exact-prompt] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
+                    " [--device D] [--gpus N] [--on-device] [--prompt-batch N] [--exact-prompt] [--print_header] [--write-synthetic 7b|13b|tiny[:q8][:layers=N]] [prompt]"
                  << endl;
             exit(0);
         } else if (streq(a, "--verbose") || streq(a, "-v")) {
@@ -254,6 +255,8 @@ int llava_context::run(int argc, char** argv) {
             on_device = true;
         } else if (streq(a, "--exact-prompt")) {
             exact_prompt = true;
+        } else if (streq(a, "--prompt-batch")) {
+            prompt_batch = u32(strtoul(need_value(i), nullptr, 10));
         } else if (streq(a, "--tokens")) {
             tokens_path = need_value(i);
         } else if (streq(a, "--n-predict")) {
@@ -407,6 +410,7 @@ int llava_context::run(int argc, char** argv) {
     if (server_mode) {
         // llava_context.cpp:246-249: sessions are created and driven by the clients; standard input or a signal ends it
         lsrv::session_wrapper::set_deterministic_sessions(greedy);
+        lsrv::session_wrapper::set_prompt_batch(prompt_batch);
         lsrv::tlv_server server(this, u16(server_port), bind_address.c_str(), true);
         if (!server.open()) return 1;
         server.serve_forever();
@@ -418,6 +422,10 @@ int llava_context::run(int argc, char** argv) {
     llava_session session(this);
     session.set_deterministic(greedy);
     if (have_seed) session.set_seed(seed);
+    if (prompt_batch > 1 && !session.set_max_batch(prompt_batch)) {
+        cerr << "[!] --prompt-batch takes 1.." << llava_session::max_batch_limit << " (sharded: 6 or more, where the shard shapes fit the tiles)" << endl;
+        return finish(1);
+    }
     if (!tokens_path.empty()) {
         vector<u32> ids;
         if (!read_token_file(tokens_path, &ids)) {

@@ -13,6 +13,7 @@ using namespace lsrv;
 
 u32 session_wrapper::ticker = 1U;
 bool session_wrapper::deterministic = false;
+u32 session_wrapper::prompt_batch = 1;
 
 session_wrapper::session_wrapper(session_owner* _owner) : session_id(ticker++), owner(_owner) {}
 
@@ -48,6 +49,7 @@ void session_wrapper::run() {
     }
     llava_session session(owner->context());
     session.set_deterministic(deterministic);
+    if (prompt_batch > 1 && !session.set_max_batch(prompt_batch)) cerr << "[?] prompt batches of " << prompt_batch << " refused; token by token" << endl;
 
     group_scheduler* sched = owner->scheduler();
     bool registered = false;                 // counted by the scheduler among the sessions that ask for token after token

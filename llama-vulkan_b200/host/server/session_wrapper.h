@@ -46,6 +46,8 @@ public:
     void join();
     // greedy decoding for every session started afterwards (the reference always samples)
     static void set_deterministic_sessions(bool on) { deterministic = on; }
+    // tokens per recorded step while a session ingests a prompt (llava_session::set_max_batch; 1 = token by token)
+    static void set_prompt_batch(u32 n) { prompt_batch = n; }
 
 private:
     void run();
@@ -65,6 +67,7 @@ private:
     bool should_die = false;
     static u32 ticker;
     static bool deterministic;
+    static u32 prompt_batch;
 };
 
 }  // namespace lsrv

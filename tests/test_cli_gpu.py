@@ -42,7 +42,8 @@ def cli(pkg, tmp_path_factory):
     return dict(exe=exe, model=model, tokens=tokens_file, greedy=greedy, text=text)
 
 
-@pytest.mark.parametrize("extra", [[], ["--on-device"]], ids=["host-in-the-loop", "device-resident"])
+@pytest.mark.parametrize("extra", [[], ["--on-device"], ["--prompt-batch", "16", "--exact-prompt"]],
+                         ids=["host-in-the-loop", "device-resident", "prompt-as-one-batch"])
 def test_cli_prints_the_oracles_greedy_tokens(cli, extra):
     out = subprocess.run([cli["exe"], "-m", cli["model"], "--greedy", "--tokens", cli["tokens"], "--n-predict", str(N_PREDICT),
                           "--ignore-eos"] + extra, check=True, timeout=600, stdout=subprocess.PIPE).stdout
