@@ -47,6 +47,41 @@ def load_pkg():
     return sys.modules[name]
 
 
+def group_steps(args):
+    """K sessions, each with its own 32-token prompt, then args.iters shared steps (one pass over the weights per step)."""
+    import time
+    import numpy as np
+    pkg = load_pkg()
+    wt = 2 if args.wtype == "q4_0" else 8
+    path = os.path.join(os.environ.get("LV_MODEL_DIR", "/tmp/lv_models"), f"7b_L{args.layers}_t{wt}_seed1234.ggjt")
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    if not os.path.exists(path):
+        pkg.write_synthetic_model(path, "7b", n_layers=args.layers, wtype=wt)
+    ctx = pkg.HostContext(path, 0)
+    sessions = []
+    for i in range(args.sessions):
+        s = ctx.session()
+        s.set_deterministic(True)
+        assert s.set_max_batch(64)
+        for t in np.random.default_rng(1000 + i).integers(3, 32000, 32):
+            assert s.push_token(int(t))
+        tok = s.predict_next_token()
+        assert tok != pkg.NO_TOKEN and s.push_token(tok)
+        sessions.append(s)
+    group = pkg.SessionGroup(ctx, sessions)
+    assert group.generate_greedy_on_device(2) is not None          # records the step
+    t0 = time.perf_counter()
+    assert group.generate_greedy_on_device(args.iters) is not None
+    sec = time.perf_counter() - t0
+    print(json.dumps({"sessions": args.sessions, "layers": args.layers, "wtype": args.wtype, "steps": args.iters,
+                      "ms_per_step": sec * 1e3 / args.iters, "tokens_per_s": args.sessions * args.iters / sec,
+                      "launches_per_step": group.kernel_launches()}), flush=True)
+    group.close()
+    for s in sessions:
+        s.close()
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", nargs="*", default=sorted(SHAPES))
@@ -58,7 +93,13 @@ def main():
     ap.add_argument("--pos", type=int, default=200, help="cache rows already filled, for the attn shape")
     ap.add_argument("--copies", type=int, default=0,
                     help="override the ring length; 1 keeps the matrix resident in L2 and shows the kernel's compute ceiling")
+    ap.add_argument("--sessions", type=int, default=0,
+                    help="instead of single products: K sessions of the 7B model (--layers, --wtype) decoding together through "
+                         "llava_session_group, --iters steps fed back on the device; prints the time per shared step")
+    ap.add_argument("--layers", type=int, default=32)
     args = ap.parse_args()
+    if args.sessions:
+        return group_steps(args)
 
     import numpy as np
     import torch
