@@ -33,6 +33,7 @@ WORKLOADS = {
 }
 PROMPT_SEED = 4321
 MODEL_DIR = os.environ.get("LV_MODEL_DIR", "/tmp/lv_models")
+RESULT_OUT = None    # where the JSON line goes (main() keeps the original stdout here)
 
 
 def load_pkg():
@@ -281,7 +282,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_OUT or sys.stdout, flush=True)
 
 
 PARITY_MODELS = (("7b", 2, 2), ("13b", 2, 2))        # geometry, layers, type: BASELINE config 0 and its 13B-geometry twin
@@ -416,7 +417,7 @@ def parity_check(rig):
                                                                         "greedy_tokens_identical": ok}
         if not ok:
             if rig.rank == 0:
-                print(json.dumps({"parity": out, "failed": why}), flush=True)
+                print(json.dumps({"parity": out, "failed": why}), file=RESULT_OUT or sys.stdout, flush=True)
             raise SystemExit(f"parity check against the CPU oracle failed on {rig.world} GPU(s): {why}")
     out["against"] = "CPU oracle (oracle/llava_oracle.c), rank 0"
     return out
@@ -670,9 +671,12 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
-    # NCCL writes its version banner (NCCL_DEBUG=VERSION and up) to stdout unless told otherwise; stdout carries the
-    # one JSON line and nothing else
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # stdout carries the one JSON line and nothing else: libraries that write to descriptor 1 (NCCL's version banner)
+    # get stderr instead, and the line goes to the descriptor kept aside here
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         return run_reference(args, rank, world)
 
@@ -767,7 +771,7 @@ def main():
         # not part of the metric: wall time of the prompt's evaluation, first use (records the steps) included
         "prompt_eval": m["prompt_eval"],
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_OUT or sys.stdout, flush=True)
     if rig.dist is not None:
         rig.dist.destroy_process_group()
 
