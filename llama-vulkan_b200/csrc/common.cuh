@@ -153,6 +153,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
+// Four consecutive flag words with one acquire load (16-byte aligned): each word is an acquire read of its own.
+__device__ __forceinline__ uint4 ld_acquire_sys_v4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.acquire.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 // Device-scope release store / acquire load: flags between CTAs of one GPU.
 __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -164,12 +164,17 @@ __global__ void __launch_bounds__(W * 32, W <= 8 && QT == T_Q4_0 ? 2 : 1) lv_qro
     if (tp_pull) {
         // wait until every CTA of every rank's producer launch has delivered its rows to this rank's window
         const uint32_t epoch = tp_epoch(p.tp, p.tp.pull_exchange);
-        const uint32_t total = uint32_t(p.tp.n_ranks) * p.tp.pull_ctas;
+        // four flags per acquire load: ranks x CTAs / 4 loads (296 at 8 ranks of 148 CTAs) fit one round of the CTA's
+        // threads, where a load per flag took up to three acquire round trips in a row
+        const uint32_t quads = (p.tp.pull_ctas + 3) / 4, total = uint32_t(p.tp.n_ranks) * quads;
         for (uint32_t idx = threadIdx.x; idx < total && ok; idx += blockDim.x) {
-            const uint32_t src = idx / p.tp.pull_ctas, cta = idx - src * p.tp.pull_ctas;
+            const uint32_t src = idx / quads, cta = (idx - src * quads) * 4;
             const uint32_t* flag = tp_flag(p.tp, p.tp.rank, p.tp.pull_exchange, int(src), cta);
+            const uint32_t live = p.tp.pull_ctas - cta;                  // words of this quad that a producer CTA writes
             const long long t0 = clock64();
-            while (ld_acquire_sys(flag) != epoch) {
+            for (;;) {
+                const uint4 f = ld_acquire_sys_v4(flag);
+                if (f.x == epoch && (live < 2 || f.y == epoch) && (live < 3 || f.z == epoch) && (live < 4 || f.w == epoch)) break;
                 if (*reinterpret_cast<volatile uint32_t*>(p.err) != 0 || clock64() - t0 > kWaitCycleLimit) {
                     atomicOr(p.err, ERR_PEER_TIMEOUT);
                     ok = false;

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_mirostat_kernel(const f
     __shared__ float s_f[64];
     __shared__ uint32_t s_u[64];
     __shared__ float s_total, s_kept_sum, s_target;
-    __shared__ uint32_t s_pick, s_last_kept, s_kept_count;
+    __shared__ uint32_t s_pick, s_last_kept;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_tokens = *n_tokens_word;
     const float mu = __uint_as_float(state[0]);
@@ -150,7 +150,6 @@ __global__ void __launch_bounds__(kSampleThreads) sample_mirostat_kernel(const f
             l = max(l, s_u[32 + w]);
         }
         s_kept_sum = run;
-        s_kept_count = c;
         s_last_kept = l;
         float u = forced_u;
         if (!(u >= 0.f && u < 1.f)) u = float(philox_first_word(state[2], 0u, state[1], 0x6c763230u) >> 8) * (1.0f / 16777216.0f);
