@@ -231,8 +231,8 @@ int lv_argmax_advance_group(lv_ctx* ctx, const float* logits, uint32_t vocab, co
  * matrix once for up to 64 tokens: q4_0 / q8_0 blocks are dequantised in the
  * kernel into exact fp16 (hi, lo) tiles and multiplied on the tcgen05 tensor
  * cores with fp32 accumulation.  The activations enter as the two fp16 planes that
- * lv_act_split_f16 writes.  rows: multiple of 128 (64 for the SiLU pair);
- * cols: multiple of 256; batch 1..64; wtype q4_0 (2) or q8_0 (8).
+ * lv_act_split_f16 writes.  rows: multiple of 32 (a CTA covers 128 rows, 64 of
+ * each matrix of the SiLU pair; a last tile may be ragged); cols: multiple of 256; batch 1..64; wtype q4_0 (2) or q8_0 (8).
  *
  * There are two forms of the weight tiles.  The default writes one fp16 plane,
  * fp16((q - 8) * d) or fp16(q * d): the weight is rounded to 11 significant bits

@@ -244,8 +244,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
     const uint32_t rows_per_cta = pair ? kTcRows / 2 : kTcRows;
 
     // which matrix this CTA works on, and its first row there
-    uint32_t t0 = p.m[0].rows / rows_per_cta;
-    uint32_t t1 = t0 + (p.n_mat > 1 ? p.m[1].rows / rows_per_cta : 0);
+    // (a last tile may reach past the matrix: the tensor map fills the missing rows with zero blocks and the epilogue
+    // leaves them out)
+    uint32_t t0 = (p.m[0].rows + rows_per_cta - 1) / rows_per_cta;
+    uint32_t t1 = t0 + (p.n_mat > 1 ? (p.m[1].rows + rows_per_cta - 1) / rows_per_cta : 0);
     int mi = 0;
     const uint32_t tile_all = blockIdx.x / p.splits, split = blockIdx.x - tile_all * p.splits;
     uint32_t tile = tile_all;
@@ -673,6 +675,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
         // 16 tokens z0 .. z0+15 of one output row (tile row tr)
         auto store_plain = [&](uint32_t tr, uint32_t z0, const float (&r32)[16]) {
                 const uint32_t row = row0 + tr;
+                if (row >= M.rows) return;
                 if (M.epilogue == EPI_STORE_F16_AT_POS && p.group != nullptr) {
                     // matrix 0 is wk, matrix 2 is wv (lv_gemm_tc_qkv_kvappend_group)
 #pragma unroll
@@ -710,6 +713,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmTcPara
             };
         auto store_pair = [&](uint32_t tr, uint32_t z0, const float (&up)[16], const float (&gate)[16]) {
                 const uint32_t row = row0 + tr;
+                if (row >= M.rows) return;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const uint32_t z = z0 + i;
@@ -940,9 +944,9 @@ static int launch_gemm_tc_typed(lv_ctx* ctx, GemmTcParams& p, const __half* xh) 
     uint32_t tiles = 0;
     for (int i = 0; i < p.n_mat; ++i) {
         LV_REQUIRE(p.m[i].w != nullptr && (reinterpret_cast<uintptr_t>(p.m[i].w) & 15u) == 0, "matrix pointer null or not 16-byte aligned");
-        LV_REQUIRE(p.m[i].rows != 0 && p.m[i].rows % rows_per_cta == 0, "rows must be a multiple of 128 (64 for the SiLU pair)");
+        LV_REQUIRE(p.m[i].rows != 0 && p.m[i].rows % 32 == 0, "rows must be a non-zero multiple of 32");
         if (int rc = make_weight_map(&maps.w[i], p.m[i].w, p.m[i].rows, row_bytes, rows_per_cta, tc_raw_row_bytes<QT>())) return rc;
-        tiles += p.m[i].rows / rows_per_cta;
+        tiles += (p.m[i].rows + rows_per_cta - 1) / rows_per_cta;
     }
     if (pair) {
         LV_REQUIRE((reinterpret_cast<uintptr_t>(p.m[0].w_gate) & 15u) == 0, "matrix pointer not 16-byte aligned");

@@ -442,7 +442,7 @@ bool llava_session::set_backlog_size(u32 new_size) {
 bool llava_session::tensor_core_shapes_ok() const {
     const u32 ranks = ctx->tp_size();
     if (ranks == 1) return true;
-    return (model->get_header().dim / ranks) % 128 == 0 && (model->get_ff_size() / ranks) % 64 == 0;
+    return (model->get_header().dim / ranks) % 128 == 0 && (model->get_ff_size() / ranks) % 32 == 0;
 }
 
 bool llava_session::set_max_batch(u32 n) {

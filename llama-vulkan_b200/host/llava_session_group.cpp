@@ -31,7 +31,7 @@ llava_session_group::llava_session_group(llava_context* _ctx, vector<llava_sessi
     if (!ctx->output_w->weight_buffer_is_f16() || ctx->get_layers().empty() || !ctx->get_layers()[0]->wq()->weight_buffer_is_f16()) return;
     const ggml_header& h = ctx->get_model()->get_header();
     const u32 dim = h.dim, ffn = ctx->get_model()->get_ff_size(), n_layers = u32(ctx->get_layers().size());
-    if (h.vocab_size % 128 != 0) return;                       // rows of the output matrix fill 128-row tiles
+    if (h.vocab_size % 32 != 0) return;                        // what the batched product of the output matrix asks of its rows
     const auto F = ggml_value_type::f32;
     memory = new llava_device_memory(ctx);
     x = new llava_buffer(ctx, F, dim, k, memory, "group_x");

@@ -103,7 +103,8 @@ def test_act_split_planes_add_up_to_the_input(gpu, pkg):
 
 
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0], ids=["q4_0", "q8_0"])
-@pytest.mark.parametrize("rows,cols,batch", [(128, 256, 16), (256, 4096, 5), (4096, 4096, 64), (384, 11008, 33), (640, 5120, 17)])
+@pytest.mark.parametrize("rows,cols,batch", [(128, 256, 16), (256, 4096, 5), (4096, 4096, 64), (384, 11008, 33), (640, 5120, 17),
+                                             (160, 512, 16), (4000, 1024, 9)])       # the last two end in a ragged row tile
 def test_gemm_tc_store_and_add(gpu, pkg, rows, cols, batch, wtype, form):
     rng = np.random.default_rng(51)
     W = matrix(rng, rows, cols, wtype=wtype)
@@ -189,7 +190,7 @@ def test_gemm_tc_refuses_what_it_cannot_do(gpu, pkg):
     lib, h = gpu.lib, gpu.handle
     d = gpu.zeros(1 << 16)
     assert lib.lv_gemm_tc(h, d, d, 0, d, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS            # f32 matrices are not taken
-    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 100, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # rows not a multiple of 128
+    assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 100, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # rows not a multiple of 32
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 96, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS       # cols not a multiple of 256
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, d, 128, 256, 65, 0) == pkg.LV_ERR_BAD_ARGUMENTS      # batch above 64
     assert lib.lv_gemm_tc(h, d, d, qn.Q4_0, None, 128, 256, 16, 0) == pkg.LV_ERR_BAD_ARGUMENTS
@@ -269,16 +270,19 @@ def test_gemm_tc_on_the_shard_shapes_of_eight_ranks(gpu, pkg, rows, cols, used, 
     close(gpu.download(out, np.float32, batch * rows).reshape(batch, rows)[::5], want, **loose(form, qn.Q4_0))
 
 
-def test_gemm_tc_silu_pair_on_the_13b_shard_of_eight_ranks(gpu, pkg, form):
+@pytest.mark.parametrize("ff,dim,batch", [(1728, 5120, 64), (1376, 4096, 64), (96, 512, 7)], ids=["13b", "7b-ragged-last-tile", "small-ragged"])
+def test_gemm_tc_silu_pair_on_the_shards_of_eight_ranks(gpu, pkg, ff, dim, batch, form):
+    """11008 / 8 = 1376 rows are 21 tiles of 64 and one of 32: the last CTA's missing rows read as zero blocks and are
+    not stored."""
     rng = np.random.default_rng(62)
-    ff, dim, batch = 1728, 5120, 64
     w3, w1 = matrix(rng, ff, dim), matrix(rng, ff, dim)
     x = rng.standard_normal((batch, dim)).astype(np.float32)
     nw = (1 + 0.05 * rng.standard_normal(dim)).astype(np.float32)
     xh = split(gpu, pkg, x, nw)
-    out = gpu.zeros(batch * ff * 4)
+    out = gpu.upload(np.full((batch + 1, ff), 7.0, np.float32))
     pkg.check(gpu.lib.lv_gemm_tc_silu(gpu.handle, out, gpu.upload(w3), gpu.upload(w1), qn.Q4_0, xh, ff, dim, batch))
     gpu.sync()
-    got = gpu.download(out, np.float32, batch * ff).reshape(batch, ff)
-    for z in range(0, batch, 13):
+    got = gpu.download(out, np.float32, (batch + 1) * ff).reshape(batch + 1, ff)
+    for z in list(range(0, batch, 13)) + [batch - 1]:
         close(got[z], ob.gemv_silu(w3, w1, qn.Q4_0, ob.norm(x[z], nw), ff, dim, workers_for(dim)), **loose(form, qn.Q4_0))
+    assert (got[batch] == 7.0).all()                                     # the ragged tile wrote nothing past the matrix
