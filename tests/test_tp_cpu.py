@@ -43,6 +43,21 @@ def test_shard_geometry_of_the_7b_and_13b_matrices(pkg):
     assert shape(lib, qn.Q4_0, 4096, 4096, COLS, 2, 2) is None          # rank out of range
 
 
+@pytest.mark.parametrize("dim,ff", [(4096, 11008), (5120, 13824)], ids=["7b", "13b"])
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_shard_shapes_fit_the_batched_products(pkg, dim, ff, n):
+    """What lets a sharded session ingest prompts in batches (llava_session::tensor_core_shapes_ok and the argument
+    checks of lv_gemm_tc*): row shards of a multiple of 32 rows (a last row tile may be ragged), column shards padded
+    to a multiple of 256 columns, activations to pad in multiples of 8."""
+    lib = pkg.load_host()
+    for rows, cols in ((dim, dim), (ff, dim)):                           # wq/wk/wv and w1/w3
+        r, c, u, _ = shape(lib, qn.Q4_0, rows, cols, ROWS, n - 1, n)
+        assert r % 32 == 0 and c == u == cols and c % 256 == 0
+    for rows, cols in ((dim, dim), (dim, ff)):                           # wo and w2
+        r, c, u, _ = shape(lib, qn.Q4_0, rows, cols, COLS, n - 1, n)
+        assert r % 128 == 0 and c % 256 == 0 and u % 8 == 0 and 0 <= c - u < 256
+
+
 @pytest.mark.parametrize("wtype", [qn.Q4_0, qn.Q8_0])
 @pytest.mark.parametrize("n", [2, 4, 8])
 def test_shards_reassemble_and_partial_products_add_up(pkg, wtype, n):
